@@ -1,0 +1,204 @@
+// Causal grouped-query attention over the paged cache, for any mix of prompt portions and
+// single decoded tokens in one launch.
+//
+//   s = (q . k) * scale over the request's cached keys with  lo <= key position <= query
+//   position, lo = max(0, pos - window + 1) with a window, else 0; q head i reads kv head
+//   i / (nh / nkv); softmax in float; o = softmax(s) v
+//   (snowllm/models/lfm2/layers.py:36-70; tests/test_lfm2_long_attention.py:36-47)
+//
+// Work split: one block per (query row, kv head, key chunk); its warps are the q heads of
+// that kv head, which share each tile of keys and values through shared memory.  Key
+// chunks are aligned to absolute positions, so what a row computes depends on its own
+// position and on the chunk length only, never on the rest of the batch.  With more than
+// one chunk the blocks write partial (o, max, sum) to scratch and a second kernel merges
+// them in chunk order.
+//
+// Pool layout: [page, 2 (k, v), kv head, page_size, head_dim].
+#include "common.cuh"
+
+#define ATT_TILE 32            // keys per tile: one per lane
+#define ATT_MAX_WARPS 8        // q heads handled by one block
+#define ATT_MAX_DPL 16         // head_dim <= 512
+
+template <typename T>
+__global__ void paged_attention_kernel(
+    const T* __restrict__ q, const T* __restrict__ pool, const int* __restrict__ block_table,
+    int max_pages, int page_size, const int* __restrict__ positions, const int* __restrict__ row_seg,
+    T* __restrict__ out, float* __restrict__ part_o, float* __restrict__ part_ml, int nh, int nkv,
+    int hd, int window, int chunk, int num_chunks, float scale) {
+  extern __shared__ float sh[];
+  const int group = nh / nkv;
+  const int heads_per_block = blockDim.x >> 5;
+  const int blocks_per_kv = (group + heads_per_block - 1) / heads_per_block;
+  const int m = blockIdx.x;
+  const int kvh = blockIdx.y / blocks_per_kv;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int head_in_group = (blockIdx.y % blocks_per_kv) * heads_per_block + warp;
+  const bool active = head_in_group < group;
+  const int head = kvh * group + head_in_group;
+
+  const int pos = positions[m];
+  const int lo = window > 0 ? max(0, pos - window + 1) : 0;
+  const int first_chunk = lo / chunk;
+  const int c = first_chunk + blockIdx.z;
+  if ((long long)c * chunk > pos) return;                  // no key of this row in this chunk
+  const int k_begin = max(lo, c * chunk);
+  const int k_end = min(pos + 1, (c + 1) * chunk);         // exclusive
+
+  const int kstride = hd + 1;
+  float* ks = sh;                                          // [ATT_TILE][hd + 1]
+  float* vs = ks + ATT_TILE * kstride;                     // [ATT_TILE][hd]
+  float* qs = vs + ATT_TILE * hd;                          // [warps][hd]
+
+  if (active) {
+    const T* qrow = q + ((size_t)m * nh + head) * hd;
+    for (int d = lane; d < hd; d += 32) qs[warp * hd + d] = to_f<T>(qrow[d]) * scale;
+  }
+  const int* bt = block_table + (size_t)row_seg[m] * max_pages;
+  const size_t page_stride = (size_t)2 * nkv * page_size * hd;
+  const size_t v_off = (size_t)nkv * page_size * hd;
+
+  float mx = -INFINITY, l = 0.f;
+  float o[ATT_MAX_DPL];
+#pragma unroll
+  for (int i = 0; i < ATT_MAX_DPL; ++i) o[i] = 0.f;
+  const int dpl = (hd + 31) / 32;
+
+  // Tiles start at multiples of ATT_TILE counted from the chunk's absolute start.
+  const int t_first = c * chunk + ((k_begin - c * chunk) / ATT_TILE) * ATT_TILE;
+  for (int t0 = t_first; t0 < k_end; t0 += ATT_TILE) {
+    __syncthreads();
+    for (int idx = threadIdx.x; idx < ATT_TILE * hd; idx += blockDim.x) {
+      const int j = idx / hd, d = idx - j * hd;
+      const int kp = t0 + j;
+      float kv = 0.f, vv = 0.f;
+      if (kp >= k_begin && kp < k_end) {
+        const int page = bt[kp / page_size];
+        const size_t base = (size_t)page * page_stride +
+                            ((size_t)kvh * page_size + kp % page_size) * hd + d;
+        kv = to_f<T>(pool[base]);
+        vv = to_f<T>(pool[base + v_off]);
+      }
+      ks[j * kstride + d] = kv;
+      vs[j * hd + d] = vv;
+    }
+    __syncthreads();
+    if (!active) continue;
+    const int kp = t0 + lane;
+    const bool valid = kp >= k_begin && kp < k_end;
+    float s = 0.f;
+    const float* qw = qs + warp * hd;
+    const float* kr = ks + lane * kstride;
+    for (int d = 0; d < hd; ++d) s = fmaf(qw[d], kr[d], s);
+    s = valid ? s : -INFINITY;
+    const float tmax = warp_max(s);
+    const float m_new = fmaxf(mx, tmax);                   // finite: each tile run has a valid key
+    const float corr = expf(mx - m_new);                   // exp(-inf) = 0 on the first tile
+    const float p = valid ? expf(s - m_new) : 0.f;
+    l = l * corr + warp_sum(p);
+    mx = m_new;
+#pragma unroll
+    for (int i = 0; i < ATT_MAX_DPL; ++i)
+      if (i < dpl) o[i] *= corr;
+    for (int j = 0; j < ATT_TILE; ++j) {
+      const float pj = __shfl_sync(0xffffffffu, p, j);
+#pragma unroll
+      for (int i = 0; i < ATT_MAX_DPL; ++i)
+        if (i < dpl) {
+          const int d = lane + 32 * i;
+          if (d < hd) o[i] = fmaf(pj, vs[j * hd + d], o[i]);
+        }
+    }
+  }
+  if (!active) return;
+  if (num_chunks == 1) {
+    const float inv = 1.f / l;
+    T* orow = out + ((size_t)m * nh + head) * hd;
+#pragma unroll
+    for (int i = 0; i < ATT_MAX_DPL; ++i)
+      if (i < dpl) {
+        const int d = lane + 32 * i;
+        if (d < hd) orow[d] = from_f<T>(o[i] * inv);
+      }
+  } else {
+    const size_t slot = ((size_t)m * nh + head) * num_chunks + blockIdx.z;
+    float* po = part_o + slot * hd;
+#pragma unroll
+    for (int i = 0; i < ATT_MAX_DPL; ++i)
+      if (i < dpl) {
+        const int d = lane + 32 * i;
+        if (d < hd) po[d] = o[i];
+      }
+    if (lane == 0) {
+      part_ml[slot * 2] = mx;
+      part_ml[slot * 2 + 1] = l;
+    }
+  }
+}
+
+// Merge the chunks of one (row, head) in chunk order.
+template <typename T>
+__global__ void attention_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
+                                       const int* __restrict__ positions, T* __restrict__ out, int nh,
+                                       int hd, int window, int chunk, int num_chunks) {
+  const int m = blockIdx.x, head = blockIdx.y;
+  const int pos = positions[m];
+  const int lo = window > 0 ? max(0, pos - window + 1) : 0;
+  const int n = pos / chunk - lo / chunk + 1;              // chunks this row really has
+  const size_t base = ((size_t)m * nh + head) * num_chunks;
+  float mx = -INFINITY;
+  for (int z = 0; z < n; ++z) mx = fmaxf(mx, part_ml[(base + z) * 2]);
+  float l = 0.f;
+  for (int z = 0; z < n; ++z) l += part_ml[(base + z) * 2 + 1] * expf(part_ml[(base + z) * 2] - mx);
+  const float inv = 1.f / l;
+  for (int d = threadIdx.x; d < hd; d += blockDim.x) {
+    float acc = 0.f;
+    for (int z = 0; z < n; ++z)
+      acc = fmaf(part_o[(base + z) * hd + d], expf(part_ml[(base + z) * 2] - mx), acc);
+    out[((size_t)m * nh + head) * hd + d] = from_f<T>(acc * inv);
+  }
+}
+
+// Bytes of scratch the launch below needs for `num_chunks` > 1 (0 for one chunk).
+SNK_API long long snk_paged_attention_scratch_bytes(int M, int nh, int hd, int num_chunks) {
+  if (num_chunks <= 1) return 0;
+  return (long long)M * nh * num_chunks * (hd + 2) * (long long)sizeof(float);
+}
+
+SNK_API int snk_paged_attention(const void* q, const void* pool, const int* block_table,
+                                int max_pages, int page_size, const int* positions,
+                                const int* row_seg, void* out, void* scratch, int M, int nh,
+                                int nkv, int hd, int window, int chunk, int num_chunks,
+                                float scale, int dtype, cudaStream_t stream) {
+  if (M <= 0) return 0;
+  if (nkv <= 0 || nh % nkv || hd <= 0 || hd > 32 * ATT_MAX_DPL) return SNK_ERR_SIZE;
+  if (chunk <= 0 || chunk % ATT_TILE || num_chunks < 1 || num_chunks > 65535) return SNK_ERR_SIZE;
+  if (num_chunks > 1 && scratch == nullptr) return SNK_ERR_SIZE;
+  const int group = nh / nkv;
+  const int warps = group < ATT_MAX_WARPS ? group : ATT_MAX_WARPS;
+  const int blocks_per_kv = (group + warps - 1) / warps;
+  if ((long long)nkv * blocks_per_kv > 65535) return SNK_ERR_SIZE;
+  dim3 grid(M, nkv * blocks_per_kv, num_chunks);
+  const size_t smem = ((size_t)ATT_TILE * (2 * hd + 1) + (size_t)warps * hd) * sizeof(float);
+  float* part_o = static_cast<float*>(scratch);
+  float* part_ml = part_o ? part_o + (size_t)M * nh * num_chunks * hd : nullptr;
+  SNK_DISPATCH(dtype, {
+    if (smem > 48 * 1024)
+      cudaFuncSetAttribute(paged_attention_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                           (int)smem);
+    paged_attention_kernel<T><<<grid, warps * 32, smem, stream>>>(
+        static_cast<const T*>(q), static_cast<const T*>(pool), block_table, max_pages, page_size,
+        positions, row_seg, static_cast<T*>(out), part_o, part_ml, nh, nkv, hd, window, chunk,
+        num_chunks, scale);
+  });
+  SNK_LAUNCH_CHECK();
+  if (num_chunks > 1) {
+    dim3 mgrid(M, nh);
+    const int threads = hd <= 32 ? 32 : (hd <= 64 ? 64 : 128);
+    SNK_DISPATCH(dtype, attention_merge_kernel<T><<<mgrid, threads, 0, stream>>>(
+                            part_o, part_ml, positions, static_cast<T*>(out), nh, hd, window,
+                            chunk, num_chunks));
+    SNK_LAUNCH_CHECK();
+  }
+  return 0;
+}

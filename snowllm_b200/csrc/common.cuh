@@ -1,0 +1,89 @@
+// Shared helpers of the sm_100a kernels: dtype traits, reductions, launch checks.
+//
+// Every entry point is a plain C function (`snk_*`) that takes device pointers, sizes
+// and a stream, launches on that stream and returns 0 or an error code; it never
+// allocates and never synchronises.  Activations come in the engine's compute dtype
+// (float or bfloat16, `dtype` argument); statistics, accumulators and the residual
+// stream are always float.
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#define SNK_API extern "C" __attribute__((visibility("default")))
+
+enum { SNK_F32 = 0, SNK_BF16 = 1 };
+
+// Error codes above any cudaError_t value.
+enum {
+  SNK_ERR_DTYPE = 20001,      // dtype code not known
+  SNK_ERR_SIZE = 20002,       // a size this kernel refuses
+  SNK_ERR_ALIGN = 20003,      // a pointer or a row pitch that is not aligned as required
+};
+
+typedef __nv_bfloat16 bf16;
+
+template <typename T> __device__ __forceinline__ float to_f(T v);
+template <> __device__ __forceinline__ float to_f<float>(float v) { return v; }
+template <> __device__ __forceinline__ float to_f<bf16>(bf16 v) { return __bfloat162float(v); }
+
+template <typename T> __device__ __forceinline__ T from_f(float v);
+template <> __device__ __forceinline__ float from_f<float>(float v) { return v; }
+template <> __device__ __forceinline__ bf16 from_f<bf16>(float v) { return __float2bfloat16_rn(v); }
+
+// The value after a round trip through T: the identity for float, round-to-nearest-even
+// for bfloat16.  Marks the places where the 16-bit path rounds an intermediate.
+template <typename T> __device__ __forceinline__ float round_f(float v) { return to_f<T>(from_f<T>(v)); }
+
+// A small vector (norm weight, conv taps, router matrix) that stays float when the file
+// stores it so, whatever the compute dtype.
+struct SmallVec {
+  const void* p;
+  int is_f32;
+  __device__ __forceinline__ float operator[](size_t i) const {
+    return is_f32 ? static_cast<const float*>(p)[i]
+                  : __bfloat162float(static_cast<const bf16*>(p)[i]);
+  }
+};
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+
+// Sum over a block of up to 1024 threads; every thread gets the result.  `red` is 33 floats
+// of shared memory.  The order of the additions depends on the block size only.
+__device__ __forceinline__ float block_sum(float v, float* red) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int nwarp = (blockDim.x + 31) >> 5;
+  v = warp_sum(v);
+  __syncthreads();
+  if (lane == 0) red[warp] = v;
+  __syncthreads();
+  if (warp == 0) {
+    float t = lane < nwarp ? red[lane] : 0.f;
+    t = warp_sum(t);
+    if (lane == 0) red[32] = t;
+  }
+  __syncthreads();
+  return red[32];
+}
+
+#define SNK_LAUNCH_CHECK()                       \
+  do {                                           \
+    cudaError_t e_ = cudaGetLastError();         \
+    if (e_ != cudaSuccess) return (int)e_;       \
+  } while (0)
+
+#define SNK_DISPATCH(dtype, ...)                                  \
+  do {                                                            \
+    if ((dtype) == SNK_F32) { typedef float T; __VA_ARGS__; }     \
+    else if ((dtype) == SNK_BF16) { typedef bf16 T; __VA_ARGS__; }\
+    else return SNK_ERR_DTYPE;                                    \
+  } while (0)

@@ -1,0 +1,118 @@
+// Embedding gather, fused residual-add + RMSNorm, SwiGLU activation.
+//
+// Embedding: h[m,:] = E[ids[m],:]                      (snowllm/ops/embedding.py:12-25)
+// RMSNorm:   n = x * rsqrt(mean(x^2) + eps) in float, rounded to the compute dtype, then
+//            times the weight, rounded again            (snowllm/ops/norm.py:11-30)
+// SwiGLU:    out = round(silu(gate)) * up               (snowllm/ops/mlp.py:12-20)
+// The residual stream is float here, so the residual sum is a 32-bit sum.
+#include "common.cuh"
+
+// ---------------------------------------------------------------------------------------
+template <typename T>
+__global__ void embedding_kernel(const int* __restrict__ ids, const T* __restrict__ table,
+                                 float* __restrict__ out, int H, int V) {
+  const int m = blockIdx.x;
+  int id = ids[m];
+  const bool ok = id >= 0 && id < V;     // the host checks ids; a bad one reads nothing
+  const T* row = table + (size_t)(ok ? id : 0) * H;
+  float* o = out + (size_t)m * H;
+  for (int i = threadIdx.x; i < H; i += blockDim.x) o[i] = ok ? to_f<T>(row[i]) : 0.f;
+}
+
+SNK_API int snk_embedding(const int* ids, const void* table, float* out, int M, int H, int V,
+                          int dtype, cudaStream_t stream) {
+  if (M <= 0) return 0;
+  const int threads = H >= 1024 ? 256 : 128;
+  SNK_DISPATCH(dtype, embedding_kernel<T><<<M, threads, 0, stream>>>(
+                          ids, static_cast<const T*>(table), out, H, V));
+  SNK_LAUNCH_CHECK();
+  return 0;
+}
+
+// ---------------------------------------------------------------------------------------
+// One block per output row.  rows == nullptr: row r is residual row r; delta (if any) is
+// added into the residual and the sum is written back.  rows != nullptr: output row r
+// normalises residual[rows[r]] + delta[rows[r]] and nothing is written back.
+template <typename T>
+__global__ void add_rmsnorm_kernel(float* __restrict__ residual, const float* __restrict__ delta,
+                                   SmallVec gamma, T* __restrict__ out,
+                                   const int* __restrict__ rows, int H, float eps) {
+  extern __shared__ float xs[];          // H floats + 33 for the reduction
+  float* red = xs + H;
+  const int r = blockIdx.x;
+  const size_t src = rows ? (size_t)rows[r] : (size_t)r;
+  float* res = residual + src * H;
+  const float* d = delta ? delta + src * H : nullptr;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < H; i += blockDim.x) {
+    float v = res[i];
+    if (d) {
+      v += d[i];
+      if (!rows) res[i] = v;
+    }
+    xs[i] = v;
+    ss += v * v;
+  }
+  ss = block_sum(ss, red);
+  const float inv = rsqrtf(ss / (float)H + eps);
+  T* o = out + (size_t)r * H;
+  for (int i = threadIdx.x; i < H; i += blockDim.x)
+    o[i] = from_f<T>(round_f<T>(xs[i] * inv) * gamma[i]);
+}
+
+SNK_API int snk_add_rmsnorm(float* residual, const float* delta, const void* gamma,
+                            int gamma_is_f32, void* out, const int* rows, int R, int H,
+                            float eps, int dtype, cudaStream_t stream) {
+  if (R <= 0) return 0;
+  if (H <= 0 || H > 65536) return SNK_ERR_SIZE;
+  // The block size depends on H alone, so a row's statistics never depend on the batch.
+  const int threads = H >= 2048 ? 512 : (H >= 512 ? 256 : 128);
+  const size_t smem = (size_t)(H + 33) * sizeof(float);
+  SmallVec g{gamma, gamma_is_f32};
+  SNK_DISPATCH(dtype, {
+    if (smem > 48 * 1024)
+      cudaFuncSetAttribute(add_rmsnorm_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                           (int)smem);
+    add_rmsnorm_kernel<T><<<R, threads, smem, stream>>>(residual, delta, g,
+                                                        static_cast<T*>(out), rows, H, eps);
+  });
+  SNK_LAUNCH_CHECK();
+  return 0;
+}
+
+// ---------------------------------------------------------------------------------------
+// Residual update without a norm: residual += delta (used where no norm follows).
+__global__ void add_kernel(float* __restrict__ residual, const float* __restrict__ delta, size_t n) {
+  size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n) residual[i] += delta[i];
+}
+
+SNK_API int snk_residual_add(float* residual, const float* delta, long long n, cudaStream_t stream) {
+  if (n <= 0) return 0;
+  add_kernel<<<(unsigned)((n + 255) / 256), 256, 0, stream>>>(residual, delta, (size_t)n);
+  SNK_LAUNCH_CHECK();
+  return 0;
+}
+
+// ---------------------------------------------------------------------------------------
+// gu: [M, 2I] with the gate in columns [0, I) and the up projection in [I, 2I).
+template <typename T>
+__global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ out, int I, size_t total) {
+  size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= total) return;
+  const size_t m = idx / I;
+  const int i = (int)(idx - m * I);
+  const float g = to_f<T>(gu[m * 2 * I + i]);
+  const float u = to_f<T>(gu[m * 2 * I + I + i]);
+  const float s = round_f<T>(g / (1.f + expf(-g)));
+  out[idx] = from_f<T>(s * u);
+}
+
+SNK_API int snk_swiglu(const void* gu, void* out, int M, int I, int dtype, cudaStream_t stream) {
+  const size_t total = (size_t)M * I;
+  if (total == 0) return 0;
+  SNK_DISPATCH(dtype, swiglu_kernel<T><<<(unsigned)((total + 255) / 256), 256, 0, stream>>>(
+                          static_cast<const T*>(gu), static_cast<T*>(out), I, total));
+  SNK_LAUNCH_CHECK();
+  return 0;
+}

@@ -1,0 +1,107 @@
+// Gated short convolution over a flat batch of segments, and its per-request history.
+//
+//   bcx row = [B | C | x] (thirds);  g = round(B * x)
+//   conv[t,c] = sum_{j<L} w[c,j] * g~[t-(L-1)+j, c], float accumulation in tap order, where g~
+//   is the request's history (the last L-1 rows of g of earlier steps; zeros for a request
+//   that starts at position 0, whatever its slot holds) followed by this step's g
+//   y = round(C * round(conv));   state <- the last L-1 rows of g~ (oldest first)
+//   (snowllm/models/lfm2/layers.py:26-33; snowllm/ops/lfm2.py:8-26; tests/test_lfm2.py:41-49)
+//
+// Two launches: the first only reads the state, the second rewrites it, so that tokens of
+// one segment may be spread over many blocks.  Each value depends on its own segment only,
+// and the taps are summed in one fixed order, so a sequence gives the same bits however it
+// is cut into steps.
+#include "common.cuh"
+
+#define CONV_MAX_L 16
+#define CONV_ROWS_PER_BLOCK 8
+
+template <typename T>
+__device__ __forceinline__ float gated(const T* __restrict__ bcx, size_t row, int H, int c) {
+  const T* r = bcx + row * 3 * (size_t)H;
+  return round_f<T>(to_f<T>(r[c]) * to_f<T>(r[2 * H + c]));
+}
+
+template <typename T>
+__global__ void short_conv_kernel(const T* __restrict__ bcx, SmallVec w, const T* __restrict__ state,
+                                  const int* __restrict__ cu_seqlens, const int* __restrict__ seg_start,
+                                  const int* __restrict__ seg_slot, const int* __restrict__ row_seg,
+                                  T* __restrict__ out, int M, int H, int L) {
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= H) return;
+  float taps[CONV_MAX_L];
+#pragma unroll
+  for (int j = 0; j < CONV_MAX_L; ++j) taps[j] = j < L ? w[(size_t)c * L + j] : 0.f;
+  const int row0 = blockIdx.y * CONV_ROWS_PER_BLOCK;
+  for (int m = row0; m < min(M, row0 + CONV_ROWS_PER_BLOCK); ++m) {
+    const int seg = row_seg[m];
+    const int first = cu_seqlens[seg];
+    const int t = m - first;                         // index within this step's segment
+    const bool has_state = seg_start[seg] > 0;
+    const T* st = state + (size_t)seg_slot[seg] * (L - 1) * H;
+    float acc = 0.f;
+#pragma unroll
+    for (int j = 0; j < CONV_MAX_L; ++j) {
+      if (j < L) {
+        const int s = t - (L - 1) + j;               // index into this step's g; < 0: history
+        float g;
+        if (s >= 0) g = gated<T>(bcx, (size_t)(first + s), H, c);
+        else g = has_state ? to_f<T>(st[(size_t)(s + L - 1) * H + c]) : 0.f;
+        acc = fmaf(taps[j], g, acc);
+      }
+    }
+    const float cgate = to_f<T>(bcx[(size_t)m * 3 * H + H + c]);
+    out[(size_t)m * H + c] = from_f<T>(cgate * round_f<T>(acc));
+  }
+}
+
+template <typename T>
+__global__ void short_conv_state_kernel(const T* __restrict__ bcx, T* __restrict__ state,
+                                        const int* __restrict__ cu_seqlens,
+                                        const int* __restrict__ seg_start,
+                                        const int* __restrict__ seg_slot, int H, int L) {
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= H) return;
+  const int seg = blockIdx.y;
+  const int first = cu_seqlens[seg], n = cu_seqlens[seg + 1] - first;
+  if (n <= 0) return;
+  const bool has_state = seg_start[seg] > 0;
+  T* st = state + (size_t)seg_slot[seg] * (L - 1) * H;
+  float next[CONV_MAX_L];
+  // history ++ g has L-1+n rows; the new state is rows n .. n+L-2 of it.
+#pragma unroll
+  for (int i = 0; i < CONV_MAX_L; ++i) {
+    if (i < L - 1) {
+      const int idx = n + i;
+      if (idx < L - 1) next[i] = has_state ? to_f<T>(st[(size_t)idx * H + c]) : 0.f;
+      else next[i] = gated<T>(bcx, (size_t)(first + idx - (L - 1)), H, c);
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < CONV_MAX_L; ++i)
+    if (i < L - 1) st[(size_t)i * H + c] = from_f<T>(next[i]);
+}
+
+SNK_API int snk_short_conv(const void* bcx, const void* w, int w_is_f32, void* state,
+                           const int* cu_seqlens, const int* seg_start, const int* seg_slot,
+                           const int* row_seg, void* out, int M, int B, int H, int L, int dtype,
+                           cudaStream_t stream) {
+  if (M <= 0 || B <= 0) return 0;
+  if (L < 1 || L > CONV_MAX_L) return SNK_ERR_SIZE;
+  const int threads = 128;
+  dim3 grid((H + threads - 1) / threads, (M + CONV_ROWS_PER_BLOCK - 1) / CONV_ROWS_PER_BLOCK);
+  if (grid.y > 65535u) return SNK_ERR_SIZE;
+  SmallVec wv{w, w_is_f32};
+  SNK_DISPATCH(dtype, short_conv_kernel<T><<<grid, threads, 0, stream>>>(
+                          static_cast<const T*>(bcx), wv, static_cast<const T*>(state), cu_seqlens,
+                          seg_start, seg_slot, row_seg, static_cast<T*>(out), M, H, L));
+  SNK_LAUNCH_CHECK();
+  if (L > 1) {
+    dim3 sgrid((H + threads - 1) / threads, B);
+    SNK_DISPATCH(dtype, short_conv_state_kernel<T><<<sgrid, threads, 0, stream>>>(
+                            static_cast<const T*>(bcx), static_cast<T*>(state), cu_seqlens,
+                            seg_start, seg_slot, H, L));
+    SNK_LAUNCH_CHECK();
+  }
+  return 0;
+}

@@ -1,0 +1,87 @@
+"""The step's flat batch as the kernels see it (the role of Batch and ForwardContext,
+snowllm/engine/forward_context.py:45-172, and of prefill_batch, snowllm/engine/inputs.py:10-63).
+
+A step is a list of segments, one per request in it: ``n`` next tokens of that request starting at
+position ``start`` (= tokens already cached).  A decoded token is a segment with n = 1; prompt
+portions of any length sit beside them.  All integer metadata is packed into one pinned host buffer
+and copied to the device in one transfer."""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+
+import numpy as np
+import torch
+
+ATTENTION_CHUNK = 256          # keys per block along the sequence when rows are few
+ATTENTION_ROWS_ENOUGH = 128    # from this many rows on, rows alone fill the GPU: one chunk
+ATTENTION_TILE = 32
+
+
+@dataclass
+class StepContext:
+    dtype: torch.dtype
+    device: torch.device
+    M: int                         # rows (tokens) in the step
+    B: int                         # segments (requests) in the step
+    token_ids: torch.Tensor        # int32 [M]
+    positions: torch.Tensor        # int32 [M] absolute position of each row
+    row_seg: torch.Tensor          # int32 [M] segment of each row
+    cu_seqlens: torch.Tensor       # int32 [B+1] first row of each segment
+    seg_start: torch.Tensor        # int32 [B] tokens cached before this step (0: fresh request)
+    seg_slot: torch.Tensor         # int32 [B] state slot of each segment's request
+    logit_rows: torch.Tensor       # int32 [R] rows whose logits are wanted
+    num_logit_rows: int
+    block_tables: dict             # group key -> int32 [B, max_pages]
+    page_size: int
+    host_positions: np.ndarray     # the same facts on the host, for launch decisions
+    host_seg_start: list = field(default_factory=list)
+    host_seg_len: list = field(default_factory=list)
+    _plans: dict = field(default_factory=dict)
+
+    def scratch(self, nbytes: int) -> torch.Tensor:
+        """Scratch bytes for one kernel launch (stream-ordered, from torch's caching allocator)."""
+        return torch.empty(max(int(nbytes), 1), dtype=torch.uint8, device=self.device)
+
+    def attention_plan(self, window=None) -> tuple[int, int]:
+        """(chunk, num_chunks) for the attention kernel: with many rows one chunk per row, else
+        chunks of ATTENTION_CHUNK keys so that long sequences spread over the GPU."""
+        plan = self._plans.get(window)
+        if plan is None:
+            whole = (1 << 30) - ((1 << 30) % ATTENTION_TILE)
+            pos = self.host_positions
+            if self.M >= ATTENTION_ROWS_ENOUGH or int(pos.max(initial=0)) < 2 * ATTENTION_CHUNK:
+                plan = (whole, 1)
+            else:
+                lo = np.maximum(0, pos - window + 1) if window else np.zeros_like(pos)
+                n = int((pos // ATTENTION_CHUNK - lo // ATTENTION_CHUNK).max()) + 1
+                plan = (ATTENTION_CHUNK, n) if n > 1 else (whole, 1)
+            self._plans[window] = plan
+        return plan
+
+
+class HostStaging:
+    """A small ring of pinned int32 buffers; a buffer is reused only after the copy that read it
+    has finished (the role of Staging, snowllm/engine/block_manager.py:72-104)."""
+
+    def __init__(self, device, depth: int = 4):
+        self.device, self.depth = device, depth
+        self.buffers: list = [None] * depth
+        self.events: list = [None] * depth
+        self.turn = 0
+
+    def upload(self, host: np.ndarray) -> torch.Tensor:
+        i = self.turn
+        self.turn = (self.turn + 1) % self.depth
+        n = host.size
+        buf = self.buffers[i]
+        if self.events[i] is not None:
+            self.events[i].synchronize()
+        if buf is None or buf.numel() < n:
+            buf = torch.empty(max(n, 1024) * 2, dtype=torch.int32).pin_memory()
+            self.buffers[i] = buf
+        buf[:n].numpy()[:] = host
+        dev = buf[:n].to(self.device, non_blocking=True)
+        ev = torch.cuda.Event()
+        ev.record()
+        self.events[i] = ev
+        return dev

@@ -1,0 +1,117 @@
+"""The one step function: a batch of (request, its next tokens) in, logits at the wanted places out.
+
+It runs only the tokens it is given, as one batch, against the cache that earlier steps left, and
+records afterwards that the requests' caches grew.  Prompt portions and single decoded tokens may
+be mixed and cut anywhere (the role of runner.forward, snowllm/engine/runner.py:498-526, without
+its split into prefill-only and decode-only batches)."""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Sequence
+
+import numpy as np
+import torch
+
+from ..cache import CacheManager, RequestCache
+from ..errors import CapacityError, KernelError, SnowLLMError
+from ..ops import kernels
+from .context import HostStaging, StepContext
+
+
+@dataclass
+class StepEntry:
+    cache: RequestCache
+    tokens: Sequence[int]
+    want: Sequence[int] = field(default_factory=tuple)   # places among ``tokens`` whose logits are asked
+
+
+class ModelRunner:
+    def __init__(self, model, cache: CacheManager, device="cuda"):
+        if not torch.cuda.is_available():
+            raise KernelError("no CUDA device: this engine runs on the GPU only")
+        if not model.bound:
+            raise SnowLLMError("the model has no weights bound")
+        self.model, self.cache = model, cache
+        self.device = torch.device(device)
+        self.staging = HostStaging(self.device)
+        kernels.libraries_for(model.libraries())
+        self.steps = 0
+        self.tokens = 0
+
+    def step(self, entries: Sequence[StepEntry]) -> torch.Tensor:
+        """Run one batch; returns float logits [wanted rows, vocab] in entry order, then ``want``
+        order.  Every entry's pages must have been taken already (``CacheManager.ensure``)."""
+        entries = [e for e in entries if len(e.tokens) > 0]
+        if not entries:
+            return torch.empty(0, self.model.vocab_size, dtype=torch.float32, device=self.device)
+        ctx = self.build_context(entries)
+        with torch.no_grad():
+            logits = self.model.forward(ctx, self.cache)
+        for e in entries:
+            self.cache.commit(e.cache, e.cache.num_tokens + len(e.tokens))
+        self.steps += 1
+        self.tokens += ctx.M
+        return logits
+
+    def build_context(self, entries: Sequence[StepEntry]) -> StepContext:
+        P = self.cache.page_size
+        V = self.model.vocab_size
+        B = len(entries)
+        lens = [len(e.tokens) for e in entries]
+        starts = [e.cache.num_tokens for e in entries]
+        M = sum(lens)
+        seen = set()
+        for e, n, s in zip(entries, lens, starts):
+            if id(e.cache) in seen:
+                raise SnowLLMError("a request appears twice in one step")
+            seen.add(id(e.cache))
+            if e.cache.freed:
+                raise SnowLLMError("a freed request cannot be stepped")
+            if s + n > self.model.spec.max_position:
+                raise SnowLLMError(f"position {s + n} exceeds the model's limit {self.model.spec.max_position}")
+            for key, table in e.cache.tables.items():
+                need = -(-(s + n) // P)
+                first = 0 if key[1] is None else max(0, s - key[1] + 1) // P
+                if len(table) < need or any(p < 0 for p in table[first:need]):
+                    raise CapacityError("the step was given tokens whose pages were not taken")
+        ids = np.fromiter((t for e in entries for t in e.tokens), dtype=np.int64, count=M)
+        if M and (ids.min() < 0 or ids.max() >= V):
+            raise SnowLLMError(f"token id outside [0, {V})")
+        cu = np.zeros(B + 1, dtype=np.int64)
+        np.cumsum(lens, out=cu[1:])
+        row_seg = np.repeat(np.arange(B), lens)
+        positions = np.arange(M) - np.repeat(cu[:-1], lens) + np.repeat(starts, lens)
+        logit_rows = []
+        for b, e in enumerate(entries):
+            for w in e.want:
+                if not 0 <= w < lens[b]:
+                    raise SnowLLMError(f"wanted place {w} is outside the entry's {lens[b]} tokens")
+                logit_rows.append(int(cu[b]) + int(w))
+        groups = list(self.cache.groups)
+        max_pages = max(1, -(-max(s + n for s, n in zip(starts, lens)) // P))
+        tables = np.zeros((len(groups), B, max_pages), dtype=np.int64)
+        for g, key in enumerate(groups):
+            for b, e in enumerate(entries):
+                t = e.cache.tables[key][:max_pages]
+                if t:
+                    tables[g, b, :len(t)] = np.maximum(np.asarray(t), 0)
+        parts = [ids, positions, row_seg, cu, np.asarray(starts), np.asarray([e.cache.slot for e in entries]),
+                 np.asarray(logit_rows, dtype=np.int64), tables.reshape(-1)]
+        sizes = [p.size for p in parts]
+        # each part starts on a 16-byte boundary
+        offs, total = [], 0
+        for s in sizes:
+            offs.append(total)
+            total += -(-s // 4) * 4
+        host = np.zeros(total, dtype=np.int32)
+        for p, o in zip(parts, offs):
+            host[o:o + p.size] = p
+        dev = self.staging.upload(host)
+        view = lambda i: dev[offs[i]:offs[i] + sizes[i]]
+        tab = view(7).view(len(groups), B, max_pages)
+        return StepContext(
+            dtype=self.model.dtype, device=self.device, M=M, B=B, token_ids=view(0), positions=view(1),
+            row_seg=view(2), cu_seqlens=view(3), seg_start=view(4), seg_slot=view(5), logit_rows=view(6),
+            num_logit_rows=len(logit_rows), block_tables={key: tab[g] for g, key in enumerate(groups)},
+            page_size=P, host_positions=positions.astype(np.int64), host_seg_start=list(starts),
+            host_seg_len=list(lens))

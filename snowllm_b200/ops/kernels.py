@@ -1,0 +1,417 @@
+"""Python side of the sm_100a kernels: checks of dtype, shape and contiguity, then one launch.
+
+Every function launches on torch's current CUDA stream and returns without synchronising.
+There is no other implementation behind these names: a tensor that is not on a CUDA device,
+or a library that cannot be built, is an error (the role of snowllm/ops/_common.py:82-112).
+"""
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_float, c_int, c_longlong, c_void_p
+
+import torch
+
+from ..csrc import build
+from ..errors import KernelError
+
+F32, BF16 = 0, 1
+_DTYPE_CODE = {torch.float32: F32, torch.bfloat16: BF16}
+
+P, I, F, LL = c_void_p, c_int, c_float, c_longlong
+_SIGNATURES = {
+    "elementwise": {
+        "snk_embedding": [P, P, P, I, I, I, I, P],
+        "snk_add_rmsnorm": [P, P, P, I, P, P, I, I, F, I, P],
+        "snk_residual_add": [P, P, LL, P],
+        "snk_swiglu": [P, P, I, I, I, P],
+    },
+    "rope_cache": {
+        "snk_qk_norm_rope_cache": [P, P, P, I, I, F, P, I, P, P, P, I, I, P, P, I, I, I, I, I, I, P],
+    },
+    "short_conv": {
+        "snk_short_conv": [P, P, I, P, P, P, P, P, P, I, I, I, I, I, P],
+    },
+    "attention": {
+        "snk_paged_attention_scratch_bytes": [I, I, I, I],
+        "snk_paged_attention": [P, P, P, I, I, P, P, P, P, I, I, I, I, I, I, I, F, I, P],
+    },
+    "gemm": {
+        "snk_gemm_simt": [P, P, P, I, I, I, P, I, P, I, I, I, I, P],
+    },
+    "moe": {
+        "snk_moe_route": [P, P, I, P, P, P, I, I, I, I, I, F, I, P],
+        "snk_moe_sort": [P, P, P, P, I, I, P],
+        "snk_moe_combine": [P, P, P, P, I, I, I, P],
+    },
+    "sampling": {
+        "snk_argmax": [P, P, I, I, P],
+        "snk_apply_penalties": [P, P, P, P, P, P, P, I, I, P],
+        "snk_sample": [P, P, P, P, P, P, I, I, P],
+    },
+}
+_RESTYPES = {"snk_paged_attention_scratch_bytes": LL}
+_functions: dict[str, object] = {}
+_library_of = {fn: lib for lib, fns in _SIGNATURES.items() for fn in fns}
+
+_ERRORS = {20001: "unknown dtype code", 20002: "a size this kernel does not take",
+           20003: "a pointer or pitch that is not aligned as the kernel needs"}
+
+
+def register_signatures(library: str, signatures: dict, restypes: dict | None = None) -> None:
+    """Let another source file of csrc/ be called through ``fn``."""
+    _SIGNATURES.setdefault(library, {}).update(signatures)
+    for name in signatures:
+        _library_of[name] = library
+    _RESTYPES.update(restypes or {})
+
+
+def fn(name: str):
+    f = _functions.get(name)
+    if f is None:
+        lib = build.load(_library_of[name])
+        f = getattr(lib, name)
+        f.argtypes = _SIGNATURES[_library_of[name]][name]
+        f.restype = _RESTYPES.get(name, c_int)
+        _functions[name] = f
+    return f
+
+
+def libraries_for(names) -> None:
+    """Build (in parallel) the libraries that hold the named groups, before first use."""
+    build.build(tuple(dict.fromkeys(names)))
+
+
+def check(status: int, what: str) -> None:
+    if status == 0:
+        return
+    if status in _ERRORS:
+        raise KernelError(f"{what}: {_ERRORS[status]}")
+    raise KernelError(f"{what}: CUDA error {status} ({_cuda_error_name(status)})")
+
+
+def _cuda_error_name(code: int) -> str:
+    try:
+        rt = ctypes.CDLL("libcudart.so")
+        rt.cudaGetErrorString.restype = ctypes.c_char_p
+        return rt.cudaGetErrorString(code).decode()
+    except OSError:
+        return "?"
+
+
+def _stream() -> c_void_p:
+    return c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _ptr(t: torch.Tensor | None) -> c_void_p:
+    return c_void_p(t.data_ptr()) if t is not None else c_void_p(0)
+
+
+def _chk(t: torch.Tensor, what: str, dtype=None, shape=None) -> None:
+    if not isinstance(t, torch.Tensor) or not t.is_cuda:
+        raise KernelError(f"{what}: needs a CUDA tensor (this engine has no CPU path)")
+    if dtype is not None and t.dtype not in (dtype if isinstance(dtype, tuple) else (dtype,)):
+        raise KernelError(f"{what}: dtype {t.dtype}, want {dtype}")
+    if not t.is_contiguous():
+        raise KernelError(f"{what}: must be contiguous")
+    if shape is not None and tuple(t.shape) != tuple(shape):
+        raise KernelError(f"{what}: shape {tuple(t.shape)}, want {tuple(shape)}")
+
+
+def code_of(dtype: torch.dtype) -> int:
+    try:
+        return _DTYPE_CODE[dtype]
+    except KeyError:
+        raise KernelError(f"compute dtype {dtype} is not supported (float32 or bfloat16)") from None
+
+
+def _small(t: torch.Tensor, what: str, compute: torch.dtype) -> int:
+    """A small weight may be float32 or the compute dtype; returns its is-float flag."""
+    _chk(t, what, (torch.float32, compute))
+    return int(t.dtype == torch.float32)
+
+
+# --- elementwise -----------------------------------------------------------------------
+
+def embedding(ids: torch.Tensor, table: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
+    """Float rows of ``table`` (compute dtype) at int32 ``ids``: the start of the residual stream."""
+    M = ids.numel()
+    V, H = table.shape
+    _chk(ids, "embedding ids", torch.int32)
+    _chk(table, "embedding table", (torch.float32, torch.bfloat16))
+    if out is None:
+        out = torch.empty(M, H, dtype=torch.float32, device=table.device)
+    _chk(out, "embedding output", torch.float32, (M, H))
+    check(fn("snk_embedding")(_ptr(ids), _ptr(table), _ptr(out), M, H, V, code_of(table.dtype),
+                              _stream()), "embedding")
+    return out
+
+
+def add_rmsnorm(residual: torch.Tensor, delta: torch.Tensor | None, gamma: torch.Tensor, eps: float,
+                dtype: torch.dtype, rows: torch.Tensor | None = None,
+                out: torch.Tensor | None = None) -> torch.Tensor:
+    """``residual += delta`` (if given), then RMSNorm of the sum into the compute dtype.  With
+    ``rows`` only those rows are normalised and the residual is left as it is."""
+    M, H = residual.shape
+    _chk(residual, "residual", torch.float32)
+    if delta is not None:
+        _chk(delta, "residual delta", torch.float32, (M, H))
+    g32 = _small(gamma, "norm weight", dtype)
+    _chk(gamma, "norm weight", shape=(H,))
+    R = M if rows is None else rows.numel()
+    if rows is not None:
+        _chk(rows, "norm rows", torch.int32)
+    if out is None:
+        out = torch.empty(R, H, dtype=dtype, device=residual.device)
+    _chk(out, "norm output", dtype, (R, H))
+    check(fn("snk_add_rmsnorm")(_ptr(residual), _ptr(delta), _ptr(gamma), g32, _ptr(out), _ptr(rows),
+                                R, H, float(eps), code_of(dtype), _stream()), "add_rmsnorm")
+    return out
+
+
+def residual_add(residual: torch.Tensor, delta: torch.Tensor) -> None:
+    _chk(residual, "residual", torch.float32)
+    _chk(delta, "residual delta", torch.float32, residual.shape)
+    check(fn("snk_residual_add")(_ptr(residual), _ptr(delta), residual.numel(), _stream()), "residual_add")
+
+
+def swiglu(gate_up: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
+    """[M, 2I] (gate | up) -> [M, I]: round(silu(gate)) * up."""
+    M, two_i = gate_up.shape
+    _chk(gate_up, "swiglu input", (torch.float32, torch.bfloat16))
+    if two_i % 2:
+        raise KernelError("swiglu input needs an even width")
+    inter = two_i // 2
+    if out is None:
+        out = torch.empty(M, inter, dtype=gate_up.dtype, device=gate_up.device)
+    _chk(out, "swiglu output", gate_up.dtype, (M, inter))
+    check(fn("snk_swiglu")(_ptr(gate_up), _ptr(out), M, inter, code_of(gate_up.dtype), _stream()), "swiglu")
+    return out
+
+
+# --- attention -------------------------------------------------------------------------
+
+def qk_norm_rope_cache(qkv, q_gamma, k_gamma, eps, inv_freq, rot_dim, positions, row_seg, block_table,
+                       page_size, pool, num_heads, num_kv_heads, head_dim, write_kv=True, q_out=None):
+    """Per-head RMSNorm of q and k (if weights are given), rotary encoding (if ``inv_freq``), k and v
+    written to the paged pool at each row's position; returns q as [M, heads, head_dim]."""
+    M = qkv.shape[0]
+    dtype = qkv.dtype
+    width = (num_heads + (2 * num_kv_heads if write_kv else 0)) * head_dim
+    _chk(qkv, "qkv", (torch.float32, torch.bfloat16), (M, width))
+    has_norm = q_gamma is not None
+    g32 = 0
+    if has_norm:
+        g32 = _small(q_gamma, "q norm weight", dtype)
+        if _small(k_gamma, "k norm weight", dtype) != g32:
+            raise KernelError("q and k norm weights must share a dtype")
+        _chk(q_gamma, "q norm weight", shape=(head_dim,))
+        _chk(k_gamma, "k norm weight", shape=(head_dim,))
+    if inv_freq is not None:
+        _chk(inv_freq, "inv_freq", torch.float32, (rot_dim // 2,))
+    _chk(positions, "positions", torch.int32, (M,))
+    _chk(row_seg, "row_seg", torch.int32, (M,))
+    _chk(block_table, "block table", torch.int32)
+    _chk(pool, "kv pool", dtype)
+    if pool.dim() != 5 or tuple(pool.shape[1:]) != (2, num_kv_heads, page_size, head_dim):
+        raise KernelError(f"kv pool shape {tuple(pool.shape)}, want [pages, 2, {num_kv_heads}, "
+                          f"{page_size}, {head_dim}]")
+    if q_out is None:
+        q_out = torch.empty(M, num_heads, head_dim, dtype=dtype, device=qkv.device)
+    _chk(q_out, "q output", dtype, (M, num_heads, head_dim))
+    check(fn("snk_qk_norm_rope_cache")(
+        _ptr(qkv), _ptr(q_gamma), _ptr(k_gamma), g32, int(has_norm), float(eps), _ptr(inv_freq),
+        int(rot_dim if inv_freq is not None else 0), _ptr(positions), _ptr(row_seg), _ptr(block_table),
+        block_table.shape[1], page_size, _ptr(pool), _ptr(q_out), M, num_heads, num_kv_heads, head_dim,
+        int(write_kv), code_of(dtype), _stream()), "qk_norm_rope_cache")
+    return q_out
+
+
+ATTENTION_TILE = 32
+
+
+def attention_scratch_bytes(M: int, num_heads: int, head_dim: int, num_chunks: int) -> int:
+    return int(fn("snk_paged_attention_scratch_bytes")(M, num_heads, head_dim, num_chunks))
+
+
+def paged_attention(q, pool, block_table, page_size, positions, row_seg, scale, window=None,
+                    chunk=None, num_chunks=1, scratch=None, out=None):
+    """Causal attention of each row of q [M, heads, head_dim] over its request's cached keys up to
+    its own position.  ``chunk`` keys per block along the sequence (a multiple of 32) and
+    ``num_chunks`` = the most chunks any row spans; more than one needs ``scratch`` bytes."""
+    M, nh, hd = q.shape
+    dtype = q.dtype
+    _chk(q, "q", (torch.float32, torch.bfloat16))
+    _chk(pool, "kv pool", dtype)
+    nkv = pool.shape[2]
+    _chk(positions, "positions", torch.int32, (M,))
+    _chk(row_seg, "row_seg", torch.int32, (M,))
+    _chk(block_table, "block table", torch.int32)
+    if chunk is None:
+        chunk = 1 << 30
+        chunk -= chunk % ATTENTION_TILE
+    if out is None:
+        out = torch.empty(M, nh * hd, dtype=dtype, device=q.device)
+    _chk(out, "attention output", dtype, (M, nh * hd))
+    if num_chunks > 1:
+        need = attention_scratch_bytes(M, nh, hd, num_chunks)
+        if scratch is None:
+            scratch = torch.empty(need, dtype=torch.uint8, device=q.device)
+        _chk(scratch, "attention scratch", torch.uint8)
+        if scratch.numel() < need:
+            raise KernelError(f"attention scratch holds {scratch.numel()} bytes, needs {need}")
+    check(fn("snk_paged_attention")(
+        _ptr(q), _ptr(pool), _ptr(block_table), block_table.shape[1], page_size, _ptr(positions),
+        _ptr(row_seg), _ptr(out), _ptr(scratch), M, nh, nkv, hd, int(window or 0), int(chunk),
+        int(num_chunks), float(scale), code_of(dtype), _stream()), "paged_attention")
+    return out
+
+
+# --- short convolution -----------------------------------------------------------------
+
+def short_conv(bcx, weight, state, cu_seqlens, seg_start, seg_slot, row_seg, out=None):
+    """Gated causal depthwise convolution over [M, 3H] rows (B | C | x) of a flat batch of segments;
+    ``state`` [slots, L-1, H] holds each request's history and is brought up to date."""
+    M, three_h = bcx.shape
+    dtype = bcx.dtype
+    H = three_h // 3
+    _chk(bcx, "conv input", (torch.float32, torch.bfloat16), (M, 3 * H))
+    w32 = _small(weight, "conv weight", dtype)
+    L = weight.shape[1]
+    _chk(weight, "conv weight", shape=(H, L))
+    _chk(state, "conv state", dtype)
+    if state.dim() != 3 or tuple(state.shape[1:]) != (max(L - 1, 0), H):
+        raise KernelError(f"conv state shape {tuple(state.shape)}, want [slots, {L - 1}, {H}]")
+    B = seg_start.numel()
+    _chk(cu_seqlens, "cu_seqlens", torch.int32, (B + 1,))
+    _chk(seg_start, "seg_start", torch.int32, (B,))
+    _chk(seg_slot, "seg_slot", torch.int32, (B,))
+    _chk(row_seg, "row_seg", torch.int32, (M,))
+    if out is None:
+        out = torch.empty(M, H, dtype=dtype, device=bcx.device)
+    _chk(out, "conv output", dtype, (M, H))
+    check(fn("snk_short_conv")(_ptr(bcx), _ptr(weight), w32, _ptr(state), _ptr(cu_seqlens), _ptr(seg_start),
+                               _ptr(seg_slot), _ptr(row_seg), _ptr(out), M, B, H, L, code_of(dtype),
+                               _stream()), "short_conv")
+    return out
+
+
+# --- matrix products -------------------------------------------------------------------
+
+def gemm_simt(a, w, out_dtype=None, out=None, a_rows=None, a_div=1, offsets=None, rows_out=None,
+              max_rows_per_group=None):
+    """a [M, K] times w [N, K]^T (or, grouped, w [G, N, K] over rows sorted by group) with float
+    accumulation in k order on the CUDA cores."""
+    dtype = a.dtype
+    _chk(a, "gemm a", (torch.float32, torch.bfloat16))
+    _chk(w, "gemm w", dtype)
+    K = a.shape[1]
+    grouped = offsets is not None
+    if grouped:
+        G, N, Kw = w.shape
+        _chk(offsets, "group offsets", torch.int32, (G + 1,))
+    else:
+        G = 1
+        N, Kw = w.shape
+    if Kw != K:
+        raise KernelError(f"gemm: a has K={K}, w has K={Kw}")
+    M = rows_out if rows_out is not None else a.shape[0]
+    if a_rows is not None:
+        _chk(a_rows, "gemm row gather", torch.int32)
+    out_dtype = out_dtype or dtype
+    if out is None:
+        out = torch.empty(M, N, dtype=out_dtype, device=a.device)
+    _chk(out, "gemm out", out_dtype, (M, N))
+    if out_dtype not in (dtype, torch.float32):
+        raise KernelError("gemm output is the compute dtype or float32")
+    check(fn("snk_gemm_simt")(_ptr(a), _ptr(w), _ptr(out), M, N, K, _ptr(a_rows), int(a_div), _ptr(offsets),
+                              G, int(max_rows_per_group if grouped else M),
+                              int(out_dtype == torch.float32), code_of(dtype), _stream()), "gemm_simt")
+    return out
+
+
+# --- routed experts --------------------------------------------------------------------
+
+def moe_route(x, router_w, bias, top_k, norm_topk_prob, scaling):
+    """(ids int32 [M, k], weights float [M, k]) of the sigmoid router, computed in float."""
+    M, H = x.shape
+    dtype = x.dtype
+    _chk(x, "router input", (torch.float32, torch.bfloat16))
+    w32 = _small(router_w, "router weight", dtype)
+    E = router_w.shape[0]
+    _chk(router_w, "router weight", shape=(E, H))
+    if bias is not None:
+        _chk(bias, "expert bias", torch.float32, (E,))
+    ids = torch.empty(M, top_k, dtype=torch.int32, device=x.device)
+    wts = torch.empty(M, top_k, dtype=torch.float32, device=x.device)
+    check(fn("snk_moe_route")(_ptr(x), _ptr(router_w), w32, _ptr(bias), _ptr(ids), _ptr(wts), M, H, E,
+                              top_k, int(bool(norm_topk_prob)), float(scaling), code_of(dtype), _stream()),
+          "moe_route")
+    return ids, wts
+
+
+def moe_sort(topk_ids, num_experts):
+    """(offsets int32 [E+1], pair_pos int32 [M*k], sorted_pair int32 [M*k]) of the pairs sorted by
+    expert."""
+    _chk(topk_ids, "top-k ids", torch.int32)
+    pairs = topk_ids.numel()
+    dev = topk_ids.device
+    offsets = torch.empty(num_experts + 1, dtype=torch.int32, device=dev)
+    pair_pos = torch.empty(pairs, dtype=torch.int32, device=dev)
+    sorted_pair = torch.empty(pairs, dtype=torch.int32, device=dev)
+    check(fn("snk_moe_sort")(_ptr(topk_ids), _ptr(offsets), _ptr(pair_pos), _ptr(sorted_pair), pairs,
+                             num_experts, _stream()), "moe_sort")
+    return offsets, pair_pos, sorted_pair
+
+
+def moe_combine(y, pair_pos, topk_w, out=None):
+    """out[m] = sum_j w[m, j] * y[pair_pos[m*k + j]] in float, j in order."""
+    M, k = topk_w.shape
+    H = y.shape[1]
+    _chk(y, "expert outputs", torch.float32, (M * k, H))
+    _chk(pair_pos, "pair positions", torch.int32, (M * k,))
+    _chk(topk_w, "top-k weights", torch.float32)
+    if out is None:
+        out = torch.empty(M, H, dtype=torch.float32, device=y.device)
+    _chk(out, "moe output", torch.float32, (M, H))
+    check(fn("snk_moe_combine")(_ptr(y), _ptr(pair_pos), _ptr(topk_w), _ptr(out), M, H, k, _stream()),
+          "moe_combine")
+    return out
+
+
+# --- sampling --------------------------------------------------------------------------
+
+def argmax(logits, out=None):
+    B, V = logits.shape
+    _chk(logits, "logits", torch.float32)
+    if out is None:
+        out = torch.empty(B, dtype=torch.int32, device=logits.device)
+    _chk(out, "argmax output", torch.int32, (B,))
+    check(fn("snk_argmax")(_ptr(logits), _ptr(out), B, V, _stream()), "argmax")
+    return out
+
+
+def apply_penalties(logits, row_offsets, ids, counts, presence, frequency, repetition):
+    B, V = logits.shape
+    _chk(logits, "logits", torch.float32)
+    _chk(row_offsets, "penalty offsets", torch.int32, (B + 1,))
+    _chk(ids, "penalty ids", torch.int32)
+    _chk(counts, "penalty counts", torch.int32, ids.shape)
+    for t, what in ((presence, "presence"), (frequency, "frequency"), (repetition, "repetition")):
+        _chk(t, what + " penalty", torch.float32, (B,))
+    check(fn("snk_apply_penalties")(_ptr(logits), _ptr(row_offsets), _ptr(ids), _ptr(counts), _ptr(presence),
+                                    _ptr(frequency), _ptr(repetition), B, V, _stream()), "apply_penalties")
+
+
+def sample(logits, temperature, top_k, top_p, uniform, out=None):
+    B, V = logits.shape
+    _chk(logits, "logits", torch.float32)
+    _chk(temperature, "temperature", torch.float32, (B,))
+    _chk(top_k, "top_k", torch.int32, (B,))
+    _chk(top_p, "top_p", torch.float32, (B,))
+    _chk(uniform, "uniform", torch.float32, (B,))
+    if out is None:
+        out = torch.empty(B, dtype=torch.int32, device=logits.device)
+    _chk(out, "sample output", torch.int32, (B,))
+    check(fn("snk_sample")(_ptr(logits), _ptr(temperature), _ptr(top_k), _ptr(top_p), _ptr(uniform),
+                           _ptr(out), B, V, _stream()), "sample")
+    return out

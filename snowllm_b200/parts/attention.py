@@ -1,0 +1,72 @@
+"""Grouped-query attention mixer over the paged cache
+(snowllm/models/lfm2/layers.py:36-70; snowllm/models/qwen3_5/layers.py:122-135).
+
+q, k, v are one fused product; a second kernel applies the per-head RMSNorm of q and k, the
+position encoding, and writes k and v into the cache pages; a third attends over the pages.
+``window`` keeps the last ``window`` keys only (None: all).  A layer that reads another layer's
+cache (``owns_cache`` False) projects q alone and writes nothing."""
+from __future__ import annotations
+
+import torch
+
+from ..ops import kernels, linear
+from .base import Part
+from .registry import lookup, register_mixer
+from .spec import INIT_ONES, KEEP_SMALL, PagedKVSpec, TensorSpec
+
+
+class Attention(Part):
+    libraries = ("gemm", "rope_cache", "attention")
+
+    def __init__(self, dtype, names, *, hidden_size: int, num_heads: int, num_kv_heads: int,
+                 head_dim: int, qk_norm_eps: float | None, position: dict, window: int | None = None,
+                 scale: float | None = None):
+        super().__init__(dtype, names)
+        if num_heads % num_kv_heads:
+            raise ValueError(f"num_heads={num_heads} is no multiple of num_kv_heads={num_kv_heads}")
+        self.hidden_size, self.num_heads, self.num_kv_heads = hidden_size, num_heads, num_kv_heads
+        self.head_dim, self.qk_norm_eps, self.window = head_dim, qk_norm_eps, window
+        self.scale = head_dim ** -0.5 if scale is None else scale
+        pos = dict(position)
+        self.position = lookup("position", pos.pop("kind"))(**pos)
+        self.wqkv = self.wq = self.wo = self.q_norm = self.k_norm = None
+
+    def cache_spec(self):
+        return PagedKVSpec(self.num_kv_heads, self.head_dim, self.window)
+
+    def declare(self, has):
+        H, hd, n = self.hidden_size, self.head_dim, self.names
+        specs = [TensorSpec("q_proj", n["q_proj"], (self.num_heads * hd, H)),
+                 TensorSpec("k_proj", n["k_proj"], (self.num_kv_heads * hd, H)),
+                 TensorSpec("v_proj", n["v_proj"], (self.num_kv_heads * hd, H)),
+                 TensorSpec("out_proj", n["out_proj"], (H, self.num_heads * hd))]
+        if self.qk_norm_eps is not None:
+            specs += [TensorSpec("q_norm", n["q_norm"], (hd,), INIT_ONES, KEEP_SMALL),
+                      TensorSpec("k_norm", n["k_norm"], (hd,), INIT_ONES, KEEP_SMALL)]
+        return specs
+
+    def bind(self, tensors):
+        self.wqkv = torch.cat((tensors["q_proj"], tensors["k_proj"], tensors["v_proj"]), 0).contiguous()
+        self.wq = self.wqkv[: self.num_heads * self.head_dim]
+        self.wo = tensors["out_proj"]
+        self.q_norm, self.k_norm = tensors.get("q_norm"), tensors.get("k_norm")
+        if self.q_norm is not None and self.q_norm.dtype != self.k_norm.dtype:
+            self.q_norm, self.k_norm = self.q_norm.float(), self.k_norm.float()
+
+    def forward(self, ctx, x, cache, owns_cache=True):
+        qkv = linear(x, self.wqkv if owns_cache else self.wq)
+        inv_freq, rot_dim = self.position.rotary(x.device)
+        q = kernels.qk_norm_rope_cache(
+            qkv, self.q_norm, self.k_norm, self.qk_norm_eps or 0.0, inv_freq, rot_dim, ctx.positions,
+            ctx.row_seg, cache.block_table, cache.page_size, cache.pool, self.num_heads,
+            self.num_kv_heads, self.head_dim, write_kv=owns_cache)
+        chunk, num_chunks = ctx.attention_plan(self.window)
+        scratch = ctx.scratch(kernels.attention_scratch_bytes(
+            ctx.M, self.num_heads, self.head_dim, num_chunks)) if num_chunks > 1 else None
+        o = kernels.paged_attention(q, cache.pool, cache.block_table, cache.page_size, ctx.positions,
+                                    ctx.row_seg, self.scale, window=self.window, chunk=chunk,
+                                    num_chunks=num_chunks, scratch=scratch)
+        return linear(o, self.wo, out_dtype=torch.float32)
+
+
+register_mixer("attention", Attention)

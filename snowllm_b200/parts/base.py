@@ -1,0 +1,45 @@
+"""What every part is: constants as constructor parameters, weights declared by checkpoint
+name, bound once they are on the device, and a forward over the step's flat batch.
+
+Interfaces (duck-typed; these base classes only hold what is common):
+
+* every part:  ``__init__(dtype, names, **params)``, ``declare(has) -> [TensorSpec]``,
+  ``bind(tensors)``; ``libraries`` names the csrc sources its kernels come from.
+* mixer:       ``cache_spec() -> PagedKVSpec | SlotStateSpec | None`` and
+               ``forward(ctx, x[M,H], cache, owns_cache) -> float delta [M,H]``
+* feed-forward ``forward(ctx, x[M,H]) -> float delta [M,H]``
+* norm:        ``forward(ctx, residual, delta, rows=None) -> x[M,H]`` (adds delta into the float
+               residual, then normalises into the compute dtype)
+* position:    ``rotary(device) -> (inv_freq float [rot_dim/2] | None, rot_dim)``
+* block:       ``forward(ctx, residual, delta, cache, owns_cache) -> delta`` (how mixer, feed-
+               forward and norms are arranged around the residual stream)
+
+No part knows which model it is in: what it needs comes through its parameters, its tensors
+and the step context.
+"""
+from __future__ import annotations
+
+from typing import Callable, Mapping
+
+import torch
+
+from .spec import TensorSpec
+
+
+class Part:
+    libraries: tuple[str, ...] = ()
+
+    def __init__(self, dtype: torch.dtype, names: Mapping[str, str]):
+        self.dtype = dtype
+        self.names = dict(names)
+
+    def declare(self, has: Callable[[str], bool]) -> list[TensorSpec]:
+        """The checkpoint tensors this part needs; ``has(name)`` tells which spellings exist."""
+        return []
+
+    def bind(self, tensors: Mapping[str, torch.Tensor]) -> None:
+        """Take the loaded tensors (keyed by TensorSpec.local), fuse or reshape as needed."""
+
+    def parts(self):
+        """Parts nested in this one (their tensors are declared and bound through it)."""
+        return ()

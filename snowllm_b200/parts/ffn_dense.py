@@ -1,0 +1,37 @@
+"""Dense SwiGLU feed-forward: down(round(silu(gate x)) * up x)
+(snowllm/models/lfm2/layers.py:76-88; snowllm/ops/mlp.py:12-20).  Gate and up are one fused
+product [2I, H]; the down product leaves a float delta for the residual sum."""
+from __future__ import annotations
+
+import torch
+
+from ..ops import kernels, linear
+from .base import Part
+from .registry import register_ffn
+from .spec import TensorSpec
+
+
+class SwiGLU(Part):
+    libraries = ("gemm", "elementwise")
+
+    def __init__(self, dtype, names, *, hidden_size: int, intermediate_size: int):
+        super().__init__(dtype, names)
+        self.hidden_size, self.intermediate_size = hidden_size, intermediate_size
+        self.w13 = self.w2 = None
+
+    def declare(self, has):
+        H, I = self.hidden_size, self.intermediate_size
+        return [TensorSpec("gate", self.names["gate"], (I, H)),
+                TensorSpec("up", self.names["up"], (I, H)),
+                TensorSpec("down", self.names["down"], (H, I))]
+
+    def bind(self, tensors):
+        self.w13 = torch.cat((tensors["gate"], tensors["up"]), 0).contiguous()
+        self.w2 = tensors["down"]
+
+    def forward(self, ctx, x):
+        act = kernels.swiglu(linear(x, self.w13))
+        return linear(act, self.w2, out_dtype=torch.float32)
+
+
+register_ffn("swiglu", SwiGLU)

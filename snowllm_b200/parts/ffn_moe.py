@@ -1,0 +1,75 @@
+"""Sigmoid-routed top-k experts, each a SwiGLU feed-forward, no shared expert
+(snowllm/models/qwen3_5/layers.py:166-188; router formula tests/test_lfm2_reference.py:113-119;
+tensor names and the fused / per-expert spellings snowllm/models/lfm2/weights.py:79-92).
+
+Steps: router in float -> sort the (token, pick) pairs by expert -> grouped gate|up product over
+the sorted rows (rows gathered from x) -> SwiGLU -> grouped down product (float) -> weighted sum
+per token in pick order.  Only experts that own rows are read."""
+from __future__ import annotations
+
+import torch
+
+from ..ops import grouped_linear, kernels
+from .base import Part
+from .registry import register_ffn
+from .spec import INIT_BIAS, KEEP_F32, KEEP_SMALL, TensorSpec
+
+
+class SigmoidMoE(Part):
+    libraries = ("gemm", "moe", "elementwise")
+
+    def __init__(self, dtype, names, *, hidden_size: int, intermediate_size: int, num_experts: int,
+                 top_k: int, norm_topk_prob: bool, use_expert_bias: bool, routed_scaling_factor: float):
+        super().__init__(dtype, names)
+        self.hidden_size, self.intermediate_size = hidden_size, intermediate_size
+        self.num_experts, self.top_k = num_experts, top_k
+        self.norm_topk_prob, self.use_expert_bias = norm_topk_prob, use_expert_bias
+        self.routed_scaling_factor = routed_scaling_factor
+        self.router = self.bias = self.w13 = self.w2 = None
+        self._fused = False
+
+    def declare(self, has):
+        H, I, E = self.hidden_size, self.intermediate_size, self.num_experts
+        n = self.names
+        specs = [TensorSpec("router", n["router"], (E, H), keep=KEEP_SMALL)]
+        if self.use_expert_bias:
+            specs.append(TensorSpec("expert_bias", n["expert_bias"], (E,), INIT_BIAS, KEEP_F32))
+        self._fused = has(n["fused_gate_up"])
+        if self._fused:
+            specs += [TensorSpec("gate_up", n["fused_gate_up"], (E, 2 * I, H)),
+                      TensorSpec("down", n["fused_down"], (E, H, I))]
+        else:
+            for e in range(E):
+                p = f"{n['experts']}{e}."
+                specs += [TensorSpec(f"gate.{e}", p + n["expert_gate"], (I, H)),
+                          TensorSpec(f"up.{e}", p + n["expert_up"], (I, H)),
+                          TensorSpec(f"down.{e}", p + n["expert_down"], (H, I))]
+        return specs
+
+    def bind(self, tensors):
+        E = self.num_experts
+        self.router = tensors["router"]
+        self.bias = tensors.get("expert_bias") if self.use_expert_bias else None
+        if self._fused:
+            self.w13, self.w2 = tensors["gate_up"].contiguous(), tensors["down"].contiguous()
+        else:
+            self.w13 = torch.stack([torch.cat((tensors[f"gate.{e}"], tensors[f"up.{e}"]), 0)
+                                    for e in range(E)]).contiguous()
+            self.w2 = torch.stack([tensors[f"down.{e}"] for e in range(E)]).contiguous()
+
+    def route(self, x):
+        return kernels.moe_route(x, self.router, self.bias, self.top_k, self.norm_topk_prob,
+                                 self.routed_scaling_factor)
+
+    def forward(self, ctx, x):
+        M, k = x.shape[0], self.top_k
+        ids, weights = self.route(x)
+        offsets, pair_pos, sorted_pair = kernels.moe_sort(ids, self.num_experts)
+        cap = min(M, M * k)          # an expert gets a token at most once
+        h = grouped_linear(x, self.w13, offsets, M * k, cap, a_rows=sorted_pair, a_div=k)
+        act = kernels.swiglu(h)
+        y = grouped_linear(act, self.w2, offsets, M * k, cap, out_dtype=torch.float32)
+        return kernels.moe_combine(y, pair_pos, weights)
+
+
+register_ffn("sigmoid_moe", SigmoidMoE)

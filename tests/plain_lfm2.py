@@ -1,0 +1,263 @@
+"""Plain, slow LFM2 / LFM2.5 forward pass: the oracle of the test-suite.
+
+Whole sequences, no cache, one function per part, float32 arithmetic throughout,
+plain PyTorch on whatever device the tensors live on (the CPU in the tests).  It
+shares no code with ``snowllm_b200``: it has its own config reading, its own
+safetensors parser and its own formulas.
+
+Anchoring.  SnowLLM's own model code cannot be imported or compiled on a CPU (its
+modules load a closed HIP kernel library at import time), so this file rests on
+the formulas alone.  Each function cites the place in SnowLLM/SnowLLM (path within
+that project) from which its formula is read.
+"""
+from __future__ import annotations
+
+import json
+import math
+import pathlib
+import struct
+
+import torch
+import torch.nn.functional as F
+
+_ST_DTYPES = {
+    "F32": torch.float32, "BF16": torch.bfloat16, "F16": torch.float16,
+    "I32": torch.int32, "I64": torch.int64, "F64": torch.float64,
+}
+
+
+def read_safetensors(path):
+    """name -> tensor, from one .safetensors file (8-byte little-endian header
+    length, JSON header, raw bytes; snowllm/checkpoint/reader.py:64-76)."""
+    raw = pathlib.Path(path).read_bytes()
+    (n,) = struct.unpack("<Q", raw[:8])
+    header = json.loads(raw[8:8 + n])
+    base = 8 + n
+    out = {}
+    for name, meta in header.items():
+        if name == "__metadata__":
+            continue
+        lo, hi = meta["data_offsets"]
+        buf = bytearray(raw[base + lo:base + hi])
+        t = torch.frombuffer(buf, dtype=_ST_DTYPES[meta["dtype"]]) if hi > lo else \
+            torch.empty(0, dtype=_ST_DTYPES[meta["dtype"]])
+        out[name] = t.reshape(meta["shape"]).clone()
+    return out
+
+
+def read_model_dir(path):
+    """(config dict, tensors as float32) of a model folder
+    (snowllm/checkpoint/loader.py:203-212: text_config is taken when present)."""
+    path = pathlib.Path(path)
+    raw = json.loads((path / "config.json").read_text())
+    cfg = dict(raw.get("text_config", raw))
+    cfg.setdefault("architectures", raw.get("architectures"))
+    tensors = {k: v.float() for k, v in read_safetensors(path / "model.safetensors").items()}
+    return cfg, tensors
+
+
+def rope_theta(cfg):
+    """snowllm/models/lfm2/weights.py:44: rope_parameters.rope_theta, else rope_theta,
+    else 5,000,000."""
+    return (cfg.get("rope_parameters") or {}).get("rope_theta", cfg.get("rope_theta", 5000000.0))
+
+
+def head_dim(cfg):
+    """snowllm/models/lfm2/weights.py:36-39: hidden_size // num_attention_heads
+    (an explicit head_dim key, where a config gives one, takes precedence)."""
+    return cfg.get("head_dim") or cfg["hidden_size"] // cfg["num_attention_heads"]
+
+
+def rmsnorm(x, weight, eps):
+    """x * rsqrt(mean(x^2) + eps) * weight, the weight multiplying directly
+    (tests/test_lfm2_dspark_reference.py:16-19; snowllm/ops/norm.py:11-30)."""
+    x = x.float()
+    return x * torch.rsqrt(x.square().mean(-1, keepdim=True) + eps) * weight.float()
+
+
+def rope_angles(positions, hd, theta):
+    """ang[m, i] = pos[m] * theta^(-2i/hd), float32
+    (snowllm/models/lfm2/layers.py:116-117; snowllm/ops/rope.py:11-24)."""
+    inv_freq = 1.0 / (theta ** (torch.arange(0, hd, 2, dtype=torch.float32) / hd))
+    return positions.to(torch.float32)[:, None] * inv_freq[None, :].to(positions.device)
+
+
+def apply_rope(x, ang):
+    """Split-half rotation over the whole head: x*cos + rot(x)*sin with
+    rot(x) = [-x[hd/2:], x[:hd/2]] (tests/test_lfm2.py:108-118).  x: [T, heads, hd]."""
+    cos = torch.cat((ang.cos(), ang.cos()), -1)[:, None, :]
+    sin = torch.cat((ang.sin(), ang.sin()), -1)[:, None, :]
+    half = x.shape[-1] // 2
+    rot = torch.cat((-x[..., half:], x[..., :half]), -1)
+    return x * cos + rot * sin
+
+
+def short_conv_mixer(u, w_in, w_conv, w_out):
+    """Gated short convolution (snowllm/models/lfm2/layers.py:26-33;
+    tests/test_lfm2.py:41-49): BCx = in_proj(u); B, C, x = thirds; g = B*x; causal
+    depthwise conv of length L with zero history (the last tap multiplies the
+    current token); y = C*conv; out_proj(y).  u: [T, H]; w_conv: [H, L]."""
+    T, H = u.shape
+    L = w_conv.shape[-1]
+    bcx = u @ w_in.T
+    B, C, x = bcx.chunk(3, dim=-1)
+    g = B * x
+    conv = F.conv1d(g.T[None], w_conv.reshape(H, 1, L), padding=L - 1, groups=H)[0, :, :T].T
+    return (C * conv) @ w_out.T
+
+
+def attention_mixer(u, wq, wk, wv, wo, q_norm, k_norm, eps, n_heads, n_kv, hd, theta,
+                    window=None, positions=None):
+    """Causal grouped-query attention with per-head RMSNorm on q and k, then RoPE
+    (snowllm/models/lfm2/layers.py:36-70; grouping and mask as in
+    tests/test_lfm2_long_attention.py:36-47): q head i reads kv head i // (nh/nkv);
+    scale hd^-0.5; softmax in float32.  ``window`` (not an LFM2 option) keeps only the
+    last ``window`` keys, the query's own included."""
+    T = u.shape[0]
+    pos = torch.arange(T) if positions is None else positions
+    q = (u @ wq.T).view(T, n_heads, hd)
+    k = (u @ wk.T).view(T, n_kv, hd)
+    v = (u @ wv.T).view(T, n_kv, hd)
+    q = rmsnorm(q, q_norm, eps)
+    k = rmsnorm(k, k_norm, eps)
+    ang = rope_angles(pos, hd, theta)
+    q, k = apply_rope(q, ang), apply_rope(k, ang)
+    group = n_heads // n_kv
+    q = q.view(T, n_kv, group, hd)
+    scores = torch.einsum("tghd,sgd->tghs", q, k) * hd ** -0.5
+    i = torch.arange(T)
+    mask = i[None, :] > i[:, None]
+    if window is not None:
+        mask = mask | (i[None, :] <= i[:, None] - window)
+    scores = scores.masked_fill(mask[:, None, None, :], float("-inf"))
+    out = torch.einsum("tghs,sgd->tghd", scores.softmax(-1), v).reshape(T, n_heads * hd)
+    return out @ wo.T
+
+
+def dense_ffn(u, w1, w3, w2):
+    """SwiGLU: w2(silu(w1 u) * w3 u) (snowllm/models/lfm2/layers.py:81-88)."""
+    return (F.silu(u @ w1.T) * (u @ w3.T)) @ w2.T
+
+
+def route(u, gate_w, expert_bias, top_k, norm_topk_prob, scaling):
+    """Sigmoid router in float32 (tests/test_lfm2_reference.py:113-119): p = sigmoid(u W^T);
+    the k largest of p + bias select (the bias only selects); weights p[sel], divided by
+    (sum + 1e-6) when norm_topk_prob, times routed_scaling_factor.  Ties go to the lower
+    expert index."""
+    p = (u.float() @ gate_w.float().T).sigmoid()
+    score = p if expert_bias is None else p + expert_bias.float()
+    # stable descending sort: equal scores keep index order, so the lower index wins
+    ids = torch.sort(score, dim=-1, descending=True, stable=True).indices[:, :top_k]
+    w = p.gather(1, ids)
+    if norm_topk_prob:
+        w = w / (w.sum(-1, keepdim=True) + 1e-6)
+    return ids, w * scaling
+
+
+def moe_ffn(u, gate_w, expert_bias, w1, w3, w2, top_k, norm_topk_prob, scaling):
+    """Routed SwiGLU experts, no shared expert (snowllm/models/qwen3_5/layers.py:176-188;
+    formula tests/test_lfm2_reference.py:113-119).  w1, w3: [E, I, H]; w2: [E, H, I]."""
+    ids, w = route(u, gate_w, expert_bias, top_k, norm_topk_prob, scaling)
+    out = torch.zeros_like(u)
+    for t in range(u.shape[0]):
+        for j in range(top_k):
+            e = int(ids[t, j])
+            out[t] += w[t, j] * dense_ffn(u[t:t + 1], w1[e], w3[e], w2[e])[0]
+    return out
+
+
+def expert_stack(tensors, prefix, n_experts):
+    """Per-expert tensors stacked, or the fused gate_up_proj split in two
+    (snowllm/models/lfm2/weights.py:84-91)."""
+    key = prefix + "feed_forward.experts."
+    if key + "gate_up_proj" in tensors:
+        w1, w3 = tensors[key + "gate_up_proj"].chunk(2, dim=1)
+        return w1, w3, tensors[key + "down_proj"]
+    stack = lambda n: torch.stack([tensors[f"{key}{e}.{n}.weight"] for e in range(n_experts)])
+    return stack("w1"), stack("w3"), stack("w2")
+
+
+def layer_mixer(cfg, tensors, i, u):
+    """Mixer of layer i chosen by layer_types (snowllm/models/lfm2/weights.py:72-76)."""
+    p = f"model.layers.{i}."
+    if cfg["layer_types"][i] == "conv":
+        H = cfg["hidden_size"]
+        return short_conv_mixer(u, tensors[p + "conv.in_proj.weight"],
+                                tensors[p + "conv.conv.weight"].reshape(H, -1),
+                                tensors[p + "conv.out_proj.weight"])
+    a = p + "self_attn."
+    return attention_mixer(u, tensors[a + "q_proj.weight"], tensors[a + "k_proj.weight"],
+                           tensors[a + "v_proj.weight"], tensors[a + "out_proj.weight"],
+                           tensors[a + "q_layernorm.weight"], tensors[a + "k_layernorm.weight"],
+                           cfg["norm_eps"], cfg["num_attention_heads"],
+                           cfg["num_key_value_heads"], head_dim(cfg), rope_theta(cfg))
+
+
+def is_dense_model(cfg):
+    archs = cfg.get("architectures") or []
+    return "Lfm2ForCausalLM" in archs
+
+
+def layer_ffn(cfg, tensors, i, u):
+    """Dense SwiGLU below num_dense_layers, routed experts from there on
+    (snowllm/models/lfm2/weights.py:77-92)."""
+    p = f"model.layers.{i}."
+    if is_dense_model(cfg) or i < cfg.get("num_dense_layers", 0):
+        f = p + "feed_forward."
+        return dense_ffn(u, tensors[f + "w1.weight"], tensors[f + "w3.weight"],
+                         tensors[f + "w2.weight"])
+    w1, w3, w2 = expert_stack(tensors, p, cfg["num_experts"])
+    bias = tensors[p + "feed_forward.expert_bias"] if cfg.get("use_expert_bias", False) else None
+    return moe_ffn(u, tensors[p + "feed_forward.gate.weight"], bias, w1, w3, w2,
+                   cfg["num_experts_per_tok"], cfg.get("norm_topk_prob", False),
+                   cfg.get("routed_scaling_factor", 1.0))
+
+
+def hidden_states(cfg, tensors, ids):
+    """Embedding, then per layer x += mixer(norm(x)); x += ffn(norm(x)), then the final
+    norm (snowllm/models/lfm2/layers.py:97-104, 119-131)."""
+    eps = cfg["norm_eps"]
+    x = tensors["model.embed_tokens.weight"][torch.as_tensor(ids, dtype=torch.long)].float()
+    for i in range(cfg["num_hidden_layers"]):
+        p = f"model.layers.{i}."
+        x = x + layer_mixer(cfg, tensors, i, rmsnorm(x, tensors[p + "operator_norm.weight"], eps))
+        x = x + layer_ffn(cfg, tensors, i, rmsnorm(x, tensors[p + "ffn_norm.weight"], eps))
+    return rmsnorm(x, tensors["model.embedding_norm.weight"], eps)
+
+
+def logits(cfg, tensors, ids):
+    """[T, V] float32 logits of one whole sequence; the head is the embedding when
+    tie_word_embeddings (snowllm/models/lfm2/weights.py:63-66), else lm_head.weight."""
+    tied = cfg.get("tie_word_embeddings", True)
+    head = tensors["model.embed_tokens.weight"] if tied else tensors["lm_head.weight"]
+    with torch.no_grad():
+        return hidden_states(cfg, tensors, ids) @ head.float().T
+
+
+def greedy(cfg, tensors, prompt, n_new):
+    """n_new greedy tokens, each from a whole-sequence pass."""
+    toks = list(prompt)
+    for _ in range(n_new):
+        toks.append(int(logits(cfg, tensors, toks)[-1].argmax()))
+    return toks[len(prompt):]
+
+
+def softmax_sample_reference(row, temperature, top_k, top_p, u):
+    """Reference of the sampler's draw (snowllm/engine/sampler.py:86-104 order:
+    temperature softmax, top-k, top-p, inverse CDF from a supplied uniform):
+    keep the k most probable, then the smallest prefix of them whose mass reaches
+    top_p (ties at the cut all kept), renormalise, walk the CDF in index order."""
+    p = torch.softmax(row.double() / temperature, -1)
+    keep = torch.ones_like(p, dtype=torch.bool)
+    if 0 < top_k < p.numel():
+        kth = torch.sort(p, descending=True).values[top_k - 1]
+        keep &= p >= kth
+    if top_p < 1.0:
+        q = torch.where(keep, p, torch.zeros_like(p))
+        s = torch.sort(q, descending=True).values
+        c = torch.cumsum(s, 0)
+        n = int((c < top_p * c[-1]).sum()) + 1
+        keep &= p >= s[min(n, s.numel()) - 1]
+    q = torch.where(keep, p, torch.zeros_like(p))
+    c = torch.cumsum(q, 0)
+    return int(torch.searchsorted(c, u * c[-1], right=True).clamp(max=p.numel() - 1))
