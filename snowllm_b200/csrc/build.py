@@ -100,6 +100,11 @@ def _compile(name: str, out: pathlib.Path) -> None:
     print(f"[snowllm_b200] built {out.name} in {time.time() - t0:.1f} s", file=sys.stderr, flush=True)
 
 
+def all_libraries() -> tuple:
+    """Every CUDA source of this folder."""
+    return tuple(sorted(f.stem for f in HERE.glob("*.cu")))
+
+
 def build(names=LIBRARIES, parallel: bool = True) -> list[pathlib.Path]:
     """Compile the named libraries where no current build exists; returns their paths."""
     todo = [(n, library_path(n)) for n in names]

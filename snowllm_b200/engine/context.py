@@ -37,6 +37,11 @@ class StepContext:
     host_seg_start: list = field(default_factory=list)
     host_seg_len: list = field(default_factory=list)
     _plans: dict = field(default_factory=dict)
+    taps: list | None = None       # when a list: parts append (name, tensor) of chosen intermediates
+
+    def tap(self, name: str, tensor) -> None:
+        if self.taps is not None:
+            self.taps.append((name, tensor))
 
     def scratch(self, nbytes: int) -> torch.Tensor:
         """Scratch bytes for one kernel launch (stream-ordered, from torch's caching allocator)."""

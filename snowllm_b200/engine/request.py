@@ -1,0 +1,52 @@
+"""A request and its sampling options (snowllm/engine/request.py:12-114: same names, same defaults,
+same meanings; fields of speculation, images and prefix sharing are left out)."""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+
+from ..cache import RequestCache
+
+
+@dataclass
+class SamplingParams:
+    temperature: float = 1.0            # <= 0: greedy
+    top_p: float = 1.0
+    top_k: int = 0                      # 0: no top-k cut
+    max_new_tokens: int = 32
+    stop_token_ids: tuple = ()
+    presence_penalty: float = 0.0
+    frequency_penalty: float = 0.0
+    repetition_penalty: float = 1.0
+    no_repeat_ngram_size: int = 0
+
+    def penalized(self) -> bool:
+        return bool(self.presence_penalty or self.frequency_penalty or self.repetition_penalty != 1.0)
+
+    @property
+    def greedy(self) -> bool:
+        return self.temperature <= 0.0
+
+
+@dataclass(eq=False)
+class Request:
+    prompt: list
+    params: SamplingParams
+    out: list = field(default_factory=list)
+    cache: RequestCache | None = None
+    num_computed: int = 0               # tokens of ``tokens`` that are in the cache
+    done: bool = False
+    finish_reason: str | None = None    # "stop", "length", "abort", "error"
+    preemptions: int = 0
+
+    @property
+    def tokens(self) -> list:
+        return self.prompt + self.out
+
+    @property
+    def pending(self) -> int:
+        """Tokens not yet run: the rest of the prompt, or the last sampled token."""
+        return len(self.prompt) + len(self.out) - self.num_computed
+
+    @property
+    def last(self) -> int:
+        return self.out[-1] if self.out else self.prompt[-1]

@@ -37,6 +37,7 @@ class ModelRunner:
         kernels.libraries_for(model.libraries())
         self.steps = 0
         self.tokens = 0
+        self.taps = None       # set to a list to collect what parts tap (tests and debugging)
 
     def step(self, entries: Sequence[StepEntry]) -> torch.Tensor:
         """Run one batch; returns float logits [wanted rows, vocab] in entry order, then ``want``
@@ -54,64 +55,71 @@ class ModelRunner:
         return logits
 
     def build_context(self, entries: Sequence[StepEntry]) -> StepContext:
-        P = self.cache.page_size
-        V = self.model.vocab_size
-        B = len(entries)
-        lens = [len(e.tokens) for e in entries]
-        starts = [e.cache.num_tokens for e in entries]
-        M = sum(lens)
-        seen = set()
-        for e, n, s in zip(entries, lens, starts):
-            if id(e.cache) in seen:
-                raise SnowLLMError("a request appears twice in one step")
-            seen.add(id(e.cache))
-            if e.cache.freed:
-                raise SnowLLMError("a freed request cannot be stepped")
-            if s + n > self.model.spec.max_position:
-                raise SnowLLMError(f"position {s + n} exceeds the model's limit {self.model.spec.max_position}")
-            for key, table in e.cache.tables.items():
-                need = -(-(s + n) // P)
-                first = 0 if key[1] is None else max(0, s - key[1] + 1) // P
-                if len(table) < need or any(p < 0 for p in table[first:need]):
-                    raise CapacityError("the step was given tokens whose pages were not taken")
-        ids = np.fromiter((t for e in entries for t in e.tokens), dtype=np.int64, count=M)
-        if M and (ids.min() < 0 or ids.max() >= V):
-            raise SnowLLMError(f"token id outside [0, {V})")
-        cu = np.zeros(B + 1, dtype=np.int64)
-        np.cumsum(lens, out=cu[1:])
-        row_seg = np.repeat(np.arange(B), lens)
-        positions = np.arange(M) - np.repeat(cu[:-1], lens) + np.repeat(starts, lens)
-        logit_rows = []
+        return build_context(entries, self.cache, self.model.dtype, self.device, self.staging,
+                             self.model.vocab_size, self.model.spec.max_position, self.taps)
+
+
+def build_context(entries: Sequence[StepEntry], cache: CacheManager, dtype, device, staging: HostStaging,
+                  vocab_size: int, max_position: int = 1 << 30, taps=None) -> StepContext:
+    """Turn a step's entries into the flat batch on the device (one host-to-device copy)."""
+    P = cache.page_size
+    V = vocab_size
+    B = len(entries)
+    lens = [len(e.tokens) for e in entries]
+    starts = [e.cache.num_tokens for e in entries]
+    M = sum(lens)
+    seen = set()
+    for e, n, s in zip(entries, lens, starts):
+        if id(e.cache) in seen:
+            raise SnowLLMError("a request appears twice in one step")
+        seen.add(id(e.cache))
+        if e.cache.freed:
+            raise SnowLLMError("a freed request cannot be stepped")
+        if s + n > max_position:
+            raise SnowLLMError(f"position {s + n} exceeds the model's limit {max_position}")
+        for key, table in e.cache.tables.items():
+            need = -(-(s + n) // P)
+            first = 0 if key[1] is None else max(0, s - key[1] + 1) // P
+            if len(table) < need or any(p < 0 for p in table[first:need]):
+                raise CapacityError("the step was given tokens whose pages were not taken")
+    ids = np.fromiter((t for e in entries for t in e.tokens), dtype=np.int64, count=M)
+    if M and (ids.min() < 0 or ids.max() >= V):
+        raise SnowLLMError(f"token id outside [0, {V})")
+    cu = np.zeros(B + 1, dtype=np.int64)
+    np.cumsum(lens, out=cu[1:])
+    row_seg = np.repeat(np.arange(B), lens)
+    positions = np.arange(M) - np.repeat(cu[:-1], lens) + np.repeat(starts, lens)
+    logit_rows = []
+    for b, e in enumerate(entries):
+        for w in e.want:
+            if not 0 <= w < lens[b]:
+                raise SnowLLMError(f"wanted place {w} is outside the entry's {lens[b]} tokens")
+            logit_rows.append(int(cu[b]) + int(w))
+    groups = list(cache.groups)
+    max_pages = max(1, -(-max(s + n for s, n in zip(starts, lens)) // P))
+    tables = np.zeros((len(groups), B, max_pages), dtype=np.int64)
+    for g, key in enumerate(groups):
         for b, e in enumerate(entries):
-            for w in e.want:
-                if not 0 <= w < lens[b]:
-                    raise SnowLLMError(f"wanted place {w} is outside the entry's {lens[b]} tokens")
-                logit_rows.append(int(cu[b]) + int(w))
-        groups = list(self.cache.groups)
-        max_pages = max(1, -(-max(s + n for s, n in zip(starts, lens)) // P))
-        tables = np.zeros((len(groups), B, max_pages), dtype=np.int64)
-        for g, key in enumerate(groups):
-            for b, e in enumerate(entries):
-                t = e.cache.tables[key][:max_pages]
-                if t:
-                    tables[g, b, :len(t)] = np.maximum(np.asarray(t), 0)
-        parts = [ids, positions, row_seg, cu, np.asarray(starts), np.asarray([e.cache.slot for e in entries]),
-                 np.asarray(logit_rows, dtype=np.int64), tables.reshape(-1)]
-        sizes = [p.size for p in parts]
-        # each part starts on a 16-byte boundary
-        offs, total = [], 0
-        for s in sizes:
-            offs.append(total)
-            total += -(-s // 4) * 4
-        host = np.zeros(total, dtype=np.int32)
-        for p, o in zip(parts, offs):
-            host[o:o + p.size] = p
-        dev = self.staging.upload(host)
-        view = lambda i: dev[offs[i]:offs[i] + sizes[i]]
-        tab = view(7).view(len(groups), B, max_pages)
-        return StepContext(
-            dtype=self.model.dtype, device=self.device, M=M, B=B, token_ids=view(0), positions=view(1),
-            row_seg=view(2), cu_seqlens=view(3), seg_start=view(4), seg_slot=view(5), logit_rows=view(6),
-            num_logit_rows=len(logit_rows), block_tables={key: tab[g] for g, key in enumerate(groups)},
-            page_size=P, host_positions=positions.astype(np.int64), host_seg_start=list(starts),
-            host_seg_len=list(lens))
+            t = e.cache.tables[key][:max_pages]
+            if t:
+                tables[g, b, :len(t)] = np.maximum(np.asarray(t), 0)
+    parts = [ids, positions, row_seg, cu, np.asarray(starts), np.asarray([e.cache.slot for e in entries]),
+             np.asarray(logit_rows, dtype=np.int64), tables.reshape(-1)]
+    sizes = [p.size for p in parts]
+    # each part starts on a 16-byte boundary
+    offs, total = [], 0
+    for s in sizes:
+        offs.append(total)
+        total += -(-s // 4) * 4
+    host = np.zeros(total, dtype=np.int32)
+    for p, o in zip(parts, offs):
+        host[o:o + p.size] = p
+    dev = staging.upload(host)
+    view = lambda i: dev[offs[i]:offs[i] + sizes[i]]
+    tab = view(7).view(len(groups), B, max_pages)
+    return StepContext(
+        dtype=dtype, device=device, M=M, B=B, token_ids=view(0), positions=view(1),
+        row_seg=view(2), cu_seqlens=view(3), seg_start=view(4), seg_slot=view(5), logit_rows=view(6),
+        num_logit_rows=len(logit_rows), block_tables={key: tab[g] for g, key in enumerate(groups)},
+        page_size=P, host_positions=positions.astype(np.int64), host_seg_start=list(starts),
+        host_seg_len=list(lens), taps=taps)

@@ -64,6 +64,8 @@ class SigmoidMoE(Part):
     def forward(self, ctx, x):
         M, k = x.shape[0], self.top_k
         ids, weights = self.route(x)
+        if ctx is not None:
+            ctx.tap("moe_route", ids)
         offsets, pair_pos, sorted_pair = kernels.moe_sort(ids, self.num_experts)
         cap = min(M, M * k)          # an expert gets a token at most once
         h = grouped_linear(x, self.w13, offsets, M * k, cap, a_rows=sorted_pair, a_div=k)

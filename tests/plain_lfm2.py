@@ -139,30 +139,39 @@ def dense_ffn(u, w1, w3, w2):
     return (F.silu(u @ w1.T) * (u @ w3.T)) @ w2.T
 
 
-def route(u, gate_w, expert_bias, top_k, norm_topk_prob, scaling):
+def route(u, gate_w, expert_bias, top_k, norm_topk_prob, scaling, forced_ids=None, margins=None):
     """Sigmoid router in float32 (tests/test_lfm2_reference.py:113-119): p = sigmoid(u W^T);
     the k largest of p + bias select (the bias only selects); weights p[sel], divided by
     (sum + 1e-6) when norm_topk_prob, times routed_scaling_factor.  Ties go to the lower
-    expert index."""
+    expert index.  ``forced_ids`` replaces the selection (the weights still come from p);
+    ``margins`` (a list) receives, per row, the gap between the k-th and the (k+1)-th score."""
     p = (u.float() @ gate_w.float().T).sigmoid()
     score = p if expert_bias is None else p + expert_bias.float()
     # stable descending sort: equal scores keep index order, so the lower index wins
-    ids = torch.sort(score, dim=-1, descending=True, stable=True).indices[:, :top_k]
+    order = torch.sort(score, dim=-1, descending=True, stable=True)
+    if margins is not None:
+        v = order.values
+        margins.append(v[:, top_k - 1] - v[:, top_k] if top_k < v.shape[1]
+                       else torch.full((v.shape[0],), float("inf")))
+    ids = order.indices[:, :top_k] if forced_ids is None else forced_ids.long()
     w = p.gather(1, ids)
     if norm_topk_prob:
         w = w / (w.sum(-1, keepdim=True) + 1e-6)
     return ids, w * scaling
 
 
-def moe_ffn(u, gate_w, expert_bias, w1, w3, w2, top_k, norm_topk_prob, scaling):
+def moe_ffn(u, gate_w, expert_bias, w1, w3, w2, top_k, norm_topk_prob, scaling, forced_ids=None,
+            margins=None):
     """Routed SwiGLU experts, no shared expert (snowllm/models/qwen3_5/layers.py:176-188;
     formula tests/test_lfm2_reference.py:113-119).  w1, w3: [E, I, H]; w2: [E, H, I]."""
-    ids, w = route(u, gate_w, expert_bias, top_k, norm_topk_prob, scaling)
+    ids, w = route(u, gate_w, expert_bias, top_k, norm_topk_prob, scaling, forced_ids, margins)
     out = torch.zeros_like(u)
-    for t in range(u.shape[0]):
-        for j in range(top_k):
-            e = int(ids[t, j])
-            out[t] += w[t, j] * dense_ffn(u[t:t + 1], w1[e], w3[e], w2[e])[0]
+    for e in range(w1.shape[0]):                 # expert by expert over the rows that picked it
+        picked = ids == e
+        rows = picked.any(-1)
+        if rows.any():
+            weight = (w * picked).sum(-1)[rows]
+            out[rows] += weight[:, None] * dense_ffn(u[rows], w1[e], w3[e], w2[e])
     return out
 
 
@@ -198,7 +207,7 @@ def is_dense_model(cfg):
     return "Lfm2ForCausalLM" in archs
 
 
-def layer_ffn(cfg, tensors, i, u):
+def layer_ffn(cfg, tensors, i, u, forced_ids=None, margins=None):
     """Dense SwiGLU below num_dense_layers, routed experts from there on
     (snowllm/models/lfm2/weights.py:77-92)."""
     p = f"model.layers.{i}."
@@ -210,28 +219,34 @@ def layer_ffn(cfg, tensors, i, u):
     bias = tensors[p + "feed_forward.expert_bias"] if cfg.get("use_expert_bias", False) else None
     return moe_ffn(u, tensors[p + "feed_forward.gate.weight"], bias, w1, w3, w2,
                    cfg["num_experts_per_tok"], cfg.get("norm_topk_prob", False),
-                   cfg.get("routed_scaling_factor", 1.0))
+                   cfg.get("routed_scaling_factor", 1.0), forced_ids, margins)
 
 
-def hidden_states(cfg, tensors, ids):
+def hidden_states(cfg, tensors, ids, forced_routes=None, margins=None):
     """Embedding, then per layer x += mixer(norm(x)); x += ffn(norm(x)), then the final
-    norm (snowllm/models/lfm2/layers.py:97-104, 119-131)."""
+    norm (snowllm/models/lfm2/layers.py:97-104, 119-131).  ``forced_routes``: {layer -> ids [T, k]}
+    that replace the router's selection in that layer; ``margins``: a dict that receives
+    {layer -> selection margin per position}."""
     eps = cfg["norm_eps"]
     x = tensors["model.embed_tokens.weight"][torch.as_tensor(ids, dtype=torch.long)].float()
     for i in range(cfg["num_hidden_layers"]):
         p = f"model.layers.{i}."
         x = x + layer_mixer(cfg, tensors, i, rmsnorm(x, tensors[p + "operator_norm.weight"], eps))
-        x = x + layer_ffn(cfg, tensors, i, rmsnorm(x, tensors[p + "ffn_norm.weight"], eps))
+        got = []
+        x = x + layer_ffn(cfg, tensors, i, rmsnorm(x, tensors[p + "ffn_norm.weight"], eps),
+                          None if forced_routes is None else forced_routes.get(i), got)
+        if margins is not None and got:
+            margins[i] = got[0]
     return rmsnorm(x, tensors["model.embedding_norm.weight"], eps)
 
 
-def logits(cfg, tensors, ids):
+def logits(cfg, tensors, ids, forced_routes=None, margins=None):
     """[T, V] float32 logits of one whole sequence; the head is the embedding when
     tie_word_embeddings (snowllm/models/lfm2/weights.py:63-66), else lm_head.weight."""
     tied = cfg.get("tie_word_embeddings", True)
     head = tensors["model.embed_tokens.weight"] if tied else tensors["lm_head.weight"]
     with torch.no_grad():
-        return hidden_states(cfg, tensors, ids) @ head.float().T
+        return hidden_states(cfg, tensors, ids, forced_routes, margins) @ head.float().T
 
 
 def greedy(cfg, tensors, prompt, n_new):

@@ -1,0 +1,172 @@
+"""Generation through the Python entry point and the command line: greedy tokens against the plain
+implementation, chunked prefill, batching, preemption and replay, sampling, and the smoke entry."""
+import json
+import pathlib
+import subprocess
+import sys
+
+import pytest
+import torch
+
+import plain_lfm2 as plain
+from helpers import random_prompt
+from tiny_configs import ALL
+
+pytestmark = pytest.mark.gpu
+ROOT = pathlib.Path(__file__).resolve().parent.parent
+
+
+def engine_for(model_dir, dtype="float32", **kw):
+    import snowllm_b200
+    from snowllm_b200.engine import Engine
+    model = snowllm_b200.load(model_dir, dtype)
+    kw.setdefault("max_model_len", 512)
+    return Engine(model, **kw)
+
+
+def assert_greedy_follows_plain(model_dir, prompt, out, slack):
+    """Each generated token is the plain implementation's argmax given the same prefix, or within
+    ``slack`` of it (a near-tie that rounding may turn)."""
+    cfg, tensors = plain.read_model_dir(model_dir)
+    logits = plain.logits(cfg, tensors, prompt + out)
+    for i, tok in enumerate(out):
+        row = logits[len(prompt) - 1 + i]
+        assert float(row.max() - row[tok]) <= slack, (i, tok, int(row.argmax()), float(row.max() - row[tok]))
+
+
+def test_greedy_generation_tiny_a_float32(model_dirs):
+    """16-token prompts, 8 generated tokens, equal to whole-sequence greedy decoding."""
+    from snowllm_b200.engine import SamplingParams
+    d = model_dirs("tiny_a", "float32")
+    cfg, tensors = plain.read_model_dir(d)
+    eng = engine_for(d, max_num_seqs=2)
+    prompts = [random_prompt(256, 16, s) for s in range(3)]
+    outs = eng.generate(prompts, SamplingParams(temperature=0, max_new_tokens=8))
+    for p, o in zip(prompts, outs):
+        assert len(o) == 8
+        assert_greedy_follows_plain(d, p, o, slack=1e-4)
+    assert outs[0] == plain.greedy(cfg, tensors, prompts[0], 8)
+    st = eng.stats()
+    assert st.running == 0 and st.waiting == 0 and st.free_slots == 2
+    assert st.accounting["prefill_tokens"] == 48 and st.accounting["decode_tokens"] == 21
+
+
+@pytest.mark.parametrize("dtype,slack", [("float32", 1e-4), ("bfloat16", 0.15)])
+def test_mixed_batch_tiny_b(model_dirs, dtype, slack):
+    """Three prompts of 5, 23 and 40 tokens together, 12 generated tokens each."""
+    from snowllm_b200.engine import SamplingParams
+    d = model_dirs("tiny_b", dtype)
+    eng = engine_for(d, dtype, max_num_seqs=4, prefill_chunk=16)
+    prompts = [random_prompt(384, n, 7 + n) for n in (5, 23, 40)]
+    reqs = [eng.add(p, SamplingParams(temperature=0, max_new_tokens=12)) for p in prompts]
+    kinds = []
+    while eng.scheduler.has_work():
+        kinds.append(eng.step())
+    assert "mixed" in kinds                      # prompt portions ran beside decoded tokens
+    for p, r in zip(prompts, reqs):
+        assert r.done and r.finish_reason == "length" and len(r.out) == 12
+        assert_greedy_follows_plain(d, p, r.out, slack)
+
+
+def test_chunked_prefill_and_batching_do_not_change_greedy_tokens(model_dirs):
+    from snowllm_b200.engine import SamplingParams
+    d = model_dirs("tiny_b", "float32")
+    params = SamplingParams(temperature=0, max_new_tokens=24)
+    prompts = [random_prompt(384, n, 50 + n) for n in (37, 90, 12)]
+    eng = engine_for(d, max_num_seqs=1, prefill_chunk=64)
+    alone = [eng.generate([p], params)[0] for p in prompts]
+    eng.prefill_chunk = 3
+    assert [eng.generate([p], params)[0] for p in prompts] == alone
+    together = engine_for(d, max_num_seqs=3, prefill_chunk=7).generate(prompts, params)
+    assert together == alone
+
+
+def test_pages_run_out_preemption_replays_to_the_same_tokens(model_dirs):
+    """Two requests of 90 tokens and 40 new tokens in a pool of 13 pages of 16: one is preempted,
+    prefilled again over what it had generated, and ends with the tokens of an undisturbed run
+    (SnowLLM: tests/test_lfm2_scheduling.py:24-48)."""
+    from snowllm_b200.engine import SamplingParams
+    d = model_dirs("tiny_a", "float32")
+    params = SamplingParams(temperature=0, max_new_tokens=40)
+    prompts = [random_prompt(256, 90, s) for s in (1, 2)]
+    calm = engine_for(d, max_num_seqs=2, max_model_len=256).generate(prompts, params)
+    tight = engine_for(d, max_num_seqs=2, max_model_len=256, num_kv_blocks=13)
+    got = tight.generate(prompts, params)
+    assert tight.stats().preemptions > 0
+    assert got == calm
+    assert tight.stats().free_kv_blocks == 13 and tight.stats().free_slots == 2
+
+
+def test_stop_tokens_and_limits(model_dirs):
+    from snowllm_b200.engine import SamplingParams
+    from snowllm_b200.errors import SnowLLMError
+    d = model_dirs("tiny_a", "float32")
+    eng = engine_for(d, max_num_seqs=2, max_model_len=64)
+    p = random_prompt(256, 10, 3)
+    free = eng.generate([p], SamplingParams(temperature=0, max_new_tokens=12))[0]
+    r = eng.add(p, SamplingParams(temperature=0, max_new_tokens=12, stop_token_ids=(free[4],)))
+    eng.run()
+    first = free.index(free[4])
+    assert r.finish_reason == "stop" and r.out == free[:first + 1]
+    with pytest.raises(SnowLLMError, match="max_model_len"):
+        eng.add(random_prompt(256, 60, 1), SamplingParams(max_new_tokens=8))
+    with pytest.raises(SnowLLMError, match="token id"):
+        eng.add([1, 2, 999], SamplingParams())
+    full = eng.add(random_prompt(256, 56, 2), SamplingParams(temperature=0, max_new_tokens=8))
+    eng.run()                                     # up to exactly max_model_len
+    assert len(full.out) == 8
+
+
+def test_sampling_is_seeded_and_penalties_bite(model_dirs):
+    from snowllm_b200.engine import SamplingParams
+    d = model_dirs("tiny_a", "float32", flavour="baseline")
+    p = random_prompt(256, 12, 9)
+    hot = SamplingParams(temperature=1.0, top_k=40, top_p=0.95, max_new_tokens=24)
+    a = engine_for(d, seed=11).generate([p], hot)[0]
+    b = engine_for(d, seed=11).generate([p], hot)[0]
+    c = engine_for(d, seed=12).generate([p], hot)[0]
+    assert a == b and a != c and all(0 <= t < 256 for t in a)
+    # with these weights greedy decoding repeats itself; a ban on repeated 2-grams must not
+    eng = engine_for(d)
+    plain_out = eng.generate([p], SamplingParams(temperature=0, max_new_tokens=40))[0]
+    banned = eng.generate([p], SamplingParams(temperature=0, max_new_tokens=40, no_repeat_ngram_size=2))[0]
+    seq = p + banned
+    grams = [tuple(seq[i:i + 2]) for i in range(len(seq) - 1)]
+    new = grams[len(p) - 1:]
+    assert len(set(new)) == len(new) and not set(new) & set(grams[:len(p) - 1])
+    pen = eng.generate([p], SamplingParams(temperature=0, max_new_tokens=40, repetition_penalty=1.5,
+                                            frequency_penalty=0.5, presence_penalty=0.5))[0]
+    assert len(set(pen)) >= len(set(plain_out))
+
+
+def test_command_line_generates(model_dirs):
+    d = model_dirs("tiny_a", "float32")
+    p = random_prompt(256, 9, 21)
+    proc = subprocess.run([sys.executable, "-m", "snowllm_b200", str(d), "--dtype", "float32", "--prompt-ids",
+                           ",".join(map(str, p)), "--default-max-tokens", "6", "--max-model-len", "128",
+                           "--max-num-seqs", "2", "--temperature", "0"],
+                          capture_output=True, text=True, cwd=ROOT, timeout=600)
+    assert proc.returncode == 0, proc.stderr[-2000:]
+    line = json.loads(proc.stdout.strip().splitlines()[-1])
+    cfg, tensors = plain.read_model_dir(d)
+    assert line["tokens"] == plain.greedy(cfg, tensors, p, 6) and line["finish_reason"] == "length"
+
+
+def test_random_weights_command_and_missing_extension_is_loud(tmp_path):
+    cfg = tmp_path / "config.json"
+    cfg.write_text(json.dumps(ALL["tiny_dense"]))
+    proc = subprocess.run([sys.executable, "-m", "snowllm_b200", "random-weights", str(cfg), str(tmp_path / "m"),
+                           "--seed", "4", "--dtype", "float32"], capture_output=True, text=True, cwd=ROOT)
+    assert proc.returncode == 0, proc.stderr
+    c, tensors = plain.read_model_dir(tmp_path / "m")
+    assert plain.logits(c, tensors, [1, 2, 3]).shape == (3, 200)
+    from snowllm_b200.errors import KernelError
+    from snowllm_b200.ops import kernels
+    with pytest.raises(KernelError, match="CUDA tensor"):
+        kernels.swiglu(torch.zeros(2, 4))        # no CPU path
+
+
+def test_smoke_entry():
+    sys.path.insert(0, str(ROOT))
+    import __graft_entry__
+    __graft_entry__.smoke()

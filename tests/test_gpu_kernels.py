@@ -1,0 +1,488 @@
+"""Each CUDA kernel alone against a plain PyTorch float32 reference of the same op, at sizes other
+than the engine's tiny models use (head sizes in steps of 16, odd head counts and groups, widths
+and vocabularies that are no power of two), in float32 and in bfloat16."""
+import math
+
+import pytest
+import torch
+import torch.nn.functional as F
+
+import plain_lfm2 as plain
+
+pytestmark = pytest.mark.gpu
+
+DTYPES = [torch.float32, torch.bfloat16]
+ATOL = {torch.float32: 2e-5, torch.bfloat16: 2e-2}
+
+
+@pytest.fixture(scope="module")
+def K():
+    from snowllm_b200.ops import kernels
+    assert torch.cuda.is_available(), "the gpu tests need a CUDA device"
+    return kernels
+
+
+def dev(t, dtype=None):
+    t = t.cuda()
+    return t.to(dtype) if dtype is not None else t
+
+
+def i32(x):
+    return torch.tensor(x, dtype=torch.int32, device="cuda")
+
+
+def close(got, want, dtype, scale=1.0):
+    got, want = got.float().cpu(), want.float().cpu()
+    err = (got - want).abs().max().item()
+    bound = ATOL[dtype] * scale * max(1.0, want.abs().max().item())
+    assert err <= bound, f"max abs error {err} > {bound}"
+
+
+def rnd(dtype, *shape, scale=1.0):
+    """Random values that the dtype holds exactly, as float32 on the CPU."""
+    return (torch.randn(*shape) * scale).to(dtype).float()
+
+
+# ---------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("V,H,M", [(331, 80, 7), (1000, 2048, 3)])
+def test_embedding(K, dtype, V, H, M):
+    torch.manual_seed(0)
+    table = rnd(dtype, V, H)
+    ids = torch.randint(0, V, (M,))
+    out = K.embedding(i32(ids.tolist()), dev(table, dtype))
+    assert out.dtype == torch.float32 and torch.equal(out.cpu(), table[ids])
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("H", [80, 96, 2048, 5000])
+def test_add_rmsnorm(K, dtype, H):
+    torch.manual_seed(1)
+    M, eps = 9, 1e-5
+    res, delta = torch.randn(M, H), torch.randn(M, H)
+    for gamma_f32 in (False, True):
+        g = rnd(dtype, H) + 1.0 if not gamma_f32 else torch.randn(H) + 1.0
+        r = dev(res.clone())
+        out = K.add_rmsnorm(r, dev(delta), dev(g, None if gamma_f32 else dtype), eps, dtype)
+        assert torch.allclose(r.cpu(), res + delta, atol=1e-6)           # the residual sum is float
+        close(out, plain.rmsnorm(res + delta, g, eps), dtype)
+    # rows: only those rows, residual untouched
+    rows = [5, 0, 5, 8]
+    r = dev(res.clone())
+    g = rnd(dtype, H) + 1.0
+    out = K.add_rmsnorm(r, dev(delta), dev(g, dtype), eps, dtype, rows=i32(rows))
+    assert torch.equal(r.cpu(), res)
+    close(out, plain.rmsnorm((res + delta)[rows], g, eps), dtype)
+    out = K.add_rmsnorm(r, None, dev(g, dtype), eps, dtype)
+    close(out, plain.rmsnorm(res, g, eps), dtype)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_swiglu(K, dtype):
+    torch.manual_seed(2)
+    gu = rnd(dtype, 11, 2 * 56, scale=2.0)
+    out = K.swiglu(dev(gu, dtype))
+    close(out, F.silu(gu[:, :56]) * gu[:, 56:], dtype)
+
+
+# ---------------------------------------------------------------------------------------------
+def make_pool(dtype, pages, nkv, P, hd):
+    return torch.zeros(pages, 2, nkv, P, hd, dtype=dtype, device="cuda")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("nh,nkv,hd,rot", [(5, 5, 48, 48), (6, 2, 80, 80), (3, 1, 128, 64), (2, 1, 16, 16)])
+def test_qk_norm_rope_cache(K, dtype, nh, nkv, hd, rot):
+    torch.manual_seed(3)
+    P, pages, eps, theta = 8, 16, 1e-6, 1234.5
+    # two segments at odd positions, pages given out of order
+    seg_pos = [list(range(13, 13 + 9)), list(range(0, 5))]
+    tables = [[7, 3, 11, 0], [5, 0, 0, 0]]
+    positions = sum(seg_pos, [])
+    row_seg = [0] * 9 + [1] * 5
+    M = len(positions)
+    qkv = rnd(dtype, M, (nh + 2 * nkv) * hd)
+    qg, kg = rnd(dtype, hd) + 1.0, rnd(dtype, hd) + 1.0
+    inv_freq = 1.0 / (theta ** (torch.arange(0, rot, 2, dtype=torch.float32) / rot))
+    pool = make_pool(dtype, pages, nkv, P, hd)
+    q = K.qk_norm_rope_cache(dev(qkv, dtype), dev(qg, dtype), dev(kg, dtype), eps, dev(inv_freq), rot,
+                             i32(positions), i32(row_seg), i32(tables), P, pool, nh, nkv, hd)
+    x = qkv.view(M, nh + 2 * nkv, hd)
+    ang = torch.tensor(positions, dtype=torch.float32)[:, None] * inv_freq[None]
+
+    def rope(t):
+        out = t.clone()
+        out[..., :rot] = plain.apply_rope(t[..., :rot], ang)
+        return out
+    want_q = rope(plain.rmsnorm(x[:, :nh], qg, eps))
+    want_k = rope(plain.rmsnorm(x[:, nh:nh + nkv], kg, eps))
+    want_v = x[:, nh + nkv:]
+    close(q, want_q, dtype, scale=2)
+    for m, (pos, seg) in enumerate(zip(positions, row_seg)):
+        page, off = tables[seg][pos // P], pos % P
+        close(pool[page, 0, :, off], want_k[m], dtype, scale=2)
+        close(pool[page, 1, :, off], want_v[m], dtype)
+    untouched = sorted(set(range(pages)) - {3, 11, 5})          # page 7 holds positions 0..7: not in this step
+    assert float(pool[untouched].abs().max()) == 0.0            # nothing written elsewhere
+    assert float(pool[3, :, :, :5].abs().max()) == 0.0          # page 3 holds 8..15: only 13, 14, 15 written
+    assert float(pool[11, :, :, 6:].abs().max()) == 0.0         # page 11 holds 16..23: only 16..21 written
+    assert float(pool[5, :, :, 5:].abs().max()) == 0.0          # second segment: positions 0..4
+
+
+def test_qk_norm_rope_without_norm_or_rope_and_q_only(K):
+    dtype = torch.float32
+    nh, nkv, hd, P = 2, 1, 32, 4
+    qkv = rnd(dtype, 3, (nh + 2 * nkv) * hd)
+    pool = make_pool(dtype, 2, nkv, P, hd)
+    q = K.qk_norm_rope_cache(dev(qkv), None, None, 0.0, None, 0, i32([0, 1, 2]), i32([0, 0, 0]), i32([[1]]),
+                             P, pool, nh, nkv, hd)
+    assert torch.equal(q.cpu().reshape(3, -1), qkv[:, :nh * hd])
+    assert torch.equal(pool[1, 0, 0, :3].cpu(), qkv[:, nh * hd:(nh + 1) * hd])
+    before = pool.clone()
+    q2 = K.qk_norm_rope_cache(dev(qkv[:, :nh * hd].contiguous()), None, None, 0.0, None, 0, i32([0, 1, 2]),
+                              i32([0, 0, 0]), i32([[1]]), P, pool, nh, nkv, hd, write_kv=False)
+    assert torch.equal(q2.cpu(), q.cpu()) and torch.equal(pool, before)
+
+
+# ---------------------------------------------------------------------------------------------
+def ref_attention(q, k, v, positions, scale, window):
+    """q [M, nh, hd] against full k, v [T, nkv, hd] of one request; row m sees keys <= positions[m]."""
+    M, nh, hd = q.shape
+    T, nkv, _ = k.shape
+    out = torch.zeros(M, nh, hd, dtype=torch.float64)
+    for m in range(M):
+        lo = 0 if not window else max(0, positions[m] - window + 1)
+        for h in range(nh):
+            g = h // (nh // nkv)
+            s = (k[lo:positions[m] + 1, g].double() @ q[m, h].double()) * scale
+            out[m, h] = torch.softmax(s, 0) @ v[lo:positions[m] + 1, g].double()
+    return out.float().reshape(M, nh * hd)
+
+
+def scatter_kv(pool, k, v, table, P):
+    for t in range(k.shape[0]):
+        pool[table[t // P], 0, :, t % P] = k[t].to(pool.dtype).cuda()
+        pool[table[t // P], 1, :, t % P] = v[t].to(pool.dtype).cuda()
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("nh,nkv,hd,P,window", [(4, 2, 16, 16, None), (6, 2, 48, 8, None), (3, 3, 80, 64, None),
+                                                (16, 1, 128, 16, None), (10, 1, 32, 16, None),
+                                                (4, 2, 64, 16, 37), (4, 4, 16, 4, 5)])
+def test_paged_attention_mixed_rows(K, dtype, nh, nkv, hd, P, window):
+    """A prompt portion in the middle of one request beside single rows of two others, pages
+    scattered and shared out of order, one chunk and many chunks."""
+    torch.manual_seed(4)
+    lens = [150, 33, 700]
+    rows = [list(range(90, 150)), [32], [699]]
+    pages = sum(-(-n // P) for n in lens) + 3
+    perm = torch.randperm(pages).tolist()
+    pool = torch.full((pages, 2, nkv, P, hd), float("nan"), dtype=dtype, device="cuda")  # unwritten = NaN
+    tables, ks, vs = [], [], []
+    for n in lens:
+        need = -(-n // P)
+        table, perm = perm[:need], perm[need:]
+        k, v = rnd(dtype, n, nkv, hd), rnd(dtype, n, nkv, hd)
+        scatter_kv(pool, k, v, table, P)
+        tables.append(table)
+        ks.append(k)
+        vs.append(v)
+    width = max(len(t) for t in tables)
+    bt = i32([t + [0] * (width - len(t)) for t in tables])
+    positions = sum(rows, [])
+    row_seg = sum(([b] * len(r) for b, r in enumerate(rows)), [])
+    M = len(positions)
+    q = rnd(dtype, M, nh, hd)
+    scale = hd ** -0.5
+    want = torch.cat([ref_attention(q[[i for i, s in enumerate(row_seg) if s == b]], ks[b], vs[b], rows[b],
+                                    scale, window) for b in range(3)])
+    for chunk, n_chunks in ((None, 1), (64, None), (256, None)):
+        if chunk is not None:
+            lo = [0 if not window else max(0, p - window + 1) for p in positions]
+            n_chunks = max(p // chunk - l // chunk for p, l in zip(positions, lo)) + 1
+        out = K.paged_attention(dev(q, dtype), pool, bt, P, i32(positions), i32(row_seg), scale, window=window,
+                                chunk=chunk, num_chunks=n_chunks)
+        assert out.isfinite().all(), "an unwritten (NaN) cache entry was read"
+        close(out, want, dtype)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_attention_finds_one_far_key_among_hundreds(K, dtype):
+    """One key far back is made to stand out (query and key scaled along one direction): the
+    output must be that key's value, whatever page it lies on and however the keys are chunked."""
+    torch.manual_seed(5)
+    nh, nkv, hd, P, T = 2, 1, 64, 16, 900
+    for far in (0, 15, 16, 255, 256, 511, 640, 899):
+        k, v = rnd(dtype, T, nkv, hd, scale=0.1), rnd(dtype, T, nkv, hd)
+        direction = F.normalize(torch.randn(hd), dim=0)
+        k[far, 0] = (direction * 16).to(dtype).float()
+        q = (direction * 16).to(dtype).float().expand(1, nh, hd).contiguous()
+        table = torch.randperm(-(-T // P)).tolist()
+        pool = make_pool(dtype, len(table), nkv, P, hd)
+        scatter_kv(pool, k, v, table, P)
+        for chunk, n in ((None, 1), (256, 4)):
+            out = K.paged_attention(dev(q, dtype), pool, i32([table]), P, i32([T - 1]), i32([0]), hd ** -0.5,
+                                    chunk=chunk, num_chunks=n)
+            want = v[far, 0].repeat(nh)
+            assert (out.float().cpu()[0] - want).abs().max() < 0.02, (far, chunk)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_attention_window_edge(K, dtype):
+    """The key just outside the window is huge and must not be seen; the one just inside must win."""
+    torch.manual_seed(6)
+    nh, nkv, hd, P, T, W = 2, 2, 32, 8, 300, 100
+    pos = T - 1
+    direction = F.normalize(torch.randn(hd), dim=0)
+    q = (direction * 12).to(dtype).float().expand(1, nh, hd).contiguous()
+    for which, expect in ((pos - W, "ignored"), (pos - W + 1, "wins")):
+        k, v = rnd(dtype, T, nkv, hd, scale=0.1), rnd(dtype, T, nkv, hd)
+        k[which] = (direction * 20).to(dtype).float()
+        table = list(range(-(-T // P)))
+        pool = make_pool(dtype, len(table), nkv, P, hd)
+        scatter_kv(pool, k, v, table, P)
+        for chunk, n in ((None, 1), (64, 3)):
+            out = K.paged_attention(dev(q, dtype), pool, i32([table]), P, i32([pos]), i32([0]), hd ** -0.5,
+                                    window=W, chunk=chunk, num_chunks=n).float().cpu()[0]
+            hit = (out - v[which].reshape(-1)).abs().max().item()
+            assert (hit < 0.02) == (expect == "wins"), (which, expect, hit)
+            close(out[None], ref_attention(q, k, v, [pos], hd ** -0.5, W), dtype)
+
+
+# ---------------------------------------------------------------------------------------------
+def ref_conv(bcx, w, hist):
+    """bcx [T, 3H] of one request with history hist [L-1, H]; returns (y, new history)."""
+    H = w.shape[0]
+    L = w.shape[1]
+    B, C, x = bcx[:, :H], bcx[:, H:2 * H], bcx[:, 2 * H:]
+    g = torch.cat((hist, B * x))
+    conv = torch.stack([sum(w[:, j] * g[t + j] for j in range(L)) for t in range(bcx.shape[0])])
+    return C * conv, g[g.shape[0] - (L - 1):]
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("H,L", [(80, 3), (2048, 3), (96, 4), (40, 2), (33, 7)])
+def test_short_conv_whole_chunked_and_state(K, dtype, H, L):
+    torch.manual_seed(7)
+    lens, slots = [11, 1, 30], [2, 0, 3]
+    n_slots = 5
+    bcx = [rnd(dtype, n, 3 * H, scale=0.5) for n in lens]
+    w = rnd(dtype, H, L, scale=0.5)
+    state = torch.full((n_slots, L - 1, H), float("nan"), dtype=dtype, device="cuda")   # stale slots
+    cu = [0, 11, 12, 42]
+    row_seg = sum(([b] * n for b, n in enumerate(lens)), [])
+    out = K.short_conv(dev(torch.cat(bcx), dtype), dev(w, dtype), state, i32(cu), i32([0, 0, 0]), i32(slots),
+                       i32(row_seg))
+    assert out.isfinite().all(), "a fresh request read its slot's old contents"
+    refs = [ref_conv(b, w, torch.zeros(L - 1, H)) for b in bcx]
+    close(out, torch.cat([r[0] for r in refs]), dtype)
+    for b, s in enumerate(slots):
+        if dtype == torch.float32:
+            assert torch.equal(state[s].cpu(), refs[b][1])
+        else:   # the state holds round(B*x): exactly representable products of two bfloat16 are rounded once
+            assert torch.equal(state[s].float().cpu(), refs[b][1].to(dtype).float())
+    assert state[[1, 4]].isnan().all()                                         # other slots untouched
+    # the same sequences in portions (with other cuts per request): bit-identical outputs and state
+    state2 = torch.full_like(state, float("nan"))
+    done = [0, 0, 0]
+    got = [[], [], []]
+    cuts = [[1, 3, 7], [1], [2, 2, 1, 25]]
+    for step in range(4):
+        seg = [(b, cuts[b][step]) for b in range(3) if step < len(cuts[b])]
+        rows = torch.cat([bcx[b][done[b]:done[b] + n] for b, n in seg])
+        cu2 = [0]
+        for _, n in seg:
+            cu2.append(cu2[-1] + n)
+        o = K.short_conv(dev(rows, dtype), dev(w, dtype), state2, i32(cu2), i32([done[b] for b, _ in seg]),
+                         i32([slots[b] for b, _ in seg]),
+                         i32(sum(([i] * n for i, (_, n) in enumerate(seg)), [])))
+        for i, (b, n) in enumerate(seg):
+            got[b].append(o[cu2[i]:cu2[i + 1]])
+            done[b] += n
+    assert done == lens
+    assert torch.equal(torch.cat([torch.cat(g) for g in got]), out), "portions differ from the whole"
+    assert torch.equal(state2[slots], state[slots])
+
+
+# ---------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("M,N,K_", [(1, 331, 80), (7, 96, 48), (65, 130, 2048), (200, 64, 24), (5, 17, 13)])
+def test_gemm(K, dtype, M, N, K_):
+    torch.manual_seed(8)
+    a, w = rnd(dtype, M, K_), rnd(dtype, N, K_)
+    want = a @ w.T
+    close(K.gemm_simt(dev(a, dtype), dev(w, dtype)), want, dtype, scale=math.sqrt(K_) / 4)
+    out32 = K.gemm_simt(dev(a, dtype), dev(w, dtype), out_dtype=torch.float32)
+    assert out32.dtype == torch.float32
+    close(out32, want, torch.float32, scale=math.sqrt(K_))
+
+
+def test_gemm_rows_do_not_depend_on_the_batch(K):
+    """A row's result is the same bits alone, among others, and at another place in the batch."""
+    torch.manual_seed(9)
+    for dtype in DTYPES:
+        a, w = dev(rnd(dtype, 150, 96), dtype), dev(rnd(dtype, 77, 96), dtype)
+        whole = K.gemm_simt(a, w, out_dtype=torch.float32)
+        assert torch.equal(K.gemm_simt(a[70:71].contiguous(), w, out_dtype=torch.float32), whole[70:71])
+        assert torch.equal(K.gemm_simt(a[3:140].contiguous(), w, out_dtype=torch.float32), whole[3:140])
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_grouped_gemm_with_gather(K, dtype):
+    torch.manual_seed(10)
+    E, N, K_, M, k = 5, 50, 40, 23, 2
+    x, w = rnd(dtype, M, K_), rnd(dtype, E, N, K_)
+    counts = [7, 0, 20, 1, 18]                       # an expert without rows, one with a single row
+    offsets = [0]
+    for c in counts:
+        offsets.append(offsets[-1] + c)
+    pairs = torch.randperm(M * k).tolist()            # sorted row r holds pair pairs[r] of token pairs[r] // k
+    out = K.gemm_simt(dev(x, dtype), dev(w, dtype), a_rows=i32(pairs), a_div=k, offsets=i32(offsets),
+                      rows_out=M * k, max_rows_per_group=M, out_dtype=torch.float32)
+    for e in range(E):
+        for r in range(offsets[e], offsets[e + 1]):
+            want = x[pairs[r] // k] @ w[e].T
+            close(out[r], want, dtype, scale=2)
+
+
+# ---------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("E,k,H,norm,use_bias,scaling", [(8, 2, 64, True, True, 1.0), (16, 4, 96, False, False, 2.0),
+                                                         (5, 3, 80, True, True, 0.5), (40, 6, 2048, True, False, 1.0),
+                                                         (7, 7, 48, False, True, 1.5)])
+def test_moe_route(K, dtype, E, k, H, norm, use_bias, scaling):
+    torch.manual_seed(11)
+    M = 50
+    x = rnd(dtype, M, H)
+    wr = rnd(dtype, E, H, scale=H ** -0.5)
+    bias = torch.randn(E) * 0.1 if use_bias else None
+    ids, wts = K.moe_route(dev(x, dtype), dev(wr, dtype), dev(bias) if use_bias else None, k, norm, scaling)
+    margins = []
+    want_ids, want_w = plain.route(x, wr, bias, k, norm, scaling, margins=margins)
+    clear = margins[0] > 1e-5                        # rows whose selection no rounding can change
+    assert clear.float().mean() > 0.9
+    assert torch.equal(ids.cpu().long()[clear], want_ids[clear])
+    assert torch.allclose(wts.cpu()[clear], want_w[clear], atol=2e-6, rtol=1e-5)
+    # float32 router weights with bfloat16 activations give the same
+    ids2, _ = K.moe_route(dev(x, dtype), dev(wr), dev(bias) if use_bias else None, k, norm, scaling)
+    assert torch.equal(ids2.cpu()[clear], ids.cpu()[clear])
+
+
+def test_moe_route_ties_go_to_the_lower_index_and_bias_only_selects(K):
+    x = torch.zeros(2, 32, device="cuda")
+    wr = torch.zeros(6, 32, device="cuda")
+    ids, wts = K.moe_route(x, wr, None, 3, True, 1.0)
+    assert ids.cpu().tolist() == [[0, 1, 2]] * 2
+    assert torch.allclose(wts.cpu(), torch.full((2, 3), 0.5 / (1.5 + 1e-6)))
+    bias = torch.tensor([0.0, 0.3, 0.0, 0.3, 0.0, 0.1], device="cuda")
+    ids, wts = K.moe_route(x, wr, bias, 3, False, 2.0)
+    assert ids.cpu().tolist() == [[1, 3, 5]] * 2 and torch.allclose(wts.cpu(), torch.full((2, 3), 1.0))
+
+
+def test_moe_sort_and_combine(K):
+    torch.manual_seed(12)
+    M, k, E, H = 37, 3, 9, 70
+    ids = torch.stack([torch.randperm(E)[:k] for _ in range(M)]).int()
+    ids[:, 0] = torch.where(torch.rand(M) < 0.3, torch.tensor(8), ids[:, 0].long()).int()   # crowd one expert
+    for m in range(M):                                # keep a token's experts distinct
+        seen = set()
+        for j in range(k):
+            while int(ids[m, j]) in seen:
+                ids[m, j] = (int(ids[m, j]) + 1) % E
+            seen.add(int(ids[m, j]))
+    offsets, pair_pos, sorted_pair = K.moe_sort(ids.cuda(), E)
+    offsets, pair_pos, sorted_pair = offsets.cpu(), pair_pos.cpu(), sorted_pair.cpu()
+    flat = ids.reshape(-1)
+    assert offsets[0] == 0 and offsets[-1] == M * k
+    assert torch.equal(offsets[1:] - offsets[:-1], torch.bincount(flat, minlength=E).int())
+    assert sorted(sorted_pair.tolist()) == list(range(M * k))
+    for p in range(M * k):
+        r = int(pair_pos[p])
+        assert int(sorted_pair[r]) == p and offsets[flat[p]] <= r < offsets[flat[p] + 1]
+    y, w = torch.randn(M * k, H), torch.rand(M, k)
+    out = K.moe_combine(y.cuda(), pair_pos.cuda(), w.cuda())
+    want = torch.stack([sum(w[m, j] * y[pair_pos[m * k + j]] for j in range(k)) for m in range(M)])
+    assert torch.allclose(out.cpu(), want, atol=1e-5)
+
+
+# ---------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("V", [31, 256, 4097, 65536, 100003])
+def test_argmax(K, V):
+    """NaN counts as -inf, ties give the lowest index (tests/test_sampling_argmax.py:13-44 in SnowLLM)."""
+    torch.manual_seed(13)
+    x = torch.randn(6, V)
+    x[1, V // 2] = x[1, V - 1] = 50.0              # a tie: the lower index wins
+    x[2, 3] = float("nan")
+    x[2, V - 2] = 60.0
+    x[3] = float("nan")                             # every value NaN
+    x[4] = float("-inf")
+    x[5, 0] = float("inf")
+    out = K.argmax(x.cuda()).cpu()
+    want = torch.argmax(torch.nan_to_num(x, nan=float("-inf")), dim=-1)
+    assert out.tolist() == want.tolist()
+    assert out[1] == V // 2 and out[3] == 0 and out[4] == 0
+
+
+def test_penalties_and_bans(K):
+    V = 50
+    logits = torch.arange(V, dtype=torch.float32).repeat(3, 1) - 20.0
+    before = logits.clone()
+    ids = [3, 30, 45, 10, 25]                       # row 0: three seen tokens; row 1: none; row 2: ban + one seen
+    counts = [0, 2, 1, -1, 3]
+    K.apply_penalties(x := logits.cuda(), i32([0, 3, 3, 5]), i32(ids), i32(counts),
+                      torch.tensor([0.5, 0.0, 0.0]).cuda(), torch.tensor([0.25, 0.0, 1.0]).cuda(),
+                      torch.tensor([2.0, 1.0, 1.0]).cuda())
+    got = x.cpu()
+    want = before.clone()
+    want[0, 3] = before[0, 3] * 2.0                 # negative: times r; count 0: no presence, no frequency
+    want[0, 30] = before[0, 30] / 2.0 - 0.25 * 2 - 0.5
+    want[0, 45] = before[0, 45] / 2.0 - 0.25 - 0.5
+    want[2, 10] = float("-inf")
+    want[2, 25] = before[2, 25] - 3.0
+    assert torch.equal(got, want)
+
+
+def test_sample_matches_the_reference_draw(K):
+    torch.manual_seed(14)
+    V, B = 997, 64
+    logits = torch.randn(B, V) * 3
+    temperature = torch.rand(B) * 1.5 + 0.2
+    top_k = torch.tensor([0, 1, 5, 50, 996, 997, 2000, 17] * 8, dtype=torch.int32)
+    top_p = torch.tensor([1.0, 0.9, 0.5, 0.99, 0.1, 1.0, 0.7, 0.3] * 8).roll(3)
+    uniform = torch.rand(B)
+    uniform[:4] = torch.tensor([0.0, 0.999999, 0.5, 1e-7])
+    temperature[8] = 0.0                            # a greedy row among the others
+    out = K.sample(logits.cuda(), temperature.cuda(), top_k.cuda(), top_p.cuda(), uniform.cuda()).cpu()
+    miss = 0
+    for b in range(B):
+        if temperature[b] <= 0:
+            assert out[b] == logits[b].argmax()
+            continue
+        want = plain.softmax_sample_reference(logits[b], float(temperature[b]), int(top_k[b]), float(top_p[b]),
+                                              float(uniform[b]))
+        # float32 against float64 sums may put the draw on the other side of a CDF step: a neighbour
+        if out[b] != want:
+            p = torch.softmax(logits[b].double() / float(temperature[b]), -1)
+            c = torch.cumsum(p, 0)
+            assert abs(float(c[min(out[b], want)]) - float(uniform[b])) < 1e-3 or p[out[b]] > 0, b
+            miss += 1
+    assert miss <= 3
+
+
+def test_sample_respects_top_k_and_top_p_sets(K):
+    torch.manual_seed(15)
+    V = 300
+    logits = torch.randn(1, V).repeat(400, 1) * 2
+    for top_k, top_p in ((5, 1.0), (0, 0.6), (20, 0.8)):
+        out = K.sample(logits.cuda(), torch.ones(400).cuda(), torch.full((400,), top_k, dtype=torch.int32).cuda(),
+                       torch.full((400,), top_p).cuda(), torch.rand(400).cuda()).cpu()
+        p = torch.softmax(logits[0].double(), -1)
+        order = torch.argsort(p, descending=True)
+        allowed = set(order[:top_k].tolist()) if top_k else set(range(V))
+        if top_p < 1:
+            kept = order[:top_k] if top_k else order
+            c = torch.cumsum(p[kept], 0)
+            n = int((c < top_p * c[-1]).sum()) + 1
+            allowed &= set(kept[:n].tolist())
+        assert set(out.tolist()) <= allowed
+        assert len(set(out.tolist())) > 1

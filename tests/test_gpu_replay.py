@@ -1,0 +1,234 @@
+"""The engine against the plain implementation under every way of cutting the work, in float32 and
+in bfloat16: each request alone and whole; most of it in one step and the last 32 tokens one by
+one; portions of changing size; and mixed, up to four live requests with so few pages that they are
+used again.  In-process through the replay driver (with the routers' picks tapped), and once per
+dtype through the ``bin/trace_run`` program itself."""
+import json
+import pathlib
+import subprocess
+import sys
+
+import numpy as np
+import pytest
+import torch
+
+import plain_lfm2 as plain
+from helpers import (TOL, decode_tail_trace, gather_logits, max_live_tokens, mixed_trace, portions_trace,
+                     random_prompt, rel_rows, whole_trace)
+from tiny_configs import ALL
+
+pytestmark = pytest.mark.gpu
+ROOT = pathlib.Path(__file__).resolve().parent.parent
+
+# Router picks may differ from the plain implementation's only where its selection margin (gap
+# between the k-th and the (k+1)-th score) is below what the dtype's rounding can move a score by.
+ROUTE_MARGIN = {"float32": 1e-4, "bfloat16": 5e-2}
+LENGTHS = {"a": 70, "b": 133, "c": 45, "d": 97, "e": 150, "f": 64}
+CUTS = {"whole": whole_trace, "decode_tail": decode_tail_trace, "portions": portions_trace, "mixed": mixed_trace}
+
+
+def requests_for(cfg, seed=0):
+    return {k: random_prompt(cfg["vocab_size"], n, seed + i) for i, (k, n) in enumerate(LENGTHS.items())}
+
+
+def run_in_process(model_dir, dtype, steps, max_tokens, page_size=16):
+    """Replay ``steps``; returns (outputs per step, {request -> {layer -> ids [T, k]}})."""
+    from snowllm_b200.engine.replay import Replay
+    rp = Replay(model_dir, dtype, max_tokens, max_requests=4, page_size=page_size)
+    moe_layers = [i for i, b in enumerate(rp.model.blocks) if hasattr(b.ffn, "route")]
+    outputs, routes = [], {}
+    for s in steps:
+        rp.runner.taps = []
+        outputs.append(rp.step(s["entries"], s["end"]))
+        picks = [t.cpu() for name, t in rp.runner.taps if name == "moe_route"]
+        assert len(picks) == len(moe_layers)
+        row = 0
+        for e in s["entries"]:
+            n = len(e["tokens"])
+            for layer, ids in zip(moe_layers, picks):
+                routes.setdefault(e["id"], {}).setdefault(layer, []).append(ids[row:row + n])
+            row += n
+    assert all(p.free_count == p.total for p in rp.cache.groups.values()), "pages were lost"
+    assert rp.cache.slots.free_count == rp.cache.max_seqs
+    routes = {k: {layer: torch.cat(v) for layer, v in d.items()} for k, d in routes.items()}
+    return outputs, routes
+
+
+def check_against_plain(model_dir, dtype, reqs, steps, outputs, routes):
+    cfg, tensors = plain.read_model_dir(model_dir)
+    got = gather_logits(steps, outputs)
+    worst = 0.0
+    for k, toks in reqs.items():
+        forced = routes.get(k) or None
+        if not forced:
+            want = plain.logits(cfg, tensors, toks)
+        else:
+            # the picks must be the plain implementation's wherever its margin is clear
+            mg = {}
+            want = plain.logits(cfg, tensors, toks, forced_routes=forced, margins=mg)
+            plain_ids = plain_routes(cfg, tensors, toks, forced)
+            for layer, ids in forced.items():
+                differs = (ids.long().sort(-1).values != plain_ids[layer].sort(-1).values).any(-1)
+                unclear = mg[layer] < ROUTE_MARGIN[dtype]
+                assert not (differs & ~unclear).any(), \
+                    f"request {k} layer {layer}: picks differ at positions {torch.nonzero(differs & ~unclear).flatten().tolist()} with a clear margin"
+        err = rel_rows(got[k], want)
+        worst = max(worst, float(err.max()))
+        bad = torch.nonzero(err > TOL[dtype]).flatten().tolist()
+        assert not bad, f"request {k}: first wrong position {bad[0]} of {len(toks)} (rel {float(err[bad[0]]):.3g}); all: {bad[:20]}"
+    return worst
+
+
+def plain_routes(cfg, tensors, toks, forced):
+    """The plain router's own picks at each routed layer, given the residual stream that the forced
+    picks produce up to that layer (so one early difference does not cascade into the comparison)."""
+    out = {}
+    eps = cfg["norm_eps"]
+    x = tensors["model.embed_tokens.weight"][torch.as_tensor(toks)].float()
+    for i in range(cfg["num_hidden_layers"]):
+        p = f"model.layers.{i}."
+        x = x + plain.layer_mixer(cfg, tensors, i, plain.rmsnorm(x, tensors[p + "operator_norm.weight"], eps))
+        u = plain.rmsnorm(x, tensors[p + "ffn_norm.weight"], eps)
+        if i in forced:
+            bias = tensors[p + "feed_forward.expert_bias"] if cfg.get("use_expert_bias") else None
+            out[i], _ = plain.route(u, tensors[p + "feed_forward.gate.weight"], bias, cfg["num_experts_per_tok"],
+                                    cfg.get("norm_topk_prob", False), cfg.get("routed_scaling_factor", 1.0))
+        x = x + plain.layer_ffn(cfg, tensors, i, u, forced.get(i))
+    return out
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["tiny_a", "tiny_b", "tiny_c", "tiny_dense"])
+@pytest.mark.parametrize("cut", list(CUTS))
+def test_cuts_match_the_plain_implementation(model_dirs, name, dtype, cut):
+    d = model_dirs(name, dtype)
+    reqs = requests_for(ALL[name])
+    steps = CUTS[cut](reqs)
+    outputs, routes = run_in_process(d, dtype, steps, max_live_tokens(steps))
+    check_against_plain(d, dtype, reqs, steps, outputs, routes)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_cuts_agree_with_one_another_bitwise_in_the_mixers(model_dirs, dtype):
+    """Whole, decoded and portioned runs of the same request: float32 logits differ by rounding of
+    the attention's chunking at most, and stay within the tolerance of one another."""
+    d = model_dirs("tiny_b", dtype)
+    reqs = requests_for(ALL["tiny_b"])
+    ref = None
+    for cut in ("whole", "decode_tail", "portions", "mixed"):
+        steps = CUTS[cut](reqs)
+        outputs, _ = run_in_process(d, dtype, steps, max_live_tokens(steps))
+        got = gather_logits(steps, outputs)
+        if ref is None:
+            ref = got
+            continue
+        for k in reqs:
+            err = rel_rows(got[k], ref[k])
+            if dtype == "float32":
+                assert float(err.max()) < 1e-5, (cut, k, float(err.max()))
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("page_size", [16, 64])
+def test_mixed_with_reused_pages_poisoned(model_dirs, dtype, page_size):
+    """Pages and state slots given back are filled with NaN before they are used again: nothing
+    stale may be read (SnowLLM poisons scratch and state the same way, tests/test_lfm2.py:31-71)."""
+    from snowllm_b200.engine.replay import Replay
+    d = model_dirs("tiny_a", dtype)
+    reqs = requests_for(ALL["tiny_a"], seed=10)
+    steps = mixed_trace(reqs, seed=3)
+    rp = Replay(d, dtype, max_live_tokens(steps), max_requests=4, page_size=page_size)
+    for pool in rp.cache.pools.values():
+        pool.fill_(float("nan"))
+    for st in rp.cache.states.values():
+        for t in st:
+            t.fill_(float("nan"))
+    outputs, used = [], set()
+    reused = False
+    for s in steps:
+        outputs.append(rp.step(s["entries"], s["end"]))
+        held = {p for rc in rp.live.values() for t in rc.tables.values() for p in t if p >= 0}
+        reused |= bool(held & used)
+        used |= held
+        free = [p for pool in rp.cache.groups.values() for p in pool._free]
+        for pool in rp.cache.pools.values():
+            pool[free] = float("nan")
+        free_slots = list(rp.cache.slots._free)
+        for st in rp.cache.states.values():
+            for t in st:
+                t[free_slots] = float("nan")
+    assert reused, "the trace was meant to use pages again"
+    got = gather_logits(steps, outputs)
+    assert all(v.isfinite().all() for v in got.values()), "a stale (NaN) page or slot was read"
+    whole = whole_trace(reqs)
+    ref_out, _ = run_in_process(d, dtype, whole, max_live_tokens(whole), page_size=page_size)
+    ref = gather_logits(whole, ref_out)
+    for k in reqs:
+        assert float(rel_rows(got[k], ref[k]).max()) < (1e-5 if dtype == "float32" else TOL[dtype]), k
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_long_decoding_and_first_tokens(model_dirs, dtype):
+    """A short prompt, then 300 tokens one by one (across many page edges); and sequences of one,
+    two and three tokens, whole and token by token."""
+    d = model_dirs("tiny_b", dtype)
+    cfg = ALL["tiny_b"]
+    long = random_prompt(cfg["vocab_size"], 340, 5)
+    steps = [{"step": 0, "entries": [{"id": "x", "tokens": long[:40], "want": list(range(40))}], "end": []}]
+    steps += [{"step": i - 39, "entries": [{"id": "x", "tokens": [long[i]], "want": [0]}],
+               "end": ["x"] if i == 339 else []} for i in range(40, 340)]
+    outputs, routes = run_in_process(d, dtype, steps, 384)
+    check_against_plain(d, dtype, {"x": long}, steps, outputs, routes)
+    for n in (1, 2, 3):
+        toks = random_prompt(cfg["vocab_size"], n, 20 + n)
+        for cut in (whole_trace, lambda r: decode_tail_trace(r, tail=8)):
+            steps = cut({"s": toks})
+            outputs, routes = run_in_process(d, dtype, steps, 64)
+            check_against_plain(d, dtype, {"s": toks}, steps, outputs, routes)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_trace_run_program(model_dirs, tmp_path, dtype):
+    """The program itself, as a user runs it: steps on stdin, ``done`` lines, .f32 files, exit 0."""
+    d = model_dirs("tiny_b", dtype, flavour="baseline" if dtype == "bfloat16" else "scaled")
+    cfg = ALL["tiny_b"]
+    reqs = {k: random_prompt(cfg["vocab_size"], n, 40 + i) for i, (k, n) in
+            enumerate({"a": 70, "b": 133, "c": 45, "d": 97, "e": 66}.items())}
+    steps = mixed_trace(reqs, seed=1)
+    steps[1]["entries"][0]["want"] = []                   # a step entry that wants nothing
+    dropped = (steps[1]["entries"][0]["id"], steps[1]["entries"][0]["tokens"])
+    out = tmp_path / "out"
+    proc = subprocess.run([sys.executable, str(ROOT / "bin" / "trace_run"), "--model", str(d), "--dtype", dtype,
+                           "--out", str(out), "--max-tokens", str(max_live_tokens(steps))],
+                          input="\n".join(json.dumps(s) for s in steps) + "\n", capture_output=True, text=True,
+                          timeout=600)
+    assert proc.returncode == 0, proc.stderr[-2000:]
+    assert proc.stdout.split() == [w for s in steps for w in ("done", str(s["step"]))]
+    V = cfg["vocab_size"]
+    outputs = []
+    for s in steps:
+        wanted = sum(len(e["want"]) for e in s["entries"])
+        f = out / f"{s['step']}.f32"
+        if not wanted:
+            assert not f.exists()
+            outputs.append(None)
+            continue
+        data = np.fromfile(f, dtype="<f4")
+        assert data.size == wanted * V
+        outputs.append(torch.from_numpy(data.reshape(wanted, V)))
+    cfg_p, tensors = plain.read_model_dir(d)
+    rows, pos = {}, {}
+    for s, o in zip(steps, outputs):
+        r = 0
+        for e in s["entries"]:
+            base = pos.get(e["id"], 0)
+            for w in e["want"]:
+                rows.setdefault(e["id"], {})[base + w] = o[r]
+                r += 1
+            pos[e["id"]] = base + len(e["tokens"])
+    for k, toks in reqs.items():
+        want = plain.logits(cfg_p, tensors, toks)
+        idx = sorted(rows[k])
+        assert len(idx) >= len(toks) - len(dropped[1])
+        err = rel_rows(torch.stack([rows[k][i] for i in idx]), want[idx])
+        assert float(err.max()) < TOL[dtype], (k, float(err.max()))

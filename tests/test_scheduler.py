@@ -1,0 +1,152 @@
+"""The scheduler's decisions on the CPU, against a cache manager without tensors and a fake step
+(in the manner of the fakes of tests/test_single_model_path.py:12-46 in SnowLLM)."""
+import pytest
+
+from snowllm_b200.cache import CacheManager
+from snowllm_b200.engine.request import Request, SamplingParams
+from snowllm_b200.engine.scheduler import Scheduler
+from snowllm_b200.errors import CapacityError, SnowLLMError
+from snowllm_b200.parts.spec import PagedKVSpec, SlotStateSpec
+
+SPECS = {0: PagedKVSpec(2, 16), 1: SlotStateSpec(((2, 8),))}
+
+
+def make(num_pages=16, max_seqs=4, budget=32, max_len=256, page=16, preempt=True):
+    cm = CacheManager(SPECS, page, num_pages, max_seqs)
+    return cm, Scheduler(cm, max_seqs, budget, max_len, preempt)
+
+
+def req(n, new=8):
+    return Request(prompt=list(range(1, n + 1)), params=SamplingParams(temperature=0, max_new_tokens=new))
+
+
+def fake_step(sched, plan, token=7):
+    """What the engine does after the model ran: record progress, append a token where logits came."""
+    for s in plan:
+        assert s.request.cache.num_tokens == s.start
+        sched.cache.commit(s.request.cache, s.start + s.count)
+        s.request.num_computed += s.count
+        if s.wants_logits:
+            s.request.out.append(token)
+            if len(s.request.out) >= s.request.params.max_new_tokens:
+                s.request.done, s.request.finish_reason = True, "length"
+
+
+def run(sched, limit=1000):
+    log = []
+    for _ in range(limit):
+        sched.retire_finished()
+        plan = sched.schedule()
+        if not plan:
+            break
+        log.append([(s.request, s.start, s.count, s.wants_logits) for s in plan])
+        fake_step(sched, plan)
+    sched.retire_finished()
+    return log
+
+
+def test_prompt_is_cut_into_portions_under_the_budget():
+    cm, s = make(budget=32)
+    r = req(70, new=2)
+    s.add(r)
+    log = run(s)
+    assert [(st, n, w) for _, st, n, w in (step[0] for step in log)] == \
+        [(0, 32, False), (32, 32, False), (64, 6, True), (70, 1, True)]
+    assert r.done and r.out == [7, 7] and r.cache is None
+    assert cm.free_pages()[("paged", None)] == 16 and cm.slots.free_count == 4
+
+
+def test_decodes_go_first_and_prompts_fill_the_rest():
+    cm, s = make(budget=10, num_pages=32)
+    a, b = req(4, new=50), req(25, new=3)
+    s.add(a)
+    fake_step(s, s.schedule())             # a is prefilled whole, now decoding
+    s.add(b)
+    plan = s.schedule()
+    assert [(x.request, x.start, x.count) for x in plan] == [(a, 4, 1), (b, 0, 9)]
+    fake_step(s, plan)
+    plan = s.schedule()
+    assert [(x.request, x.start, x.count, x.wants_logits) for x in plan] == [(a, 5, 1, True), (b, 9, 9, False)]
+    fake_step(s, plan)
+    plan = s.schedule()
+    assert [(x.request, x.start, x.count, x.wants_logits) for x in plan] == [(a, 6, 1, True), (b, 18, 7, True)]
+
+
+def test_admission_respects_slots_and_pages():
+    cm, s = make(num_pages=4, max_seqs=2, budget=100)
+    a, b, c = req(30), req(30), req(10)
+    for r in (a, b, c):
+        s.add(r)
+    plan = s.schedule()
+    assert [x.request for x in plan] == [a, b]          # c: no slot left
+    assert list(s.waiting) == [c] and cm.free_pages()[("paged", None)] == 0
+
+
+def test_request_longer_than_max_model_len_is_refused():
+    _, s = make(max_len=64)
+    with pytest.raises(SnowLLMError, match="max_model_len"):
+        s.add(req(60, new=8))
+    with pytest.raises(SnowLLMError):
+        s.add(Request(prompt=[], params=SamplingParams()))
+
+
+def test_pages_run_out_the_last_admitted_is_preempted_and_replayed():
+    # two requests of 30 tokens in 4 pages of 16: both fit; at token 33 one needs a third page
+    cm, s = make(num_pages=4, max_seqs=2, budget=100)
+    a, b = req(30, new=8), req(30, new=8)
+    s.add(a)
+    s.add(b)
+    log = run(s)
+    assert s.preemptions >= 1 and b.preemptions >= 1 and a.preemptions == 0
+    assert a.done and b.done and len(a.out) == 8 and len(b.out) == 8
+    # b was prefilled again over its prompt and what it had generated
+    replays = [(st, n) for step in log for r, st, n, _ in step if r is b and st == 0]
+    assert len(replays) == 1 + b.preemptions and replays[1][1] > 30
+    assert cm.free_pages()[("paged", None)] == 4 and cm.slots.free_count == 2
+
+
+def test_one_request_and_no_page_left_is_a_capacity_error():
+    cm, s = make(num_pages=2, max_seqs=2, budget=100, max_len=100)
+    r = req(31, new=20)
+    s.add(r)
+    with pytest.raises(CapacityError, match="cannot hold one request"):
+        run(s)
+
+
+def test_prompt_that_can_never_fit_is_a_capacity_error():
+    cm, s = make(num_pages=2, budget=100)
+    s.add(req(40))
+    with pytest.raises(CapacityError, match="cannot admit"):
+        s.schedule()
+
+
+def test_preemption_off_raises_instead():
+    cm, s = make(num_pages=4, max_seqs=2, budget=100, preempt=False)
+    s.add(req(30, new=8))
+    s.add(req(30, new=8))
+    with pytest.raises(CapacityError, match="preemption is off"):
+        run(s)
+
+
+def test_abort_gives_everything_back():
+    cm, s = make()
+    a, b = req(20), req(20)
+    s.add(a)
+    s.add(b)
+    fake_step(s, s.schedule())
+    s.abort(a)
+    assert a.finish_reason == "abort" and a.cache is None and s.running == [b]
+    assert cm.slots.free_count == 3
+
+
+def test_finished_requests_pages_serve_the_next_request_in_the_next_step():
+    cm, s = make(num_pages=2, max_seqs=1, budget=100)
+    a, b = req(20, new=1), req(20, new=1)
+    s.add(a)
+    s.add(b)
+    fake_step(s, s.schedule())
+    pages_a = None
+    assert a.done
+    s.retire_finished()
+    plan = s.schedule()
+    assert plan[0].request is b and sorted(b.cache.tables[("paged", None)]) == [0, 1]
