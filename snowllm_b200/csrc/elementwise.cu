@@ -1,10 +1,12 @@
 // Embedding gather, fused residual-add + RMSNorm, SwiGLU activation.
 //
 // Embedding: h[m,:] = E[ids[m],:]                      (snowllm/ops/embedding.py:12-25)
-// RMSNorm:   n = x * rsqrt(mean(x^2) + eps) in float, rounded to the compute dtype, then
-//            times the weight, rounded again            (snowllm/ops/norm.py:11-30)
-// SwiGLU:    out = round(silu(gate)) * up               (snowllm/ops/mlp.py:12-20)
-// The residual stream is float here, so the residual sum is a 32-bit sum.
+// RMSNorm:   y = x * rsqrt(mean(x^2) + eps) * weight    (snowllm/ops/norm.py:11-30)
+// SwiGLU:    out = silu(gate) * up                      (snowllm/ops/mlp.py:12-20)
+// Both are evaluated in float and rounded to the compute dtype once, at the store (SnowLLM's
+// bf16 kernels also round the normalised value before the weight, and silu before the product;
+// those extra roundings are left out).  The residual stream is float, so the residual sum is a
+// 32-bit sum.
 #include "common.cuh"
 
 // ---------------------------------------------------------------------------------------
@@ -57,7 +59,7 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ residual, const float* __
   const float inv = rsqrtf(ss / (float)H + eps);
   T* o = out + (size_t)r * H;
   for (int i = threadIdx.x; i < H; i += blockDim.x)
-    o[i] = from_f<T>(round_f<T>(xs[i] * inv) * gamma[i]);
+    o[i] = from_f<T>(xs[i] * inv * gamma[i]);
 }
 
 SNK_API int snk_add_rmsnorm(float* residual, const float* delta, const void* gamma,
@@ -104,7 +106,7 @@ __global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ out, int
   const int i = (int)(idx - m * I);
   const float g = to_f<T>(gu[m * 2 * I + i]);
   const float u = to_f<T>(gu[m * 2 * I + I + i]);
-  const float s = round_f<T>(g / (1.f + expf(-g)));
+  const float s = g / (1.f + expf(-g));
   out[idx] = from_f<T>(s * u);
 }
 

@@ -1,11 +1,11 @@
 // Per-head RMSNorm of q and k, rotary position encoding, and the write of k and v into the
 // paged cache, in one pass over the fused qkv rows.
 //
-//   q, k: n = x * rsqrt(mean_hd(x^2) + eps) -> round -> * weight -> round
-//         (snowllm/models/lfm2/layers.py:55-59, round-before-weight)
+//   q, k: x * rsqrt(mean_hd(x^2) + eps) * weight   (snowllm/models/lfm2/layers.py:55-59)
 //   rope: ang = pos * inv_freq[i] in float; split-half rotation over the first rot_dim
 //         elements of the head: x'[i] = x[i] cos - x[i+h] sin; x'[i+h] = x[i+h] cos + x[i] sin
-//         (snowllm/ops/rope.py:11-24; tests/test_lfm2.py:108-118)
+//         (snowllm/ops/rope.py:11-24; tests/test_lfm2.py:108-118); norm and rotation run in
+//         float and the result is rounded to the compute dtype once, at the store
 //   cache: k and v rows go to page block_table[seg][pos / P], offset pos % P
 //         (snowllm/ops/cache.py:12-20).  Pool layout: [page, 2 (k, v), kv head, P, hd].
 #include "common.cuh"
@@ -52,7 +52,7 @@ __global__ void qk_norm_rope_cache_kernel(
       for (int j = 0; j < ROPE_MAX_PER_LANE; ++j)
         if (j < per) {
           const int d = lane + 32 * j;
-          if (d < hd) x[j] = round_f<T>(round_f<T>(x[j] * inv) * g[d]);
+          if (d < hd) x[j] = x[j] * inv * g[d];
         }
     }
     if (inv_freq != nullptr && rot_dim > 0) {

@@ -4,7 +4,7 @@
 //   conv[t,c] = sum_{j<L} w[c,j] * g~[t-(L-1)+j, c], float accumulation in tap order, where g~
 //   is the request's history (the last L-1 rows of g of earlier steps; zeros for a request
 //   that starts at position 0, whatever its slot holds) followed by this step's g
-//   y = round(C * round(conv));   state <- the last L-1 rows of g~ (oldest first)
+//   y = round(C * conv);   state <- the last L-1 rows of g~ (oldest first)
 //   (snowllm/models/lfm2/layers.py:26-33; snowllm/ops/lfm2.py:8-26; tests/test_lfm2.py:41-49)
 //
 // Two launches: the first only reads the state, the second rewrites it, so that tokens of
@@ -51,7 +51,7 @@ __global__ void short_conv_kernel(const T* __restrict__ bcx, SmallVec w, const T
       }
     }
     const float cgate = to_f<T>(bcx[(size_t)m * 3 * H + H + c]);
-    out[(size_t)m * H + c] = from_f<T>(cgate * round_f<T>(acc));
+    out[(size_t)m * H + c] = from_f<T>(cgate * acc);
   }
 }
 

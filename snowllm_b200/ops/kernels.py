@@ -175,7 +175,7 @@ def residual_add(residual: torch.Tensor, delta: torch.Tensor) -> None:
 
 
 def swiglu(gate_up: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
-    """[M, 2I] (gate | up) -> [M, I]: round(silu(gate)) * up."""
+    """[M, 2I] (gate | up) -> [M, I]: silu(gate) * up."""
     M, two_i = gate_up.shape
     _chk(gate_up, "swiglu input", (torch.float32, torch.bfloat16))
     if two_i % 2:

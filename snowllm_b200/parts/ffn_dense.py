@@ -1,4 +1,4 @@
-"""Dense SwiGLU feed-forward: down(round(silu(gate x)) * up x)
+"""Dense SwiGLU feed-forward: down(silu(gate x) * up x)
 (snowllm/models/lfm2/layers.py:76-88; snowllm/ops/mlp.py:12-20).  Gate and up are one fused
 product [2I, H]; the down product leaves a float delta for the residual sum."""
 from __future__ import annotations

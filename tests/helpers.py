@@ -8,12 +8,28 @@ import torch
 import plain_lfm2 as plain
 from tiny_configs import ALL
 
-# Per-position relative L2 error allowed between the engine and the plain implementation.
-# float32: both sides sum in float32 in different orders; a few 1e-6 per product, about 1e-5 after
-# a handful of layers.  bfloat16: 8 mantissa bits, about 2^-9 relative per rounding, some tens of
-# roundings in a row through norms and softmax (SnowLLM's own bf16 tests allow 0.025 over 3 layers,
-# tests/test_lfm2_reference.py:66-161).
-TOL = {"float32": 2e-5, "bfloat16": 4e-2}
+# Relative L2 error allowed between the engine and the plain implementation.
+# float32: both sides sum in float32 in different orders: a few 1e-6 per product, about 1e-5 after a
+# handful of layers; the bound holds for every single position.
+# bfloat16: the bound over a whole request starts from SnowLLM's own acceptance bound for its bf16
+# kernels against a float reference: rel-L2 < 0.025 for a 3-layer model
+# (tests/test_lfm2_reference.py:66-161).  Rounding errors of successive layers are independent and
+# add in quadrature, so a model of L layers gets 0.025 * sqrt(L / 3).  A single position is one
+# sample of that error, and the largest of some hundred samples lies a few times above their root
+# mean square, so single positions get 0.1: enough to name the first wrong position of a real
+# fault (a wrong page, slot or key gives errors of order 1), which the float32 runs of the same
+# kernels pin down to 2e-5.
+TOL = {"float32": 2e-5, "bfloat16": 0.1}
+
+
+def tol_request(dtype: str, num_layers: int) -> float:
+    return 2e-5 if dtype == "float32" else 0.025 * (max(num_layers, 3) / 3) ** 0.5
+
+
+def rel_all(got, want) -> float:
+    """Relative L2 error over all rows together."""
+    got, want = got.double(), want.double()
+    return float((got - want).norm() / want.norm().clamp_min(1e-30))
 
 
 def make_model_dir(folder, name, dtype="float32", flavour="scaled", seed=1):
@@ -55,7 +71,7 @@ def decode_tail_trace(reqs: dict, tail: int = 32) -> list:
     for k, v in reqs.items():
         head = max(1, len(v) - tail)
         steps.append({"step": len(steps), "entries": [{"id": k, "tokens": v[:head], "want": list(range(head))}],
-                      "end": []})
+                      "end": [k] if head == len(v) else []})
         for i in range(head, len(v)):
             steps.append({"step": len(steps), "entries": [{"id": k, "tokens": v[i:i + 1], "want": [0]}],
                           "end": [k] if i == len(v) - 1 else []})

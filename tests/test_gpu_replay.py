@@ -14,7 +14,7 @@ import torch
 
 import plain_lfm2 as plain
 from helpers import (TOL, decode_tail_trace, gather_logits, max_live_tokens, mixed_trace, portions_trace,
-                     random_prompt, rel_rows, whole_trace)
+                     random_prompt, rel_all, rel_rows, tol_request, whole_trace)
 from tiny_configs import ALL
 
 pytestmark = pytest.mark.gpu
@@ -76,6 +76,9 @@ def check_against_plain(model_dir, dtype, reqs, steps, outputs, routes):
         worst = max(worst, float(err.max()))
         bad = torch.nonzero(err > TOL[dtype]).flatten().tolist()
         assert not bad, f"request {k}: first wrong position {bad[0]} of {len(toks)} (rel {float(err[bad[0]]):.3g}); all: {bad[:20]}"
+        whole = rel_all(got[k], want)
+        assert whole < tol_request(dtype, cfg["num_hidden_layers"]), \
+            f"request {k}: rel-L2 over all positions {whole:.3g}"
     return worst
 
 
@@ -165,6 +168,7 @@ def test_mixed_with_reused_pages_poisoned(model_dirs, dtype, page_size):
     ref = gather_logits(whole, ref_out)
     for k in reqs:
         assert float(rel_rows(got[k], ref[k]).max()) < (1e-5 if dtype == "float32" else TOL[dtype]), k
+        assert rel_all(got[k], ref[k]) < (1e-5 if dtype == "float32" else tol_request(dtype, 4)), k
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
@@ -187,24 +191,13 @@ def test_long_decoding_and_first_tokens(model_dirs, dtype):
             check_against_plain(d, dtype, {"s": toks}, steps, outputs, routes)
 
 
-@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-def test_trace_run_program(model_dirs, tmp_path, dtype):
-    """The program itself, as a user runs it: steps on stdin, ``done`` lines, .f32 files, exit 0."""
-    d = model_dirs("tiny_b", dtype, flavour="baseline" if dtype == "bfloat16" else "scaled")
-    cfg = ALL["tiny_b"]
-    reqs = {k: random_prompt(cfg["vocab_size"], n, 40 + i) for i, (k, n) in
-            enumerate({"a": 70, "b": 133, "c": 45, "d": 97, "e": 66}.items())}
-    steps = mixed_trace(reqs, seed=1)
-    steps[1]["entries"][0]["want"] = []                   # a step entry that wants nothing
-    dropped = (steps[1]["entries"][0]["id"], steps[1]["entries"][0]["tokens"])
-    out = tmp_path / "out"
-    proc = subprocess.run([sys.executable, str(ROOT / "bin" / "trace_run"), "--model", str(d), "--dtype", dtype,
-                           "--out", str(out), "--max-tokens", str(max_live_tokens(steps))],
+def run_program(model_dir, dtype, steps, out):
+    proc = subprocess.run([sys.executable, str(ROOT / "bin" / "trace_run"), "--model", str(model_dir), "--dtype",
+                           dtype, "--out", str(out), "--max-tokens", str(max_live_tokens(steps))],
                           input="\n".join(json.dumps(s) for s in steps) + "\n", capture_output=True, text=True,
                           timeout=600)
     assert proc.returncode == 0, proc.stderr[-2000:]
     assert proc.stdout.split() == [w for s in steps for w in ("done", str(s["step"]))]
-    V = cfg["vocab_size"]
     outputs = []
     for s in steps:
         wanted = sum(len(e["want"]) for e in s["entries"])
@@ -214,21 +207,29 @@ def test_trace_run_program(model_dirs, tmp_path, dtype):
             outputs.append(None)
             continue
         data = np.fromfile(f, dtype="<f4")
-        assert data.size == wanted * V
-        outputs.append(torch.from_numpy(data.reshape(wanted, V)))
-    cfg_p, tensors = plain.read_model_dir(d)
-    rows, pos = {}, {}
-    for s, o in zip(steps, outputs):
-        r = 0
-        for e in s["entries"]:
-            base = pos.get(e["id"], 0)
-            for w in e["want"]:
-                rows.setdefault(e["id"], {})[base + w] = o[r]
-                r += 1
-            pos[e["id"]] = base + len(e["tokens"])
-    for k, toks in reqs.items():
-        want = plain.logits(cfg_p, tensors, toks)
-        idx = sorted(rows[k])
-        assert len(idx) >= len(toks) - len(dropped[1])
-        err = rel_rows(torch.stack([rows[k][i] for i in idx]), want[idx])
-        assert float(err.max()) < TOL[dtype], (k, float(err.max()))
+        outputs.append(torch.from_numpy(data.reshape(wanted, -1)))
+    return outputs
+
+
+@pytest.mark.parametrize("name,dtype", [("tiny_b", "float32"), ("tiny_dense", "bfloat16"), ("tiny_b", "bfloat16")])
+def test_trace_run_program(model_dirs, tmp_path, name, dtype):
+    """The program itself, as a user runs it: steps on stdin, ``done`` lines, .f32 files, exit 0.
+    Its logits are those of the in-process replay bit for bit (it drives the same engine), and they
+    match the plain implementation (with a router, in bfloat16, through the in-process run's picks)."""
+    d = model_dirs(name, dtype)
+    cfg = ALL[name]
+    reqs = {k: random_prompt(cfg["vocab_size"], n, 40 + i) for i, (k, n) in
+            enumerate({"a": 70, "b": 133, "c": 45, "d": 97, "e": 66}.items())}
+    steps = mixed_trace(reqs, seed=1)
+    outputs = run_program(d, dtype, steps, tmp_path / "out")
+    assert outputs[0].shape[1] == cfg["vocab_size"]
+    inproc, routes = run_in_process(d, dtype, steps, max_live_tokens(steps))
+    for a, b in zip(outputs, inproc):
+        assert (a is None and b is None) or torch.equal(a, b)
+    check_against_plain(d, dtype, reqs, steps, outputs, routes)
+    # entries may want nothing, and a step may want nothing at all
+    quiet = [dict(s, entries=[dict(e, want=[] if i % 2 else e["want"]) for e in s["entries"]])
+             for i, s in enumerate(steps)]
+    outputs2 = run_program(d, dtype, quiet, tmp_path / "out2")
+    for i, (a, b) in enumerate(zip(outputs, outputs2)):
+        assert (b is None) if i % 2 else torch.equal(a, b)
