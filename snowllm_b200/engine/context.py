@@ -73,6 +73,7 @@ class HostStaging:
         self.buffers: list = [None] * depth
         self.events: list = [None] * depth
         self.turn = 0
+        self.bytes_uploaded = 0
 
     def upload(self, host: np.ndarray) -> torch.Tensor:
         i = self.turn
@@ -86,6 +87,7 @@ class HostStaging:
             self.buffers[i] = buf
         buf[:n].numpy()[:] = host
         dev = buf[:n].to(self.device, non_blocking=True)
+        self.bytes_uploaded += n * 4
         ev = torch.cuda.Event()
         ev.record()
         self.events[i] = ev

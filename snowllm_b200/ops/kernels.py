@@ -81,8 +81,18 @@ def libraries_for(names) -> None:
     build.build(tuple(dict.fromkeys(names)))
 
 
-def check(status: int, what: str) -> None:
+_launches = 0
+
+
+def launch_count() -> int:
+    """Kernels launched through this module so far (each wrapper reports how many it starts)."""
+    return _launches
+
+
+def check(status: int, what: str, launches: int = 1) -> None:
+    global _launches
     if status == 0:
+        _launches += launches
         return
     if status in _ERRORS:
         raise KernelError(f"{what}: {_ERRORS[status]}")
@@ -262,7 +272,8 @@ def paged_attention(q, pool, block_table, page_size, positions, row_seg, scale, 
     check(fn("snk_paged_attention")(
         _ptr(q), _ptr(pool), _ptr(block_table), block_table.shape[1], page_size, _ptr(positions),
         _ptr(row_seg), _ptr(out), _ptr(scratch), M, nh, nkv, hd, int(window or 0), int(chunk),
-        int(num_chunks), float(scale), code_of(dtype), _stream()), "paged_attention")
+        int(num_chunks), float(scale), code_of(dtype), _stream()), "paged_attention",
+        launches=2 if num_chunks > 1 else 1)
     return out
 
 
@@ -291,7 +302,7 @@ def short_conv(bcx, weight, state, cu_seqlens, seg_start, seg_slot, row_seg, out
     _chk(out, "conv output", dtype, (M, H))
     check(fn("snk_short_conv")(_ptr(bcx), _ptr(weight), w32, _ptr(state), _ptr(cu_seqlens), _ptr(seg_start),
                                _ptr(seg_slot), _ptr(row_seg), _ptr(out), M, B, H, L, code_of(dtype),
-                               _stream()), "short_conv")
+                               _stream()), "short_conv", launches=2 if L > 1 else 1)
     return out
 
 
