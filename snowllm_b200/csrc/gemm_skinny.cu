@@ -1,0 +1,161 @@
+// C[M,N] = A[M,K] . W[N,K]^T in bfloat16 for few rows (decode: M up to 64), bound by the read of W.
+//
+// Weights stream from HBM exactly once, straight into tensor-core fragments; nothing of W passes
+// through shared memory.  A block owns 16 rows of W (16 output features).  Its 8 warps split K in
+// interleaved 32-element blocks; a warp multiplies its 16x32 piece of W with up to 64 tokens by
+// mma.sync m16n8k16 (W as the 16-row operand, 8 tokens as the 8-column operand) and the 8 partial
+// sums meet in shared memory, added in warp order: no atomics, the same bits every run, and a
+// token's result does not depend on which other tokens the launch holds.
+//
+// Fragment trick: lane (g, t) loads 16 contiguous bytes (8 k-values at k0 + 8t) of W rows g and
+// g + 8 and of token row g.  The first four values feed one MMA, the last four a second one; the
+// two MMAs see a permutation of the 32 k-values, the same one for both operands, which a dot
+// product does not mind.  So every global load is a full 16-byte vector and no shuffle is needed.
+//
+// Grouped form (routed experts): rows are sorted by group; group e owns rows
+// [offsets[e], offsets[e+1]) and uses W + e*N*K; a_rows gathers A (row r reads A[a_rows[r] / a_div]).
+// A group with more than 64 rows is walked in passes of 64 (W is then re-read from L2).
+// (the role of snowllm/ops/gemm.py:33-41 and the expert products of snowllm/ops/inference.py:60-76
+// at decode shapes)
+#include "common.cuh"
+
+#define SK_WARPS 8
+#define SK_ROWS 16
+#define SK_KBLOCK 32
+#define SK_UNROLL 4
+
+__device__ __forceinline__ uint4 ldg_stream(const void* p) {
+  uint4 v;
+  asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+  return v;
+}
+
+__device__ __forceinline__ void mma_bf16(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                         uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+               "{%0,%1,%2,%3};"
+               : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+               : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+template <int MT, typename OutT>
+__global__ void __launch_bounds__(SK_WARPS * 32)
+gemm_skinny_kernel(const bf16* __restrict__ A, const bf16* __restrict__ W, OutT* __restrict__ C, int M,
+                   int N, int K, const int* __restrict__ a_rows, int a_div,
+                   const int* __restrict__ offsets) {
+  __shared__ float red[SK_WARPS][MT * 8][SK_ROWS + 1];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int g = lane >> 2, t = lane & 3;
+  const int n0 = blockIdx.x * SK_ROWS;
+  int row_begin = 0, row_end = M;
+  const bf16* Wg = W;
+  if (offsets) {
+    row_begin = offsets[blockIdx.y];
+    row_end = offsets[blockIdx.y + 1];
+    Wg = W + (size_t)blockIdx.y * N * K;
+  }
+  if (row_begin >= row_end) return;
+  // the two W rows of this lane (rows past N read row N-1 and are dropped at the store)
+  const bf16* w_lo = Wg + (size_t)min(n0 + g, N - 1) * K + 8 * t;
+  const bf16* w_hi = Wg + (size_t)min(n0 + g + 8, N - 1) * K + 8 * t;
+  const int kblocks = (K + SK_KBLOCK - 1) / SK_KBLOCK;
+
+  for (int m0 = row_begin; m0 < row_end; m0 += MT * 8) {
+    const bf16* a_ptr[MT];
+    bool a_ok[MT];
+#pragma unroll
+    for (int i = 0; i < MT; ++i) {
+      const int r = m0 + i * 8 + g;
+      a_ok[i] = r < row_end;
+      const int src = a_ok[i] ? (a_rows ? a_rows[r] / a_div : r) : 0;
+      a_ptr[i] = A + (size_t)src * K + 8 * t;
+    }
+    float acc[MT][4];
+#pragma unroll
+    for (int i = 0; i < MT; ++i)
+#pragma unroll
+      for (int j = 0; j < 4; ++j) acc[i][j] = 0.f;
+
+    for (int kb0 = warp; kb0 < kblocks; kb0 += SK_WARPS * SK_UNROLL) {
+      uint4 wl[SK_UNROLL], wh[SK_UNROLL];
+#pragma unroll
+      for (int u = 0; u < SK_UNROLL; ++u) {
+        const int kb = kb0 + u * SK_WARPS;
+        const int k = kb * SK_KBLOCK + 8 * t;
+        if (kb < kblocks && k < K) {              // K is a multiple of 8: a lane's 8 values are all in or all out
+          wl[u] = ldg_stream(w_lo + (size_t)kb * SK_KBLOCK);
+          wh[u] = ldg_stream(w_hi + (size_t)kb * SK_KBLOCK);
+        } else {
+          wl[u] = make_uint4(0, 0, 0, 0);
+          wh[u] = make_uint4(0, 0, 0, 0);
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < SK_UNROLL; ++u) {
+        const int kb = kb0 + u * SK_WARPS;
+        const int k = kb * SK_KBLOCK + 8 * t;
+        const bool k_ok = kb < kblocks && k < K;
+#pragma unroll
+        for (int i = 0; i < MT; ++i) {
+          uint4 x = make_uint4(0, 0, 0, 0);
+          if (k_ok && a_ok[i]) x = *reinterpret_cast<const uint4*>(a_ptr[i] + (size_t)kb * SK_KBLOCK);
+          mma_bf16(acc[i], wl[u].x, wh[u].x, wl[u].y, wh[u].y, x.x, x.y);
+          mma_bf16(acc[i], wl[u].z, wh[u].z, wl[u].w, wh[u].w, x.z, x.w);
+        }
+      }
+    }
+    // acc[i] = {(row g, token 2t), (row g, token 2t+1), (row g+8, token 2t), (row g+8, token 2t+1)}
+    __syncthreads();
+#pragma unroll
+    for (int i = 0; i < MT; ++i) {
+      red[warp][i * 8 + 2 * t][g] = acc[i][0];
+      red[warp][i * 8 + 2 * t + 1][g] = acc[i][1];
+      red[warp][i * 8 + 2 * t][g + 8] = acc[i][2];
+      red[warp][i * 8 + 2 * t + 1][g + 8] = acc[i][3];
+    }
+    __syncthreads();
+    for (int idx = threadIdx.x; idx < MT * 8 * SK_ROWS; idx += SK_WARPS * 32) {
+      const int tok = idx / SK_ROWS, r = idx % SK_ROWS;
+      const int m = m0 + tok, n = n0 + r;
+      if (m < row_end && n < N) {
+        float s = 0.f;
+#pragma unroll
+        for (int w = 0; w < SK_WARPS; ++w) s += red[w][tok][r];
+        C[(size_t)m * N + n] = from_f<OutT>(s);
+      }
+    }
+  }
+}
+
+template <int MT>
+static int launch_skinny(const void* A, const void* W, void* C, int M, int N, int K, const int* a_rows,
+                         int a_div, const int* offsets, int groups, int out_f32, cudaStream_t stream) {
+  dim3 grid((N + SK_ROWS - 1) / SK_ROWS, offsets ? groups : 1);
+  if (out_f32)
+    gemm_skinny_kernel<MT, float><<<grid, SK_WARPS * 32, 0, stream>>>(
+        static_cast<const bf16*>(A), static_cast<const bf16*>(W), static_cast<float*>(C), M, N, K, a_rows,
+        a_div, offsets);
+  else
+    gemm_skinny_kernel<MT, bf16><<<grid, SK_WARPS * 32, 0, stream>>>(
+        static_cast<const bf16*>(A), static_cast<const bf16*>(W), static_cast<bf16*>(C), M, N, K, a_rows,
+        a_div, offsets);
+  SNK_LAUNCH_CHECK();
+  return 0;
+}
+
+// rows_hint: the most rows one group (or the whole product) is expected to hold; picks how many
+// 8-token tiles a pass covers.  More rows than that still give the right result, in more passes.
+SNK_API int snk_gemm_skinny(const void* A, const void* W, void* C, int M, int N, int K, const int* a_rows,
+                            int a_div, const int* offsets, int groups, int rows_hint, int out_f32,
+                            cudaStream_t stream) {
+  if (M <= 0 || N <= 0) return 0;
+  if (K <= 0 || K % 8) return SNK_ERR_SIZE;
+  if (((uintptr_t)A % 16) || ((uintptr_t)W % 16)) return SNK_ERR_ALIGN;
+  if (groups > 65535) return SNK_ERR_SIZE;
+  if (a_div <= 0) a_div = 1;
+  if (rows_hint <= 8) return launch_skinny<1>(A, W, C, M, N, K, a_rows, a_div, offsets, groups, out_f32, stream);
+  if (rows_hint <= 16) return launch_skinny<2>(A, W, C, M, N, K, a_rows, a_div, offsets, groups, out_f32, stream);
+  if (rows_hint <= 32) return launch_skinny<4>(A, W, C, M, N, K, a_rows, a_div, offsets, groups, out_f32, stream);
+  return launch_skinny<8>(A, W, C, M, N, K, a_rows, a_div, offsets, groups, out_f32, stream);
+}

@@ -38,6 +38,9 @@ _SIGNATURES = {
     "gemm": {
         "snk_gemm_simt": [P, P, P, I, I, I, P, I, P, I, I, I, I, P],
     },
+    "gemm_skinny": {
+        "snk_gemm_skinny": [P, P, P, I, I, I, P, I, P, I, I, I, P],
+    },
     "moe": {
         "snk_moe_route": [P, P, I, P, P, P, I, I, I, I, I, F, I, P],
         "snk_moe_sort": [P, P, P, P, I, I, P],
@@ -337,6 +340,43 @@ def gemm_simt(a, w, out_dtype=None, out=None, a_rows=None, a_div=1, offsets=None
     check(fn("snk_gemm_simt")(_ptr(a), _ptr(w), _ptr(out), M, N, K, _ptr(a_rows), int(a_div), _ptr(offsets),
                               G, int(max_rows_per_group if grouped else M),
                               int(out_dtype == torch.float32), code_of(dtype), _stream()), "gemm_simt")
+    return out
+
+
+def gemm_skinny_ok(a, w) -> bool:
+    """Whether the few-rows bfloat16 kernel takes these operands."""
+    return (a.dtype == torch.bfloat16 and a.shape[1] % 8 == 0 and a.data_ptr() % 16 == 0
+            and w.data_ptr() % 16 == 0)
+
+
+def gemm_skinny(a, w, out_dtype=None, out=None, a_rows=None, a_div=1, offsets=None, rows_out=None,
+                rows_hint=None):
+    """bfloat16 a [M, K] times w [N, K]^T (or grouped w [G, N, K]) for few rows: W streams from memory
+    once into tensor-core fragments.  ``rows_hint``: rows expected per group (sets the pass size)."""
+    _chk(a, "gemm a", torch.bfloat16)
+    _chk(w, "gemm w", torch.bfloat16)
+    K = a.shape[1]
+    grouped = offsets is not None
+    if grouped:
+        G, N, Kw = w.shape
+        _chk(offsets, "group offsets", torch.int32, (G + 1,))
+    else:
+        G = 1
+        N, Kw = w.shape
+    if Kw != K:
+        raise KernelError(f"gemm: a has K={K}, w has K={Kw}")
+    M = rows_out if rows_out is not None else a.shape[0]
+    if a_rows is not None:
+        _chk(a_rows, "gemm row gather", torch.int32)
+    out_dtype = out_dtype or torch.bfloat16
+    if out is None:
+        out = torch.empty(M, N, dtype=out_dtype, device=a.device)
+    _chk(out, "gemm out", out_dtype, (M, N))
+    if out_dtype not in (torch.bfloat16, torch.float32):
+        raise KernelError("gemm output is bfloat16 or float32")
+    check(fn("snk_gemm_skinny")(_ptr(a), _ptr(w), _ptr(out), M, N, K, _ptr(a_rows), int(a_div), _ptr(offsets),
+                                G, int(rows_hint if rows_hint is not None else M),
+                                int(out_dtype == torch.float32), _stream()), "gemm_skinny")
     return out
 
 

@@ -486,3 +486,38 @@ def test_sample_respects_top_k_and_top_p_sets(K):
             allowed &= set(kept[:n].tolist())
         assert set(out.tolist()) <= allowed
         assert len(set(out.tolist())) > 1
+
+
+# ---------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("M,N,K_", [(1, 331, 80), (8, 96, 48), (9, 2048, 2048), (33, 130, 264), (64, 17, 8),
+                                    (5, 64, 7168)])
+def test_gemm_skinny(K, M, N, K_):
+    """The few-rows bfloat16 kernel against the float product, and row by row against itself."""
+    torch.manual_seed(20)
+    dtype = torch.bfloat16
+    a, w = rnd(dtype, M, K_), rnd(dtype, N, K_)
+    want = a @ w.T
+    out = K.gemm_skinny(dev(a, dtype), dev(w, dtype), out_dtype=torch.float32)
+    close(out, want, torch.float32, scale=math.sqrt(K_))
+    close(K.gemm_skinny(dev(a, dtype), dev(w, dtype)), want, dtype, scale=math.sqrt(K_) / 4)
+    for m in (0, M - 1):       # a row alone gives the same bits as among the others
+        alone = K.gemm_skinny(dev(a[m:m + 1], dtype), dev(w, dtype), out_dtype=torch.float32)
+        assert torch.equal(alone, out[m:m + 1])
+
+
+def test_gemm_skinny_grouped_with_gather(K):
+    torch.manual_seed(21)
+    dtype = torch.bfloat16
+    E, N, K_, M, k = 5, 50, 40, 40, 2
+    x, w = rnd(dtype, M, K_), rnd(dtype, E, N, K_)
+    counts = [7, 0, 38, 1, 34]                        # more rows than one pass holds, none, one
+    offsets = [0]
+    for c in counts:
+        offsets.append(offsets[-1] + c)
+    pairs = torch.randperm(M * k).tolist()
+    for hint in (8, 16, 64):
+        out = K.gemm_skinny(dev(x, dtype), dev(w, dtype), a_rows=i32(pairs), a_div=k, offsets=i32(offsets),
+                            rows_out=M * k, rows_hint=hint, out_dtype=torch.float32)
+        for e in range(E):
+            for r in range(offsets[e], offsets[e + 1]):
+                close(out[r], x[pairs[r] // k] @ w[e].T, torch.float32, scale=8)
