@@ -164,23 +164,23 @@ def fill_cache_random(cache, rc, tokens: int, gen) -> None:
 
 
 def decode_run(model, batch: int, context: int, steps: int, warmup: int, page_size: int, seed: int = 0,
-               count_experts: bool = False):
+               count_experts: bool = False, graphs: bool = True):
     """Device-timed decode: returns (ms per step, launches in the timed region, bytes read per step)."""
     import torch
 
     from snowllm_b200.cache import CacheManager
     from snowllm_b200.engine import ModelRunner, StepEntry
     from snowllm_b200.ops import kernels
-    total = context + steps + warmup + 2
+    total = context + steps + warmup + 3
     pages = batch * (-(-total // page_size))
     cache = CacheManager(model.cache_specs(), page_size, pages, batch, model.dtype, "cuda")
-    runner = ModelRunner(model, cache, "cuda")
+    runner = ModelRunner(model, cache, "cuda", use_graphs=graphs)
     gen = torch.Generator(device="cuda").manual_seed(seed)
     live = [cache.admit() for _ in range(batch)]
     for rc in live:
         fill_cache_random(cache, rc, context, gen)
     V = model.vocab_size
-    ids = torch.randint(0, V, (steps + warmup + 1, batch), generator=torch.Generator().manual_seed(seed)).tolist()
+    ids = torch.randint(0, V, (steps + warmup + 2, batch), generator=torch.Generator().manual_seed(seed)).tolist()
 
     def one(i):
         for rc in live:
@@ -208,7 +208,13 @@ def decode_run(model, batch: int, context: int, steps: int, warmup: int, page_si
     torch.cuda.synchronize()
     ms = start.elapsed_time(end) / steps
     nbytes = weight_bytes(model, touched) + cache_bytes(cache, live)
+    # a replayed graph launches what its capture launched: count one step's launches and scale
     launches = kernels.launch_count() - launches0
+    if runner.graph_replays:
+        runner.use_graphs = False
+        l0 = kernels.launch_count()
+        one(steps + warmup + 1)
+        launches = (kernels.launch_count() - l0) * steps
     for rc in live:
         cache.free(rc)
     del cache, runner
@@ -287,6 +293,7 @@ def main() -> int:
     ap.add_argument("--layers", type=int, default=24, help="run the first N layers only (memory or time)")
     ap.add_argument("--dtype", default="bfloat16", choices=("bfloat16", "float32"))
     ap.add_argument("--page-size", type=int, default=None)
+    ap.add_argument("--enforce-eager", action="store_true", help="no CUDA graphs for the decode steps")
     ap.add_argument("--skip", default="", help="comma list of: e2e, prefill, points")
     a = ap.parse_args()
     if a.impl == "reference":
@@ -316,7 +323,8 @@ def main() -> int:
 
     sampler = ClockSampler()
     sampler.start()
-    ms, launches, nbytes, touched = decode_run(model, a.batch, a.context, a.steps, warmup, page, count_experts=True)
+    ms, launches, nbytes, touched = decode_run(model, a.batch, a.context, a.steps, warmup, page, count_experts=True,
+                                                graphs=not a.enforce_eager)
     clocks = sampler.stop()
     value = a.batch / (ms / 1e3)
     achieved = nbytes / (ms / 1e3) / 1e9
@@ -332,7 +340,8 @@ def main() -> int:
                    "heads": 32, "kv_heads": 8, "head_dim": 64, "conv_L": 3, "dense_layers": 2,
                    "dense_inter": 7168, "experts": 32, "top_k": 4, "moe_inter": 1792, "vocab": 65536,
                    "global_batch": a.batch, "seq_len": a.context, "page_size": page, "parallelism": "single GPU",
-                   "l2": "inputs larger than L2 (%.1f GB read per step)" % (nbytes / 1e9)},
+                   "l2": "inputs larger than L2 (%.1f GB read per step)" % (nbytes / 1e9),
+                   "cuda_graphs": not a.enforce_eager},
         "clocks": clocks,
         "gpu_launches": launches,
         "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
@@ -350,7 +359,7 @@ def main() -> int:
         points = {}
         for b in (1, 64):
             n = max(8, a.steps // 4)
-            pms, _, pb, _ = decode_run(model, b, a.context, n, 3, page)
+            pms, _, pb, _ = decode_run(model, b, a.context, n, 3, page, graphs=not a.enforce_eager)
             points[f"decode_b{b}"] = round(b / (pms / 1e3), 2)
             points[f"decode_b{b}_ms"] = round(pms, 4)
         points["decode_b%d" % a.batch] = round(value, 2)

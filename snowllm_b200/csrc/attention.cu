@@ -7,7 +7,9 @@
 //   (snowllm/models/lfm2/layers.py:36-70; tests/test_lfm2_long_attention.py:36-47)
 //
 // Work split: one block per (query row, kv head, key chunk); its warps are the q heads of
-// that kv head, which share each tile of keys and values through shared memory.  Key
+// that kv head, which share each tile of keys and values through shared memory.  Tiles of 32
+// keys come in by 16-byte cp.async copies, three tiles in flight per block, straight from the
+// pages in the cache dtype; keys outside the row's range are zero-filled, never read.  Key
 // chunks are aligned to absolute positions, so what a row computes depends on its own
 // position and on the chunk length only, never on the rest of the batch.  With more than
 // one chunk the blocks write partial (o, max, sum) to scratch and a second kernel merges
@@ -19,6 +21,37 @@
 #define ATT_TILE 32            // keys per tile: one per lane
 #define ATT_MAX_WARPS 8        // q heads handled by one block
 #define ATT_MAX_DPL 16         // head_dim <= 512
+#define ATT_STAGES 3           // tiles in flight per block (cp.async ring)
+
+// 16-byte vectors of the cache dtype, unpacked to float.
+template <typename T> struct Vec16;
+template <> struct Vec16<float> {
+  static constexpr int N = 4;
+  static __device__ __forceinline__ void unpack(const uint4& v, float (&f)[4]) {
+    f[0] = __uint_as_float(v.x); f[1] = __uint_as_float(v.y);
+    f[2] = __uint_as_float(v.z); f[3] = __uint_as_float(v.w);
+  }
+};
+template <> struct Vec16<bf16> {
+  static constexpr int N = 8;
+  static __device__ __forceinline__ void unpack(const uint4& v, float (&f)[8]) {
+    // a bfloat16 is the upper half of a float
+    f[0] = __uint_as_float(v.x << 16); f[1] = __uint_as_float(v.x & 0xffff0000u);
+    f[2] = __uint_as_float(v.y << 16); f[3] = __uint_as_float(v.y & 0xffff0000u);
+    f[4] = __uint_as_float(v.z << 16); f[5] = __uint_as_float(v.z & 0xffff0000u);
+    f[6] = __uint_as_float(v.w << 16); f[7] = __uint_as_float(v.w & 0xffff0000u);
+  }
+};
+
+__device__ __forceinline__ void cp_async16(void* smem, const void* gmem, bool valid) {
+  const unsigned dst = (unsigned)__cvta_generic_to_shared(smem);
+  const int bytes = valid ? 16 : 0;                // 0: the 16 bytes are filled with zeros
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(gmem), "r"(bytes));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;"); }
+template <int N> __device__ __forceinline__ void cp_async_wait() {
+  asm volatile("cp.async.wait_group %0;" ::"n"(N));
+}
 
 template <typename T>
 __global__ void paged_attention_kernel(
@@ -26,7 +59,8 @@ __global__ void paged_attention_kernel(
     int max_pages, int page_size, const int* __restrict__ positions, const int* __restrict__ row_seg,
     T* __restrict__ out, float* __restrict__ part_o, float* __restrict__ part_ml, int nh, int nkv,
     int hd, int window, int chunk, int num_chunks, float scale) {
-  extern __shared__ float sh[];
+  extern __shared__ __align__(16) unsigned char sh_raw[];
+  constexpr int VEC = Vec16<T>::N;
   const int group = nh / nkv;
   const int heads_per_block = blockDim.x >> 5;
   const int blocks_per_kv = (group + heads_per_block - 1) / heads_per_block;
@@ -45,10 +79,13 @@ __global__ void paged_attention_kernel(
   const int k_begin = max(lo, c * chunk);
   const int k_end = min(pos + 1, (c + 1) * chunk);         // exclusive
 
-  const int kstride = hd + 1;
-  float* ks = sh;                                          // [ATT_TILE][hd + 1]
-  float* vs = ks + ATT_TILE * kstride;                     // [ATT_TILE][hd]
-  float* qs = vs + ATT_TILE * hd;                          // [warps][hd]
+  // shared memory: [stages][k | v][ATT_TILE rows of hd*sizeof(T) + 16 bytes], then q as float
+  const int row_bytes = hd * (int)sizeof(T);
+  const int rstride = row_bytes + 16;                      // the pad keeps 16-byte row reads off one bank
+  const int vecs_per_row = row_bytes / 16;
+  const int tile_bytes = ATT_TILE * rstride;
+  unsigned char* kv_smem = sh_raw;
+  float* qs = reinterpret_cast<float*>(sh_raw + (size_t)ATT_STAGES * 2 * tile_bytes);
 
   if (active) {
     const T* qrow = q + ((size_t)m * nh + head) * hd;
@@ -58,38 +95,64 @@ __global__ void paged_attention_kernel(
   const size_t page_stride = (size_t)2 * nkv * page_size * hd;
   const size_t v_off = (size_t)nkv * page_size * hd;
 
+  // Tiles start at multiples of ATT_TILE counted from the chunk's absolute start.
+  const int t_first = c * chunk + ((k_begin - c * chunk) / ATT_TILE) * ATT_TILE;
+  const int ntiles = (k_end - t_first + ATT_TILE - 1) / ATT_TILE;
+
+  auto issue = [&](int tile) {
+    if (tile < ntiles) {
+      const int t0 = t_first + tile * ATT_TILE;
+      unsigned char* ks = kv_smem + (size_t)(tile % ATT_STAGES) * 2 * tile_bytes;
+      unsigned char* vs = ks + tile_bytes;
+      for (int v = threadIdx.x; v < ATT_TILE * vecs_per_row; v += blockDim.x) {
+        const int j = v / vecs_per_row, cv = v - j * vecs_per_row;
+        const int kp = t0 + j;
+        const bool valid = kp >= k_begin && kp < k_end;
+        const T* src = pool;
+        if (valid) {
+          const int page = bt[kp / page_size];
+          src = pool + (size_t)page * page_stride + ((size_t)kvh * page_size + kp % page_size) * hd + cv * VEC;
+        }
+        cp_async16(ks + j * rstride + cv * 16, src, valid);
+        cp_async16(vs + j * rstride + cv * 16, valid ? src + v_off : src, valid);
+      }
+    }
+    cp_async_commit();
+  };
+
   float mx = -INFINITY, l = 0.f;
   float o[ATT_MAX_DPL];
 #pragma unroll
   for (int i = 0; i < ATT_MAX_DPL; ++i) o[i] = 0.f;
   const int dpl = (hd + 31) / 32;
 
-  // Tiles start at multiples of ATT_TILE counted from the chunk's absolute start.
-  const int t_first = c * chunk + ((k_begin - c * chunk) / ATT_TILE) * ATT_TILE;
-  for (int t0 = t_first; t0 < k_end; t0 += ATT_TILE) {
-    __syncthreads();
-    for (int idx = threadIdx.x; idx < ATT_TILE * hd; idx += blockDim.x) {
-      const int j = idx / hd, d = idx - j * hd;
-      const int kp = t0 + j;
-      float kv = 0.f, vv = 0.f;
-      if (kp >= k_begin && kp < k_end) {
-        const int page = bt[kp / page_size];
-        const size_t base = (size_t)page * page_stride +
-                            ((size_t)kvh * page_size + kp % page_size) * hd + d;
-        kv = to_f<T>(pool[base]);
-        vv = to_f<T>(pool[base + v_off]);
-      }
-      ks[j * kstride + d] = kv;
-      vs[j * hd + d] = vv;
-    }
-    __syncthreads();
+#pragma unroll
+  for (int s = 0; s < ATT_STAGES - 1; ++s) issue(s);
+  for (int tile = 0; tile < ntiles; ++tile) {
+    cp_async_wait<ATT_STAGES - 2>();
+    __syncthreads();                                       // tile is in; everyone is done with tile - 1
+    issue(tile + ATT_STAGES - 1);
     if (!active) continue;
+    const int t0 = t_first + tile * ATT_TILE;
+    const unsigned char* ks = kv_smem + (size_t)(tile % ATT_STAGES) * 2 * tile_bytes;
+    const unsigned char* vs = ks + tile_bytes;
     const int kp = t0 + lane;
     const bool valid = kp >= k_begin && kp < k_end;
     float s = 0.f;
     const float* qw = qs + warp * hd;
-    const float* kr = ks + lane * kstride;
-    for (int d = 0; d < hd; ++d) s = fmaf(qw[d], kr[d], s);
+    const unsigned char* kr = ks + lane * rstride;
+    for (int cv = 0; cv < vecs_per_row; ++cv) {
+      float f[VEC];
+      Vec16<T>::unpack(*reinterpret_cast<const uint4*>(kr + cv * 16), f);
+#pragma unroll
+      for (int e = 0; e < VEC; e += 4) {
+        const float4 q4 = *reinterpret_cast<const float4*>(qw + cv * VEC + e);
+        s = fmaf(q4.x, f[e], s);
+        s = fmaf(q4.y, f[e + 1], s);
+        s = fmaf(q4.z, f[e + 2], s);
+        s = fmaf(q4.w, f[e + 3], s);
+      }
+    }
     s = valid ? s : -INFINITY;
     const float tmax = warp_max(s);
     const float m_new = fmaxf(mx, tmax);                   // finite: each tile run has a valid key
@@ -100,16 +163,19 @@ __global__ void paged_attention_kernel(
 #pragma unroll
     for (int i = 0; i < ATT_MAX_DPL; ++i)
       if (i < dpl) o[i] *= corr;
+    const T* vrow = reinterpret_cast<const T*>(vs);
+    const int vstride = rstride / (int)sizeof(T);
     for (int j = 0; j < ATT_TILE; ++j) {
       const float pj = __shfl_sync(0xffffffffu, p, j);
 #pragma unroll
       for (int i = 0; i < ATT_MAX_DPL; ++i)
         if (i < dpl) {
           const int d = lane + 32 * i;
-          if (d < hd) o[i] = fmaf(pj, vs[j * hd + d], o[i]);
+          if (d < hd) o[i] = fmaf(pj, to_f<T>(vrow[j * vstride + d]), o[i]);
         }
     }
   }
+  cp_async_wait<0>();
   if (!active) return;
   if (num_chunks == 1) {
     const float inv = 1.f / l;
@@ -179,7 +245,10 @@ SNK_API int snk_paged_attention(const void* q, const void* pool, const int* bloc
   const int blocks_per_kv = (group + warps - 1) / warps;
   if ((long long)nkv * blocks_per_kv > 65535) return SNK_ERR_SIZE;
   dim3 grid(M, nkv * blocks_per_kv, num_chunks);
-  const size_t smem = ((size_t)ATT_TILE * (2 * hd + 1) + (size_t)warps * hd) * sizeof(float);
+  const size_t esz = dtype == SNK_F32 ? 4 : 2;
+  if ((hd * esz) % 16 || ((uintptr_t)pool % 16)) return SNK_ERR_ALIGN;
+  const size_t smem = (size_t)ATT_STAGES * 2 * ATT_TILE * (hd * esz + 16) + (size_t)warps * hd * sizeof(float);
+  if (smem > 227 * 1024) return SNK_ERR_SIZE;
   float* part_o = static_cast<float*>(scratch);
   float* part_ml = part_o ? part_o + (size_t)M * nh * num_chunks * hd : nullptr;
   SNK_DISPATCH(dtype, {

@@ -91,7 +91,10 @@ SNK_API int snk_moe_route(const void* x, const void* wr, int wr_is_f32, const fl
   SNK_DISPATCH(dtype, {
     if (smem > 48 * 1024)
       cudaFuncSetAttribute(moe_route_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    moe_route_kernel<T><<<M, ROUTE_THREADS, smem, stream>>>(static_cast<const T*>(x), w, bias, topk_ids,
+    // one warp per expert where it fits: the few rows of a decode step would otherwise leave most
+    // of the GPU idle.  A dot product's order does not depend on the number of warps.
+    const int threads = E >= 32 ? 1024 : (E >= 16 ? 512 : (E >= 8 ? 256 : ROUTE_THREADS));
+    moe_route_kernel<T><<<M, threads, smem, stream>>>(static_cast<const T*>(x), w, bias, topk_ids,
                                                             topk_w, H, E, k, norm_topk, scaling);
   });
   SNK_LAUNCH_CHECK();

@@ -14,7 +14,7 @@
 #include "common.cuh"
 
 #define CONV_MAX_L 16
-#define CONV_ROWS_PER_BLOCK 8
+#define CONV_ROWS_PER_BLOCK 1
 
 template <typename T>
 __device__ __forceinline__ float gated(const T* __restrict__ bcx, size_t row, int H, int c) {

@@ -37,6 +37,7 @@ class StepContext:
     host_seg_start: list = field(default_factory=list)
     host_seg_len: list = field(default_factory=list)
     _plans: dict = field(default_factory=dict)
+    fixed_chunks: int | None = None  # a captured step: the key-chunk count its launches were built for
     taps: list | None = None       # when a list: parts append (name, tensor) of chosen intermediates
 
     def tap(self, name: str, tensor) -> None:
@@ -51,6 +52,10 @@ class StepContext:
         """(chunk, num_chunks) for the attention kernel: with many rows one chunk per row, else
         chunks of ATTENTION_CHUNK keys so that long sequences spread over the GPU."""
         plan = self._plans.get(window)
+        if plan is None and self.fixed_chunks is not None:
+            whole = (1 << 30) - ((1 << 30) % ATTENTION_TILE)
+            plan = (ATTENTION_CHUNK, self.fixed_chunks) if self.fixed_chunks > 1 else (whole, 1)
+            self._plans[window] = plan
         if plan is None:
             whole = (1 << 30) - ((1 << 30) % ATTENTION_TILE)
             pos = self.host_positions
@@ -75,7 +80,8 @@ class HostStaging:
         self.turn = 0
         self.bytes_uploaded = 0
 
-    def upload(self, host: np.ndarray) -> torch.Tensor:
+    def upload(self, host: np.ndarray, into: torch.Tensor | None = None) -> torch.Tensor:
+        """Copy ``host`` to the device through a pinned buffer: into a new tensor, or into ``into``."""
         i = self.turn
         self.turn = (self.turn + 1) % self.depth
         n = host.size
@@ -86,7 +92,11 @@ class HostStaging:
             buf = torch.empty(max(n, 1024) * 2, dtype=torch.int32).pin_memory()
             self.buffers[i] = buf
         buf[:n].numpy()[:] = host
-        dev = buf[:n].to(self.device, non_blocking=True)
+        if into is not None:
+            into[:n].copy_(buf[:n], non_blocking=True)
+            dev = into
+        else:
+            dev = buf[:n].to(self.device, non_blocking=True)
         self.bytes_uploaded += n * 4
         ev = torch.cuda.Event()
         ev.record()

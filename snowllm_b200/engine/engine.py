@@ -89,7 +89,7 @@ class Engine:
                 f"the memory budget leaves {max(budget, 0) >> 20} MiB (gpu_memory_utilization="
                 f"{gpu_memory_utilization}); lower max_model_len or num_kv_blocks")
         self.cache = CacheManager(specs, page_size, num_kv_blocks, max_num_seqs, model.dtype, self.device)
-        self.runner = ModelRunner(model, self.cache, self.device)
+        self.runner = ModelRunner(model, self.cache, self.device, use_graphs=not enforce_eager)
         self.scheduler = Scheduler(self.cache, max_num_seqs, int(prefill_chunk), max_model_len, preempt)
         self.sampler = Sampler(stop_token_ids, seed, self.device)
         self.acct = StepAccounting()

