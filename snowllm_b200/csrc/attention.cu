@@ -53,7 +53,9 @@ template <int N> __device__ __forceinline__ void cp_async_wait() {
   asm volatile("cp.async.wait_group %0;" ::"n"(N));
 }
 
-template <typename T>
+// DPL: output elements per lane, head_dim <= 32 * DPL (a compile-time bound keeps the inner loops
+// free of dead iterations).
+template <typename T, int DPL>
 __global__ void paged_attention_kernel(
     const T* __restrict__ q, const T* __restrict__ pool, const int* __restrict__ block_table,
     int max_pages, int page_size, const int* __restrict__ positions, const int* __restrict__ row_seg,
@@ -121,10 +123,9 @@ __global__ void paged_attention_kernel(
   };
 
   float mx = -INFINITY, l = 0.f;
-  float o[ATT_MAX_DPL];
+  float o[DPL];
 #pragma unroll
-  for (int i = 0; i < ATT_MAX_DPL; ++i) o[i] = 0.f;
-  const int dpl = (hd + 31) / 32;
+  for (int i = 0; i < DPL; ++i) o[i] = 0.f;
 
 #pragma unroll
   for (int s = 0; s < ATT_STAGES - 1; ++s) issue(s);
@@ -161,18 +162,16 @@ __global__ void paged_attention_kernel(
     l = l * corr + warp_sum(p);
     mx = m_new;
 #pragma unroll
-    for (int i = 0; i < ATT_MAX_DPL; ++i)
-      if (i < dpl) o[i] *= corr;
+    for (int i = 0; i < DPL; ++i) o[i] *= corr;
     const T* vrow = reinterpret_cast<const T*>(vs);
     const int vstride = rstride / (int)sizeof(T);
     for (int j = 0; j < ATT_TILE; ++j) {
       const float pj = __shfl_sync(0xffffffffu, p, j);
 #pragma unroll
-      for (int i = 0; i < ATT_MAX_DPL; ++i)
-        if (i < dpl) {
-          const int d = lane + 32 * i;
-          if (d < hd) o[i] = fmaf(pj, to_f<T>(vrow[j * vstride + d]), o[i]);
-        }
+      for (int i = 0; i < DPL; ++i) {
+        const int d = lane + 32 * i;
+        if (d < hd) o[i] = fmaf(pj, to_f<T>(vrow[j * vstride + d]), o[i]);
+      }
     }
   }
   cp_async_wait<0>();
@@ -181,20 +180,18 @@ __global__ void paged_attention_kernel(
     const float inv = 1.f / l;
     T* orow = out + ((size_t)m * nh + head) * hd;
 #pragma unroll
-    for (int i = 0; i < ATT_MAX_DPL; ++i)
-      if (i < dpl) {
-        const int d = lane + 32 * i;
-        if (d < hd) orow[d] = from_f<T>(o[i] * inv);
-      }
+    for (int i = 0; i < DPL; ++i) {
+      const int d = lane + 32 * i;
+      if (d < hd) orow[d] = from_f<T>(o[i] * inv);
+    }
   } else {
     const size_t slot = ((size_t)m * nh + head) * num_chunks + blockIdx.z;
     float* po = part_o + slot * hd;
 #pragma unroll
-    for (int i = 0; i < ATT_MAX_DPL; ++i)
-      if (i < dpl) {
-        const int d = lane + 32 * i;
-        if (d < hd) po[d] = o[i];
-      }
+    for (int i = 0; i < DPL; ++i) {
+      const int d = lane + 32 * i;
+      if (d < hd) po[d] = o[i];
+    }
     if (lane == 0) {
       part_ml[slot * 2] = mx;
       part_ml[slot * 2 + 1] = l;
@@ -251,15 +248,24 @@ SNK_API int snk_paged_attention(const void* q, const void* pool, const int* bloc
   if (smem > 227 * 1024) return SNK_ERR_SIZE;
   float* part_o = static_cast<float*>(scratch);
   float* part_ml = part_o ? part_o + (size_t)M * nh * num_chunks * hd : nullptr;
+#define ATT_LAUNCH(DPL_)                                                                             \
+  do {                                                                                               \
+    if (smem > 48 * 1024)                                                                            \
+      cudaFuncSetAttribute(paged_attention_kernel<T, DPL_>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
+                           (int)smem);                                                               \
+    paged_attention_kernel<T, DPL_><<<grid, warps * 32, smem, stream>>>(                             \
+        static_cast<const T*>(q), static_cast<const T*>(pool), block_table, max_pages, page_size,    \
+        positions, row_seg, static_cast<T*>(out), part_o, part_ml, nh, nkv, hd, window, chunk,       \
+        num_chunks, scale);                                                                          \
+  } while (0)
   SNK_DISPATCH(dtype, {
-    if (smem > 48 * 1024)
-      cudaFuncSetAttribute(paged_attention_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                           (int)smem);
-    paged_attention_kernel<T><<<grid, warps * 32, smem, stream>>>(
-        static_cast<const T*>(q), static_cast<const T*>(pool), block_table, max_pages, page_size,
-        positions, row_seg, static_cast<T*>(out), part_o, part_ml, nh, nkv, hd, window, chunk,
-        num_chunks, scale);
+    if (hd <= 32) ATT_LAUNCH(1);
+    else if (hd <= 64) ATT_LAUNCH(2);
+    else if (hd <= 128) ATT_LAUNCH(4);
+    else if (hd <= 256) ATT_LAUNCH(8);
+    else ATT_LAUNCH(16);
   });
+#undef ATT_LAUNCH
   SNK_LAUNCH_CHECK();
   if (num_chunks > 1) {
     dim3 mgrid(M, nh);

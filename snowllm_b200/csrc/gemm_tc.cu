@@ -1,0 +1,381 @@
+// C[M,N] = A[M,K] . W[N,K]^T in bfloat16 on the 5th-generation tensor cores (tcgen05), for many rows
+// (prefill).  One block computes one 128 x 128 tile of C:
+//
+//   warp 0, one lane   TMA producer: 128x64 tiles of A and of W into a ring of shared-memory stages
+//                      (cp.async.bulk.tensor, 128-byte swizzle, completion counted on an mbarrier)
+//   warp 1, one lane   MMA issuer: per stage four tcgen05.mma (M 128, N 128, K 16) straight from shared
+//                      memory into a float accumulator in tensor memory; tcgen05.commit hands the stage
+//                      back to the producer and, after the last k-block, the accumulator to the epilogue
+//   warps 2..5         epilogue: tcgen05.ld of the accumulator (each warp its 32 lanes = 32 rows of C),
+//                      conversion, guarded stores
+//
+// Both operands are K-major, which is how activations and checkpoint weights already lie in memory,
+// so nothing is re-tiled at load.  Rows past M (or past a group's end) and k past K are zero-filled
+// by TMA and masked at the store.
+//
+// Grouped form (routed experts): rows of A are already sorted by group and contiguous; group e owns
+// rows [offsets[e], offsets[e+1]) and multiplies them with W[e].  Row tiles are counted per group, so
+// a tile never mixes groups in its stored rows.
+//
+// Every wait on an mbarrier is bounded by wall time: when it runs out the block records an error
+// code (see snk_gemm_tc_status), lets its remaining steps run through without waiting, frees its
+// tensor memory and returns.
+// (the role of snowllm/ops/gemm.py:33-41 and the expert products of snowllm/ops/inference.py:60-76
+// at prefill shapes)
+#include <cuda.h>
+
+#include <mutex>
+#include <unordered_map>
+
+#include "common.cuh"
+
+#define TC_BM 128
+#define TC_BN 128
+#define TC_BK 64
+#define TC_STAGES 5
+#define TC_THREADS 192
+#define TC_WAIT_NS 1500000000ull      // 1.5 s per wait before giving up
+
+enum { TC_ERR_WAIT_FULL = 1, TC_ERR_WAIT_EMPTY = 2, TC_ERR_WAIT_ACC = 3 };
+
+__device__ int g_tc_status;            // 0, or the first error code a block recorded
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ uint64_t global_ns() {
+  uint64_t t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}"
+      : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+  return ok != 0;
+}
+// Wait for a phase, for TC_WAIT_NS at most.  `aborted` (shared) short-cuts every later wait of the block.
+__device__ __forceinline__ void mbar_wait(uint64_t* bar, uint32_t parity, volatile int* aborted, int code) {
+  if (*aborted) return;
+  if (mbar_try_wait(bar, parity)) return;
+  const uint64_t start = global_ns();
+  while (!mbar_try_wait(bar, parity)) {
+    if (*aborted) return;
+    if (global_ns() - start > TC_WAIT_NS) {
+      *aborted = 1;
+      atomicCAS(&g_tc_status, 0, code);
+      return;
+    }
+  }
+}
+
+__device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* map, uint64_t* bar, int x, int y) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar)), "r"(x), "r"(y)
+      : "memory");
+}
+
+// Shared-memory matrix descriptor of a K-major tile whose rows are 128 bytes, written by TMA with the
+// 128-byte swizzle: 8-row groups lie 1024 bytes apart (stride byte offset); the leading byte offset is
+// not used by swizzled K-major layouts; descriptor version 1; layout type 2 = 128-byte swizzle.
+__device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t smem_addr) {
+  uint64_t d = 0;
+  d |= (uint64_t)((smem_addr & 0x3ffff) >> 4);          // start address, bits [0, 14)
+  d |= (uint64_t)1 << 16;                               // leading byte offset (unused), bits [16, 30)
+  d |= (uint64_t)(1024 >> 4) << 32;                     // stride byte offset, bits [32, 46)
+  d |= (uint64_t)1 << 46;                               // version, bits [46, 48)
+  d |= (uint64_t)2 << 61;                               // layout type, bits [61, 64)
+  return d;
+}
+
+// Instruction descriptor of kind::f16: D float, A and B bfloat16, both K-major, M 128, N TC_BN.
+__device__ __forceinline__ uint32_t instr_desc_bf16() {
+  return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(TC_BN >> 3) << 17) | ((uint32_t)(TC_BM >> 4) << 24);
+}
+
+__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                          uint32_t accumulate) {
+  asm volatile(
+      "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n"
+      " tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}"
+      ::"r"(tmem_d), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
+               : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+        "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+        "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr));
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+struct __align__(8) TcShared {
+  uint64_t full[TC_STAGES];
+  uint64_t empty[TC_STAGES];
+  uint64_t acc_ready;
+  uint32_t tmem_base;
+  int aborted;
+};
+
+template <typename OutT>
+__global__ void __launch_bounds__(TC_THREADS)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
+               OutT* __restrict__ C, int M, int N, int K, const int* __restrict__ offsets, int groups) {
+  extern __shared__ unsigned char smem_raw[];
+  // tiles need 1024-byte alignment for the 128-byte swizzle
+  unsigned char* tiles = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  unsigned char* tiles_a = tiles;
+  unsigned char* tiles_w = tiles + (size_t)TC_STAGES * TC_BM * TC_BK * 2;
+  TcShared* sh = reinterpret_cast<TcShared*>(tiles_w + (size_t)TC_STAGES * TC_BN * TC_BK * 2);
+
+  // which rows this block owns
+  int row0, row_end, w_row0;
+  if (offsets) {
+    int tile = blockIdx.y, e = 0;
+    row0 = -1;
+    for (; e < groups; ++e) {
+      const int cnt = offsets[e + 1] - offsets[e];
+      const int tiles_e = (cnt + TC_BM - 1) / TC_BM;
+      if (tile < tiles_e) { row0 = offsets[e] + tile * TC_BM; break; }
+      tile -= tiles_e;
+    }
+    if (row0 < 0) return;                                // past the last tile of the last group
+    row_end = offsets[e + 1];
+    w_row0 = e * N;
+  } else {
+    row0 = blockIdx.y * TC_BM;
+    row_end = M;
+    w_row0 = 0;
+  }
+  const int n0 = blockIdx.x * TC_BN;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int k_tiles = (K + TC_BK - 1) / TC_BK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < TC_STAGES; ++s) {
+      mbar_init(&sh->full[s], 1);
+      mbar_init(&sh->empty[s], 1);
+    }
+    mbar_init(&sh->acc_ready, 1);
+    sh->aborted = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  if (warp == 1) {                                       // one warp allocates the accumulator columns
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+                 ::"r"(smem_u32(&sh->tmem_base)), "r"((uint32_t)TC_BN) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_acc = sh->tmem_base;
+  volatile int* aborted = &sh->aborted;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      for (int kt = 0; kt < k_tiles; ++kt) {
+        const int s = kt % TC_STAGES;
+        mbar_wait(&sh->empty[s], ((kt / TC_STAGES) & 1) ^ 1, aborted, TC_ERR_WAIT_EMPTY);
+        mbar_expect_tx(&sh->full[s], (TC_BM + TC_BN) * TC_BK * 2);
+        tma_load_2d(tiles_a + (size_t)s * TC_BM * TC_BK * 2, &map_a, &sh->full[s], kt * TC_BK, row0);
+        tma_load_2d(tiles_w + (size_t)s * TC_BN * TC_BK * 2, &map_w, &sh->full[s], kt * TC_BK, w_row0 + n0);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      const uint32_t idesc = instr_desc_bf16();
+      for (int kt = 0; kt < k_tiles; ++kt) {
+        const int s = kt % TC_STAGES;
+        mbar_wait(&sh->full[s], (kt / TC_STAGES) & 1, aborted, TC_ERR_WAIT_FULL);
+        tc_fence_after();
+        const uint32_t a_addr = smem_u32(tiles_a + (size_t)s * TC_BM * TC_BK * 2);
+        const uint32_t w_addr = smem_u32(tiles_w + (size_t)s * TC_BN * TC_BK * 2);
+#pragma unroll
+        for (int k = 0; k < TC_BK / 16; ++k) {
+          // 16 k-values = 32 bytes further along the swizzled 128-byte rows
+          umma_bf16(tmem_acc, smem_desc_sw128(a_addr + k * 32), smem_desc_sw128(w_addr + k * 32), idesc,
+                    (kt > 0 || k > 0) ? 1u : 0u);
+        }
+        umma_commit(&sh->empty[s]);                      // the stage is free once these MMAs have read it
+      }
+      umma_commit(&sh->acc_ready);
+    }
+  } else {
+    mbar_wait(&sh->acc_ready, 0, aborted, TC_ERR_WAIT_ACC);
+    tc_fence_after();
+    const int lane_group = warp & 3;                     // a warp reads the 32 tensor-memory lanes 32*(warp%4)..
+    const int row = row0 + lane_group * 32 + lane;
+    const bool vec_ok = (N % 8) == 0;
+#pragma unroll 1
+    for (int c0 = 0; c0 < TC_BN; c0 += 32) {
+      uint32_t r[32];
+      tmem_ld32(tmem_acc + ((uint32_t)(lane_group * 32) << 16) + (uint32_t)c0, r);
+      if (row < row_end && !*aborted) {
+        OutT* dst = C + (size_t)row * N + n0 + c0;
+        if (vec_ok && n0 + c0 + 32 <= N) {
+          if constexpr (sizeof(OutT) == 4) {
+#pragma unroll
+            for (int i = 0; i < 32; i += 4)
+              *reinterpret_cast<uint4*>(dst + i) = make_uint4(r[i], r[i + 1], r[i + 2], r[i + 3]);
+          } else {
+#pragma unroll
+            for (int i = 0; i < 32; i += 8) {
+              uint32_t p[4];
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                const __nv_bfloat162 v = __floats2bfloat162_rn(__uint_as_float(r[i + 2 * j]),
+                                                               __uint_as_float(r[i + 2 * j + 1]));
+                p[j] = *reinterpret_cast<const uint32_t*>(&v);
+              }
+              *reinterpret_cast<uint4*>(dst + i) = make_uint4(p[0], p[1], p[2], p[3]);
+            }
+          }
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i)
+            if (n0 + c0 + i < N) dst[i] = from_f<OutT>(__uint_as_float(r[i]));
+        }
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_acc), "r"((uint32_t)TC_BN)
+                 : "memory");
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// Tensor maps: 2-D, bfloat16, inner dimension K, box 64 x 128, 128-byte swizzle.  Built through the
+// driver entry point (no link against the driver library) and cached by (pointer, rows, K).
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+  });
+  return fn;
+}
+
+struct MapKey {
+  const void* ptr;
+  long long rows, k;
+  bool operator==(const MapKey& o) const { return ptr == o.ptr && rows == o.rows && k == o.k; }
+};
+struct MapKeyHash {
+  size_t operator()(const MapKey& m) const {
+    return std::hash<const void*>()(m.ptr) ^ (std::hash<long long>()(m.rows) * 1315423911u) ^
+           (std::hash<long long>()(m.k) * 2654435761u);
+  }
+};
+
+static int tensor_map(const void* ptr, long long rows, long long k, CUtensorMap* out) {
+  static std::unordered_map<MapKey, CUtensorMap, MapKeyHash> cache;
+  static std::mutex mu;
+  std::lock_guard<std::mutex> lock(mu);
+  const MapKey key{ptr, rows, k};
+  auto it = cache.find(key);
+  if (it != cache.end()) { *out = it->second; return 0; }
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return SNK_ERR_SIZE + 100;
+  const cuuint64_t dims[2] = {(cuuint64_t)k, (cuuint64_t)rows};
+  const cuuint64_t strides[1] = {(cuuint64_t)k * 2};
+  const cuuint32_t box[2] = {TC_BK, TC_BM};
+  const cuuint32_t estr[2] = {1, 1};
+  CUtensorMap m;
+  const CUresult r = fn(&m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return 30000 + (int)r;
+  if (cache.size() > 8192) cache.clear();
+  cache.emplace(key, m);
+  *out = m;
+  return 0;
+}
+
+// M: rows of A (all groups together).  Grouped: offsets[groups+1] on the device, W = [groups, N, K];
+// max_row_tiles bounds the number of 128-row tiles over all groups (M/128 + groups is always enough).
+SNK_API int snk_gemm_tc(const void* A, const void* W, void* C, int M, int N, int K, const int* offsets,
+                        int groups, int max_row_tiles, int out_f32, cudaStream_t stream) {
+  if (M <= 0 || N <= 0) return 0;
+  if (K <= 0 || K % 8) return SNK_ERR_SIZE;                   // TMA: the row pitch is a multiple of 16 bytes
+  if (((uintptr_t)A % 16) || ((uintptr_t)W % 16) || ((uintptr_t)C % 16)) return SNK_ERR_ALIGN;
+  static_assert(TC_BM == TC_BN, "one box shape serves both operands");
+  CUtensorMap map_a, map_w;
+  int rc = tensor_map(A, M, K, &map_a);
+  if (rc) return rc;
+  rc = tensor_map(W, (long long)(offsets ? groups : 1) * N, K, &map_w);
+  if (rc) return rc;
+  const int row_tiles = offsets ? max_row_tiles : (M + TC_BM - 1) / TC_BM;
+  if (row_tiles <= 0 || row_tiles > 65535) return SNK_ERR_SIZE;
+  dim3 grid((N + TC_BN - 1) / TC_BN, row_tiles);
+  const size_t smem = 1024 + (size_t)TC_STAGES * (TC_BM + TC_BN) * TC_BK * 2 + sizeof(TcShared);
+  if (out_f32) {
+    cudaFuncSetAttribute(gemm_tc_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    gemm_tc_kernel<float><<<grid, TC_THREADS, smem, stream>>>(map_a, map_w, static_cast<float*>(C), M, N, K,
+                                                              offsets, groups);
+  } else {
+    cudaFuncSetAttribute(gemm_tc_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    gemm_tc_kernel<bf16><<<grid, TC_THREADS, smem, stream>>>(map_a, map_w, static_cast<bf16*>(C), M, N, K,
+                                                             offsets, groups);
+  }
+  SNK_LAUNCH_CHECK();
+  return 0;
+}
+
+// 0, or the first error a block of any earlier launch recorded (a wait that ran out); reading clears
+// it.  Synchronises the device.
+SNK_API int snk_gemm_tc_status() {
+  int v = 0, zero = 0;
+  if (cudaMemcpyFromSymbol(&v, g_tc_status, sizeof(int)) != cudaSuccess) return -1;
+  if (v) cudaMemcpyToSymbol(g_tc_status, &zero, sizeof(int));
+  return v;
+}
+
+// ---------------------------------------------------------------------------------------------
+// out[r, :] = in[rows[r] / div, :]  (bfloat16 rows of K elements, K a multiple of 8)
+__global__ void gather_rows_kernel(const uint4* __restrict__ in, uint4* __restrict__ out,
+                                   const int* __restrict__ rows, int div, int vecs) {
+  const uint4* src = in + (size_t)(rows[blockIdx.x] / div) * vecs;
+  uint4* dst = out + (size_t)blockIdx.x * vecs;
+  for (int i = threadIdx.x; i < vecs; i += blockDim.x) dst[i] = src[i];
+}
+
+SNK_API int snk_gather_rows_bf16(const void* in, void* out, const int* rows, int div, int R, int K,
+                                 cudaStream_t stream) {
+  if (R <= 0) return 0;
+  if (K % 8 || ((uintptr_t)in % 16) || ((uintptr_t)out % 16)) return SNK_ERR_ALIGN;
+  gather_rows_kernel<<<R, 128, 0, stream>>>(static_cast<const uint4*>(in), static_cast<uint4*>(out), rows,
+                                            div <= 0 ? 1 : div, K / 8);
+  SNK_LAUNCH_CHECK();
+  return 0;
+}

@@ -41,6 +41,11 @@ _SIGNATURES = {
     "gemm_skinny": {
         "snk_gemm_skinny": [P, P, P, I, I, I, P, I, P, I, I, I, P],
     },
+    "gemm_tc": {
+        "snk_gemm_tc": [P, P, P, I, I, I, P, I, I, I, P],
+        "snk_gemm_tc_status": [],
+        "snk_gather_rows_bf16": [P, P, P, I, I, I, P],
+    },
     "moe": {
         "snk_moe_route": [P, P, I, P, P, P, I, I, I, I, I, F, I, P],
         "snk_moe_sort": [P, P, P, P, I, I, P],
@@ -377,6 +382,61 @@ def gemm_skinny(a, w, out_dtype=None, out=None, a_rows=None, a_div=1, offsets=No
     check(fn("snk_gemm_skinny")(_ptr(a), _ptr(w), _ptr(out), M, N, K, _ptr(a_rows), int(a_div), _ptr(offsets),
                                 G, int(rows_hint if rows_hint is not None else M),
                                 int(out_dtype == torch.float32), _stream()), "gemm_skinny")
+    return out
+
+
+TC_TILE = 128
+
+
+def gemm_tc_ok(a, w) -> bool:
+    """Whether the tcgen05 kernel takes these operands (bfloat16, K a multiple of 8, 16-byte aligned)."""
+    return (a.dtype == torch.bfloat16 and a.shape[1] % 8 == 0 and a.data_ptr() % 16 == 0
+            and w.data_ptr() % 16 == 0)
+
+
+def gemm_tc(a, w, out_dtype=None, out=None, offsets=None):
+    """bfloat16 a [M, K] times w [N, K]^T on the tcgen05 tensor cores, float accumulation in tensor
+    memory.  Grouped: w [G, N, K], rows of ``a`` sorted by group, ``offsets`` int32 [G+1]."""
+    _chk(a, "gemm a", torch.bfloat16)
+    _chk(w, "gemm w", torch.bfloat16)
+    M, K = a.shape
+    grouped = offsets is not None
+    if grouped:
+        G, N, Kw = w.shape
+        _chk(offsets, "group offsets", torch.int32, (G + 1,))
+    else:
+        G = 1
+        N, Kw = w.shape
+    if Kw != K:
+        raise KernelError(f"gemm: a has K={K}, w has K={Kw}")
+    out_dtype = out_dtype or torch.bfloat16
+    if out is None:
+        out = torch.empty(M, N, dtype=out_dtype, device=a.device)
+    _chk(out, "gemm out", out_dtype, (M, N))
+    if out_dtype not in (torch.bfloat16, torch.float32):
+        raise KernelError("gemm output is bfloat16 or float32")
+    row_tiles = -(-M // TC_TILE) + (G if grouped else 0)
+    check(fn("snk_gemm_tc")(_ptr(a), _ptr(w), _ptr(out), M, N, K, _ptr(offsets), G, row_tiles,
+                            int(out_dtype == torch.float32), _stream()), "gemm_tc")
+    return out
+
+
+def gemm_tc_status() -> int:
+    """0, or the code of a wait that ran out inside a tcgen05 kernel since the last call
+    (synchronises the device; 1: operands never arrived, 2: a stage never came back, 3: the
+    accumulator never became ready)."""
+    return int(fn("snk_gemm_tc_status")())
+
+
+def gather_rows(x, rows, div=1, out=None):
+    """out[r] = x[rows[r] // div] for bfloat16 rows (the sorted copy the grouped tcgen05 product reads)."""
+    _chk(x, "gather input", torch.bfloat16)
+    _chk(rows, "gather rows", torch.int32)
+    R, K = rows.numel(), x.shape[1]
+    if out is None:
+        out = torch.empty(R, K, dtype=x.dtype, device=x.device)
+    _chk(out, "gather output", x.dtype, (R, K))
+    check(fn("snk_gather_rows_bf16")(_ptr(x), _ptr(out), _ptr(rows), int(div), R, K, _stream()), "gather_rows")
     return out
 
 

@@ -2,7 +2,9 @@
 
 float32: the CUDA-core kernel of csrc/gemm.cu (true 32-bit, sums in k order).
 bfloat16, up to 64 rows (decode): csrc/gemm_skinny.cu, which streams W once into mma.sync fragments.
-bfloat16, more rows: the CUDA-core kernel, until the tensor-core kernel for large tiles takes over.
+bfloat16, more rows (prefill): csrc/gemm_tc.cu, 128 x 128 tiles on the tcgen05 tensor cores with TMA
+loads and the accumulator in tensor memory.
+bfloat16 operands that neither takes (K no multiple of 8, unaligned views): the CUDA-core kernel.
 (the role of snowllm/models/projection.py:27-35)
 """
 from __future__ import annotations
@@ -11,25 +13,30 @@ import torch
 
 from . import kernels
 
-
 SKINNY_MAX_ROWS = 64       # up to here the product is bound by the read of W: the few-rows kernel
 
 
 def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype | None = None,
            out: torch.Tensor | None = None) -> torch.Tensor:
     """x [M, K] times w [N, K]^T -> [M, N] in ``out_dtype`` (the compute dtype or float32)."""
-    if x.shape[0] <= SKINNY_MAX_ROWS and kernels.gemm_skinny_ok(x, w):
-        return kernels.gemm_skinny(x, w, out_dtype=out_dtype, out=out)
+    if kernels.gemm_skinny_ok(x, w):
+        if x.shape[0] <= SKINNY_MAX_ROWS:
+            return kernels.gemm_skinny(x, w, out_dtype=out_dtype, out=out)
+        return kernels.gemm_tc(x, w, out_dtype=out_dtype, out=out)
     return kernels.gemm_simt(x, w, out_dtype=out_dtype, out=out)
 
 
 def grouped_linear(x, w, offsets, rows_out, max_rows_per_group, a_rows=None, a_div=1, out_dtype=None):
     """Rows sorted by group: row r in [offsets[g], offsets[g+1]) is x[a_rows[r] // a_div] (or x[r])
     times w[g] [N, K]^T.  ``max_rows_per_group`` bounds the rows one group can own."""
-    if max_rows_per_group <= SKINNY_MAX_ROWS and kernels.gemm_skinny_ok(x, w):
-        # a pass covers about twice the mean rows of a group; fuller groups take more passes
-        hint = min(max_rows_per_group, max(8, 2 * -(-rows_out // w.shape[0])))
-        return kernels.gemm_skinny(x, w, out_dtype=out_dtype, a_rows=a_rows, a_div=a_div, offsets=offsets,
-                                   rows_out=rows_out, rows_hint=hint)
+    if kernels.gemm_skinny_ok(x, w):
+        if max_rows_per_group <= SKINNY_MAX_ROWS:
+            # a pass covers about twice the mean rows of a group; fuller groups take more passes
+            hint = min(max_rows_per_group, max(8, 2 * -(-rows_out // w.shape[0])))
+            return kernels.gemm_skinny(x, w, out_dtype=out_dtype, a_rows=a_rows, a_div=a_div, offsets=offsets,
+                                       rows_out=rows_out, rows_hint=hint)
+        # TMA reads whole tiles of contiguous rows: bring the rows into sorted order first
+        xs = kernels.gather_rows(x, a_rows, a_div) if a_rows is not None else x
+        return kernels.gemm_tc(xs, w, out_dtype=out_dtype, offsets=offsets)
     return kernels.gemm_simt(x, w, out_dtype=out_dtype, a_rows=a_rows, a_div=a_div, offsets=offsets,
                              rows_out=rows_out, max_rows_per_group=max_rows_per_group)

@@ -521,3 +521,42 @@ def test_gemm_skinny_grouped_with_gather(K):
         for e in range(E):
             for r in range(offsets[e], offsets[e + 1]):
                 close(out[r], x[pairs[r] // k] @ w[e].T, torch.float32, scale=8)
+
+
+# ---------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("M,N,K_", [(128, 128, 64), (65, 17, 8), (200, 136, 72), (300, 100, 1000), (257, 384, 2048),
+                                    (1000, 96, 48)])
+def test_gemm_tc(K, M, N, K_):
+    """The tcgen05 kernel (TMA loads, accumulator in tensor memory) against the float product: tiles
+    cut by M, N and K, float and bfloat16 stores; no wait inside the kernel ran out."""
+    torch.manual_seed(30)
+    dtype = torch.bfloat16
+    a, w = rnd(dtype, M, K_), rnd(dtype, N, K_)
+    want = a @ w.T
+    out = K.gemm_tc(dev(a, dtype), dev(w, dtype), out_dtype=torch.float32)
+    close(out, want, torch.float32, scale=math.sqrt(K_))
+    close(K.gemm_tc(dev(a, dtype), dev(w, dtype)), want, dtype, scale=math.sqrt(K_) / 4)
+    assert K.gemm_tc_status() == 0
+    # a row's result does not depend on the rows around it
+    part = K.gemm_tc(dev(a[3:70], dtype), dev(w, dtype), out_dtype=torch.float32)
+    assert torch.equal(part, out[3:70])
+
+
+def test_gemm_tc_grouped_after_gather(K):
+    torch.manual_seed(31)
+    dtype = torch.bfloat16
+    E, N, K_, M, k = 5, 200, 192, 280, 2
+    x, w = rnd(dtype, M, K_), rnd(dtype, E, N, K_)
+    counts = [130, 0, 1, 300, 129]                    # more than one tile, none, one row, tile edge + 1
+    offsets = [0]
+    for c in counts:
+        offsets.append(offsets[-1] + c)
+    pairs = torch.randperm(M * k).tolist()
+    xs = K.gather_rows(dev(x, dtype), i32(pairs), k)
+    assert torch.equal(xs.float().cpu(), x[[p // k for p in pairs]])
+    out = K.gemm_tc(xs, dev(w, dtype), out_dtype=torch.float32, offsets=i32(offsets))
+    assert K.gemm_tc_status() == 0
+    for e in range(E):
+        r = slice(offsets[e], offsets[e + 1])
+        if counts[e]:
+            close(out[r], xs[r].float().cpu() @ w[e].T, torch.float32, scale=16)
