@@ -277,3 +277,55 @@ SNK_API int snk_paged_attention(const void* q, const void* pool, const int* bloc
   }
   return 0;
 }
+
+// ---------------------------------------------------------------------------------------------
+// The entry point that allocates nothing (see attention_static.h for who needs it and its rules).
+#include "attention_static.h"
+
+#include <mutex>
+
+// Scratch for the partial results of split rows.  In host code this name is only a handle for the
+// symbol, not an address the GPU understands: its device address is looked up below, per device.
+static __device__ __align__(256) unsigned char g_static_scratch[SNK_ATTENTION_STATIC_SCRATCH_BYTES];
+
+#define SNK_STATIC_MAX_DEVICES 64
+
+// Device address of g_static_scratch on the current device; looked up on the first call per device.
+static int static_scratch_address(void** out) {
+  static void* address[SNK_STATIC_MAX_DEVICES] = {nullptr};
+  static std::mutex mu;
+  int device = 0;
+  cudaError_t e = cudaGetDevice(&device);
+  if (e != cudaSuccess) return (int)e;
+  if (device < 0 || device >= SNK_STATIC_MAX_DEVICES) return SNK_ERR_STATIC_SETUP;
+  std::lock_guard<std::mutex> lock(mu);
+  if (address[device] == nullptr) {
+    void* p = nullptr;
+    e = cudaGetSymbolAddress(&p, g_static_scratch);      // resolves the symbol for the current device
+    if (e != cudaSuccess) return (int)e;
+    if (p == nullptr) return SNK_ERR_STATIC_SETUP;
+    address[device] = p;
+  }
+  *out = address[device];
+  return 0;
+}
+
+SNK_API long long snk_paged_attention_static_need(int M, int nh, int hd, int num_chunks) {
+  return snk_paged_attention_scratch_bytes(M, nh, hd, num_chunks);
+}
+
+SNK_API int snk_paged_attention_static(const void* q, const void* pool, const int* block_table, int max_pages,
+                                       int page_size, const int* positions, const int* row_seg, void* out,
+                                       int M, int nh, int nkv, int hd, int window, int chunk, int num_chunks,
+                                       float scale, int dtype, cudaStream_t stream) {
+  if (M <= 0) return 0;
+  if (snk_paged_attention_scratch_bytes(M, nh, hd, num_chunks) > (long long)SNK_ATTENTION_STATIC_SCRATCH_BYTES)
+    return SNK_ERR_STATIC_SCRATCH;
+  void* scratch = nullptr;
+  const int rc = static_scratch_address(&scratch);
+  if (rc) return rc;
+  // Every partial (o, max, sum) that the merge kernel reads is written by this call's first kernel, so
+  // the array needs no clearing.  The regular entry point does the launches; it allocates nothing.
+  return snk_paged_attention(q, pool, block_table, max_pages, page_size, positions, row_seg, out, scratch, M,
+                             nh, nkv, hd, window, chunk, num_chunks, scale, dtype, stream);
+}
