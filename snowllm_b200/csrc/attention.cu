@@ -60,13 +60,13 @@ __global__ void paged_attention_kernel(
     const T* __restrict__ q, const T* __restrict__ pool, const int* __restrict__ block_table,
     int max_pages, int page_size, const int* __restrict__ positions, const int* __restrict__ row_seg,
     T* __restrict__ out, float* __restrict__ part_o, float* __restrict__ part_ml, int nh, int nkv,
-    int hd, int window, int chunk, int num_chunks, float scale) {
+    int hd, int window, int chunk, int num_chunks, float scale, const int* __restrict__ row_list) {
   extern __shared__ __align__(16) unsigned char sh_raw[];
   constexpr int VEC = Vec16<T>::N;
   const int group = nh / nkv;
   const int heads_per_block = blockDim.x >> 5;
   const int blocks_per_kv = (group + heads_per_block - 1) / heads_per_block;
-  const int m = blockIdx.x;
+  const int m = row_list ? row_list[blockIdx.x] : blockIdx.x;    // the row of the batch this block serves
   const int kvh = blockIdx.y / blocks_per_kv;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int head_in_group = (blockIdx.y % blocks_per_kv) * heads_per_block + warp;
@@ -185,7 +185,7 @@ __global__ void paged_attention_kernel(
       if (d < hd) orow[d] = from_f<T>(o[i] * inv);
     }
   } else {
-    const size_t slot = ((size_t)m * nh + head) * num_chunks + blockIdx.z;
+    const size_t slot = ((size_t)blockIdx.x * nh + head) * num_chunks + blockIdx.z;
     float* po = part_o + slot * hd;
 #pragma unroll
     for (int i = 0; i < DPL; ++i) {
@@ -203,12 +203,13 @@ __global__ void paged_attention_kernel(
 template <typename T>
 __global__ void attention_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                        const int* __restrict__ positions, T* __restrict__ out, int nh,
-                                       int hd, int window, int chunk, int num_chunks) {
-  const int m = blockIdx.x, head = blockIdx.y;
+                                       int hd, int window, int chunk, int num_chunks,
+                                       const int* __restrict__ row_list) {
+  const int m = row_list ? row_list[blockIdx.x] : blockIdx.x, head = blockIdx.y;
   const int pos = positions[m];
   const int lo = window > 0 ? max(0, pos - window + 1) : 0;
   const int n = pos / chunk - lo / chunk + 1;              // chunks this row really has
-  const size_t base = ((size_t)m * nh + head) * num_chunks;
+  const size_t base = ((size_t)blockIdx.x * nh + head) * num_chunks;
   float mx = -INFINITY;
   for (int z = 0; z < n; ++z) mx = fmaxf(mx, part_ml[(base + z) * 2]);
   float l = 0.f;
@@ -228,11 +229,12 @@ SNK_API long long snk_paged_attention_scratch_bytes(int M, int nh, int hd, int n
   return (long long)M * nh * num_chunks * (hd + 2) * (long long)sizeof(float);
 }
 
-SNK_API int snk_paged_attention(const void* q, const void* pool, const int* block_table,
-                                int max_pages, int page_size, const int* positions,
-                                const int* row_seg, void* out, void* scratch, int M, int nh,
-                                int nkv, int hd, int window, int chunk, int num_chunks,
-                                float scale, int dtype, cudaStream_t stream) {
+// row_list (may be null): the M rows of the batch to serve, when not all of them.
+SNK_API int snk_paged_attention_rows(const void* q, const void* pool, const int* block_table,
+                                     int max_pages, int page_size, const int* positions,
+                                     const int* row_seg, void* out, void* scratch, int M, int nh,
+                                     int nkv, int hd, int window, int chunk, int num_chunks,
+                                     float scale, int dtype, const int* row_list, cudaStream_t stream) {
   if (M <= 0) return 0;
   if (nkv <= 0 || nh % nkv || hd <= 0 || hd > 32 * ATT_MAX_DPL) return SNK_ERR_SIZE;
   if (chunk <= 0 || chunk % ATT_TILE || num_chunks < 1 || num_chunks > 65535) return SNK_ERR_SIZE;
@@ -256,7 +258,7 @@ SNK_API int snk_paged_attention(const void* q, const void* pool, const int* bloc
     paged_attention_kernel<T, DPL_><<<grid, warps * 32, smem, stream>>>(                             \
         static_cast<const T*>(q), static_cast<const T*>(pool), block_table, max_pages, page_size,    \
         positions, row_seg, static_cast<T*>(out), part_o, part_ml, nh, nkv, hd, window, chunk,       \
-        num_chunks, scale);                                                                          \
+        num_chunks, scale, row_list);                                                                \
   } while (0)
   SNK_DISPATCH(dtype, {
     if (hd <= 32) ATT_LAUNCH(1);
@@ -272,10 +274,19 @@ SNK_API int snk_paged_attention(const void* q, const void* pool, const int* bloc
     const int threads = hd <= 32 ? 32 : (hd <= 64 ? 64 : 128);
     SNK_DISPATCH(dtype, attention_merge_kernel<T><<<mgrid, threads, 0, stream>>>(
                             part_o, part_ml, positions, static_cast<T*>(out), nh, hd, window,
-                            chunk, num_chunks));
+                            chunk, num_chunks, row_list));
     SNK_LAUNCH_CHECK();
   }
   return 0;
+}
+
+SNK_API int snk_paged_attention(const void* q, const void* pool, const int* block_table,
+                                int max_pages, int page_size, const int* positions,
+                                const int* row_seg, void* out, void* scratch, int M, int nh,
+                                int nkv, int hd, int window, int chunk, int num_chunks,
+                                float scale, int dtype, cudaStream_t stream) {
+  return snk_paged_attention_rows(q, pool, block_table, max_pages, page_size, positions, row_seg, out, scratch,
+                                  M, nh, nkv, hd, window, chunk, num_chunks, scale, dtype, nullptr, stream);
 }
 
 // ---------------------------------------------------------------------------------------------

@@ -1,0 +1,259 @@
+// Causal grouped-query attention for prompt portions in bfloat16, on the tensor cores.
+//
+// One block takes 64 consecutive rows of one request's portion and one q head and walks that
+// request's cached keys in tiles of 64, from the first key any of its rows may see to the last
+// row's own position (flash attention: running max and sum per row in float, the output
+// accumulator rescaled as the max moves).  S = Q K^T and O += P V are mma.sync m16n8k16 with
+// float accumulation; each of the 4 warps owns 16 rows.  Keys and values come straight from the
+// cache pages by 16-byte cp.async into two shared-memory stages (XOR-swizzled 16-byte chunks, so
+// that ldmatrix reads are free of bank conflicts); nothing outside a row's range [lo, pos] enters
+// its softmax, and key rows past the tile's last position are zero-filled, never read.
+//
+//   s = (q . k) * scale for lo <= key position <= query position, lo = max(0, pos - window + 1)
+//   with a window, else 0; softmax in float; o = softmax(s) v        (snowllm/models/lfm2/layers.py:36-70;
+//   tests/test_lfm2_long_attention.py:36-47)
+//
+// The tile order is fixed by positions alone, so a row's result does not depend on what else the
+// launch holds.  Head sizes 64 and 128; other sizes, float32 and rows of short segments go through
+// csrc/attention.cu.  Pool layout: [page, 2 (k, v), kv head, page_size, head_dim].
+#include "common.cuh"
+
+#define FA_BQ 64
+#define FA_BK 64
+#define FA_WARPS 4
+
+__device__ __forceinline__ void fa_cp_async16(uint32_t dst, const void* gmem, bool valid) {
+  const int bytes = valid ? 16 : 0;
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(gmem), "r"(bytes));
+}
+__device__ __forceinline__ void fa_commit() { asm volatile("cp.async.commit_group;"); }
+template <int N> __device__ __forceinline__ void fa_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N)); }
+
+__device__ __forceinline__ void ldmatrix_x4(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2,
+                                                  uint32_t& r3) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+__device__ __forceinline__ void fa_mma(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                       uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+               "{%0,%1,%2,%3};"
+               : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+               : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+  const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<const uint32_t*>(&v);
+}
+
+// Byte offset of 16-byte chunk `c` of row `r` in a tile whose rows hold CHUNKS chunks.
+template <int CHUNKS> __device__ __forceinline__ uint32_t swz(int r, int c) {
+  return (uint32_t)(r * CHUNKS + (c ^ (r & 7))) * 16u;
+}
+
+// tiles: int32 [n_tiles][4] = {segment, first row of the tile in the batch, rows in the tile (<= 64),
+// position of the first row}.
+template <int HD>
+__global__ void __launch_bounds__(FA_WARPS * 32)
+attention_prefill_kernel(const bf16* __restrict__ q, const bf16* __restrict__ pool,
+                         const int* __restrict__ block_table, int max_pages, int page_size,
+                         const int* __restrict__ tiles, bf16* __restrict__ out, int nh, int nkv, int window,
+                         float scale_log2) {
+  constexpr int CH = HD / 8;                       // 16-byte chunks per row
+  constexpr int KT = HD / 16;                      // k-steps of the QK^T product
+  constexpr int NT = HD / 8;                       // n-tiles of the output
+  extern __shared__ __align__(16) unsigned char fa_smem[];
+  const uint32_t sm_q = (uint32_t)__cvta_generic_to_shared(fa_smem);
+  const uint32_t sm_kv = sm_q + FA_BQ * HD * 2;    // [2 stages][k | v][FA_BK rows]
+  constexpr uint32_t TILE_BYTES = FA_BK * HD * 2;
+
+  const int* tile = tiles + (size_t)blockIdx.x * 4;
+  const int seg = tile[0], row0 = tile[1], rows = tile[2], pos0 = tile[3];
+  const int head = blockIdx.y;
+  const int kvh = head / (nh / nkv);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int g = lane >> 2, t = lane & 3;
+  const int* bt = block_table + (size_t)seg * max_pages;
+  const size_t page_stride = (size_t)2 * nkv * page_size * HD;
+  const size_t v_off = (size_t)nkv * page_size * HD;
+
+  // keys this tile needs: from the first row's lower bound to the last row's position
+  const int last_pos = pos0 + rows - 1;
+  const int key_lo = window > 0 ? max(0, pos0 - window + 1) : 0;
+  const int k_first = (key_lo / FA_BK) * FA_BK;    // key tiles are aligned to absolute positions
+  const int n_kt = (last_pos - k_first) / FA_BK + 1;
+
+  // Q tile -> shared memory (rows past the portion's end are zero)
+  for (int v = threadIdx.x; v < FA_BQ * CH; v += FA_WARPS * 32) {
+    const int r = v / CH, c = v % CH;
+    fa_cp_async16(sm_q + swz<CH>(r, c), q + ((size_t)(row0 + min(r, rows - 1)) * nh + head) * HD + c * 8, r < rows);
+  }
+  auto load_kv = [&](int kt) {
+    if (kt < n_kt) {
+      const int k0 = k_first + kt * FA_BK;
+      const uint32_t ks = sm_kv + (uint32_t)(kt & 1) * 2 * TILE_BYTES, vs = ks + TILE_BYTES;
+      for (int v = threadIdx.x; v < FA_BK * CH; v += FA_WARPS * 32) {
+        const int r = v / CH, c = v % CH;
+        const int kp = k0 + r;
+        const bool valid = kp <= last_pos;
+        const bf16* src = pool;
+        if (valid) {
+          const int page = bt[kp / page_size];
+          src = pool + (size_t)page * page_stride + ((size_t)kvh * page_size + kp % page_size) * HD + c * 8;
+        }
+        fa_cp_async16(ks + swz<CH>(r, c), src, valid);
+        fa_cp_async16(vs + swz<CH>(r, c), valid ? src + v_off : src, valid);
+      }
+    }
+    fa_commit();
+  };
+  load_kv(0);                                      // group 0: Q and the first key tile
+
+  float acc_o[NT][4];
+#pragma unroll
+  for (int i = 0; i < NT; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) acc_o[i][j] = 0.f;
+  float row_max[2] = {-INFINITY, -INFINITY}, row_sum[2] = {0.f, 0.f};
+  uint32_t qf[KT][4];
+  // positions and lower bounds of this thread's two rows (g and g + 8 of the warp's 16)
+  const int r_lo = warp * 16 + g, r_hi = r_lo + 8;
+  const int p_lo = pos0 + r_lo, p_hi = pos0 + r_hi;
+  const int lo_lo = window > 0 ? max(0, p_lo - window + 1) : 0;
+  const int lo_hi = window > 0 ? max(0, p_hi - window + 1) : 0;
+
+  for (int kt = 0; kt < n_kt; ++kt) {
+    load_kv(kt + 1);
+    fa_wait<1>();
+    __syncthreads();
+    if (kt == 0) {
+#pragma unroll
+      for (int k = 0; k < KT; ++k) {
+        const int r = warp * 16 + (lane & 7) + 8 * ((lane >> 3) & 1), c = 2 * k + (lane >> 4);
+        ldmatrix_x4(sm_q + swz<CH>(r, c), qf[k][0], qf[k][1], qf[k][2], qf[k][3]);
+      }
+    }
+    const int k0 = k_first + kt * FA_BK;
+    const uint32_t ks = sm_kv + (uint32_t)(kt & 1) * 2 * TILE_BYTES, vs = ks + TILE_BYTES;
+    // a warp whose rows all lie before this key tile (causal), or behind it (window), skips it
+    const int warp_first_pos = pos0 + warp * 16, warp_last_pos = min(warp_first_pos + 15, last_pos);
+    const int warp_lo = window > 0 ? max(0, warp_first_pos - window + 1) : 0;
+    const bool active = warp * 16 < rows && k0 <= warp_last_pos && k0 + FA_BK > warp_lo;
+    if (active) {
+      float s[FA_BK / 8][4];
+#pragma unroll
+      for (int i = 0; i < FA_BK / 8; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) s[i][j] = 0.f;
+#pragma unroll
+      for (int k = 0; k < KT; ++k) {
+#pragma unroll
+        for (int n = 0; n < FA_BK / 16; ++n) {      // two 8-key tiles per ldmatrix.x4
+          uint32_t b0, b1, b2, b3;
+          const int r = n * 16 + (lane & 7) + 8 * (lane >> 4), c = 2 * k + ((lane >> 3) & 1);
+          ldmatrix_x4(ks + swz<CH>(r, c), b0, b1, b2, b3);
+          fa_mma(s[2 * n], qf[k][0], qf[k][1], qf[k][2], qf[k][3], b0, b1);
+          fa_mma(s[2 * n + 1], qf[k][0], qf[k][1], qf[k][2], qf[k][3], b2, b3);
+        }
+      }
+      // mask and running max: s[i] = {(row g, key 8i+2t), (g, 8i+2t+1), (g+8, 8i+2t), (g+8, 8i+2t+1)}
+      float mx[2] = {row_max[0], row_max[1]};
+#pragma unroll
+      for (int i = 0; i < FA_BK / 8; ++i) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const int kp = k0 + 8 * i + 2 * t + (j & 1);
+          const bool hi = j >= 2;
+          const bool ok = hi ? (kp <= p_hi && kp >= lo_hi) : (kp <= p_lo && kp >= lo_lo);
+          s[i][j] = ok ? s[i][j] * scale_log2 : -INFINITY;
+          mx[hi] = fmaxf(mx[hi], s[i][j]);
+        }
+      }
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 1));
+        mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 2));
+      }
+      float alpha[2], base[2];
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        base[h] = mx[h] == -INFINITY ? 0.f : mx[h];        // a row with nothing to see yet: exp2(-inf) = 0
+        alpha[h] = exp2f(row_max[h] - base[h]);            // row_max = -inf on the first tile: 0
+        row_max[h] = mx[h];
+        row_sum[h] *= alpha[h];
+      }
+#pragma unroll
+      for (int i = 0; i < NT; ++i) {
+        acc_o[i][0] *= alpha[0]; acc_o[i][1] *= alpha[0];
+        acc_o[i][2] *= alpha[1]; acc_o[i][3] *= alpha[1];
+      }
+      uint32_t pf[FA_BK / 16][4];
+#pragma unroll
+      for (int i = 0; i < FA_BK / 8; ++i) {
+        const float p0 = exp2f(s[i][0] - base[0]), p1 = exp2f(s[i][1] - base[0]);
+        const float p2 = exp2f(s[i][2] - base[1]), p3 = exp2f(s[i][3] - base[1]);
+        row_sum[0] += p0 + p1;
+        row_sum[1] += p2 + p3;
+        pf[i >> 1][(i & 1) * 2] = pack_bf16(p0, p1);       // rows g: a0 (even 8-key tile), a2 (odd)
+        pf[i >> 1][(i & 1) * 2 + 1] = pack_bf16(p2, p3);   // rows g+8: a1, a3
+      }
+#pragma unroll
+      for (int kk = 0; kk < FA_BK / 16; ++kk) {
+#pragma unroll
+        for (int n = 0; n < NT / 2; ++n) {
+          uint32_t b0, b1, b2, b3;
+          const int r = kk * 16 + (lane & 7) + 8 * ((lane >> 3) & 1), c = 2 * n + (lane >> 4);
+          ldmatrix_x4_trans(vs + swz<CH>(r, c), b0, b1, b2, b3);
+          fa_mma(acc_o[2 * n], pf[kk][0], pf[kk][1], pf[kk][2], pf[kk][3], b0, b1);
+          fa_mma(acc_o[2 * n + 1], pf[kk][0], pf[kk][1], pf[kk][2], pf[kk][3], b2, b3);
+        }
+      }
+    }
+    __syncthreads();                               // everyone is done with this stage before it is refilled
+  }
+  fa_wait<0>();
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    row_sum[h] += __shfl_xor_sync(0xffffffffu, row_sum[h], 1);
+    row_sum[h] += __shfl_xor_sync(0xffffffffu, row_sum[h], 2);
+  }
+  const float inv_lo = 1.f / row_sum[0], inv_hi = 1.f / row_sum[1];
+#pragma unroll
+  for (int i = 0; i < NT; ++i) {
+    const int d = 8 * i + 2 * t;
+    if (r_lo < rows)
+      *reinterpret_cast<uint32_t*>(out + ((size_t)(row0 + r_lo) * nh + head) * HD + d) =
+          pack_bf16(acc_o[i][0] * inv_lo, acc_o[i][1] * inv_lo);
+    if (r_hi < rows)
+      *reinterpret_cast<uint32_t*>(out + ((size_t)(row0 + r_hi) * nh + head) * HD + d) =
+          pack_bf16(acc_o[i][2] * inv_hi, acc_o[i][3] * inv_hi);
+  }
+}
+
+SNK_API int snk_attention_prefill(const void* q, const void* pool, const int* block_table, int max_pages,
+                                  int page_size, const int* tiles, int n_tiles, void* out, int nh, int nkv,
+                                  int hd, int window, float scale, cudaStream_t stream) {
+  if (n_tiles <= 0) return 0;
+  if (nkv <= 0 || nh % nkv || nh > 65535) return SNK_ERR_SIZE;
+  if (hd != 64 && hd != 128) return SNK_ERR_SIZE;
+  if (((uintptr_t)q % 16) || ((uintptr_t)pool % 16) || ((uintptr_t)out % 4)) return SNK_ERR_ALIGN;
+  const float scale_log2 = scale * 1.4426950408889634f;
+  dim3 grid(n_tiles, nh);
+  const size_t smem = (size_t)(FA_BQ + 4 * FA_BK) * hd * 2;
+  const bf16 *qp = static_cast<const bf16*>(q), *pp = static_cast<const bf16*>(pool);
+  bf16* op = static_cast<bf16*>(out);
+  if (hd == 64) {
+    attention_prefill_kernel<64><<<grid, FA_WARPS * 32, smem, stream>>>(qp, pp, block_table, max_pages, page_size,
+                                                                        tiles, op, nh, nkv, window, scale_log2);
+  } else {
+    cudaFuncSetAttribute(attention_prefill_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    attention_prefill_kernel<128><<<grid, FA_WARPS * 32, smem, stream>>>(qp, pp, block_table, max_pages, page_size,
+                                                                         tiles, op, nh, nkv, window, scale_log2);
+  }
+  SNK_LAUNCH_CHECK();
+  return 0;
+}

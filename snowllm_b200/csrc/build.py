@@ -13,6 +13,7 @@ import ctypes
 import hashlib
 import os
 import pathlib
+import re
 import shutil
 import subprocess
 import sys
@@ -26,7 +27,7 @@ HERE = pathlib.Path(__file__).resolve().parent
 ARCH_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a"]
 NVCC_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "--shared", "-Xcompiler", "-fPIC",
               "-Xcompiler", "-fvisibility=hidden"]
-LIBRARIES = ("elementwise", "rope_cache", "short_conv", "attention", "gemm", "gemm_skinny", "gemm_tc", "moe", "sampling")
+LIBRARIES = ("elementwise", "rope_cache", "short_conv", "attention", "attention_prefill", "gemm", "gemm_skinny", "gemm_tc", "moe", "sampling")
 EXTRA_LINK: dict[str, list[str]] = {}
 
 _loaded: dict[str, ctypes.CDLL] = {}
@@ -94,8 +95,9 @@ def _compile(name: str, out: pathlib.Path) -> None:
         tmp.unlink(missing_ok=True)
         raise KernelError(f"nvcc failed on {src.name}:\n{log}")
     os.replace(tmp, out)            # atomic: a concurrent process sees the old state or the whole file
+    stale = re.compile(rf"libsnk_{re.escape(name)}_[0-9a-f]{{16}}\.so")     # this source's older builds only
     for old in out.parent.glob(f"libsnk_{name}_*.so"):
-        if old != out and ".tmp" not in old.name:
+        if old != out and stale.fullmatch(old.name):
             old.unlink(missing_ok=True)
     print(f"[snowllm_b200] built {out.name} in {time.time() - t0:.1f} s", file=sys.stderr, flush=True)
 

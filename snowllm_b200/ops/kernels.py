@@ -34,6 +34,10 @@ _SIGNATURES = {
     "attention": {
         "snk_paged_attention_scratch_bytes": [I, I, I, I],
         "snk_paged_attention": [P, P, P, I, I, P, P, P, P, I, I, I, I, I, I, I, F, I, P],
+        "snk_paged_attention_rows": [P, P, P, I, I, P, P, P, P, I, I, I, I, I, I, I, F, I, P, P],
+    },
+    "attention_prefill": {
+        "snk_attention_prefill": [P, P, P, I, I, P, I, P, I, I, I, I, F, P],
     },
     "gemm": {
         "snk_gemm_simt": [P, P, P, I, I, I, P, I, P, I, I, I, I, P],
@@ -252,10 +256,11 @@ def attention_scratch_bytes(M: int, num_heads: int, head_dim: int, num_chunks: i
 
 
 def paged_attention(q, pool, block_table, page_size, positions, row_seg, scale, window=None,
-                    chunk=None, num_chunks=1, scratch=None, out=None):
+                    chunk=None, num_chunks=1, scratch=None, out=None, rows=None):
     """Causal attention of each row of q [M, heads, head_dim] over its request's cached keys up to
     its own position.  ``chunk`` keys per block along the sequence (a multiple of 32) and
-    ``num_chunks`` = the most chunks any row spans; more than one needs ``scratch`` bytes."""
+    ``num_chunks`` = the most chunks any row spans; more than one needs ``scratch`` bytes.
+    ``rows`` (int32): serve only these rows of the batch; the others of ``out`` are left alone."""
     M, nh, hd = q.shape
     dtype = q.dtype
     _chk(q, "q", (torch.float32, torch.bfloat16))
@@ -270,18 +275,48 @@ def paged_attention(q, pool, block_table, page_size, positions, row_seg, scale, 
     if out is None:
         out = torch.empty(M, nh * hd, dtype=dtype, device=q.device)
     _chk(out, "attention output", dtype, (M, nh * hd))
+    served = M
+    if rows is not None:
+        _chk(rows, "attention rows", torch.int32)
+        served = rows.numel()
     if num_chunks > 1:
-        need = attention_scratch_bytes(M, nh, hd, num_chunks)
+        need = attention_scratch_bytes(served, nh, hd, num_chunks)
         if scratch is None:
             scratch = torch.empty(need, dtype=torch.uint8, device=q.device)
         _chk(scratch, "attention scratch", torch.uint8)
         if scratch.numel() < need:
             raise KernelError(f"attention scratch holds {scratch.numel()} bytes, needs {need}")
-    check(fn("snk_paged_attention")(
+    check(fn("snk_paged_attention_rows")(
         _ptr(q), _ptr(pool), _ptr(block_table), block_table.shape[1], page_size, _ptr(positions),
-        _ptr(row_seg), _ptr(out), _ptr(scratch), M, nh, nkv, hd, int(window or 0), int(chunk),
-        int(num_chunks), float(scale), code_of(dtype), _stream()), "paged_attention",
+        _ptr(row_seg), _ptr(out), _ptr(scratch), served, nh, nkv, hd, int(window or 0), int(chunk),
+        int(num_chunks), float(scale), code_of(dtype), _ptr(rows), _stream()), "paged_attention",
         launches=2 if num_chunks > 1 else 1)
+    return out
+
+
+PREFILL_TILE_ROWS = 64
+PREFILL_HEAD_DIMS = (64, 128)
+
+
+def attention_prefill_ok(q) -> bool:
+    """Whether the tensor-core prompt kernel takes this q [M, heads, head_dim]."""
+    return q.dtype == torch.bfloat16 and q.shape[2] in PREFILL_HEAD_DIMS
+
+
+def attention_prefill(q, pool, block_table, page_size, tiles, scale, out, window=None):
+    """Tensor-core causal attention for prompt portions: ``tiles`` int32 [n, 4] = (segment, first row,
+    rows <= 64, position of the first row); writes those rows of ``out`` [M, heads*head_dim]."""
+    M, nh, hd = q.shape
+    _chk(q, "q", torch.bfloat16)
+    _chk(pool, "kv pool", torch.bfloat16)
+    _chk(tiles, "attention tiles", torch.int32)
+    _chk(block_table, "block table", torch.int32)
+    _chk(out, "attention output", torch.bfloat16, (M, nh * hd))
+    if tiles.dim() != 2 or tiles.shape[1] != 4:
+        raise KernelError("attention tiles must be [n, 4]")
+    check(fn("snk_attention_prefill")(
+        _ptr(q), _ptr(pool), _ptr(block_table), block_table.shape[1], page_size, _ptr(tiles), tiles.shape[0],
+        _ptr(out), nh, pool.shape[2], hd, int(window or 0), float(scale), _stream()), "attention_prefill")
     return out
 
 

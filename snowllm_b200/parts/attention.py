@@ -2,13 +2,16 @@
 (snowllm/models/lfm2/layers.py:36-70; snowllm/models/qwen3_5/layers.py:122-135).
 
 q, k, v are one fused product; a second kernel applies the per-head RMSNorm of q and k, the
-position encoding, and writes k and v into the cache pages; a third attends over the pages.
+position encoding, and writes k and v into the cache pages; then the rows attend over the pages:
+prompt portions (bfloat16, head sizes 64 and 128) in 64-row tiles on the tensor cores, all other
+rows one by one with their keys split into chunks.
 ``window`` keeps the last ``window`` keys only (None: all).  A layer that reads another layer's
 cache (``owns_cache`` False) projects q alone and writes nothing."""
 from __future__ import annotations
 
 import torch
 
+from ..engine.context import PREFILL_MIN_ROWS
 from ..ops import kernels, linear
 from .base import Part
 from .registry import lookup, register_mixer
@@ -16,7 +19,7 @@ from .spec import INIT_ONES, KEEP_SMALL, PagedKVSpec, TensorSpec
 
 
 class Attention(Part):
-    libraries = ("gemm", "gemm_skinny", "gemm_tc", "rope_cache", "attention")
+    libraries = ("gemm", "gemm_skinny", "gemm_tc", "rope_cache", "attention", "attention_prefill")
 
     def __init__(self, dtype, names, *, hidden_size: int, num_heads: int, num_kv_heads: int,
                  head_dim: int, qk_norm_eps: float | None, position: dict, window: int | None = None,
@@ -60,12 +63,22 @@ class Attention(Part):
             qkv, self.q_norm, self.k_norm, self.qk_norm_eps or 0.0, inv_freq, rot_dim, ctx.positions,
             ctx.row_seg, cache.block_table, cache.page_size, cache.pool, self.num_heads,
             self.num_kv_heads, self.head_dim, write_kv=owns_cache)
-        chunk, num_chunks = ctx.attention_plan(self.window)
+        o = torch.empty(ctx.M, self.num_heads * self.head_dim, dtype=q.dtype, device=q.device)
+        rows = rows_host = None
+        if kernels.attention_prefill_ok(q) and max(ctx.host_seg_len) >= PREFILL_MIN_ROWS:
+            # prompt portions on the tensor cores; rows of short segments (decoded tokens) row by row
+            tiles, rows, rows_host = ctx.attention_split(kernels.PREFILL_TILE_ROWS)
+            kernels.attention_prefill(q, cache.pool, cache.block_table, cache.page_size, tiles, self.scale, o,
+                                      window=self.window)
+            if not rows_host:
+                return linear(o, self.wo, out_dtype=torch.float32)
+        chunk, num_chunks = ctx.attention_plan(self.window, rows_host)
+        served = ctx.M if rows_host is None else len(rows_host)
         scratch = ctx.scratch(kernels.attention_scratch_bytes(
-            ctx.M, self.num_heads, self.head_dim, num_chunks)) if num_chunks > 1 else None
-        o = kernels.paged_attention(q, cache.pool, cache.block_table, cache.page_size, ctx.positions,
-                                    ctx.row_seg, self.scale, window=self.window, chunk=chunk,
-                                    num_chunks=num_chunks, scratch=scratch)
+            served, self.num_heads, self.head_dim, num_chunks)) if num_chunks > 1 else None
+        kernels.paged_attention(q, cache.pool, cache.block_table, cache.page_size, ctx.positions,
+                                ctx.row_seg, self.scale, window=self.window, chunk=chunk,
+                                num_chunks=num_chunks, scratch=scratch, out=o, rows=rows)
         return linear(o, self.wo, out_dtype=torch.float32)
 
 

@@ -560,3 +560,74 @@ def test_gemm_tc_grouped_after_gather(K):
         r = slice(offsets[e], offsets[e + 1])
         if counts[e]:
             close(out[r], xs[r].float().cpu() @ w[e].T, torch.float32, scale=16)
+
+
+# ---------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("nh,nkv,hd,P,window", [(4, 2, 64, 16, None), (6, 1, 128, 16, None), (2, 2, 64, 64, None),
+                                                (4, 2, 64, 16, 100), (3, 1, 128, 8, 37)])
+def test_attention_prefill_tiles(K, nh, nkv, hd, P, window):
+    """The tensor-core prompt kernel: a portion from position 0, one in the middle of a long request
+    (not aligned to tiles or pages), a short one; pages scattered; unwritten cache entries are NaN."""
+    from snowllm_b200.engine.context import prefill_tiles
+    torch.manual_seed(40)
+    dtype = torch.bfloat16
+    starts, lens = [0, 333, 700], [200, 150, 17]
+    totals = [s + n for s, n in zip(starts, lens)]
+    pages = sum(-(-n // P) for n in totals) + 2
+    perm = torch.randperm(pages).tolist()
+    pool = torch.full((pages, 2, nkv, P, hd), float("nan"), dtype=dtype, device="cuda")
+    tables, ks, vs = [], [], []
+    for n in totals:
+        need = -(-n // P)
+        table, perm = perm[:need], perm[need:]
+        k, v = rnd(dtype, n, nkv, hd), rnd(dtype, n, nkv, hd)
+        scatter_kv(pool, k, v, table, P)
+        tables.append(table)
+        ks.append(k)
+        vs.append(v)
+    width = max(len(t) for t in tables)
+    bt = i32([t + [0] * (width - len(t)) for t in tables])
+    tiles, rest = prefill_tiles(starts, lens, 64)
+    assert not rest and len(tiles) == 4 + 3 + 1
+    M = sum(lens)
+    q = rnd(dtype, M, nh, hd)
+    out = torch.full((M, nh * hd), float("nan"), dtype=dtype, device="cuda")
+    K.attention_prefill(dev(q, dtype), pool, bt, P, i32(tiles), hd ** -0.5, out, window=window)
+    assert out.isfinite().all(), "a row was not written, or an unwritten cache entry was read"
+    first = 0
+    for b in range(3):
+        rows = list(range(starts[b], totals[b]))
+        want = ref_attention(q[first:first + lens[b]], ks[b], vs[b], rows, hd ** -0.5, window)
+        close(out[first:first + lens[b]], want, dtype)
+        first += lens[b]
+    # the row-wise kernel on the same rows agrees (it serves the rows the tiles leave out)
+    positions = sum((list(range(s, t)) for s, t in zip(starts, totals)), [])
+    row_seg = sum(([b] * n for b, n in enumerate(lens)), [])
+    some = [0, 5, 199, 200, 349, 350, 366]
+    other = K.paged_attention(dev(q, dtype), pool, bt, P, i32(positions), i32(row_seg), hd ** -0.5, window=window,
+                              out=torch.zeros_like(out), rows=i32(some))
+    close(other[some], out[some].float(), dtype)
+    untouched = [i for i in range(M) if i not in some]
+    assert float(other[untouched].abs().max()) == 0.0
+
+
+def test_attention_prefill_far_key_and_diagonal(K):
+    """A key far back is made to stand out for the last row of a portion, and every row's own key for
+    itself: the far key must win in the one row, the diagonal in all others (the causal edge)."""
+    torch.manual_seed(41)
+    dtype, nh, nkv, hd, P, T = torch.bfloat16, 2, 1, 64, 16, 640
+    k, v = rnd(dtype, T, nkv, hd, scale=0.05), rnd(dtype, T, nkv, hd)
+    q = rnd(dtype, T, nh, hd, scale=0.05)
+    direction = F.normalize(torch.randn(hd), dim=0)
+    k[7, 0] = (direction * 16).to(dtype).float()
+    q[T - 1] = (direction * 16).to(dtype).float()
+    table = torch.randperm(T // P).tolist()
+    pool = make_pool(dtype, len(table), nkv, P, hd)
+    scatter_kv(pool, k, v, table, P)
+    tiles = [[0, r, min(64, T - r), r] for r in range(0, T, 64)]
+    out = torch.zeros(T, nh * hd, dtype=dtype, device="cuda")
+    K.attention_prefill(dev(q, dtype), pool, i32([table]), P, i32(tiles), hd ** -0.5, out)
+    got = out.float().cpu()
+    assert (got[T - 1] - v[7, 0].repeat(nh)).abs().max() < 0.02
+    close(got, ref_attention(q, k, v, list(range(T)), hd ** -0.5, None), dtype)
+    assert torch.allclose(got[0], v[0, 0].repeat(nh), atol=1e-2)     # the first row sees its own key only
