@@ -31,6 +31,7 @@ class RequestCache:
     tables: dict = field(default_factory=dict)        # group key -> list of page ids (-1: given back)
     num_tokens: int = 0                               # positions [0, num_tokens) are in the cache
     freed: bool = False
+    synced: dict = field(default_factory=dict)        # group key -> table entries a host mirror already holds
 
 
 @dataclass
@@ -119,11 +120,14 @@ class CacheManager:
     def missing_pages(self, rc: RequestCache, total_tokens: int) -> dict:
         """{group key -> pages still to take} so that positions [num_tokens, total_tokens) fit."""
         need = {}
+        want = pages_for(total_tokens, self.page_size)
         for key in self.groups:
             table = rc.tables[key]
-            want = pages_for(total_tokens, self.page_size)
-            first = self._first_needed_page(key, rc.num_tokens)
             have = len(table)
+            if key[1] is None:                         # every key is kept: the table has no holes
+                need[key] = max(0, want - have)
+                continue
+            first = self._first_needed_page(key, rc.num_tokens)
             # entries below `first` are never needed again; entries [have, want) are new
             need[key] = max(0, want - max(have, first)) + sum(
                 1 for i in range(first, min(have, want)) if table[i] < 0)
@@ -142,12 +146,14 @@ class CacheManager:
         want = pages_for(total_tokens, self.page_size)
         for key, pool in self.groups.items():
             table = rc.tables[key]
-            first = self._first_needed_page(key, rc.num_tokens)
-            while len(table) < min(first, want):
-                table.append(-1)                       # positions a window has passed already
-            for i in range(first, min(len(table), want)):
-                if table[i] < 0:
-                    table[i] = pool.alloc(1)[0]
+            if key[1] is not None:
+                first = self._first_needed_page(key, rc.num_tokens)
+                while len(table) < min(first, want):
+                    table.append(-1)                   # positions a window has passed already
+                for i in range(first, min(len(table), want)):
+                    if table[i] < 0:
+                        table[i] = pool.alloc(1)[0]
+                        rc.synced[key] = min(rc.synced.get(key, 0), i)
             if want > len(table):
                 table.extend(pool.alloc(want - len(table)))
         return True
@@ -166,6 +172,7 @@ class CacheManager:
                 if table[i] >= 0:
                     pool.release([table[i]])
                     table[i] = -1
+                    rc.synced[key] = min(rc.synced.get(key, 0), i)
 
     def free(self, rc: RequestCache) -> None:
         """Give back everything the request holds."""

@@ -35,17 +35,51 @@ SNK_API int snk_embedding(const int* ids, const void* table, float* out, int M, 
 // One block per output row.  rows == nullptr: row r is residual row r; delta (if any) is
 // added into the residual and the sum is written back.  rows != nullptr: output row r
 // normalises residual[rows[r]] + delta[rows[r]] and nothing is written back.
+template <typename T> __device__ __forceinline__ void store4(T* p, float a, float b, float c, float d);
+template <> __device__ __forceinline__ void store4<float>(float* p, float a, float b, float c, float d) {
+  *reinterpret_cast<float4*>(p) = make_float4(a, b, c, d);
+}
+template <> __device__ __forceinline__ void store4<bf16>(bf16* p, float a, float b, float c, float d) {
+  const __nv_bfloat162 lo = __floats2bfloat162_rn(a, b), hi = __floats2bfloat162_rn(c, d);
+  *reinterpret_cast<uint2*>(p) = make_uint2(*reinterpret_cast<const uint32_t*>(&lo),
+                                            *reinterpret_cast<const uint32_t*>(&hi));
+}
+
 template <typename T>
 __global__ void add_rmsnorm_kernel(float* __restrict__ residual, const float* __restrict__ delta,
                                    SmallVec gamma, T* __restrict__ out,
-                                   const int* __restrict__ rows, int H, float eps) {
-  extern __shared__ float xs[];          // H floats + 33 for the reduction
-  float* red = xs + H;
+                                   const int* __restrict__ rows, int H, float eps, int vec4) {
+  extern __shared__ __align__(16) float xs[];   // H floats + 33 for the reduction
+  float* red = xs + ((H + 3) & ~3);
   const int r = blockIdx.x;
   const size_t src = rows ? (size_t)rows[r] : (size_t)r;
   float* res = residual + src * H;
   const float* d = delta ? delta + src * H : nullptr;
   float ss = 0.f;
+  T* o = out + (size_t)r * H;
+  if (vec4) {                                   // H a multiple of 4 and 16-byte aligned rows
+    float4* xs4 = reinterpret_cast<float4*>(xs);
+    float4* res4 = reinterpret_cast<float4*>(res);
+    const float4* d4 = reinterpret_cast<const float4*>(d);
+    for (int i = threadIdx.x; i < H / 4; i += blockDim.x) {
+      float4 v = res4[i];
+      if (d) {
+        const float4 e = d4[i];
+        v.x += e.x; v.y += e.y; v.z += e.z; v.w += e.w;
+        if (!rows) res4[i] = v;
+      }
+      xs4[i] = v;
+      ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+    }
+    ss = block_sum(ss, red);
+    const float inv = rsqrtf(ss / (float)H + eps);
+    for (int i = threadIdx.x; i < H / 4; i += blockDim.x) {
+      const float4 v = xs4[i];
+      store4<T>(o + 4 * i, v.x * inv * gamma[4 * i], v.y * inv * gamma[4 * i + 1], v.z * inv * gamma[4 * i + 2],
+                v.w * inv * gamma[4 * i + 3]);
+    }
+    return;
+  }
   for (int i = threadIdx.x; i < H; i += blockDim.x) {
     float v = res[i];
     if (d) {
@@ -57,7 +91,6 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ residual, const float* __
   }
   ss = block_sum(ss, red);
   const float inv = rsqrtf(ss / (float)H + eps);
-  T* o = out + (size_t)r * H;
   for (int i = threadIdx.x; i < H; i += blockDim.x)
     o[i] = from_f<T>(xs[i] * inv * gamma[i]);
 }
@@ -69,14 +102,16 @@ SNK_API int snk_add_rmsnorm(float* residual, const float* delta, const void* gam
   if (H <= 0 || H > 65536) return SNK_ERR_SIZE;
   // The block size depends on H alone, so a row's statistics never depend on the batch.
   const int threads = H >= 2048 ? 512 : (H >= 512 ? 256 : 128);
-  const size_t smem = (size_t)(H + 33) * sizeof(float);
+  const size_t smem = (size_t)(((H + 3) & ~3) + 33) * sizeof(float);
   SmallVec g{gamma, gamma_is_f32};
+  const int vec4 = H % 4 == 0 && (uintptr_t)residual % 16 == 0 && (uintptr_t)delta % 16 == 0 &&
+                   (uintptr_t)out % 16 == 0;
   SNK_DISPATCH(dtype, {
     if (smem > 48 * 1024)
       cudaFuncSetAttribute(add_rmsnorm_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                            (int)smem);
     add_rmsnorm_kernel<T><<<R, threads, smem, stream>>>(residual, delta, g,
-                                                        static_cast<T*>(out), rows, H, eps);
+                                                        static_cast<T*>(out), rows, H, eps, vec4);
   });
   SNK_LAUNCH_CHECK();
   return 0;

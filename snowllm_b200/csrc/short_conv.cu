@@ -82,6 +82,34 @@ __global__ void short_conv_state_kernel(const T* __restrict__ bcx, T* __restrict
     if (i < L - 1) st[(size_t)i * H + c] = from_f<T>(next[i]);
 }
 
+// Every segment holds one token (a decode step): one thread per (segment, channel) reads the
+// history, computes the output and writes the new history; no second launch.
+template <typename T>
+__global__ void short_conv_decode_kernel(const T* __restrict__ bcx, SmallVec w, T* __restrict__ state,
+                                         const int* __restrict__ seg_start, const int* __restrict__ seg_slot,
+                                         T* __restrict__ out, int H, int L) {
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= H) return;
+  const int seg = blockIdx.y;                        // = the row: one token per segment
+  const bool has_state = seg_start[seg] > 0;
+  T* st = state + (size_t)seg_slot[seg] * (L - 1) * H;
+  float hist[CONV_MAX_L];
+#pragma unroll
+  for (int j = 0; j < CONV_MAX_L; ++j)
+    if (j < L - 1) hist[j] = has_state ? to_f<T>(st[(size_t)j * H + c]) : 0.f;
+  const float g = gated<T>(bcx, (size_t)seg, H, c);
+  float acc = 0.f;
+#pragma unroll
+  for (int j = 0; j < CONV_MAX_L; ++j)
+    if (j < L - 1) acc = fmaf(w[(size_t)c * L + j], hist[j], acc);
+  acc = fmaf(w[(size_t)c * L + L - 1], g, acc);
+  const float cgate = to_f<T>(bcx[(size_t)seg * 3 * H + H + c]);
+  out[(size_t)seg * H + c] = from_f<T>(cgate * acc);
+#pragma unroll
+  for (int j = 0; j < CONV_MAX_L; ++j)
+    if (j < L - 1) st[(size_t)j * H + c] = from_f<T>(j + 1 < L - 1 ? hist[j + 1] : g);
+}
+
 SNK_API int snk_short_conv(const void* bcx, const void* w, int w_is_f32, void* state,
                            const int* cu_seqlens, const int* seg_start, const int* seg_slot,
                            const int* row_seg, void* out, int M, int B, int H, int L, int dtype,
@@ -89,6 +117,15 @@ SNK_API int snk_short_conv(const void* bcx, const void* w, int w_is_f32, void* s
   if (M <= 0 || B <= 0) return 0;
   if (L < 1 || L > CONV_MAX_L) return SNK_ERR_SIZE;
   const int threads = 128;
+  if (M == B && L > 1 && B <= 65535) {               // one token per segment
+    dim3 dgrid((H + threads - 1) / threads, B);
+    SmallVec dw{w, w_is_f32};
+    SNK_DISPATCH(dtype, short_conv_decode_kernel<T><<<dgrid, threads, 0, stream>>>(
+                            static_cast<const T*>(bcx), dw, static_cast<T*>(state), seg_start, seg_slot,
+                            static_cast<T*>(out), H, L));
+    SNK_LAUNCH_CHECK();
+    return 0;
+  }
   dim3 grid((H + threads - 1) / threads, (M + CONV_ROWS_PER_BLOCK - 1) / CONV_ROWS_PER_BLOCK);
   if (grid.y > 65535u) return SNK_ERR_SIZE;
   SmallVec wv{w, w_is_f32};

@@ -113,6 +113,32 @@ class HostStaging:
         self.events: list = [None] * depth
         self.turn = 0
         self.bytes_uploaded = 0
+        self.mirrors: dict = {}        # group key -> int32 [slots, width]: host copy of the block tables
+
+    def mirror(self, g: int, key, entries, width: int) -> np.ndarray:
+        """The host copy of group ``key``'s block tables, one row per slot, brought up to date for the
+        requests of ``entries`` (only entries that changed since the last step are written; holes of a
+        window group read as page 0, which no kernel touches)."""
+        m = self.mirrors.get(key)
+        rows = max(e.cache.slot for e in entries) + 1
+        width = max(width, max(len(e.cache.tables[key]) for e in entries))   # pages may be taken ahead of use
+        if m is None or m.shape[0] < rows or m.shape[1] < width:
+            new = np.zeros((max(rows, m.shape[0] if m is not None else 0),
+                            max(2 * width, m.shape[1] if m is not None else 0)), dtype=np.int32)
+            if m is not None:
+                new[:m.shape[0], :m.shape[1]] = m
+            self.mirrors[key] = m = new
+        for e in entries:
+            rc = e.cache
+            table = rc.tables[key]
+            if rc.synced.get("mirror") is not self:    # first time this mirror sees the request
+                rc.synced.clear()
+                rc.synced["mirror"] = self
+            done = rc.synced.get(key, 0)
+            if len(table) > done:
+                m[rc.slot, done:len(table)] = np.maximum(np.asarray(table[done:], dtype=np.int64), 0)
+            rc.synced[key] = len(table)
+        return m
 
     def upload(self, host: np.ndarray, into: torch.Tensor | None = None) -> torch.Tensor:
         """Copy ``host`` to the device through a pinned buffer: into a new tensor, or into ``into``."""

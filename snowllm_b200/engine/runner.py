@@ -157,11 +157,14 @@ def build_context(entries: Sequence[StepEntry], cache: CacheManager, dtype, devi
             raise SnowLLMError("a freed request cannot be stepped")
         if s + n > max_position:
             raise SnowLLMError(f"position {s + n} exceeds the model's limit {max_position}")
+        need = -(-(s + n) // P)
         for key, table in e.cache.tables.items():
-            need = -(-(s + n) // P)
-            first = 0 if key[1] is None else max(0, s - key[1] + 1) // P
-            if len(table) < need or any(p < 0 for p in table[first:need]):
+            if len(table) < need:
                 raise CapacityError("the step was given tokens whose pages were not taken")
+            if key[1] is not None:                     # a window group's table may have holes
+                first = max(0, s - key[1] + 1) // P
+                if any(p < 0 for p in table[first:need]):
+                    raise CapacityError("the step was given tokens whose pages were not taken")
     ids = np.fromiter((t for e in entries for t in e.tokens), dtype=np.int64, count=M)
     if M and (ids.min() < 0 or ids.max() >= V):
         raise SnowLLMError(f"token id outside [0, {V})")
@@ -181,13 +184,10 @@ def build_context(entries: Sequence[StepEntry], cache: CacheManager, dtype, devi
         max_pages = needed_pages
     elif max_pages < needed_pages:
         raise CapacityError(f"a block table of {max_pages} entries cannot hold {needed_pages} pages")
-    tables = np.zeros((len(groups), B, max_pages), dtype=np.int64)
-    for g, key in enumerate(groups):
-        for b, e in enumerate(entries):
-            t = e.cache.tables[key][:max_pages]
-            if t:
-                tables[g, b, :len(t)] = np.maximum(np.asarray(t), 0)
-    parts = [ids, positions, row_seg, cu, np.asarray(starts), np.asarray([e.cache.slot for e in entries]),
+    slots = np.asarray([e.cache.slot for e in entries])
+    tables = np.stack([staging.mirror(g, key, entries, max_pages)[slots, :max_pages] for g, key in enumerate(groups)]) \
+        if groups else np.zeros((0, B, max_pages), dtype=np.int32)
+    parts = [ids, positions, row_seg, cu, np.asarray(starts), slots,
              np.asarray(logit_rows, dtype=np.int64), tables.reshape(-1)]
     sizes = [p.size for p in parts]
     # each part starts on a 16-byte boundary

@@ -345,7 +345,7 @@ def short_conv(bcx, weight, state, cu_seqlens, seg_start, seg_slot, row_seg, out
     _chk(out, "conv output", dtype, (M, H))
     check(fn("snk_short_conv")(_ptr(bcx), _ptr(weight), w32, _ptr(state), _ptr(cu_seqlens), _ptr(seg_start),
                                _ptr(seg_slot), _ptr(row_seg), _ptr(out), M, B, H, L, code_of(dtype),
-                               _stream()), "short_conv", launches=2 if L > 1 else 1)
+                               _stream()), "short_conv", launches=2 if L > 1 and M != B else 1)
     return out
 
 

@@ -490,7 +490,7 @@ def test_sample_respects_top_k_and_top_p_sets(K):
 
 # ---------------------------------------------------------------------------------------------
 @pytest.mark.parametrize("M,N,K_", [(1, 331, 80), (8, 96, 48), (9, 2048, 2048), (33, 130, 264), (64, 17, 8),
-                                    (5, 64, 7168)])
+                                    (5, 64, 7168), (3, 40003, 72), (17, 32768, 264)])
 def test_gemm_skinny(K, M, N, K_):
     """The few-rows bfloat16 kernel against the float product, and row by row against itself."""
     torch.manual_seed(20)
@@ -521,6 +521,16 @@ def test_gemm_skinny_grouped_with_gather(K):
         for e in range(E):
             for r in range(offsets[e], offsets[e + 1]):
                 close(out[r], x[pairs[r] // k] @ w[e].T, torch.float32, scale=8)
+    # many groups
+    E, N, M = 64, 520, 70
+    x, w = rnd(dtype, M, K_), rnd(dtype, E, N, K_)
+    ids = torch.randint(0, E, (M,))
+    order = torch.argsort(ids, stable=True)
+    offsets = [0] + torch.cumsum(torch.bincount(ids, minlength=E), 0).tolist()
+    out = K.gemm_skinny(dev(x, dtype), dev(w, dtype), a_rows=i32(order.tolist()), a_div=1, offsets=i32(offsets),
+                        rows_out=M, rows_hint=8, out_dtype=torch.float32)
+    for r in range(M):
+        close(out[r], x[order[r]] @ w[ids[order[r]]].T, torch.float32, scale=8)
 
 
 # ---------------------------------------------------------------------------------------------
