@@ -255,7 +255,10 @@ def e2e_run(model, batch: int, context: int, steps: int, warmup: int, page_size:
     from snowllm_b200.engine import Engine, SamplingParams
     gen = torch.Generator().manual_seed(2)
     prompts = [torch.randint(0, model.vocab_size, (context,), generator=gen).tolist() for _ in range(batch)]
-    new = steps + warmup + 2
+    # requests reach their first token one after another (the prompts are prefilled in portions, in
+    # turn); none may finish before the timed steps are over, or the batch would shrink under them
+    stagger = batch * -(-context // PREFILL_TOKENS)
+    new = steps + warmup + stagger + 8
     engine = Engine(model, max_num_seqs=batch, max_model_len=batch * (context + new + page_size),
                     prefill_chunk=PREFILL_TOKENS, page_size=page_size)
     reqs = [engine.add(p, SamplingParams(temperature=0, max_new_tokens=new)) for p in prompts]
