@@ -1,13 +1,18 @@
 // C[M,N] = A[M,K] . W[N,K]^T in bfloat16 on the 5th-generation tensor cores (tcgen05), for many rows
-// (prefill).  One block computes one 128 x 128 tile of C:
+// (prefill).  Blocks are persistent: as many as the GPU holds, each walking tiles of 128 x BN of C
+// (BN 256 where there are enough tiles to fill the GPU, else 128), row tiles fastest so that blocks
+// running side by side share the tile of W they read:
 //
-//   warp 0, one lane   TMA producer: 128x64 tiles of A and of W into a ring of shared-memory stages
-//                      (cp.async.bulk.tensor, 128-byte swizzle, completion counted on an mbarrier)
-//   warp 1, one lane   MMA issuer: per stage four tcgen05.mma (M 128, N 128, K 16) straight from shared
+//   warp 0, one lane   TMA producer: 128x64 tiles of A and BNx64 tiles of W into a ring of shared-memory
+//                      stages (cp.async.bulk.tensor, 128-byte swizzle, completion counted on an mbarrier)
+//   warp 1, one lane   MMA issuer: per stage four tcgen05.mma (M 128, N BN, K 16) straight from shared
 //                      memory into a float accumulator in tensor memory; tcgen05.commit hands the stage
 //                      back to the producer and, after the last k-block, the accumulator to the epilogue
 //   warps 2..5         epilogue: tcgen05.ld of the accumulator (each warp its 32 lanes = 32 rows of C),
 //                      conversion, guarded stores
+//
+// There are two accumulators in tensor memory (2 x BN columns): the epilogue of one tile runs while
+// the next tile's products are issued.
 //
 // Both operands are K-major, which is how activations and checkpoint weights already lie in memory,
 // so nothing is re-tiled at load.  Rows past M (or past a group's end) and k past K are zero-filled
@@ -30,13 +35,12 @@
 #include "common.cuh"
 
 #define TC_BM 128
-#define TC_BN 128
 #define TC_BK 64
-#define TC_STAGES 5
 #define TC_THREADS 192
+#define TC_SMEM_TILES (192 * 1024)    // bytes of shared memory given to the operand stages
 #define TC_WAIT_NS 1500000000ull      // 1.5 s per wait before giving up
 
-enum { TC_ERR_WAIT_FULL = 1, TC_ERR_WAIT_EMPTY = 2, TC_ERR_WAIT_ACC = 3 };
+enum { TC_ERR_WAIT_FULL = 1, TC_ERR_WAIT_EMPTY = 2, TC_ERR_WAIT_ACC = 3, TC_ERR_WAIT_ACC_FREE = 4 };
 
 __device__ int g_tc_status;            // 0, or the first error code a block recorded
 
@@ -96,9 +100,12 @@ __device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t smem_addr) {
   return d;
 }
 
-// Instruction descriptor of kind::f16: D float, A and B bfloat16, both K-major, M 128, N TC_BN.
-__device__ __forceinline__ uint32_t instr_desc_bf16() {
-  return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(TC_BN >> 3) << 17) | ((uint32_t)(TC_BM >> 4) << 24);
+// Instruction descriptor of kind::f16: D float, A and B bfloat16, both K-major, M 128, N n.
+__device__ __forceinline__ uint32_t instr_desc_bf16(int n) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(TC_BM >> 4) << 24);
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
 
 __device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
@@ -127,61 +134,94 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 
+#define TC_MAX_STAGES 6
+
 struct __align__(8) TcShared {
-  uint64_t full[TC_STAGES];
-  uint64_t empty[TC_STAGES];
-  uint64_t acc_ready;
+  uint64_t full[TC_MAX_STAGES];
+  uint64_t empty[TC_MAX_STAGES];
+  uint64_t acc_full[2];
+  uint64_t acc_empty[2];
   uint32_t tmem_base;
   int aborted;
 };
 
-template <typename OutT>
+// Rows of C and rows of W that tile `tile` covers.  Plain: tiles = row_tiles * n_tiles, row tile fastest.
+// Grouped: row tiles are counted group by group (a tile never spans two groups).
+struct TcTile {
+  int row0, row_end, w_row0, n0;
+  bool valid;
+};
+
+__device__ __forceinline__ TcTile tc_tile(int tile, int row_tiles, int M, int N, int BN, const int* offsets,
+                                          int groups) {
+  TcTile t;
+  const int rt = tile % row_tiles, nt = tile / row_tiles;
+  t.n0 = nt * BN;
+  t.valid = t.n0 < N;
+  if (!offsets) {
+    t.row0 = rt * TC_BM;
+    t.row_end = M;
+    t.w_row0 = 0;
+    return t;
+  }
+  int left = rt;
+  t.valid = false;
+  t.row0 = t.row_end = t.w_row0 = 0;
+  if (nt * BN >= N) return t;
+  for (int e = 0; e < groups; ++e) {
+    const int begin = offsets[e], cnt = offsets[e + 1] - begin;
+    const int tiles_e = (cnt + TC_BM - 1) / TC_BM;
+    if (left < tiles_e) {
+      t.row0 = begin + left * TC_BM;
+      t.row_end = begin + cnt;
+      t.w_row0 = e * N;
+      t.valid = true;
+      return t;
+    }
+    left -= tiles_e;
+  }
+  return t;
+}
+
+template <int BN, typename OutT>
 __global__ void __launch_bounds__(TC_THREADS)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
-               OutT* __restrict__ C, int M, int N, int K, const int* __restrict__ offsets, int groups) {
+               OutT* __restrict__ C, int M, int N, int K, const int* __restrict__ offsets, int groups,
+               int row_tiles_bound) {
+  constexpr int STAGE_BYTES = (TC_BM + BN) * TC_BK * 2;
+  constexpr int STAGES = TC_SMEM_TILES / STAGE_BYTES < TC_MAX_STAGES ? TC_SMEM_TILES / STAGE_BYTES : TC_MAX_STAGES;
   extern __shared__ unsigned char smem_raw[];
   // tiles need 1024-byte alignment for the 128-byte swizzle
   unsigned char* tiles = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  unsigned char* tiles_a = tiles;
-  unsigned char* tiles_w = tiles + (size_t)TC_STAGES * TC_BM * TC_BK * 2;
-  TcShared* sh = reinterpret_cast<TcShared*>(tiles_w + (size_t)TC_STAGES * TC_BN * TC_BK * 2);
+  TcShared* sh = reinterpret_cast<TcShared*>(tiles + (size_t)STAGES * STAGE_BYTES);
 
-  // which rows this block owns
-  int row0, row_end, w_row0;
-  if (offsets) {
-    int tile = blockIdx.y, e = 0;
-    row0 = -1;
-    for (; e < groups; ++e) {
-      const int cnt = offsets[e + 1] - offsets[e];
-      const int tiles_e = (cnt + TC_BM - 1) / TC_BM;
-      if (tile < tiles_e) { row0 = offsets[e] + tile * TC_BM; break; }
-      tile -= tiles_e;
-    }
-    if (row0 < 0) return;                                // past the last tile of the last group
-    row_end = offsets[e + 1];
-    w_row0 = e * N;
-  } else {
-    row0 = blockIdx.y * TC_BM;
-    row_end = M;
-    w_row0 = 0;
-  }
-  const int n0 = blockIdx.x * TC_BN;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int k_tiles = (K + TC_BK - 1) / TC_BK;
+  // number of row tiles: known for the plain product, counted from the offsets for the grouped one
+  int row_tiles = row_tiles_bound;
+  if (offsets) {
+    row_tiles = 0;
+    for (int e = 0; e < groups; ++e) row_tiles += (offsets[e + 1] - offsets[e] + TC_BM - 1) / TC_BM;
+  }
+  const int n_tiles = (N + BN - 1) / BN;
+  const int total = row_tiles * n_tiles;
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < TC_STAGES; ++s) {
+    for (int s = 0; s < STAGES; ++s) {
       mbar_init(&sh->full[s], 1);
       mbar_init(&sh->empty[s], 1);
     }
-    mbar_init(&sh->acc_ready, 1);
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&sh->acc_full[b], 1);
+      mbar_init(&sh->acc_empty[b], 4);                   // one arrival per epilogue warp
+    }
     sh->aborted = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   }
-  if (warp == 1) {                                       // one warp allocates the accumulator columns
+  if (warp == 1) {                                       // one warp allocates both accumulators
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
-                 ::"r"(smem_u32(&sh->tmem_base)), "r"((uint32_t)TC_BN) : "memory");
+                 ::"r"(smem_u32(&sh->tmem_base)), "r"((uint32_t)(2 * BN)) : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
   tc_fence_before();
@@ -192,82 +232,110 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 
   if (warp == 0) {
     if (lane == 0) {
-      for (int kt = 0; kt < k_tiles; ++kt) {
-        const int s = kt % TC_STAGES;
-        mbar_wait(&sh->empty[s], ((kt / TC_STAGES) & 1) ^ 1, aborted, TC_ERR_WAIT_EMPTY);
-        mbar_expect_tx(&sh->full[s], (TC_BM + TC_BN) * TC_BK * 2);
-        tma_load_2d(tiles_a + (size_t)s * TC_BM * TC_BK * 2, &map_a, &sh->full[s], kt * TC_BK, row0);
-        tma_load_2d(tiles_w + (size_t)s * TC_BN * TC_BK * 2, &map_w, &sh->full[s], kt * TC_BK, w_row0 + n0);
+      int it = 0;                                        // k-blocks issued so far, over all tiles
+      for (int tile = blockIdx.x; tile < total; tile += gridDim.x) {
+        const TcTile t = tc_tile(tile, row_tiles, M, N, BN, offsets, groups);
+        if (!t.valid) continue;
+        for (int kt = 0; kt < k_tiles; ++kt, ++it) {
+          const int s = it % STAGES;
+          mbar_wait(&sh->empty[s], ((it / STAGES) & 1) ^ 1, aborted, TC_ERR_WAIT_EMPTY);
+          mbar_expect_tx(&sh->full[s], STAGE_BYTES);
+          unsigned char* stage = tiles + (size_t)s * STAGE_BYTES;
+          tma_load_2d(stage, &map_a, &sh->full[s], kt * TC_BK, t.row0);
+          tma_load_2d(stage + TC_BM * TC_BK * 2, &map_w, &sh->full[s], kt * TC_BK, t.w_row0 + t.n0);
+        }
       }
     }
   } else if (warp == 1) {
     if (lane == 0) {
-      const uint32_t idesc = instr_desc_bf16();
-      for (int kt = 0; kt < k_tiles; ++kt) {
-        const int s = kt % TC_STAGES;
-        mbar_wait(&sh->full[s], (kt / TC_STAGES) & 1, aborted, TC_ERR_WAIT_FULL);
+      const uint32_t idesc = instr_desc_bf16(BN);
+      int it = 0, local = 0;
+      for (int tile = blockIdx.x; tile < total; tile += gridDim.x) {
+        const TcTile t = tc_tile(tile, row_tiles, M, N, BN, offsets, groups);
+        if (!t.valid) continue;
+        const int buf = local & 1;
+        mbar_wait(&sh->acc_empty[buf], ((local >> 1) & 1) ^ 1, aborted, TC_ERR_WAIT_ACC_FREE);
         tc_fence_after();
-        const uint32_t a_addr = smem_u32(tiles_a + (size_t)s * TC_BM * TC_BK * 2);
-        const uint32_t w_addr = smem_u32(tiles_w + (size_t)s * TC_BN * TC_BK * 2);
+        const uint32_t d_tmem = tmem_acc + (uint32_t)(buf * BN);
+        for (int kt = 0; kt < k_tiles; ++kt, ++it) {
+          const int s = it % STAGES;
+          mbar_wait(&sh->full[s], (it / STAGES) & 1, aborted, TC_ERR_WAIT_FULL);
+          tc_fence_after();
+          const uint32_t a_addr = smem_u32(tiles + (size_t)s * STAGE_BYTES);
+          const uint32_t w_addr = a_addr + TC_BM * TC_BK * 2;
 #pragma unroll
-        for (int k = 0; k < TC_BK / 16; ++k) {
-          // 16 k-values = 32 bytes further along the swizzled 128-byte rows
-          umma_bf16(tmem_acc, smem_desc_sw128(a_addr + k * 32), smem_desc_sw128(w_addr + k * 32), idesc,
-                    (kt > 0 || k > 0) ? 1u : 0u);
+          for (int k = 0; k < TC_BK / 16; ++k) {
+            // 16 k-values = 32 bytes further along the swizzled 128-byte rows
+            umma_bf16(d_tmem, smem_desc_sw128(a_addr + k * 32), smem_desc_sw128(w_addr + k * 32), idesc,
+                      (kt > 0 || k > 0) ? 1u : 0u);
+          }
+          umma_commit(&sh->empty[s]);                    // the stage is free once these MMAs have read it
         }
-        umma_commit(&sh->empty[s]);                      // the stage is free once these MMAs have read it
+        umma_commit(&sh->acc_full[buf]);
+        ++local;
       }
-      umma_commit(&sh->acc_ready);
     }
   } else {
-    mbar_wait(&sh->acc_ready, 0, aborted, TC_ERR_WAIT_ACC);
-    tc_fence_after();
     const int lane_group = warp & 3;                     // a warp reads the 32 tensor-memory lanes 32*(warp%4)..
-    const int row = row0 + lane_group * 32 + lane;
     const bool vec_ok = (N % 8) == 0;
+    int local = 0;
+    for (int tile = blockIdx.x; tile < total; tile += gridDim.x) {
+      const TcTile t = tc_tile(tile, row_tiles, M, N, BN, offsets, groups);
+      if (!t.valid) continue;
+      const int buf = local & 1;
+      mbar_wait(&sh->acc_full[buf], (local >> 1) & 1, aborted, TC_ERR_WAIT_ACC);
+      tc_fence_after();
+      const int row = t.row0 + lane_group * 32 + lane;
 #pragma unroll 1
-    for (int c0 = 0; c0 < TC_BN; c0 += 32) {
-      uint32_t r[32];
-      tmem_ld32(tmem_acc + ((uint32_t)(lane_group * 32) << 16) + (uint32_t)c0, r);
-      if (row < row_end && !*aborted) {
-        OutT* dst = C + (size_t)row * N + n0 + c0;
-        if (vec_ok && n0 + c0 + 32 <= N) {
-          if constexpr (sizeof(OutT) == 4) {
+      for (int c0 = 0; c0 < BN; c0 += 32) {
+        uint32_t r[32];
+        tmem_ld32(tmem_acc + ((uint32_t)(lane_group * 32) << 16) + (uint32_t)(buf * BN + c0), r);
+        if (c0 + 32 >= BN) {                             // everything of this accumulator is in registers
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&sh->acc_empty[buf]);
+        }
+        if (row < t.row_end && !*aborted) {
+          OutT* dst = C + (size_t)row * N + t.n0 + c0;
+          if (vec_ok && t.n0 + c0 + 32 <= N) {
+            if constexpr (sizeof(OutT) == 4) {
 #pragma unroll
-            for (int i = 0; i < 32; i += 4)
-              *reinterpret_cast<uint4*>(dst + i) = make_uint4(r[i], r[i + 1], r[i + 2], r[i + 3]);
+              for (int i = 0; i < 32; i += 4)
+                *reinterpret_cast<uint4*>(dst + i) = make_uint4(r[i], r[i + 1], r[i + 2], r[i + 3]);
+            } else {
+#pragma unroll
+              for (int i = 0; i < 32; i += 8) {
+                uint32_t p[4];
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                  const __nv_bfloat162 v = __floats2bfloat162_rn(__uint_as_float(r[i + 2 * j]),
+                                                                 __uint_as_float(r[i + 2 * j + 1]));
+                  p[j] = *reinterpret_cast<const uint32_t*>(&v);
+                }
+                *reinterpret_cast<uint4*>(dst + i) = make_uint4(p[0], p[1], p[2], p[3]);
+              }
+            }
           } else {
 #pragma unroll
-            for (int i = 0; i < 32; i += 8) {
-              uint32_t p[4];
-#pragma unroll
-              for (int j = 0; j < 4; ++j) {
-                const __nv_bfloat162 v = __floats2bfloat162_rn(__uint_as_float(r[i + 2 * j]),
-                                                               __uint_as_float(r[i + 2 * j + 1]));
-                p[j] = *reinterpret_cast<const uint32_t*>(&v);
-              }
-              *reinterpret_cast<uint4*>(dst + i) = make_uint4(p[0], p[1], p[2], p[3]);
-            }
+            for (int i = 0; i < 32; ++i)
+              if (t.n0 + c0 + i < N) dst[i] = from_f<OutT>(__uint_as_float(r[i]));
           }
-        } else {
-#pragma unroll
-          for (int i = 0; i < 32; ++i)
-            if (n0 + c0 + i < N) dst[i] = from_f<OutT>(__uint_as_float(r[i]));
         }
       }
+      ++local;
     }
   }
   tc_fence_before();
   __syncthreads();
   if (warp == 1) {
     tc_fence_after();
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_acc), "r"((uint32_t)TC_BN)
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_acc), "r"((uint32_t)(2 * BN))
                  : "memory");
   }
 }
 
 // ---------------------------------------------------------------------------------------------
-// Tensor maps: 2-D, bfloat16, inner dimension K, box 64 x 128, 128-byte swizzle.  Built through the
+// Tensor maps: 2-D, bfloat16, inner dimension K, box 64 x (128 or 256) rows, 128-byte swizzle.  Built through the
 // driver entry point (no link against the driver library) and cached by (pointer, rows, K).
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
@@ -289,27 +357,30 @@ static EncodeTiledFn encode_fn() {
 struct MapKey {
   const void* ptr;
   long long rows, k;
-  bool operator==(const MapKey& o) const { return ptr == o.ptr && rows == o.rows && k == o.k; }
+  int box_rows;
+  bool operator==(const MapKey& o) const {
+    return ptr == o.ptr && rows == o.rows && k == o.k && box_rows == o.box_rows;
+  }
 };
 struct MapKeyHash {
   size_t operator()(const MapKey& m) const {
     return std::hash<const void*>()(m.ptr) ^ (std::hash<long long>()(m.rows) * 1315423911u) ^
-           (std::hash<long long>()(m.k) * 2654435761u);
+           (std::hash<long long>()(m.k) * 2654435761u) ^ (size_t)m.box_rows;
   }
 };
 
-static int tensor_map(const void* ptr, long long rows, long long k, CUtensorMap* out) {
+static int tensor_map(const void* ptr, long long rows, long long k, int box_rows, CUtensorMap* out) {
   static std::unordered_map<MapKey, CUtensorMap, MapKeyHash> cache;
   static std::mutex mu;
   std::lock_guard<std::mutex> lock(mu);
-  const MapKey key{ptr, rows, k};
+  const MapKey key{ptr, rows, k, box_rows};
   auto it = cache.find(key);
   if (it != cache.end()) { *out = it->second; return 0; }
   EncodeTiledFn fn = encode_fn();
   if (!fn) return SNK_ERR_SIZE + 100;
   const cuuint64_t dims[2] = {(cuuint64_t)k, (cuuint64_t)rows};
   const cuuint64_t strides[1] = {(cuuint64_t)k * 2};
-  const cuuint32_t box[2] = {TC_BK, TC_BM};
+  const cuuint32_t box[2] = {TC_BK, (cuuint32_t)box_rows};
   const cuuint32_t estr[2] = {1, 1};
   CUtensorMap m;
   const CUresult r = fn(&m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
@@ -322,6 +393,27 @@ static int tensor_map(const void* ptr, long long rows, long long k, CUtensorMap*
   return 0;
 }
 
+template <int BN, typename OutT>
+static int launch_tc(const CUtensorMap& map_a, const CUtensorMap& map_w, void* C, int M, int N, int K,
+                     const int* offsets, int groups, int row_tiles, cudaStream_t stream) {
+  constexpr int STAGE_BYTES = (TC_BM + BN) * TC_BK * 2;
+  constexpr int STAGES = TC_SMEM_TILES / STAGE_BYTES < TC_MAX_STAGES ? TC_SMEM_TILES / STAGE_BYTES : TC_MAX_STAGES;
+  const size_t smem = 1024 + (size_t)STAGES * STAGE_BYTES + sizeof(TcShared);
+  static int sms = 0;
+  if (sms == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    cudaFuncSetAttribute(gemm_tc_kernel<BN, OutT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  }
+  const long long tiles = (long long)row_tiles * ((N + BN - 1) / BN);
+  const int blocks = (int)(tiles < sms ? tiles : sms);     // one block per SM (shared memory), persistent
+  gemm_tc_kernel<BN, OutT><<<blocks, TC_THREADS, smem, stream>>>(map_a, map_w, static_cast<OutT*>(C), M, N, K,
+                                                                 offsets, groups, row_tiles);
+  SNK_LAUNCH_CHECK();
+  return 0;
+}
+
 // M: rows of A (all groups together).  Grouped: offsets[groups+1] on the device, W = [groups, N, K];
 // max_row_tiles bounds the number of 128-row tiles over all groups (M/128 + groups is always enough).
 SNK_API int snk_gemm_tc(const void* A, const void* W, void* C, int M, int N, int K, const int* offsets,
@@ -329,27 +421,20 @@ SNK_API int snk_gemm_tc(const void* A, const void* W, void* C, int M, int N, int
   if (M <= 0 || N <= 0) return 0;
   if (K <= 0 || K % 8) return SNK_ERR_SIZE;                   // TMA: the row pitch is a multiple of 16 bytes
   if (((uintptr_t)A % 16) || ((uintptr_t)W % 16) || ((uintptr_t)C % 16)) return SNK_ERR_ALIGN;
-  static_assert(TC_BM == TC_BN, "one box shape serves both operands");
-  CUtensorMap map_a, map_w;
-  int rc = tensor_map(A, M, K, &map_a);
-  if (rc) return rc;
-  rc = tensor_map(W, (long long)(offsets ? groups : 1) * N, K, &map_w);
-  if (rc) return rc;
   const int row_tiles = offsets ? max_row_tiles : (M + TC_BM - 1) / TC_BM;
-  if (row_tiles <= 0 || row_tiles > 65535) return SNK_ERR_SIZE;
-  dim3 grid((N + TC_BN - 1) / TC_BN, row_tiles);
-  const size_t smem = 1024 + (size_t)TC_STAGES * (TC_BM + TC_BN) * TC_BK * 2 + sizeof(TcShared);
-  if (out_f32) {
-    cudaFuncSetAttribute(gemm_tc_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    gemm_tc_kernel<float><<<grid, TC_THREADS, smem, stream>>>(map_a, map_w, static_cast<float*>(C), M, N, K,
-                                                              offsets, groups);
-  } else {
-    cudaFuncSetAttribute(gemm_tc_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    gemm_tc_kernel<bf16><<<grid, TC_THREADS, smem, stream>>>(map_a, map_w, static_cast<bf16*>(C), M, N, K,
-                                                             offsets, groups);
-  }
-  SNK_LAUNCH_CHECK();
-  return 0;
+  if (row_tiles <= 0) return SNK_ERR_SIZE;
+  // wide tiles where they still give every SM work; narrow ones otherwise
+  const bool wide = (long long)((M + TC_BM - 1) / TC_BM) * ((N + 255) / 256) >= 120;
+  CUtensorMap map_a, map_w;
+  int rc = tensor_map(A, M, K, TC_BM, &map_a);
+  if (rc) return rc;
+  rc = tensor_map(W, (long long)(offsets ? groups : 1) * N, K, wide ? 256 : 128, &map_w);
+  if (rc) return rc;
+  if (wide)
+    return out_f32 ? launch_tc<256, float>(map_a, map_w, C, M, N, K, offsets, groups, row_tiles, stream)
+                   : launch_tc<256, bf16>(map_a, map_w, C, M, N, K, offsets, groups, row_tiles, stream);
+  return out_f32 ? launch_tc<128, float>(map_a, map_w, C, M, N, K, offsets, groups, row_tiles, stream)
+                 : launch_tc<128, bf16>(map_a, map_w, C, M, N, K, offsets, groups, row_tiles, stream);
 }
 
 // 0, or the first error a block of any earlier launch recorded (a wait that ran out); reading clears

@@ -535,7 +535,7 @@ def test_gemm_skinny_grouped_with_gather(K):
 
 # ---------------------------------------------------------------------------------------------
 @pytest.mark.parametrize("M,N,K_", [(128, 128, 64), (65, 17, 8), (200, 136, 72), (300, 100, 1000), (257, 384, 2048),
-                                    (1000, 96, 48)])
+                                    (1000, 96, 48), (2000, 4000, 72), (1930, 4104, 136)])   # the last two: 256-wide tiles
 def test_gemm_tc(K, M, N, K_):
     """The tcgen05 kernel (TMA loads, accumulator in tensor memory) against the float product: tiles
     cut by M, N and K, float and bfloat16 stores; no wait inside the kernel ran out."""
@@ -570,6 +570,19 @@ def test_gemm_tc_grouped_after_gather(K):
         r = slice(offsets[e], offsets[e + 1])
         if counts[e]:
             close(out[r], xs[r].float().cpu() @ w[e].T, torch.float32, scale=16)
+    # enough tiles for the 256-wide form: many rows, several groups, N past a tile edge
+    E, N, K_ = 6, 1100, 72
+    counts = [700, 0, 1300, 129, 1, 870]
+    offsets = [0]
+    for c in counts:
+        offsets.append(offsets[-1] + c)
+    x, w = rnd(dtype, offsets[-1], K_), rnd(dtype, E, N, K_)
+    out = K.gemm_tc(dev(x, dtype), dev(w, dtype), out_dtype=torch.float32, offsets=i32(offsets))
+    assert K.gemm_tc_status() == 0
+    for e in range(E):
+        r = slice(offsets[e], offsets[e + 1])
+        if counts[e]:
+            close(out[r], x[r] @ w[e].T, torch.float32, scale=16)
 
 
 # ---------------------------------------------------------------------------------------------
