@@ -132,24 +132,28 @@ SNK_API int snk_residual_add(float* residual, const float* delta, long long n, c
 }
 
 // ---------------------------------------------------------------------------------------
-// gu: [M, 2I] with the gate in columns [0, I) and the up projection in [I, 2I).
+// gu: [M, 2I].  Plain: the gate in columns [0, I), the up projection in [I, 2I).  Interleaved: blocks of
+// 16 columns, 8 gate columns then the 8 up columns of the same features (what the fused products use).
 template <typename T>
-__global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ out, int I, size_t total) {
+__global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ out, int I, size_t total, int interleaved) {
   size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (idx >= total) return;
   const size_t m = idx / I;
   const int i = (int)(idx - m * I);
-  const float g = to_f<T>(gu[m * 2 * I + i]);
-  const float u = to_f<T>(gu[m * 2 * I + I + i]);
+  const size_t gcol = interleaved ? (size_t)(i / 8) * 16 + i % 8 : (size_t)i;
+  const size_t ucol = interleaved ? gcol + 8 : (size_t)I + i;
+  const float g = to_f<T>(gu[m * 2 * I + gcol]);
+  const float u = to_f<T>(gu[m * 2 * I + ucol]);
   const float s = g / (1.f + expf(-g));
   out[idx] = from_f<T>(s * u);
 }
 
-SNK_API int snk_swiglu(const void* gu, void* out, int M, int I, int dtype, cudaStream_t stream) {
+SNK_API int snk_swiglu(const void* gu, void* out, int M, int I, int interleaved, int dtype, cudaStream_t stream) {
   const size_t total = (size_t)M * I;
   if (total == 0) return 0;
+  if (interleaved && I % 8) return SNK_ERR_SIZE;
   SNK_DISPATCH(dtype, swiglu_kernel<T><<<(unsigned)((total + 255) / 256), 256, 0, stream>>>(
-                          static_cast<const T*>(gu), static_cast<T*>(out), I, total));
+                          static_cast<const T*>(gu), static_cast<T*>(out), I, total, interleaved));
   SNK_LAUNCH_CHECK();
   return 0;
 }

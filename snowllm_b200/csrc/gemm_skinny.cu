@@ -39,7 +39,10 @@ __device__ __forceinline__ void mma_bf16(float (&d)[4], uint32_t a0, uint32_t a1
                : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
-template <int MT, typename OutT>
+// SWIGLU: W holds gate and up rows interleaved in blocks of 8 (rows 16j..16j+7: gate of features
+// 8j..8j+7, rows 16j+8..16j+15: their up rows), so a block's 16 rows are 8 features' gate and up; the
+// store is then silu(gate) * up into C[M, N/2].
+template <int MT, typename OutT, bool SWIGLU>
 __global__ void __launch_bounds__(SK_WARPS * 32)
 gemm_skinny_kernel(const bf16* __restrict__ A, const bf16* __restrict__ W, OutT* __restrict__ C, int M,
                    int N, int K, const int* __restrict__ a_rows, int a_div,
@@ -115,14 +118,30 @@ gemm_skinny_kernel(const bf16* __restrict__ A, const bf16* __restrict__ W, OutT*
       red[warp][i * 8 + 2 * t + 1][g + 8] = acc[i][3];
     }
     __syncthreads();
-    for (int idx = threadIdx.x; idx < MT * 8 * SK_ROWS; idx += SK_WARPS * 32) {
-      const int tok = idx / SK_ROWS, r = idx % SK_ROWS;
-      const int m = m0 + tok, n = n0 + r;
-      if (m < row_end && n < N) {
-        float s = 0.f;
+    if constexpr (SWIGLU) {
+      for (int idx = threadIdx.x; idx < MT * 8 * (SK_ROWS / 2); idx += SK_WARPS * 32) {
+        const int tok = idx / (SK_ROWS / 2), r = idx % (SK_ROWS / 2);
+        const int m = m0 + tok, n = n0 + r;
+        if (m < row_end && n + 8 < N) {
+          float gate = 0.f, up = 0.f;
 #pragma unroll
-        for (int w = 0; w < SK_WARPS; ++w) s += red[w][tok][r];
-        C[(size_t)m * N + n] = from_f<OutT>(s);
+          for (int w = 0; w < SK_WARPS; ++w) {
+            gate += red[w][tok][r];
+            up += red[w][tok][r + 8];
+          }
+          C[(size_t)m * (N / 2) + n0 / 2 + r] = from_f<OutT>(gate / (1.f + expf(-gate)) * up);
+        }
+      }
+    } else {
+      for (int idx = threadIdx.x; idx < MT * 8 * SK_ROWS; idx += SK_WARPS * 32) {
+        const int tok = idx / SK_ROWS, r = idx % SK_ROWS;
+        const int m = m0 + tok, n = n0 + r;
+        if (m < row_end && n < N) {
+          float s = 0.f;
+#pragma unroll
+          for (int w = 0; w < SK_WARPS; ++w) s += red[w][tok][r];
+          C[(size_t)m * N + n] = from_f<OutT>(s);
+        }
       }
     }
   }
@@ -130,32 +149,36 @@ gemm_skinny_kernel(const bf16* __restrict__ A, const bf16* __restrict__ W, OutT*
 
 template <int MT>
 static int launch_skinny(const void* A, const void* W, void* C, int M, int N, int K, const int* a_rows,
-                         int a_div, const int* offsets, int groups, int out_f32, cudaStream_t stream) {
+                         int a_div, const int* offsets, int groups, int out_f32, int swiglu, cudaStream_t stream) {
   dim3 grid((N + SK_ROWS - 1) / SK_ROWS, offsets ? groups : 1);
-  if (out_f32)
-    gemm_skinny_kernel<MT, float><<<grid, SK_WARPS * 32, 0, stream>>>(
-        static_cast<const bf16*>(A), static_cast<const bf16*>(W), static_cast<float*>(C), M, N, K, a_rows,
-        a_div, offsets);
+  const bf16 *a = static_cast<const bf16*>(A), *w = static_cast<const bf16*>(W);
+  if (swiglu)
+    gemm_skinny_kernel<MT, bf16, true><<<grid, SK_WARPS * 32, 0, stream>>>(a, w, static_cast<bf16*>(C), M, N, K,
+                                                                           a_rows, a_div, offsets);
+  else if (out_f32)
+    gemm_skinny_kernel<MT, float, false><<<grid, SK_WARPS * 32, 0, stream>>>(a, w, static_cast<float*>(C), M, N,
+                                                                             K, a_rows, a_div, offsets);
   else
-    gemm_skinny_kernel<MT, bf16><<<grid, SK_WARPS * 32, 0, stream>>>(
-        static_cast<const bf16*>(A), static_cast<const bf16*>(W), static_cast<bf16*>(C), M, N, K, a_rows,
-        a_div, offsets);
+    gemm_skinny_kernel<MT, bf16, false><<<grid, SK_WARPS * 32, 0, stream>>>(a, w, static_cast<bf16*>(C), M, N, K,
+                                                                            a_rows, a_div, offsets);
   SNK_LAUNCH_CHECK();
   return 0;
 }
 
 // rows_hint: the most rows one group (or the whole product) is expected to hold; picks how many
 // 8-token tiles a pass covers.  More rows than that still give the right result, in more passes.
+// swiglu: W is gate/up interleaved in blocks of 8 rows and C is [M, N/2] bfloat16 = silu(gate) * up.
 SNK_API int snk_gemm_skinny(const void* A, const void* W, void* C, int M, int N, int K, const int* a_rows,
-                            int a_div, const int* offsets, int groups, int rows_hint, int out_f32,
+                            int a_div, const int* offsets, int groups, int rows_hint, int out_f32, int swiglu,
                             cudaStream_t stream) {
   if (M <= 0 || N <= 0) return 0;
   if (K <= 0 || K % 8) return SNK_ERR_SIZE;
+  if (swiglu && (N % 16 || out_f32)) return SNK_ERR_SIZE;
   if (((uintptr_t)A % 16) || ((uintptr_t)W % 16)) return SNK_ERR_ALIGN;
   if (groups > 65535) return SNK_ERR_SIZE;
   if (a_div <= 0) a_div = 1;
-  if (rows_hint <= 8) return launch_skinny<1>(A, W, C, M, N, K, a_rows, a_div, offsets, groups, out_f32, stream);
-  if (rows_hint <= 16) return launch_skinny<2>(A, W, C, M, N, K, a_rows, a_div, offsets, groups, out_f32, stream);
-  if (rows_hint <= 32) return launch_skinny<4>(A, W, C, M, N, K, a_rows, a_div, offsets, groups, out_f32, stream);
-  return launch_skinny<8>(A, W, C, M, N, K, a_rows, a_div, offsets, groups, out_f32, stream);
+  if (rows_hint <= 8) return launch_skinny<1>(A, W, C, M, N, K, a_rows, a_div, offsets, groups, out_f32, swiglu, stream);
+  if (rows_hint <= 16) return launch_skinny<2>(A, W, C, M, N, K, a_rows, a_div, offsets, groups, out_f32, swiglu, stream);
+  if (rows_hint <= 32) return launch_skinny<4>(A, W, C, M, N, K, a_rows, a_div, offsets, groups, out_f32, swiglu, stream);
+  return launch_skinny<8>(A, W, C, M, N, K, a_rows, a_div, offsets, groups, out_f32, swiglu, stream);
 }

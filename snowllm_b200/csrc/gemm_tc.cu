@@ -183,7 +183,9 @@ __device__ __forceinline__ TcTile tc_tile(int tile, int row_tiles, int M, int N,
   return t;
 }
 
-template <int BN, typename OutT>
+// SWIGLU: W holds gate and up rows interleaved in blocks of 8 (rows 16j..16j+7: gate of features
+// 8j..8j+7, rows 16j+8..16j+15: their up rows); the store is silu(gate) * up into C[M, N/2].
+template <int BN, typename OutT, bool SWIGLU>
 __global__ void __launch_bounds__(TC_THREADS)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
                OutT* __restrict__ C, int M, int N, int K, const int* __restrict__ offsets, int groups,
@@ -295,7 +297,26 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
           __syncwarp();
           if (lane == 0) mbar_arrive(&sh->acc_empty[buf]);
         }
-        if (row < t.row_end && !*aborted) {
+        if constexpr (SWIGLU) {
+          if (row < t.row_end && !*aborted) {
+            OutT* dst = C + (size_t)row * (N / 2) + (t.n0 + c0) / 2;
+#pragma unroll
+            for (int blk = 0; blk < 2; ++blk) {
+              if (t.n0 + c0 + blk * 16 + 16 <= N) {
+                uint32_t p[4];
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                  const float g0 = __uint_as_float(r[blk * 16 + 2 * j]), g1 = __uint_as_float(r[blk * 16 + 2 * j + 1]);
+                  const float u0 = __uint_as_float(r[blk * 16 + 8 + 2 * j]), u1 = __uint_as_float(r[blk * 16 + 9 + 2 * j]);
+                  const __nv_bfloat162 v = __floats2bfloat162_rn(g0 / (1.f + expf(-g0)) * u0,
+                                                                 g1 / (1.f + expf(-g1)) * u1);
+                  p[j] = *reinterpret_cast<const uint32_t*>(&v);
+                }
+                *reinterpret_cast<uint4*>(dst + blk * 8) = make_uint4(p[0], p[1], p[2], p[3]);
+              }
+            }
+          }
+        } else if (row < t.row_end && !*aborted) {
           OutT* dst = C + (size_t)row * N + t.n0 + c0;
           if (vec_ok && t.n0 + c0 + 32 <= N) {
             if constexpr (sizeof(OutT) == 4) {
@@ -393,7 +414,7 @@ static int tensor_map(const void* ptr, long long rows, long long k, int box_rows
   return 0;
 }
 
-template <int BN, typename OutT>
+template <int BN, typename OutT, bool SWIGLU>
 static int launch_tc(const CUtensorMap& map_a, const CUtensorMap& map_w, void* C, int M, int N, int K,
                      const int* offsets, int groups, int row_tiles, cudaStream_t stream) {
   constexpr int STAGE_BYTES = (TC_BM + BN) * TC_BK * 2;
@@ -404,11 +425,11 @@ static int launch_tc(const CUtensorMap& map_a, const CUtensorMap& map_w, void* C
     int dev = 0;
     cudaGetDevice(&dev);
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-    cudaFuncSetAttribute(gemm_tc_kernel<BN, OutT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    cudaFuncSetAttribute(gemm_tc_kernel<BN, OutT, SWIGLU>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   }
   const long long tiles = (long long)row_tiles * ((N + BN - 1) / BN);
   const int blocks = (int)(tiles < sms ? tiles : sms);     // one block per SM (shared memory), persistent
-  gemm_tc_kernel<BN, OutT><<<blocks, TC_THREADS, smem, stream>>>(map_a, map_w, static_cast<OutT*>(C), M, N, K,
+  gemm_tc_kernel<BN, OutT, SWIGLU><<<blocks, TC_THREADS, smem, stream>>>(map_a, map_w, static_cast<OutT*>(C), M, N, K,
                                                                  offsets, groups, row_tiles);
   SNK_LAUNCH_CHECK();
   return 0;
@@ -417,9 +438,10 @@ static int launch_tc(const CUtensorMap& map_a, const CUtensorMap& map_w, void* C
 // M: rows of A (all groups together).  Grouped: offsets[groups+1] on the device, W = [groups, N, K];
 // max_row_tiles bounds the number of 128-row tiles over all groups (M/128 + groups is always enough).
 SNK_API int snk_gemm_tc(const void* A, const void* W, void* C, int M, int N, int K, const int* offsets,
-                        int groups, int max_row_tiles, int out_f32, cudaStream_t stream) {
+                        int groups, int max_row_tiles, int out_f32, int swiglu, cudaStream_t stream) {
   if (M <= 0 || N <= 0) return 0;
   if (K <= 0 || K % 8) return SNK_ERR_SIZE;                   // TMA: the row pitch is a multiple of 16 bytes
+  if (swiglu && (N % 16 || out_f32)) return SNK_ERR_SIZE;
   if (((uintptr_t)A % 16) || ((uintptr_t)W % 16) || ((uintptr_t)C % 16)) return SNK_ERR_ALIGN;
   const int row_tiles = offsets ? max_row_tiles : (M + TC_BM - 1) / TC_BM;
   if (row_tiles <= 0) return SNK_ERR_SIZE;
@@ -430,11 +452,11 @@ SNK_API int snk_gemm_tc(const void* A, const void* W, void* C, int M, int N, int
   if (rc) return rc;
   rc = tensor_map(W, (long long)(offsets ? groups : 1) * N, K, wide ? 256 : 128, &map_w);
   if (rc) return rc;
-  if (wide)
-    return out_f32 ? launch_tc<256, float>(map_a, map_w, C, M, N, K, offsets, groups, row_tiles, stream)
-                   : launch_tc<256, bf16>(map_a, map_w, C, M, N, K, offsets, groups, row_tiles, stream);
-  return out_f32 ? launch_tc<128, float>(map_a, map_w, C, M, N, K, offsets, groups, row_tiles, stream)
-                 : launch_tc<128, bf16>(map_a, map_w, C, M, N, K, offsets, groups, row_tiles, stream);
+#define TC_GO(BN_, T_, S_) launch_tc<BN_, T_, S_>(map_a, map_w, C, M, N, K, offsets, groups, row_tiles, stream)
+  if (swiglu) return wide ? TC_GO(256, bf16, true) : TC_GO(128, bf16, true);
+  if (wide) return out_f32 ? TC_GO(256, float, false) : TC_GO(256, bf16, false);
+  return out_f32 ? TC_GO(128, float, false) : TC_GO(128, bf16, false);
+#undef TC_GO
 }
 
 // 0, or the first error a block of any earlier launch recorded (a wait that ran out); reading clears

@@ -23,7 +23,7 @@ _SIGNATURES = {
         "snk_embedding": [P, P, P, I, I, I, I, P],
         "snk_add_rmsnorm": [P, P, P, I, P, P, I, I, F, I, P],
         "snk_residual_add": [P, P, LL, P],
-        "snk_swiglu": [P, P, I, I, I, P],
+        "snk_swiglu": [P, P, I, I, I, I, P],
     },
     "rope_cache": {
         "snk_qk_norm_rope_cache": [P, P, P, I, I, F, P, I, P, P, P, I, I, P, P, I, I, I, I, I, I, P],
@@ -43,10 +43,10 @@ _SIGNATURES = {
         "snk_gemm_simt": [P, P, P, I, I, I, P, I, P, I, I, I, I, P],
     },
     "gemm_skinny": {
-        "snk_gemm_skinny": [P, P, P, I, I, I, P, I, P, I, I, I, P],
+        "snk_gemm_skinny": [P, P, P, I, I, I, P, I, P, I, I, I, I, P],
     },
     "gemm_tc": {
-        "snk_gemm_tc": [P, P, P, I, I, I, P, I, I, I, P],
+        "snk_gemm_tc": [P, P, P, I, I, I, P, I, I, I, I, P],
         "snk_gemm_tc_status": [],
         "snk_gather_rows_bf16": [P, P, P, I, I, I, P],
     },
@@ -196,8 +196,9 @@ def residual_add(residual: torch.Tensor, delta: torch.Tensor) -> None:
     check(fn("snk_residual_add")(_ptr(residual), _ptr(delta), residual.numel(), _stream()), "residual_add")
 
 
-def swiglu(gate_up: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
-    """[M, 2I] (gate | up) -> [M, I]: silu(gate) * up."""
+def swiglu(gate_up: torch.Tensor, out: torch.Tensor | None = None, interleaved: bool = False) -> torch.Tensor:
+    """[M, 2I] -> [M, I]: silu(gate) * up.  Columns are (gate | up), or with ``interleaved`` blocks of 8
+    gate columns followed by the 8 up columns of the same features."""
     M, two_i = gate_up.shape
     _chk(gate_up, "swiglu input", (torch.float32, torch.bfloat16))
     if two_i % 2:
@@ -206,7 +207,8 @@ def swiglu(gate_up: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tens
     if out is None:
         out = torch.empty(M, inter, dtype=gate_up.dtype, device=gate_up.device)
     _chk(out, "swiglu output", gate_up.dtype, (M, inter))
-    check(fn("snk_swiglu")(_ptr(gate_up), _ptr(out), M, inter, code_of(gate_up.dtype), _stream()), "swiglu")
+    check(fn("snk_swiglu")(_ptr(gate_up), _ptr(out), M, inter, int(interleaved), code_of(gate_up.dtype), _stream()),
+          "swiglu")
     return out
 
 
@@ -390,7 +392,7 @@ def gemm_skinny_ok(a, w) -> bool:
 
 
 def gemm_skinny(a, w, out_dtype=None, out=None, a_rows=None, a_div=1, offsets=None, rows_out=None,
-                rows_hint=None):
+                rows_hint=None, swiglu=False):
     """bfloat16 a [M, K] times w [N, K]^T (or grouped w [G, N, K]) for few rows: W streams from memory
     once into tensor-core fragments.  ``rows_hint``: rows expected per group (sets the pass size)."""
     _chk(a, "gemm a", torch.bfloat16)
@@ -409,14 +411,15 @@ def gemm_skinny(a, w, out_dtype=None, out=None, a_rows=None, a_div=1, offsets=No
     if a_rows is not None:
         _chk(a_rows, "gemm row gather", torch.int32)
     out_dtype = out_dtype or torch.bfloat16
+    cols = N // 2 if swiglu else N          # swiglu: w rows are gate/up interleaved by 8, out = silu(gate) * up
     if out is None:
-        out = torch.empty(M, N, dtype=out_dtype, device=a.device)
-    _chk(out, "gemm out", out_dtype, (M, N))
-    if out_dtype not in (torch.bfloat16, torch.float32):
-        raise KernelError("gemm output is bfloat16 or float32")
+        out = torch.empty(M, cols, dtype=out_dtype, device=a.device)
+    _chk(out, "gemm out", out_dtype, (M, cols))
+    if out_dtype not in (torch.bfloat16, torch.float32) or (swiglu and out_dtype != torch.bfloat16):
+        raise KernelError("gemm output is bfloat16 or float32 (bfloat16 with swiglu)")
     check(fn("snk_gemm_skinny")(_ptr(a), _ptr(w), _ptr(out), M, N, K, _ptr(a_rows), int(a_div), _ptr(offsets),
                                 G, int(rows_hint if rows_hint is not None else M),
-                                int(out_dtype == torch.float32), _stream()), "gemm_skinny")
+                                int(out_dtype == torch.float32), int(swiglu), _stream()), "gemm_skinny")
     return out
 
 
@@ -429,7 +432,7 @@ def gemm_tc_ok(a, w) -> bool:
             and w.data_ptr() % 16 == 0)
 
 
-def gemm_tc(a, w, out_dtype=None, out=None, offsets=None):
+def gemm_tc(a, w, out_dtype=None, out=None, offsets=None, swiglu=False):
     """bfloat16 a [M, K] times w [N, K]^T on the tcgen05 tensor cores, float accumulation in tensor
     memory.  Grouped: w [G, N, K], rows of ``a`` sorted by group, ``offsets`` int32 [G+1]."""
     _chk(a, "gemm a", torch.bfloat16)
@@ -445,14 +448,15 @@ def gemm_tc(a, w, out_dtype=None, out=None, offsets=None):
     if Kw != K:
         raise KernelError(f"gemm: a has K={K}, w has K={Kw}")
     out_dtype = out_dtype or torch.bfloat16
+    cols = N // 2 if swiglu else N          # swiglu: w rows are gate/up interleaved by 8, out = silu(gate) * up
     if out is None:
-        out = torch.empty(M, N, dtype=out_dtype, device=a.device)
-    _chk(out, "gemm out", out_dtype, (M, N))
-    if out_dtype not in (torch.bfloat16, torch.float32):
-        raise KernelError("gemm output is bfloat16 or float32")
+        out = torch.empty(M, cols, dtype=out_dtype, device=a.device)
+    _chk(out, "gemm out", out_dtype, (M, cols))
+    if out_dtype not in (torch.bfloat16, torch.float32) or (swiglu and out_dtype != torch.bfloat16):
+        raise KernelError("gemm output is bfloat16 or float32 (bfloat16 with swiglu)")
     row_tiles = -(-M // TC_TILE) + (G if grouped else 0)
     check(fn("snk_gemm_tc")(_ptr(a), _ptr(w), _ptr(out), M, N, K, _ptr(offsets), G, row_tiles,
-                            int(out_dtype == torch.float32), _stream()), "gemm_tc")
+                            int(out_dtype == torch.float32), int(swiglu), _stream()), "gemm_tc")
     return out
 
 

@@ -40,3 +40,34 @@ def grouped_linear(x, w, offsets, rows_out, max_rows_per_group, a_rows=None, a_d
         return kernels.gemm_tc(xs, w, out_dtype=out_dtype, offsets=offsets)
     return kernels.gemm_simt(x, w, out_dtype=out_dtype, a_rows=a_rows, a_div=a_div, offsets=offsets,
                              rows_out=rows_out, max_rows_per_group=max_rows_per_group)
+
+
+def interleave_gate_up(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
+    """[..., I, K] gate and up rows -> [..., 2I, K] in blocks of 8 gate rows followed by the 8 up rows of
+    the same features: the layout whose product can apply SwiGLU at its store (I a multiple of 8)."""
+    *lead, I, K = gate.shape
+    both = torch.stack((gate.reshape(*lead, I // 8, 8, K), up.reshape(*lead, I // 8, 8, K)), dim=-3)
+    return both.reshape(*lead, 2 * I, K).contiguous()
+
+
+def linear_swiglu(x: torch.Tensor, w13: torch.Tensor, interleaved: bool) -> torch.Tensor:
+    """silu(x Wg^T) * (x Wu^T) -> [M, I] with Wg, Wu held in one matrix w13 [2I, K] (plain halves, or
+    interleaved by 8).  With the interleaved layout the bfloat16 products apply SwiGLU at their store."""
+    if interleaved and kernels.gemm_skinny_ok(x, w13):
+        if x.shape[0] <= SKINNY_MAX_ROWS:
+            return kernels.gemm_skinny(x, w13, swiglu=True)
+        return kernels.gemm_tc(x, w13, swiglu=True)
+    return kernels.swiglu(linear(x, w13), interleaved=interleaved)
+
+
+def grouped_linear_swiglu(x, w13, offsets, rows_out, max_rows_per_group, a_rows, a_div, interleaved: bool):
+    """The grouped form of ``linear_swiglu`` over rows sorted by group (w13 [G, 2I, K])."""
+    if interleaved and kernels.gemm_skinny_ok(x, w13):
+        if max_rows_per_group <= SKINNY_MAX_ROWS:
+            hint = min(max_rows_per_group, max(8, 2 * -(-rows_out // w13.shape[0])))
+            return kernels.gemm_skinny(x, w13, a_rows=a_rows, a_div=a_div, offsets=offsets, rows_out=rows_out,
+                                       rows_hint=hint, swiglu=True)
+        xs = kernels.gather_rows(x, a_rows, a_div) if a_rows is not None else x
+        return kernels.gemm_tc(xs, w13, offsets=offsets, swiglu=True)
+    h = grouped_linear(x, w13, offsets, rows_out, max_rows_per_group, a_rows=a_rows, a_div=a_div)
+    return kernels.swiglu(h, interleaved=interleaved)

@@ -1,11 +1,11 @@
 """Dense SwiGLU feed-forward: down(silu(gate x) * up x)
 (snowllm/models/lfm2/layers.py:76-88; snowllm/ops/mlp.py:12-20).  Gate and up are one fused
-product [2I, H]; the down product leaves a float delta for the residual sum."""
+product [2I, H] (rows interleaved by 8, so that the product's store applies SwiGLU); the down product leaves a float delta for the residual sum."""
 from __future__ import annotations
 
 import torch
 
-from ..ops import kernels, linear
+from ..ops import interleave_gate_up, linear, linear_swiglu
 from .base import Part
 from .registry import register_ffn
 from .spec import TensorSpec
@@ -26,11 +26,14 @@ class SwiGLU(Part):
                 TensorSpec("down", self.names["down"], (H, I))]
 
     def bind(self, tensors):
-        self.w13 = torch.cat((tensors["gate"], tensors["up"]), 0).contiguous()
+        # gate and up rows interleaved by 8 where the width allows: the product then applies SwiGLU itself
+        self.interleaved = self.intermediate_size % 8 == 0
+        self.w13 = (interleave_gate_up(tensors["gate"], tensors["up"]) if self.interleaved
+                    else torch.cat((tensors["gate"], tensors["up"]), 0).contiguous())
         self.w2 = tensors["down"]
 
     def forward(self, ctx, x):
-        act = kernels.swiglu(linear(x, self.w13))
+        act = linear_swiglu(x, self.w13, self.interleaved)
         return linear(act, self.w2, out_dtype=torch.float32)
 
 

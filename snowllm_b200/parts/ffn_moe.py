@@ -9,7 +9,7 @@ from __future__ import annotations
 
 import torch
 
-from ..ops import grouped_linear, kernels
+from ..ops import grouped_linear, grouped_linear_swiglu, interleave_gate_up, kernels
 from .base import Part
 from .registry import register_ffn
 from .spec import INIT_BIAS, KEEP_F32, KEEP_SMALL, TensorSpec
@@ -51,11 +51,15 @@ class SigmoidMoE(Part):
         self.router = tensors["router"]
         self.bias = tensors.get("expert_bias") if self.use_expert_bias else None
         if self._fused:
-            self.w13, self.w2 = tensors["gate_up"].contiguous(), tensors["down"].contiguous()
+            gate, up = tensors["gate_up"].chunk(2, dim=1)
+            self.w2 = tensors["down"].contiguous()
         else:
-            self.w13 = torch.stack([torch.cat((tensors[f"gate.{e}"], tensors[f"up.{e}"]), 0)
-                                    for e in range(E)]).contiguous()
+            gate = torch.stack([tensors[f"gate.{e}"] for e in range(E)])
+            up = torch.stack([tensors[f"up.{e}"] for e in range(E)])
             self.w2 = torch.stack([tensors[f"down.{e}"] for e in range(E)]).contiguous()
+        # gate and up rows interleaved by 8 where the width allows: the product then applies SwiGLU itself
+        self.interleaved = self.intermediate_size % 8 == 0
+        self.w13 = interleave_gate_up(gate, up) if self.interleaved else torch.cat((gate, up), 1).contiguous()
 
     def route(self, x):
         return kernels.moe_route(x, self.router, self.bias, self.top_k, self.norm_topk_prob,
@@ -68,8 +72,7 @@ class SigmoidMoE(Part):
             ctx.tap("moe_route", ids)
         offsets, pair_pos, sorted_pair = kernels.moe_sort(ids, self.num_experts)
         cap = min(M, M * k)          # an expert gets a token at most once
-        h = grouped_linear(x, self.w13, offsets, M * k, cap, a_rows=sorted_pair, a_div=k)
-        act = kernels.swiglu(h)
+        act = grouped_linear_swiglu(x, self.w13, offsets, M * k, cap, sorted_pair, k, self.interleaved)
         y = grouped_linear(act, self.w2, offsets, M * k, cap, out_dtype=torch.float32)
         return kernels.moe_combine(y, pair_pos, weights)
 

@@ -654,3 +654,25 @@ def test_attention_prefill_far_key_and_diagonal(K):
     assert (got[T - 1] - v[7, 0].repeat(nh)).abs().max() < 0.02
     close(got, ref_attention(q, k, v, list(range(T)), hd ** -0.5, None), dtype)
     assert torch.allclose(got[0], v[0, 0].repeat(nh), atol=1e-2)     # the first row sees its own key only
+
+
+# ---------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("M,I,K_", [(5, 24, 48), (64, 1792, 256), (65, 56, 72), (2000, 2048, 64)])
+def test_products_with_swiglu_store(K, M, I, K_):
+    """Gate and up rows interleaved by 8: the few-rows and the tcgen05 products store silu(gate) * up,
+    and the stand-alone kernel reads the same layout."""
+    from snowllm_b200.ops import interleave_gate_up, linear_swiglu
+    torch.manual_seed(50)
+    dtype = torch.bfloat16
+    x, gate, up = rnd(dtype, M, K_), rnd(dtype, I, K_, scale=K_ ** -0.5), rnd(dtype, I, K_, scale=K_ ** -0.5)
+    want = F.silu(x @ gate.T) * (x @ up.T)
+    w13 = interleave_gate_up(dev(gate, dtype), dev(up, dtype))
+    assert torch.equal(w13[:8].cpu().float(), gate[:8]) and torch.equal(w13[8:16].cpu().float(), up[:8])
+    got = linear_swiglu(dev(x, dtype), w13, True)
+    assert got.shape == (M, I) and got.dtype == dtype
+    close(got, want, dtype, scale=2)
+    for dt in DTYPES:         # the stand-alone kernel on the interleaved product
+        h = (x @ w13.cpu().float().T).to(dt)
+        close(K.swiglu(dev(h), interleaved=True), want, dt, scale=2)
+    if dtype == torch.bfloat16:
+        assert K.gemm_tc_status() == 0
