@@ -1,0 +1,159 @@
+"""One kernel at one shape, timed on the device: the small case that profiles are taken on.
+
+    python -m snowllm_b200.ops.microbench gemm_skinny --m 8 --n 3584 --k 2048 --groups 32 --active 21
+    python -m snowllm_b200.ops.microbench gemm_tc --m 2048 --n 6144 --k 2048
+    python -m snowllm_b200.ops.microbench attention_decode --batch 8 --context 8192
+    python -m snowllm_b200.ops.microbench attention_prefill --tokens 2048
+
+Prints one JSON line: microseconds per launch (CUDA events around ``--iters`` launches after 3 warm-up
+launches, a buffer larger than L2 written between launches) and the achieved GB/s or TFLOP/s from the
+bytes or flops the kernel has to move.  Inputs are seeded random values.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import sys
+
+import torch
+
+from . import kernels
+
+L2_FLUSH_BYTES = 256 << 20
+
+
+def timed(fn, iters: int, flush: bool = True) -> float:
+    """Mean microseconds of ``fn()`` over ``iters`` launches, L2 flushed before each."""
+    scrub = torch.empty(L2_FLUSH_BYTES, dtype=torch.uint8, device="cuda") if flush else None
+    for _ in range(3):
+        fn()
+    torch.cuda.synchronize()
+    total = 0.0
+    for _ in range(iters):
+        if scrub is not None:
+            scrub.fill_(1)
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        fn()
+        end.record()
+        torch.cuda.synchronize()
+        total += start.elapsed_time(end)
+    return total / iters * 1e3
+
+
+def bf16(*shape, scale=1.0, gen=None):
+    return (torch.randn(*shape, device="cuda", generator=gen) * scale).to(torch.bfloat16)
+
+
+def gemm_skinny(a):
+    gen = torch.Generator(device="cuda").manual_seed(0)
+    G = a.groups
+    w = bf16(G, a.n, a.k, scale=a.k ** -0.5, gen=gen) if G > 1 else bf16(a.n, a.k, scale=a.k ** -0.5, gen=gen)
+    if G > 1:
+        active = min(a.active or G, G)
+        rows = a.m * active                       # a.m rows for each group that owns rows
+        counts = [a.m if e < active else 0 for e in range(G)]
+        offsets = torch.tensor([0] + list(torch.tensor(counts).cumsum(0)), dtype=torch.int32, device="cuda")
+        x = bf16(rows, a.k, gen=gen)
+        fn = lambda: kernels.gemm_skinny(x, w, offsets=offsets, rows_out=rows, rows_hint=a.m,
+                                         out_dtype=torch.float32 if a.f32 else None, swiglu=a.swiglu)
+        nbytes = active * a.n * a.k * 2
+    else:
+        x = bf16(a.m, a.k, gen=gen)
+        fn = lambda: kernels.gemm_skinny(x, w, out_dtype=torch.float32 if a.f32 else None, swiglu=a.swiglu)
+        nbytes = a.n * a.k * 2
+    us = timed(fn, a.iters)
+    return {"us": us, "GB/s": nbytes / us / 1e3, "bytes": nbytes}
+
+
+def gemm_tc(a):
+    gen = torch.Generator(device="cuda").manual_seed(0)
+    G = a.groups
+    if G > 1:
+        w = bf16(G, a.n, a.k, scale=a.k ** -0.5, gen=gen)
+        per = a.m // G
+        offsets = torch.arange(0, G + 1, dtype=torch.int32, device="cuda") * per
+        x = bf16(per * G, a.k, gen=gen)
+        fn = lambda: kernels.gemm_tc(x, w, offsets=offsets, out_dtype=torch.float32 if a.f32 else None,
+                                     swiglu=a.swiglu)
+        flops = 2.0 * per * G * a.n * a.k
+    else:
+        w, x = bf16(a.n, a.k, scale=a.k ** -0.5, gen=gen), bf16(a.m, a.k, gen=gen)
+        fn = lambda: kernels.gemm_tc(x, w, out_dtype=torch.float32 if a.f32 else None, swiglu=a.swiglu)
+        flops = 2.0 * a.m * a.n * a.k
+    us = timed(fn, a.iters)
+    assert kernels.gemm_tc_status() == 0
+    return {"us": us, "TFLOP/s": flops / us / 1e6, "flops": flops}
+
+
+def _cache(a, tokens_each, batch):
+    gen = torch.Generator(device="cuda").manual_seed(0)
+    P = a.page_size
+    pages_each = -(-tokens_each // P)
+    pool = bf16(batch * pages_each, 2, a.kv_heads, P, a.head_dim, gen=gen)
+    perm = torch.randperm(batch * pages_each, generator=torch.Generator().manual_seed(1)).to(torch.int32)
+    return pool, perm.view(batch, pages_each).cuda(), gen
+
+
+def attention_decode(a):
+    pool, bt, gen = _cache(a, a.context, a.batch)
+    q = bf16(a.batch, a.heads, a.head_dim, gen=gen)
+    positions = torch.full((a.batch,), a.context - 1, dtype=torch.int32, device="cuda")
+    row_seg = torch.arange(a.batch, dtype=torch.int32, device="cuda")
+    chunk = a.chunk
+    n = -(-a.context // chunk)
+    scratch = torch.empty(kernels.attention_scratch_bytes(a.batch, a.heads, a.head_dim, n), dtype=torch.uint8,
+                          device="cuda")
+    out = torch.empty(a.batch, a.heads * a.head_dim, dtype=torch.bfloat16, device="cuda")
+    fn = lambda: kernels.paged_attention(q, pool, bt, a.page_size, positions, row_seg, a.head_dim ** -0.5,
+                                         chunk=chunk, num_chunks=n, scratch=scratch, out=out)
+    nbytes = a.batch * a.context * 2 * a.kv_heads * a.head_dim * 2
+    us = timed(fn, a.iters)
+    return {"us": us, "GB/s": nbytes / us / 1e3, "bytes": nbytes}
+
+
+def attention_prefill(a):
+    from ..engine.context import prefill_tiles
+    pool, bt, gen = _cache(a, a.tokens, 1)
+    q = bf16(a.tokens, a.heads, a.head_dim, gen=gen)
+    tiles, _ = prefill_tiles([0], [a.tokens], kernels.PREFILL_TILE_ROWS)
+    tiles = torch.tensor(tiles, dtype=torch.int32, device="cuda")
+    out = torch.empty(a.tokens, a.heads * a.head_dim, dtype=torch.bfloat16, device="cuda")
+    fn = lambda: kernels.attention_prefill(q, pool, bt, a.page_size, tiles, a.head_dim ** -0.5, out)
+    flops = 4.0 * a.heads * a.head_dim * a.tokens * (a.tokens + 1) / 2
+    us = timed(fn, a.iters)
+    return {"us": us, "TFLOP/s": flops / us / 1e6, "flops": flops}
+
+
+KINDS = {"gemm_skinny": gemm_skinny, "gemm_tc": gemm_tc, "attention_decode": attention_decode,
+         "attention_prefill": attention_prefill}
+
+
+def main(argv=None) -> int:
+    ap = argparse.ArgumentParser(prog="python -m snowllm_b200.ops.microbench", description=__doc__.split("\n\n")[0])
+    ap.add_argument("kind", choices=sorted(KINDS))
+    ap.add_argument("--m", type=int, default=8)
+    ap.add_argument("--n", type=int, default=3584)
+    ap.add_argument("--k", type=int, default=2048)
+    ap.add_argument("--groups", type=int, default=1)
+    ap.add_argument("--active", type=int, default=0, help="groups that own rows (gemm_skinny)")
+    ap.add_argument("--f32", action="store_true", help="float32 output")
+    ap.add_argument("--swiglu", action="store_true", help="SwiGLU at the store (w rows interleaved by 8)")
+    ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--context", type=int, default=8192)
+    ap.add_argument("--tokens", type=int, default=2048)
+    ap.add_argument("--heads", type=int, default=32)
+    ap.add_argument("--kv-heads", type=int, default=8)
+    ap.add_argument("--head-dim", type=int, default=64)
+    ap.add_argument("--page-size", type=int, default=16)
+    ap.add_argument("--chunk", type=int, default=256)
+    ap.add_argument("--iters", type=int, default=20)
+    a = ap.parse_args(argv)
+    out = {"kernel": a.kind, **{k: v for k, v in vars(a).items() if k != "kind"}}
+    out.update({k: (round(v, 2) if isinstance(v, float) else v) for k, v in KINDS[a.kind](a).items()})
+    print(json.dumps(out))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())
