@@ -14,31 +14,10 @@
 #define ROUTE_THREADS 128
 #define ROUTE_MAX_EXPERTS 1024
 
-template <typename T>
-__global__ void moe_route_kernel(const T* __restrict__ x, SmallVec wr, const float* __restrict__ bias,
-                                 int* __restrict__ topk_ids, float* __restrict__ topk_w, int H, int E,
-                                 int k, int norm_topk, float scaling) {
-  extern __shared__ float sh[];
-  float* xs = sh;                // H
-  float* prob = xs + H;          // E
-  float* score = prob + E;       // E
-  const int m = blockIdx.x;
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarp = blockDim.x >> 5;
-  const T* xr = x + (size_t)m * H;
-  for (int i = threadIdx.x; i < H; i += blockDim.x) xs[i] = to_f<T>(xr[i]);
-  __syncthreads();
-  for (int e = warp; e < E; e += nwarp) {
-    float acc = 0.f;
-    for (int i = lane; i < H; i += 32) acc = fmaf(xs[i], wr[(size_t)e * H + i], acc);
-    acc = warp_sum(acc);
-    if (lane == 0) {
-      const float p = 1.f / (1.f + expf(-acc));
-      prob[e] = p;
-      score[e] = bias ? p + bias[e] : p;
-    }
-  }
-  __syncthreads();
-  if (warp != 0) return;
+// The k largest of score[] (ties to the lower index, NaN never wins) by one warp; weights from prob[],
+// normalised by (sum + 1e-6) when asked, times the scaling factor.  score[] is consumed.
+__device__ __forceinline__ void select_topk(float* prob, float* score, int* ids, float* wts, int E, int k,
+                                            int norm_topk, float scaling, int lane) {
   float wsum = 0.f;
   float my_w = 0.f;              // lane j keeps the weight of pick j (k <= 32 per round)
   int my_id = 0;
@@ -66,18 +45,76 @@ __global__ void moe_route_kernel(const T* __restrict__ x, SmallVec wr, const flo
       // flush this round of up to 32 picks; the normaliser is applied in a second pass
       const int base = j & ~31;
       if (base + lane <= j) {
-        topk_ids[(size_t)m * k + base + lane] = my_id;
-        topk_w[(size_t)m * k + base + lane] = my_w;
+        ids[base + lane] = my_id;
+        wts[base + lane] = my_w;
       }
     }
   }
   __syncwarp();
   const float mul = (norm_topk ? 1.f / (wsum + 1e-6f) : 1.f);
   for (int j = lane; j < k; j += 32) {
-    float w = topk_w[(size_t)m * k + j];
+    float w = wts[j];
     w = norm_topk ? w * mul : w;
-    topk_w[(size_t)m * k + j] = w * scaling;
+    wts[j] = w * scaling;
   }
+}
+
+template <typename T>
+__global__ void moe_route_kernel(const T* __restrict__ x, SmallVec wr, const float* __restrict__ bias,
+                                 int* __restrict__ topk_ids, float* __restrict__ topk_w, int H, int E,
+                                 int k, int norm_topk, float scaling) {
+  extern __shared__ float sh[];
+  float* xs = sh;                // H
+  float* prob = xs + H;          // E
+  float* score = prob + E;       // E
+  const int m = blockIdx.x;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarp = blockDim.x >> 5;
+  const T* xr = x + (size_t)m * H;
+  for (int i = threadIdx.x; i < H; i += blockDim.x) xs[i] = to_f<T>(xr[i]);
+  __syncthreads();
+  for (int e = warp; e < E; e += nwarp) {
+    float acc = 0.f;
+    for (int i = lane; i < H; i += 32) acc = fmaf(xs[i], wr[(size_t)e * H + i], acc);
+    acc = warp_sum(acc);
+    if (lane == 0) {
+      const float p = 1.f / (1.f + expf(-acc));
+      prob[e] = p;
+      score[e] = bias ? p + bias[e] : p;
+    }
+  }
+  __syncthreads();
+  if (warp != 0) return;
+  select_topk(prob, score, topk_ids + (size_t)m * k, topk_w + (size_t)m * k, E, k, norm_topk, scaling, lane);
+}
+
+// One warp per token: probabilities and selection from float logits [M, E] that a matrix product left.
+__global__ void moe_topk_kernel(const float* __restrict__ logits, const float* __restrict__ bias,
+                                int* __restrict__ topk_ids, float* __restrict__ topk_w, int M, int E, int k,
+                                int norm_topk, float scaling) {
+  extern __shared__ float sh[];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarp = blockDim.x >> 5;
+  const int m = blockIdx.x * nwarp + warp;
+  if (m >= M) return;
+  float* prob = sh + (size_t)warp * 2 * E;
+  float* score = prob + E;
+  for (int e = lane; e < E; e += 32) {
+    const float p = 1.f / (1.f + expf(-logits[(size_t)m * E + e]));
+    prob[e] = p;
+    score[e] = bias ? p + bias[e] : p;
+  }
+  __syncwarp();
+  select_topk(prob, score, topk_ids + (size_t)m * k, topk_w + (size_t)m * k, E, k, norm_topk, scaling, lane);
+}
+
+SNK_API int snk_moe_topk(const float* logits, const float* bias, int* topk_ids, float* topk_w, int M, int E,
+                         int k, int norm_topk, float scaling, cudaStream_t stream) {
+  if (M <= 0) return 0;
+  if (E <= 0 || E > ROUTE_MAX_EXPERTS || k <= 0 || k > E) return SNK_ERR_SIZE;
+  const int warps = 4;
+  moe_topk_kernel<<<(M + warps - 1) / warps, warps * 32, (size_t)warps * 2 * E * sizeof(float), stream>>>(
+      logits, bias, topk_ids, topk_w, M, E, k, norm_topk, scaling);
+  SNK_LAUNCH_CHECK();
+  return 0;
 }
 
 SNK_API int snk_moe_route(const void* x, const void* wr, int wr_is_f32, const float* bias,

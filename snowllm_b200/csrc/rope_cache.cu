@@ -19,12 +19,18 @@ __global__ void qk_norm_rope_cache_kernel(
     const int* __restrict__ row_seg, const int* __restrict__ block_table, int max_pages,
     int page_size, T* __restrict__ pool, T* __restrict__ q_out, int nh, int nkv, int hd,
     int write_kv) {
-  extern __shared__ float sh[];            // one head per warp: hd floats each
+  extern __shared__ float sh[];            // one head per warp: hd floats each; then cos, sin of the row
   const int warps = blockDim.x >> 5, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int m = blockIdx.x;
-  const int head = blockIdx.y * warps + warp;
   const int total_heads = write_kv ? nh + 2 * nkv : nh;
-  if (head >= total_heads) return;
+  float* cs_tab = sh + (size_t)warps * hd;
+  float* sn_tab = cs_tab + (rot_dim >> 1);
+  if (inv_freq != nullptr) {               // the row's angles once, for all of its heads
+    const float posf = (float)positions[m];
+    for (int i = threadIdx.x; i < (rot_dim >> 1); i += blockDim.x) sincosf(posf * inv_freq[i], &sn_tab[i], &cs_tab[i]);
+  }
+  __syncthreads();
+  for (int head = warp; head < total_heads; head += warps) {
   float* buf = sh + (size_t)warp * hd;
   // A layer that reads another layer's cache projects q only: its rows hold no k, v.
   const int row_width = (write_kv ? nh + 2 * nkv : nh) * hd;
@@ -64,16 +70,13 @@ __global__ void qk_norm_rope_cache_kernel(
         }
       __syncwarp();
       const int half = rot_dim >> 1;
-      const float pos = (float)positions[m];
 #pragma unroll
       for (int j = 0; j < ROPE_MAX_PER_LANE; ++j)
         if (j < per) {
           const int d = lane + 32 * j;
           if (d < rot_dim) {
             const int i = d < half ? d : d - half;
-            const float ang = pos * inv_freq[i];
-            float sn, cs;
-            sincosf(ang, &sn, &cs);
+            const float sn = sn_tab[i], cs = cs_tab[i];
             const float other = d < half ? -buf[d + half] : buf[d - half];
             x[j] = x[j] * cs + other * sn;
           }
@@ -95,6 +98,8 @@ __global__ void qk_norm_rope_cache_kernel(
       const int d = lane + 32 * j;
       if (d < hd) dst[d] = from_f<T>(x[j]);
     }
+  __syncwarp();                              // buf is reused by the warp's next head
+  }
 }
 
 SNK_API int snk_qk_norm_rope_cache(
@@ -104,10 +109,10 @@ SNK_API int snk_qk_norm_rope_cache(
     int nkv, int hd, int write_kv, int dtype, cudaStream_t stream) {
   if (M <= 0) return 0;
   if (hd <= 0 || hd > 32 * ROPE_MAX_PER_LANE || rot_dim > hd || (rot_dim & 1)) return SNK_ERR_SIZE;
-  const int warps = 4;
   const int total_heads = write_kv ? nh + 2 * nkv : nh;
-  dim3 grid(M, (total_heads + warps - 1) / warps);
-  const size_t smem = (size_t)warps * hd * sizeof(float);
+  const int warps = total_heads >= 8 ? 8 : (total_heads >= 4 ? 4 : 2);
+  dim3 grid(M);
+  const size_t smem = ((size_t)warps * hd + rot_dim) * sizeof(float);
   SmallVec qg{q_gamma, gamma_is_f32}, kg{k_gamma, gamma_is_f32};
   SNK_DISPATCH(dtype, qk_norm_rope_cache_kernel<T><<<grid, warps * 32, smem, stream>>>(
                           static_cast<const T*>(qkv), qg, kg, has_norm, eps, inv_freq, rot_dim,

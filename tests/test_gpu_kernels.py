@@ -366,6 +366,14 @@ def test_moe_route(K, dtype, E, k, H, norm, use_bias, scaling):
     # float32 router weights with bfloat16 activations give the same
     ids2, _ = K.moe_route(dev(x, dtype), dev(wr), dev(bias) if use_bias else None, k, norm, scaling)
     assert torch.equal(ids2.cpu()[clear], ids.cpu()[clear])
+    if dtype == torch.bfloat16 and H % 8 == 0:      # many rows: logits by the tensor-core product
+        xm = rnd(dtype, 300, H)
+        ids3, w3 = K.moe_route(dev(xm, dtype), dev(wr, dtype), dev(bias) if use_bias else None, k, norm, scaling)
+        mg = []
+        want3, ww3 = plain.route(xm, wr, bias, k, norm, scaling, margins=mg)
+        ok = mg[0] > 1e-4
+        assert ok.float().mean() > 0.9 and torch.equal(ids3.cpu().long()[ok], want3[ok])
+        assert torch.allclose(w3.cpu()[ok], ww3[ok], atol=1e-5, rtol=1e-4)
 
 
 def test_moe_route_ties_go_to_the_lower_index_and_bias_only_selects(K):
