@@ -280,6 +280,23 @@ SNK_API int snk_paged_attention_rows(const void* q, const void* pool, const int*
   return 0;
 }
 
+// The second half of a chunked launch on its own: adds the chunks' partial results (scratch in the
+// layout above) in chunk order.  For partials written by another kernel (csrc/attention_mma.cu).
+SNK_API int snk_attention_merge(const void* scratch, const int* positions, void* out, int M, int nh, int hd,
+                                int window, int chunk, int num_chunks, int dtype, const int* row_list,
+                                cudaStream_t stream) {
+  if (M <= 0 || num_chunks <= 1) return 0;
+  const float* part_o = static_cast<const float*>(scratch);
+  const float* part_ml = part_o + (size_t)M * nh * num_chunks * hd;
+  dim3 mgrid(M, nh);
+  const int threads = hd <= 32 ? 32 : (hd <= 64 ? 64 : 128);
+  SNK_DISPATCH(dtype, attention_merge_kernel<T><<<mgrid, threads, 0, stream>>>(
+                          part_o, part_ml, positions, static_cast<T*>(out), nh, hd, window, chunk, num_chunks,
+                          row_list));
+  SNK_LAUNCH_CHECK();
+  return 0;
+}
+
 SNK_API int snk_paged_attention(const void* q, const void* pool, const int* block_table,
                                 int max_pages, int page_size, const int* positions,
                                 const int* row_seg, void* out, void* scratch, int M, int nh,

@@ -1,5 +1,7 @@
-// Causal grouped-query attention for prompt portions in bfloat16, on the tensor cores.
+// Causal grouped-query attention in bfloat16 on the tensor cores (mma.sync): a kernel for prompt
+// portions and, below, one for the rows of decoded tokens.
 //
+// Prompt portions.
 // One block takes 64 consecutive rows of one request's portion and one q head and walks that
 // request's cached keys in tiles of 64, from the first key any of its rows may see to the last
 // row's own position (flash attention: running max and sum per row in float, the output
@@ -14,8 +16,8 @@
 //   tests/test_lfm2_long_attention.py:36-47)
 //
 // The tile order is fixed by positions alone, so a row's result does not depend on what else the
-// launch holds.  Head sizes 64 and 128; other sizes, float32 and rows of short segments go through
-// csrc/attention.cu.  Pool layout: [page, 2 (k, v), kv head, page_size, head_dim].
+// launch holds.  Head sizes 64 and 128; other sizes and float32 go through csrc/attention.cu.
+// Pool layout: [page, 2 (k, v), kv head, page_size, head_dim].
 #include "common.cuh"
 
 #define FA_BQ 64
@@ -253,6 +255,220 @@ SNK_API int snk_attention_prefill(const void* q, const void* pool, const int* bl
     cudaFuncSetAttribute(attention_prefill_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     attention_prefill_kernel<128><<<grid, FA_WARPS * 32, smem, stream>>>(qp, pp, block_table, max_pages, page_size,
                                                                          tiles, op, nh, nkv, window, scale_log2);
+  }
+  SNK_LAUNCH_CHECK();
+  return 0;
+}
+
+
+// ---------------------------------------------------------------------------------------------
+// Rows of decoded tokens (one row per request, a long run of keys each).  One block takes one row, one
+// kv head and one chunk of 256 keys.  The q heads that share the kv head are the rows of the MMA (up to
+// 16), so the chunk's keys and values are read once for all of them.  Each of the 4 warps multiplies
+// the heads with its own 64 keys; the 4 partial (max, sum, output) meet in shared memory in warp
+// order, and the chunk's partial goes to scratch in the format of csrc/attention.cu, whose merge
+// kernel adds the chunks in order (num_chunks == 1: the block writes the output itself).
+#define FD_CHUNK 256
+
+template <int HD>
+__global__ void __launch_bounds__(FA_WARPS * 32)
+attention_decode_mma_kernel(const bf16* __restrict__ q, const bf16* __restrict__ pool,
+                            const int* __restrict__ block_table, int max_pages, int page_size,
+                            const int* __restrict__ positions, const int* __restrict__ row_seg,
+                            const int* __restrict__ row_list, bf16* __restrict__ out,
+                            float* __restrict__ part_o, float* __restrict__ part_ml, int nh, int nkv,
+                            int window, int num_chunks, float scale_log2) {
+  constexpr int CH = HD / 8, KT = HD / 16, NT = HD / 8;
+  extern __shared__ __align__(16) unsigned char fd_smem[];
+  const uint32_t sm_q = (uint32_t)__cvta_generic_to_shared(fd_smem);        // [16][HD]
+  const uint32_t sm_k = sm_q + 16 * HD * 2;                                 // [256][HD]
+  const uint32_t sm_v = sm_k + FD_CHUNK * HD * 2;                           // [256][HD]
+  float* merge = reinterpret_cast<float*>(fd_smem + 16 * HD * 2);           // reuses the key tile afterwards
+
+  const int m = row_list ? row_list[blockIdx.x] : blockIdx.x;
+  const int kvh = blockIdx.y;
+  const int group = nh / nkv;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int g = lane >> 2, t = lane & 3;
+  const int pos = positions[m];
+  const int lo = window > 0 ? max(0, pos - window + 1) : 0;
+  const int c = lo / FD_CHUNK + blockIdx.z;
+  if ((long long)c * FD_CHUNK > pos) return;
+  const int k0 = c * FD_CHUNK;
+  const int k_begin = max(lo, k0), k_end = min(pos + 1, k0 + FD_CHUNK);
+  const int* bt = block_table + (size_t)row_seg[m] * max_pages;
+  const size_t page_stride = (size_t)2 * nkv * page_size * HD;
+  const size_t v_off = (size_t)nkv * page_size * HD;
+
+  for (int v = threadIdx.x; v < 16 * CH; v += FA_WARPS * 32) {
+    const int r = v / CH, cc = v % CH;
+    fa_cp_async16(sm_q + swz<CH>(r, cc), q + ((size_t)m * nh + kvh * group + min(r, group - 1)) * HD + cc * 8,
+                  r < group);
+  }
+  for (int v = threadIdx.x; v < FD_CHUNK * CH; v += FA_WARPS * 32) {
+    const int r = v / CH, cc = v % CH;
+    const int kp = k0 + r;
+    const bool valid = kp >= k_begin && kp < k_end;
+    const bf16* src = pool;
+    if (valid) {
+      const int page = bt[kp / page_size];
+      src = pool + (size_t)page * page_stride + ((size_t)kvh * page_size + kp % page_size) * HD + cc * 8;
+    }
+    fa_cp_async16(sm_k + swz<CH>(r, cc), src, valid);
+    fa_cp_async16(sm_v + swz<CH>(r, cc), valid ? src + v_off : src, valid);
+  }
+  fa_commit();
+  fa_wait<0>();
+  __syncthreads();
+
+  float acc_o[NT][4];
+#pragma unroll
+  for (int i = 0; i < NT; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) acc_o[i][j] = 0.f;
+  float row_max[2] = {-INFINITY, -INFINITY}, row_sum[2] = {0.f, 0.f};
+  const int w0 = k0 + warp * FA_BK;                       // first key of this warp's 64
+  if (w0 < k_end && w0 + FA_BK > k_begin) {
+    uint32_t qf[KT][4];
+#pragma unroll
+    for (int k = 0; k < KT; ++k) {
+      const int r = (lane & 7) + 8 * ((lane >> 3) & 1), cc = 2 * k + (lane >> 4);
+      ldmatrix_x4(sm_q + swz<CH>(r, cc), qf[k][0], qf[k][1], qf[k][2], qf[k][3]);
+    }
+    float s[FA_BK / 8][4];
+#pragma unroll
+    for (int i = 0; i < FA_BK / 8; ++i)
+#pragma unroll
+      for (int j = 0; j < 4; ++j) s[i][j] = 0.f;
+#pragma unroll
+    for (int k = 0; k < KT; ++k) {
+#pragma unroll
+      for (int n = 0; n < FA_BK / 16; ++n) {
+        uint32_t b0, b1, b2, b3;
+        const int r = warp * FA_BK + n * 16 + (lane & 7) + 8 * (lane >> 4), cc = 2 * k + ((lane >> 3) & 1);
+        ldmatrix_x4(sm_k + swz<CH>(r, cc), b0, b1, b2, b3);
+        fa_mma(s[2 * n], qf[k][0], qf[k][1], qf[k][2], qf[k][3], b0, b1);
+        fa_mma(s[2 * n + 1], qf[k][0], qf[k][1], qf[k][2], qf[k][3], b2, b3);
+      }
+    }
+    // s[i] = {(head g, key 8i+2t), (g, 8i+2t+1), (g+8, ...), (g+8, ...)}: every head sees the same keys
+    float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+    for (int i = 0; i < FA_BK / 8; ++i) {
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int kp = w0 + 8 * i + 2 * t + (j & 1);
+        s[i][j] = (kp >= k_begin && kp < k_end) ? s[i][j] * scale_log2 : -INFINITY;
+        mx[j >> 1] = fmaxf(mx[j >> 1], s[i][j]);
+      }
+    }
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 1));
+      mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 2));
+      row_max[h] = mx[h];                                 // finite: the warp has a valid key
+    }
+    uint32_t pf[FA_BK / 16][4];
+#pragma unroll
+    for (int i = 0; i < FA_BK / 8; ++i) {
+      const float p0 = exp2f(s[i][0] - mx[0]), p1 = exp2f(s[i][1] - mx[0]);
+      const float p2 = exp2f(s[i][2] - mx[1]), p3 = exp2f(s[i][3] - mx[1]);
+      row_sum[0] += p0 + p1;
+      row_sum[1] += p2 + p3;
+      pf[i >> 1][(i & 1) * 2] = pack_bf16(p0, p1);
+      pf[i >> 1][(i & 1) * 2 + 1] = pack_bf16(p2, p3);
+    }
+#pragma unroll
+    for (int kk = 0; kk < FA_BK / 16; ++kk) {
+#pragma unroll
+      for (int n = 0; n < NT / 2; ++n) {
+        uint32_t b0, b1, b2, b3;
+        const int r = warp * FA_BK + kk * 16 + (lane & 7) + 8 * ((lane >> 3) & 1), cc = 2 * n + (lane >> 4);
+        ldmatrix_x4_trans(sm_v + swz<CH>(r, cc), b0, b1, b2, b3);
+        fa_mma(acc_o[2 * n], pf[kk][0], pf[kk][1], pf[kk][2], pf[kk][3], b0, b1);
+        fa_mma(acc_o[2 * n + 1], pf[kk][0], pf[kk][1], pf[kk][2], pf[kk][3], b2, b3);
+      }
+    }
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      row_sum[h] += __shfl_xor_sync(0xffffffffu, row_sum[h], 1);
+      row_sum[h] += __shfl_xor_sync(0xffffffffu, row_sum[h], 2);
+    }
+  }
+  __syncthreads();                                        // all warps are done with the key tile: reuse it
+  // merge area: ml [4 warps][16 heads][2], then o [4 warps][16 heads][HD]
+  float* ml = merge;
+  float* mo = merge + FA_WARPS * 16 * 2;
+  if (t == 0) {
+    ml[(warp * 16 + g) * 2] = row_max[0];
+    ml[(warp * 16 + g) * 2 + 1] = row_sum[0];
+    ml[(warp * 16 + g + 8) * 2] = row_max[1];
+    ml[(warp * 16 + g + 8) * 2 + 1] = row_sum[1];
+  }
+#pragma unroll
+  for (int i = 0; i < NT; ++i) {
+    const int d = 8 * i + 2 * t;
+    mo[(warp * 16 + g) * HD + d] = acc_o[i][0];
+    mo[(warp * 16 + g) * HD + d + 1] = acc_o[i][1];
+    mo[(warp * 16 + g + 8) * HD + d] = acc_o[i][2];
+    mo[(warp * 16 + g + 8) * HD + d + 1] = acc_o[i][3];
+  }
+  __syncthreads();
+  for (int idx = threadIdx.x; idx < group * HD; idx += FA_WARPS * 32) {
+    const int r = idx / HD, d = idx % HD;
+    float mxl = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < FA_WARPS; ++w) mxl = fmaxf(mxl, ml[(w * 16 + r) * 2]);
+    float l = 0.f, o = 0.f;
+#pragma unroll
+    for (int w = 0; w < FA_WARPS; ++w) {                  // warps in key order
+      const float f = exp2f(ml[(w * 16 + r) * 2] - mxl);  // a warp without keys: exp2(-inf) = 0
+      l += ml[(w * 16 + r) * 2 + 1] * f;
+      o = fmaf(mo[(w * 16 + r) * HD + d], f, o);
+    }
+    const int head = kvh * group + r;
+    if (num_chunks == 1) {
+      out[((size_t)m * nh + head) * HD + d] = __float2bfloat16_rn(o / l);
+    } else {
+      const size_t slot = ((size_t)blockIdx.x * nh + head) * num_chunks + blockIdx.z;
+      part_o[slot * HD + d] = o;
+      if (d == 0) {
+        part_ml[slot * 2] = mxl * 0.6931471805599453f;   // the merge kernel works with natural exponents
+        part_ml[slot * 2 + 1] = l;
+      }
+    }
+  }
+}
+
+// rows: M rows to serve (row_list, or rows 0..M-1); keys in chunks of 256; scratch as in
+// snk_paged_attention_scratch_bytes when num_chunks > 1 (the caller then runs snk_attention_merge).
+SNK_API int snk_attention_decode_mma(const void* q, const void* pool, const int* block_table, int max_pages,
+                                     int page_size, const int* positions, const int* row_seg,
+                                     const int* row_list, void* out, void* scratch, int M, int nh, int nkv,
+                                     int hd, int window, int num_chunks, float scale, cudaStream_t stream) {
+  if (M <= 0) return 0;
+  if (nkv <= 0 || nh % nkv || nh / nkv > 16 || nkv > 65535 || num_chunks < 1 || num_chunks > 65535)
+    return SNK_ERR_SIZE;
+  if (hd != 64 && hd != 128) return SNK_ERR_SIZE;
+  if (num_chunks > 1 && scratch == nullptr) return SNK_ERR_SIZE;
+  if (((uintptr_t)q % 16) || ((uintptr_t)pool % 16)) return SNK_ERR_ALIGN;
+  const float scale_log2 = scale * 1.4426950408889634f;
+  dim3 grid(M, nkv, num_chunks);
+  const size_t smem = (size_t)(16 + 2 * FD_CHUNK) * hd * 2;
+  float* part_o = static_cast<float*>(scratch);
+  float* part_ml = part_o ? part_o + (size_t)M * nh * num_chunks * hd : nullptr;
+  const bf16 *qp = static_cast<const bf16*>(q), *pp = static_cast<const bf16*>(pool);
+  bf16* op = static_cast<bf16*>(out);
+  if (hd == 64) {
+    cudaFuncSetAttribute(attention_decode_mma_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    attention_decode_mma_kernel<64><<<grid, FA_WARPS * 32, smem, stream>>>(
+        qp, pp, block_table, max_pages, page_size, positions, row_seg, row_list, op, part_o, part_ml, nh, nkv,
+        window, num_chunks, scale_log2);
+  } else {
+    cudaFuncSetAttribute(attention_decode_mma_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    attention_decode_mma_kernel<128><<<grid, FA_WARPS * 32, smem, stream>>>(
+        qp, pp, block_table, max_pages, page_size, positions, row_seg, row_list, op, part_o, part_ml, nh, nkv,
+        window, num_chunks, scale_log2);
   }
   SNK_LAUNCH_CHECK();
   return 0;

@@ -64,6 +64,16 @@ class StepContext:
             self._split = (dev_tiles, dev_rows, rows)
         return self._split
 
+    def attention_chunks(self, window=None, rows=None, chunk: int = ATTENTION_CHUNK) -> int:
+        """The most chunks of ``chunk`` keys that a row (of ``rows``, or of the step) spans."""
+        if self.fixed_chunks is not None:
+            return self.fixed_chunks
+        pos = self.host_positions if rows is None else self.host_positions[np.asarray(rows, dtype=np.int64)]
+        if len(pos) == 0:
+            return 1
+        lo = np.maximum(0, pos - window + 1) if window else np.zeros_like(pos)
+        return int((pos // chunk - lo // chunk).max()) + 1
+
     def attention_plan(self, window=None, rows=None) -> tuple[int, int]:
         """(chunk, num_chunks) for the attention kernel: with many rows one chunk per row, else
         chunks of ATTENTION_CHUNK keys so that long sequences spread over the GPU."""
@@ -71,7 +81,7 @@ class StepContext:
         plan = self._plans.get(key)
         if plan is None and self.fixed_chunks is not None:
             whole = (1 << 30) - ((1 << 30) % ATTENTION_TILE)
-            plan = (ATTENTION_CHUNK, self.fixed_chunks) if self.fixed_chunks > 1 else (whole, 1)
+            plan = (ATTENTION_CHUNK, self.fixed_chunks)     # a captured step: always chunks of fixed count
             self._plans[key] = plan
         if plan is None:
             whole = (1 << 30) - ((1 << 30) % ATTENTION_TILE)

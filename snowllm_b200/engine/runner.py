@@ -15,7 +15,7 @@ import torch
 from ..cache import CacheManager, RequestCache
 from ..errors import CapacityError, KernelError, SnowLLMError
 from ..ops import kernels
-from .context import ATTENTION_CHUNK, ATTENTION_ROWS_ENOUGH, HostStaging, StepContext
+from .context import ATTENTION_CHUNK, HostStaging, StepContext
 
 
 @dataclass
@@ -80,9 +80,7 @@ class ModelRunner:
         # the table width and the number of key chunks are part of the captured launches: both are
         # rounded up to a power of two so that a graph serves a range of lengths
         width = _pow2_at_least(-(-longest // P))
-        chunks = 1
-        if B < ATTENTION_ROWS_ENOUGH and longest > 2 * ATTENTION_CHUNK:
-            chunks = _pow2_at_least(-(-longest // ATTENTION_CHUNK))
+        chunks = _pow2_at_least(-(-longest // ATTENTION_CHUNK))
         key = (B, width, chunks)
         graph = self.graphs.get(key)
         if graph is None:

@@ -35,9 +35,11 @@ _SIGNATURES = {
         "snk_paged_attention_scratch_bytes": [I, I, I, I],
         "snk_paged_attention": [P, P, P, I, I, P, P, P, P, I, I, I, I, I, I, I, F, I, P],
         "snk_paged_attention_rows": [P, P, P, I, I, P, P, P, P, I, I, I, I, I, I, I, F, I, P, P],
+        "snk_attention_merge": [P, P, P, I, I, I, I, I, I, I, P, P],
     },
-    "attention_prefill": {
+    "attention_mma": {
         "snk_attention_prefill": [P, P, P, I, I, P, I, P, I, I, I, I, F, P],
+        "snk_attention_decode_mma": [P, P, P, I, I, P, P, P, P, P, I, I, I, I, I, I, F, P],
     },
     "gemm": {
         "snk_gemm_simt": [P, P, P, I, I, I, P, I, P, I, I, I, I, P],
@@ -320,6 +322,49 @@ def attention_prefill(q, pool, block_table, page_size, tiles, scale, out, window
     check(fn("snk_attention_prefill")(
         _ptr(q), _ptr(pool), _ptr(block_table), block_table.shape[1], page_size, _ptr(tiles), tiles.shape[0],
         _ptr(out), nh, pool.shape[2], hd, int(window or 0), float(scale), _stream()), "attention_prefill")
+    return out
+
+
+DECODE_MMA_CHUNK = 256
+DECODE_MMA_MAX_GROUP = 16
+
+
+def attention_decode_mma_ok(q, num_kv_heads: int) -> bool:
+    """Whether the tensor-core kernel for decoded rows takes this q [M, heads, head_dim]."""
+    return (q.dtype == torch.bfloat16 and q.shape[2] in PREFILL_HEAD_DIMS
+            and q.shape[1] // num_kv_heads <= DECODE_MMA_MAX_GROUP)
+
+
+def attention_decode_mma(q, pool, block_table, page_size, positions, row_seg, scale, num_chunks, out,
+                         window=None, scratch=None, rows=None):
+    """Tensor-core attention for rows with long runs of keys (decoded tokens): keys in chunks of 256, the
+    q heads of a kv head as the rows of the MMA; chunks merged in order when there is more than one."""
+    M, nh, hd = q.shape
+    _chk(q, "q", torch.bfloat16)
+    _chk(pool, "kv pool", torch.bfloat16)
+    _chk(positions, "positions", torch.int32, (M,))
+    _chk(row_seg, "row_seg", torch.int32, (M,))
+    _chk(block_table, "block table", torch.int32)
+    _chk(out, "attention output", torch.bfloat16, (M, nh * hd))
+    served = M
+    if rows is not None:
+        _chk(rows, "attention rows", torch.int32)
+        served = rows.numel()
+    if num_chunks > 1:
+        need = attention_scratch_bytes(served, nh, hd, num_chunks)
+        if scratch is None:
+            scratch = torch.empty(need, dtype=torch.uint8, device=q.device)
+        _chk(scratch, "attention scratch", torch.uint8)
+        if scratch.numel() < need:
+            raise KernelError(f"attention scratch holds {scratch.numel()} bytes, needs {need}")
+    check(fn("snk_attention_decode_mma")(
+        _ptr(q), _ptr(pool), _ptr(block_table), block_table.shape[1], page_size, _ptr(positions), _ptr(row_seg),
+        _ptr(rows), _ptr(out), _ptr(scratch), served, nh, pool.shape[2], hd, int(window or 0), int(num_chunks),
+        float(scale), _stream()), "attention_decode_mma")
+    if num_chunks > 1:
+        check(fn("snk_attention_merge")(_ptr(scratch), _ptr(positions), _ptr(out), served, nh, hd, int(window or 0),
+                                        DECODE_MMA_CHUNK, int(num_chunks), BF16, _ptr(rows), _stream()),
+              "attention_merge")
     return out
 
 

@@ -105,8 +105,13 @@ def attention_decode(a):
     scratch = torch.empty(kernels.attention_scratch_bytes(a.batch, a.heads, a.head_dim, n), dtype=torch.uint8,
                           device="cuda")
     out = torch.empty(a.batch, a.heads * a.head_dim, dtype=torch.bfloat16, device="cuda")
-    fn = lambda: kernels.paged_attention(q, pool, bt, a.page_size, positions, row_seg, a.head_dim ** -0.5,
-                                         chunk=chunk, num_chunks=n, scratch=scratch, out=out)
+    if a.rowwise:      # the CUDA-core kernel of csrc/attention.cu
+        fn = lambda: kernels.paged_attention(q, pool, bt, a.page_size, positions, row_seg, a.head_dim ** -0.5,
+                                             chunk=chunk, num_chunks=n, scratch=scratch, out=out)
+    else:              # the tensor-core kernel of csrc/attention_mma.cu (chunks of 256 keys)
+        n = -(-a.context // kernels.DECODE_MMA_CHUNK)
+        fn = lambda: kernels.attention_decode_mma(q, pool, bt, a.page_size, positions, row_seg,
+                                                  a.head_dim ** -0.5, n, out, scratch=scratch)
     nbytes = a.batch * a.context * 2 * a.kv_heads * a.head_dim * 2
     us = timed(fn, a.iters)
     return {"us": us, "GB/s": nbytes / us / 1e3, "bytes": nbytes}
@@ -147,6 +152,7 @@ def main(argv=None) -> int:
     ap.add_argument("--head-dim", type=int, default=64)
     ap.add_argument("--page-size", type=int, default=16)
     ap.add_argument("--chunk", type=int, default=256)
+    ap.add_argument("--rowwise", action="store_true", help="attention_decode: the CUDA-core kernel")
     ap.add_argument("--iters", type=int, default=20)
     a = ap.parse_args(argv)
     out = {"kernel": a.kind, **{k: v for k, v in vars(a).items() if k != "kind"}}

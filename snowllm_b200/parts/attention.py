@@ -19,7 +19,7 @@ from .spec import INIT_ONES, KEEP_SMALL, PagedKVSpec, TensorSpec
 
 
 class Attention(Part):
-    libraries = ("gemm", "gemm_skinny", "gemm_tc", "rope_cache", "attention", "attention_prefill")
+    libraries = ("gemm", "gemm_skinny", "gemm_tc", "rope_cache", "attention", "attention_mma")
 
     def __init__(self, dtype, names, *, hidden_size: int, num_heads: int, num_kv_heads: int,
                  head_dim: int, qk_norm_eps: float | None, position: dict, window: int | None = None,
@@ -72,8 +72,17 @@ class Attention(Part):
                                       window=self.window)
             if not rows_host:
                 return linear(o, self.wo, out_dtype=torch.float32)
-        chunk, num_chunks = ctx.attention_plan(self.window, rows_host)
         served = ctx.M if rows_host is None else len(rows_host)
+        if kernels.attention_decode_mma_ok(q, self.num_kv_heads):
+            # rows of decoded tokens on the tensor cores: keys in chunks of 256, merged in order
+            num_chunks = ctx.attention_chunks(self.window, rows_host, kernels.DECODE_MMA_CHUNK)
+            scratch = ctx.scratch(kernels.attention_scratch_bytes(
+                served, self.num_heads, self.head_dim, num_chunks)) if num_chunks > 1 else None
+            kernels.attention_decode_mma(q, cache.pool, cache.block_table, cache.page_size, ctx.positions,
+                                         ctx.row_seg, self.scale, num_chunks, o, window=self.window,
+                                         scratch=scratch, rows=rows)
+            return linear(o, self.wo, out_dtype=torch.float32)
+        chunk, num_chunks = ctx.attention_plan(self.window, rows_host)
         scratch = ctx.scratch(kernels.attention_scratch_bytes(
             served, self.num_heads, self.head_dim, num_chunks)) if num_chunks > 1 else None
         kernels.paged_attention(q, cache.pool, cache.block_table, cache.page_size, ctx.positions,

@@ -684,3 +684,62 @@ def test_products_with_swiglu_store(K, M, I, K_):
         close(K.swiglu(dev(h), interleaved=True), want, dt, scale=2)
     if dtype == torch.bfloat16:
         assert K.gemm_tc_status() == 0
+
+
+# ---------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("nh,nkv,hd,P,window", [(4, 1, 64, 16, None), (32, 8, 64, 16, None), (16, 1, 128, 64, None),
+                                                (6, 2, 128, 8, None), (8, 2, 64, 16, 300), (3, 3, 64, 16, 37)])
+def test_attention_decode_mma(K, nh, nkv, hd, P, window):
+    """The tensor-core kernel for decoded rows: requests of very different lengths (one chunk, a chunk
+    edge, many chunks), scattered pages, unwritten cache entries NaN, a row list, windows."""
+    torch.manual_seed(60)
+    dtype = torch.bfloat16
+    lens = [1, 255, 256, 257, 700, 1500]
+    pages = sum(-(-n // P) for n in lens) + 2
+    perm = torch.randperm(pages).tolist()
+    pool = torch.full((pages, 2, nkv, P, hd), float("nan"), dtype=dtype, device="cuda")
+    tables, ks, vs = [], [], []
+    for n in lens:
+        need = -(-n // P)
+        table, perm = perm[:need], perm[need:]
+        k, v = rnd(dtype, n, nkv, hd), rnd(dtype, n, nkv, hd)
+        scatter_kv(pool, k, v, table, P)
+        tables.append(table)
+        ks.append(k)
+        vs.append(v)
+    width = max(len(t) for t in tables)
+    bt = i32([t + [0] * (width - len(t)) for t in tables])
+    positions = [n - 1 for n in lens]
+    B = len(lens)
+    q = rnd(dtype, B, nh, hd)
+    scale = hd ** -0.5
+    want = torch.cat([ref_attention(q[b:b + 1], ks[b], vs[b], [positions[b]], scale, window) for b in range(B)])
+    lo = [0 if not window else max(0, p - window + 1) for p in positions]
+    n_chunks = max(p // 256 - l // 256 for p, l in zip(positions, lo)) + 1
+    for extra in (0, 3):                           # more chunks than any row needs (a captured step)
+        out = torch.full((B, nh * hd), float("nan"), dtype=dtype, device="cuda")
+        K.attention_decode_mma(dev(q, dtype), pool, bt, P, i32(positions), i32(list(range(B))), scale,
+                               n_chunks + extra, out, window=window)
+        assert out.isfinite().all(), "an unwritten (NaN) cache entry was read, or a row was not written"
+        close(out, want, dtype)
+    some = [5, 0, 3]
+    out = torch.zeros(B, nh * hd, dtype=dtype, device="cuda")
+    K.attention_decode_mma(dev(q, dtype), pool, bt, P, i32(positions), i32(list(range(B))), scale, n_chunks, out,
+                           window=window, rows=i32(some))
+    close(out[some], want[some], dtype)
+    assert float(out[[1, 2, 4]].abs().max()) == 0.0
+    # the far key: one key of the longest request made to stand out
+    far = 300
+    direction = F.normalize(torch.randn(hd), dim=0)
+    k2 = ks[5].clone()
+    k2[far, :] = (direction * 16).to(dtype).float()
+    scatter_kv(pool, k2, vs[5], tables[5], P)
+    q2 = q.clone()
+    q2[5] = (direction * 16).to(dtype).float()
+    out = torch.zeros(B, nh * hd, dtype=dtype, device="cuda")
+    K.attention_decode_mma(dev(q2, dtype), pool, bt, P, i32(positions), i32(list(range(B))), scale, n_chunks, out,
+                           window=None if not window or window > 1300 else window)
+    if not window:
+        got = out[5].float().cpu().view(nh, hd)
+        for h in range(nh):
+            assert (got[h] - vs[5][far, h // (nh // nkv)]).abs().max() < 0.02

@@ -46,4 +46,16 @@ TINY_DENSE = {   # the dense architecture: every feed-forward a SwiGLU
     "max_position_embeddings": 4096,
 }
 
-ALL = {"tiny_a": TINY_A, "tiny_b": TINY_B, "tiny_c": TINY_C, "tiny_dense": TINY_DENSE}
+TINY_E = {   # head size 64 (the tensor-core attention kernels), one kv head for two q heads, top-1 routing
+    "architectures": ["Lfm2MoeForCausalLM"], "model_type": "lfm2_moe",
+    "vocab_size": 300, "hidden_size": 128, "num_hidden_layers": 3,
+    "layer_types": ["full_attention", "conv", "full_attention"],
+    "num_attention_heads": 2, "num_key_value_heads": 1, "conv_L_cache": 3, "conv_bias": False,
+    "num_dense_layers": 1, "intermediate_size": 192,
+    "num_experts": 4, "num_experts_per_tok": 1, "moe_intermediate_size": 64,
+    "norm_topk_prob": False, "use_expert_bias": True, "routed_scaling_factor": 1.0,
+    "rope_theta": 10000.0, "norm_eps": 1e-5, "tie_word_embeddings": True,
+    "max_position_embeddings": 4096,
+}
+
+ALL = {"tiny_e": TINY_E, "tiny_a": TINY_A, "tiny_b": TINY_B, "tiny_c": TINY_C, "tiny_dense": TINY_DENSE}
