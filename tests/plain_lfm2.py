@@ -114,7 +114,7 @@ def attention_mixer(u, wq, wk, wv, wo, q_norm, k_norm, eps, n_heads, n_kv, hd, t
     scale hd^-0.5; softmax in float32.  ``window`` (not an LFM2 option) keeps only the
     last ``window`` keys, the query's own included."""
     T = u.shape[0]
-    pos = torch.arange(T) if positions is None else positions
+    pos = torch.arange(T, device=u.device) if positions is None else positions
     q = (u @ wq.T).view(T, n_heads, hd)
     k = (u @ wk.T).view(T, n_kv, hd)
     v = (u @ wv.T).view(T, n_kv, hd)
@@ -125,7 +125,7 @@ def attention_mixer(u, wq, wk, wv, wo, q_norm, k_norm, eps, n_heads, n_kv, hd, t
     group = n_heads // n_kv
     q = q.view(T, n_kv, group, hd)
     scores = torch.einsum("tghd,sgd->tghs", q, k) * hd ** -0.5
-    i = torch.arange(T)
+    i = torch.arange(T, device=u.device)
     mask = i[None, :] > i[:, None]
     if window is not None:
         mask = mask | (i[None, :] <= i[:, None] - window)
@@ -152,7 +152,7 @@ def route(u, gate_w, expert_bias, top_k, norm_topk_prob, scaling, forced_ids=Non
     if margins is not None:
         v = order.values
         margins.append(v[:, top_k - 1] - v[:, top_k] if top_k < v.shape[1]
-                       else torch.full((v.shape[0],), float("inf")))
+                       else torch.full((v.shape[0],), float("inf"), device=v.device))
     ids = order.indices[:, :top_k] if forced_ids is None else forced_ids.long()
     w = p.gather(1, ids)
     if norm_topk_prob:
@@ -228,7 +228,8 @@ def hidden_states(cfg, tensors, ids, forced_routes=None, margins=None):
     that replace the router's selection in that layer; ``margins``: a dict that receives
     {layer -> selection margin per position}."""
     eps = cfg["norm_eps"]
-    x = tensors["model.embed_tokens.weight"][torch.as_tensor(ids, dtype=torch.long)].float()
+    table = tensors["model.embed_tokens.weight"]
+    x = table[torch.as_tensor(ids, dtype=torch.long, device=table.device)].float()
     for i in range(cfg["num_hidden_layers"]):
         p = f"model.layers.{i}."
         x = x + layer_mixer(cfg, tensors, i, rmsnorm(x, tensors[p + "operator_norm.weight"], eps))

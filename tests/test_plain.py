@@ -118,3 +118,17 @@ def test_sampling_reference_cuts():
     assert plain.softmax_sample_reference(row, 1.0, 2, 1.0, 0.999) == 1       # top-2 only
     assert plain.softmax_sample_reference(row, 1.0, 0, 0.7, 0.999) == 1       # 0.5 + 0.3 reaches 0.7
     assert plain.softmax_sample_reference(row, 1.0, 0, 0.81, 0.999) == 2
+
+
+def test_plain_implementation_still_gives_its_recorded_logits():
+    """tests/golden/plain_tiny.pt holds the oracle's own outputs (made by tests/golden/make_golden.py)."""
+    import importlib.util
+    import pathlib
+    here = pathlib.Path(__file__).resolve().parent / "golden"
+    spec = importlib.util.spec_from_file_location("make_golden", here / "make_golden.py")
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    recorded = torch.load(here / "plain_tiny.pt")
+    for name, case in mod.cases().items():
+        assert case["ids"] == recorded[name]["ids"]
+        assert torch.allclose(case["logits"], recorded[name]["logits"], atol=1e-5, rtol=1e-5), name
