@@ -12,6 +12,7 @@ from __future__ import annotations
 import torch
 
 from ..engine.context import PREFILL_MIN_ROWS
+from ..errors import ConfigError
 from ..ops import kernels, linear
 from .base import Part
 from .registry import lookup, register_mixer
@@ -26,7 +27,11 @@ class Attention(Part):
                  scale: float | None = None):
         super().__init__(dtype, names)
         if num_heads % num_kv_heads:
-            raise ValueError(f"num_heads={num_heads} is no multiple of num_kv_heads={num_kv_heads}")
+            raise ConfigError(f"num_heads={num_heads} is no multiple of num_kv_heads={num_kv_heads}")
+        vector = 8 if dtype == torch.bfloat16 else 4      # cache rows are copied in 16-byte vectors
+        if head_dim % vector or head_dim > 512:
+            raise ConfigError(f"head_dim={head_dim}: the attention kernels take multiples of {vector} up to 512 "
+                              f"in {dtype}")
         self.hidden_size, self.num_heads, self.num_kv_heads = hidden_size, num_heads, num_kv_heads
         self.head_dim, self.qk_norm_eps, self.window = head_dim, qk_norm_eps, window
         self.scale = head_dim ** -0.5 if scale is None else scale

@@ -228,3 +228,15 @@ def test_trace_run_program(model_dirs, tmp_path, name, dtype):
     outputs2 = run_program(d, dtype, quiet, tmp_path / "out2")
     for i, (a, b) in enumerate(zip(outputs, outputs2)):
         assert (b is None) if i % 2 else torch.equal(a, b)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["tiny_conv_only", "tiny_attn_only"])
+def test_models_without_pages_or_without_state(model_dirs, name, dtype):
+    """Only convolutions (no paged cache group at all, 5 taps) and only attention (one head of 24, widths 104
+    and 20 that the vector paths do not take): the mixed trace against the plain implementation."""
+    d = model_dirs(name, dtype)
+    reqs = requests_for(ALL[name], seed=30)
+    steps = mixed_trace(reqs, seed=5)
+    outputs, routes = run_in_process(d, dtype, steps, max_live_tokens(steps))
+    check_against_plain(d, dtype, reqs, steps, outputs, routes)

@@ -58,4 +58,9 @@ TINY_E = {   # head size 64 (the tensor-core attention kernels), one kv head for
     "max_position_embeddings": 4096,
 }
 
-ALL = {"tiny_e": TINY_E, "tiny_a": TINY_A, "tiny_b": TINY_B, "tiny_c": TINY_C, "tiny_dense": TINY_DENSE}
+TINY_CONV_ONLY = dict(TINY_DENSE, layer_types=["conv", "conv", "conv"], conv_L_cache=5)   # no paged cache at all
+TINY_ATTN_ONLY = dict(TINY_A, layer_types=["full_attention"] * 4, num_dense_layers=0,    # no state slots in use
+                      hidden_size=104, num_attention_heads=1, num_key_value_heads=1, head_dim=24,
+                      moe_intermediate_size=20, vocab_size=250)
+
+ALL = {"tiny_conv_only": TINY_CONV_ONLY, "tiny_attn_only": TINY_ATTN_ONLY, "tiny_e": TINY_E, "tiny_a": TINY_A, "tiny_b": TINY_B, "tiny_c": TINY_C, "tiny_dense": TINY_DENSE}
