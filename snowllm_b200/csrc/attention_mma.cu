@@ -305,14 +305,24 @@ attention_decode_mma_kernel(const bf16* __restrict__ q, const bf16* __restrict__
     fa_cp_async16(sm_q + swz<CH>(r, cc), q + ((size_t)m * nh + kvh * group + min(r, group - 1)) * HD + cc * 8,
                   r < group);
   }
+  // the chunk's pages once per block (not once per copy): first page k0 / page_size
+  __shared__ int chunk_pages[FD_CHUNK + 1];
+  const int first_page = k0 / page_size;
+  const int n_pages = (k_end - 1) / page_size - first_page + 1;
+  for (int i = threadIdx.x; i < n_pages; i += FA_WARPS * 32) chunk_pages[i] = bt[first_page + i];
+  __syncthreads();
+  const bool pow2 = (page_size & (page_size - 1)) == 0;
+  const int shift = 31 - __clz(page_size);
   for (int v = threadIdx.x; v < FD_CHUNK * CH; v += FA_WARPS * 32) {
     const int r = v / CH, cc = v % CH;
     const int kp = k0 + r;
     const bool valid = kp >= k_begin && kp < k_end;
     const bf16* src = pool;
     if (valid) {
-      const int page = bt[kp / page_size];
-      src = pool + (size_t)page * page_stride + ((size_t)kvh * page_size + kp % page_size) * HD + cc * 8;
+      const int pi = pow2 ? (kp >> shift) : kp / page_size;
+      const int in_page = pow2 ? (kp & (page_size - 1)) : kp - pi * page_size;
+      src = pool + (size_t)chunk_pages[pi - first_page] * page_stride + ((size_t)kvh * page_size + in_page) * HD +
+            cc * 8;
     }
     fa_cp_async16(sm_k + swz<CH>(r, cc), src, valid);
     fa_cp_async16(sm_v + swz<CH>(r, cc), valid ? src + v_off : src, valid);
