@@ -48,7 +48,9 @@ template <> __device__ __forceinline__ void store4<bf16>(bf16* p, float a, float
 template <typename T>
 __global__ void add_rmsnorm_kernel(float* __restrict__ residual, const float* __restrict__ delta,
                                    SmallVec gamma, T* __restrict__ out,
-                                   const int* __restrict__ rows, int H, float eps, int vec4) {
+                                   const int* __restrict__ rows, int H, float eps, int vec4,
+                                   const float* __restrict__ moe_y, const int* __restrict__ pair_pos,
+                                   const float* __restrict__ topk_w, int k) {
   extern __shared__ __align__(16) float xs[];   // H floats + 33 for the reduction
   float* red = xs + ((H + 3) & ~3);
   const int r = blockIdx.x;
@@ -57,6 +59,35 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ residual, const float* __
   const float* d = delta ? delta + src * H : nullptr;
   float ss = 0.f;
   T* o = out + (size_t)r * H;
+  if (moe_y) {
+    // The delta is the routed experts' weighted sum, formed here instead of by a kernel of its own:
+    // sum_j w[src, j] * y[pair_pos[src*k + j], :], j in order (the rows are 16-byte aligned).
+    float4* xs4 = reinterpret_cast<float4*>(xs);
+    float4* res4 = reinterpret_cast<float4*>(res);
+    for (int i = threadIdx.x; i < H / 4; i += blockDim.x) {
+      float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+      for (int j = 0; j < k; ++j) {
+        const float w = topk_w[src * k + j];
+        const float4 y = reinterpret_cast<const float4*>(moe_y + (size_t)pair_pos[src * k + j] * H)[i];
+        acc.x = fmaf(w, y.x, acc.x); acc.y = fmaf(w, y.y, acc.y);
+        acc.z = fmaf(w, y.z, acc.z); acc.w = fmaf(w, y.w, acc.w);
+      }
+      float4 v = res4[i];
+      v.x += acc.x; v.y += acc.y; v.z += acc.z; v.w += acc.w;
+      if (!rows) res4[i] = v;
+      xs4[i] = v;
+      ss = fmaf(v.x, v.x, ss); ss = fmaf(v.y, v.y, ss);      // one fixed order of the squares in every path
+      ss = fmaf(v.z, v.z, ss); ss = fmaf(v.w, v.w, ss);
+    }
+    ss = block_sum(ss, red);
+    const float inv = rsqrtf(ss / (float)H + eps);
+    for (int i = threadIdx.x; i < H / 4; i += blockDim.x) {
+      const float4 v = xs4[i];
+      store4<T>(o + 4 * i, v.x * inv * gamma[4 * i], v.y * inv * gamma[4 * i + 1], v.z * inv * gamma[4 * i + 2],
+                v.w * inv * gamma[4 * i + 3]);
+    }
+    return;
+  }
   if (vec4) {                                   // H a multiple of 4 and 16-byte aligned rows
     float4* xs4 = reinterpret_cast<float4*>(xs);
     float4* res4 = reinterpret_cast<float4*>(res);
@@ -69,7 +100,8 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ residual, const float* __
         if (!rows) res4[i] = v;
       }
       xs4[i] = v;
-      ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+      ss = fmaf(v.x, v.x, ss); ss = fmaf(v.y, v.y, ss);      // one fixed order of the squares in every path
+      ss = fmaf(v.z, v.z, ss); ss = fmaf(v.w, v.w, ss);
     }
     ss = block_sum(ss, red);
     const float inv = rsqrtf(ss / (float)H + eps);
@@ -95,11 +127,15 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ residual, const float* __
     o[i] = from_f<T>(xs[i] * inv * gamma[i]);
 }
 
+// moe_y (may be null): instead of delta, add sum_j topk_w[row, j] * moe_y[pair_pos[row*k + j], :].
 SNK_API int snk_add_rmsnorm(float* residual, const float* delta, const void* gamma,
                             int gamma_is_f32, void* out, const int* rows, int R, int H,
-                            float eps, int dtype, cudaStream_t stream) {
+                            float eps, int dtype, const float* moe_y, const int* pair_pos,
+                            const float* topk_w, int k, cudaStream_t stream) {
   if (R <= 0) return 0;
   if (H <= 0 || H > 65536) return SNK_ERR_SIZE;
+  if (moe_y && (H % 4 || (uintptr_t)moe_y % 16 || (uintptr_t)residual % 16 || (uintptr_t)out % 16 || k <= 0))
+    return SNK_ERR_ALIGN;
   // The block size depends on H alone, so a row's statistics never depend on the batch.
   const int threads = H >= 2048 ? 512 : (H >= 512 ? 256 : 128);
   const size_t smem = (size_t)(((H + 3) & ~3) + 33) * sizeof(float);
@@ -111,7 +147,8 @@ SNK_API int snk_add_rmsnorm(float* residual, const float* delta, const void* gam
       cudaFuncSetAttribute(add_rmsnorm_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                            (int)smem);
     add_rmsnorm_kernel<T><<<R, threads, smem, stream>>>(residual, delta, g,
-                                                        static_cast<T*>(out), rows, H, eps, vec4);
+                                                        static_cast<T*>(out), rows, H, eps, vec4, moe_y, pair_pos,
+                                                        topk_w, k);
   });
   SNK_LAUNCH_CHECK();
   return 0;

@@ -21,7 +21,7 @@ P, I, F, LL = c_void_p, c_int, c_float, c_longlong
 _SIGNATURES = {
     "elementwise": {
         "snk_embedding": [P, P, P, I, I, I, I, P],
-        "snk_add_rmsnorm": [P, P, P, I, P, P, I, I, F, I, P],
+        "snk_add_rmsnorm": [P, P, P, I, P, P, I, I, F, I, P, P, P, I, P],
         "snk_residual_add": [P, P, LL, P],
         "snk_swiglu": [P, P, I, I, I, I, P],
     },
@@ -171,13 +171,37 @@ def embedding(ids: torch.Tensor, table: torch.Tensor, out: torch.Tensor | None =
     return out
 
 
-def add_rmsnorm(residual: torch.Tensor, delta: torch.Tensor | None, gamma: torch.Tensor, eps: float,
+class ExpertSum:
+    """A residual delta that is still in pieces: the routed experts' outputs ``y`` [pairs, H] (float), where
+    each (token, pick) pair's row lies (``pair_pos`` int32 [M*k]) and the picks' weights (``weights`` float
+    [M, k]).  The norm that follows adds sum_j w[m, j] * y[pair_pos[m*k + j]] into the residual itself;
+    ``dense()`` forms the sum for anyone else."""
+
+    def __init__(self, y, pair_pos, weights):
+        self.y, self.pair_pos, self.weights = y, pair_pos, weights
+        self.shape = (weights.shape[0], y.shape[1])
+
+    def dense(self) -> torch.Tensor:
+        return moe_combine(self.y, self.pair_pos, self.weights)
+
+
+def add_rmsnorm(residual: torch.Tensor, delta, gamma: torch.Tensor, eps: float,
                 dtype: torch.dtype, rows: torch.Tensor | None = None,
                 out: torch.Tensor | None = None) -> torch.Tensor:
     """``residual += delta`` (if given), then RMSNorm of the sum into the compute dtype.  With
-    ``rows`` only those rows are normalised and the residual is left as it is."""
+    ``rows`` only those rows are normalised and the residual is left as it is.  ``delta`` is a float
+    tensor [M, H] or an ``ExpertSum``."""
     M, H = residual.shape
     _chk(residual, "residual", torch.float32)
+    moe = None
+    if isinstance(delta, ExpertSum):
+        if H % 4 == 0:
+            moe, delta = delta, None
+            _chk(moe.y, "expert outputs", torch.float32)
+            _chk(moe.pair_pos, "pair positions", torch.int32, (M * moe.weights.shape[1],))
+            _chk(moe.weights, "top-k weights", torch.float32)
+        else:
+            delta = delta.dense()
     if delta is not None:
         _chk(delta, "residual delta", torch.float32, (M, H))
     g32 = _small(gamma, "norm weight", dtype)
@@ -189,7 +213,9 @@ def add_rmsnorm(residual: torch.Tensor, delta: torch.Tensor | None, gamma: torch
         out = torch.empty(R, H, dtype=dtype, device=residual.device)
     _chk(out, "norm output", dtype, (R, H))
     check(fn("snk_add_rmsnorm")(_ptr(residual), _ptr(delta), _ptr(gamma), g32, _ptr(out), _ptr(rows),
-                                R, H, float(eps), code_of(dtype), _stream()), "add_rmsnorm")
+                                R, H, float(eps), code_of(dtype), _ptr(moe.y if moe else None),
+                                _ptr(moe.pair_pos if moe else None), _ptr(moe.weights if moe else None),
+                                moe.weights.shape[1] if moe else 0, _stream()), "add_rmsnorm")
     return out
 
 

@@ -7,7 +7,8 @@ Interfaces (duck-typed; these base classes only hold what is common):
   ``bind(tensors)``; ``libraries`` names the csrc sources its kernels come from.
 * mixer:       ``cache_spec() -> PagedKVSpec | SlotStateSpec | None`` and
                ``forward(ctx, x[M,H], cache, owns_cache) -> float delta [M,H]``
-* feed-forward ``forward(ctx, x[M,H]) -> float delta [M,H]``
+* feed-forward ``forward(ctx, x[M,H]) -> float delta [M,H]`` (or a ``kernels.ExpertSum``, a delta still in
+               pieces that norms add up themselves; ``.dense()`` gives the tensor)
 * norm:        ``forward(ctx, residual, delta, rows=None) -> x[M,H]`` (adds delta into the float
                residual, then normalises into the compute dtype)
 * position:    ``rotary(device) -> (inv_freq float [rot_dim/2] | None, rot_dim)``

@@ -3,8 +3,8 @@
 tensor names and the fused / per-expert spellings snowllm/models/lfm2/weights.py:79-92).
 
 Steps: router in float -> sort the (token, pick) pairs by expert -> grouped gate|up product over
-the sorted rows (rows gathered from x) -> SwiGLU -> grouped down product (float) -> weighted sum
-per token in pick order.  Only experts that own rows are read."""
+the sorted rows (rows gathered from x) with SwiGLU at its store -> grouped down product (float) ->
+weighted sum per token in pick order (left to the norm that follows: `kernels.ExpertSum`).  Only experts that own rows are read."""
 from __future__ import annotations
 
 import torch
@@ -74,7 +74,7 @@ class SigmoidMoE(Part):
         cap = min(M, M * k)          # an expert gets a token at most once
         act = grouped_linear_swiglu(x, self.w13, offsets, M * k, cap, sorted_pair, k, self.interleaved)
         y = grouped_linear(act, self.w2, offsets, M * k, cap, out_dtype=torch.float32)
-        return kernels.moe_combine(y, pair_pos, weights)
+        return kernels.ExpertSum(y, pair_pos, weights)     # the norm that follows adds it into the residual
 
 
 register_ffn("sigmoid_moe", SigmoidMoE)

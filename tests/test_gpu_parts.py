@@ -159,10 +159,20 @@ def test_feed_forwards(dtype):
         w2 = torch.stack([t[f"e.{e}.w2"] for e in range(E)])
         want = plain.moe_ffn(x, t["r"], t.get("b") if bias else None, w1, w3, w2, k, norm, scaling,
                              forced_ids=ids.cpu())
-        got = part.forward(None, x.to("cuda", dtype)).cpu()
+        delta = part.forward(None, x.to("cuda", dtype))          # an ExpertSum: the weighted sum is still to be formed
+        got = delta.dense().cpu()
         assert float(rel_rows(got, want).max()) < TOL[dtype]
-        # a single row and a batch where every row picks the last experts
-        one = part.forward(None, x[:1].to("cuda", dtype)).cpu()
+        # the norm that follows forms the sum itself: same residual as adding the dense delta
+        norm, tn = make_part("norm", "rmsnorm", dtype, dict(weight="w"), dict(size=H, eps=1e-5))
+        res_a, res_b = torch.randn(37, H).cuda(), None
+        res_b = res_a.clone()
+        out_a = norm.forward(None, res_a, delta)
+        out_b = norm.forward(None, res_b, delta.dense())
+        assert torch.allclose(res_a, res_b, atol=1e-6) and torch.equal(out_a, out_b)
+        rows = torch.tensor([3, 36, 0], dtype=torch.int32, device="cuda")
+        assert torch.equal(norm.forward(None, res_a.clone(), delta, rows=rows), norm.forward(None, res_b.clone(), delta.dense(), rows=rows))
+        # a single row
+        one = part.forward(None, x[:1].to("cuda", dtype)).dense().cpu()
         assert float(rel_rows(one, want[:1]).max()) < TOL[dtype]
 
 
