@@ -61,6 +61,7 @@ __global__ void paged_attention_kernel(
     int max_pages, int page_size, const int* __restrict__ positions, const int* __restrict__ row_seg,
     T* __restrict__ out, float* __restrict__ part_o, float* __restrict__ part_ml, int nh, int nkv,
     int hd, int window, int chunk, int num_chunks, float scale, const int* __restrict__ row_list) {
+  pdl_begin();
   extern __shared__ __align__(16) unsigned char sh_raw[];
   constexpr int VEC = Vec16<T>::N;
   const int group = nh / nkv;
@@ -205,6 +206,7 @@ __global__ void attention_merge_kernel(const float* __restrict__ part_o, const f
                                        const int* __restrict__ positions, T* __restrict__ out, int nh,
                                        int hd, int window, int chunk, int num_chunks,
                                        const int* __restrict__ row_list) {
+  pdl_begin();
   const int m = row_list ? row_list[blockIdx.x] : blockIdx.x, head = blockIdx.y;
   const int pos = positions[m];
   const int lo = window > 0 ? max(0, pos - window + 1) : 0;
@@ -255,7 +257,7 @@ SNK_API int snk_paged_attention_rows(const void* q, const void* pool, const int*
     if (smem > 48 * 1024)                                                                            \
       cudaFuncSetAttribute(paged_attention_kernel<T, DPL_>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
                            (int)smem);                                                               \
-    paged_attention_kernel<T, DPL_><<<grid, warps * 32, smem, stream>>>(                             \
+    snk_launch(paged_attention_kernel<T, DPL_>, dim3(grid), dim3(warps * 32), smem, stream,                              \
         static_cast<const T*>(q), static_cast<const T*>(pool), block_table, max_pages, page_size,    \
         positions, row_seg, static_cast<T*>(out), part_o, part_ml, nh, nkv, hd, window, chunk,       \
         num_chunks, scale, row_list);                                                                \
@@ -272,7 +274,7 @@ SNK_API int snk_paged_attention_rows(const void* q, const void* pool, const int*
   if (num_chunks > 1) {
     dim3 mgrid(M, nh);
     const int threads = hd <= 32 ? 32 : (hd <= 64 ? 64 : 128);
-    SNK_DISPATCH(dtype, attention_merge_kernel<T><<<mgrid, threads, 0, stream>>>(
+    SNK_DISPATCH(dtype, snk_launch(attention_merge_kernel<T>, dim3(mgrid), dim3(threads), 0, stream, 
                             part_o, part_ml, positions, static_cast<T*>(out), nh, hd, window,
                             chunk, num_chunks, row_list));
     SNK_LAUNCH_CHECK();
@@ -290,7 +292,7 @@ SNK_API int snk_attention_merge(const void* scratch, const int* positions, void*
   const float* part_ml = part_o + (size_t)M * nh * num_chunks * hd;
   dim3 mgrid(M, nh);
   const int threads = hd <= 32 ? 32 : (hd <= 64 ? 64 : 128);
-  SNK_DISPATCH(dtype, attention_merge_kernel<T><<<mgrid, threads, 0, stream>>>(
+  SNK_DISPATCH(dtype, snk_launch(attention_merge_kernel<T>, dim3(mgrid), dim3(threads), 0, stream, 
                           part_o, part_ml, positions, static_cast<T*>(out), nh, hd, window, chunk, num_chunks,
                           row_list));
   SNK_LAUNCH_CHECK();

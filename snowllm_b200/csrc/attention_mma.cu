@@ -65,6 +65,7 @@ attention_prefill_kernel(const bf16* __restrict__ q, const bf16* __restrict__ po
                          const int* __restrict__ block_table, int max_pages, int page_size,
                          const int* __restrict__ tiles, bf16* __restrict__ out, int nh, int nkv, int window,
                          float scale_log2) {
+  pdl_begin();
   constexpr int CH = HD / 8;                       // 16-byte chunks per row
   constexpr int KT = HD / 16;                      // k-steps of the QK^T product
   constexpr int NT = HD / 8;                       // n-tiles of the output
@@ -249,11 +250,11 @@ SNK_API int snk_attention_prefill(const void* q, const void* pool, const int* bl
   const bf16 *qp = static_cast<const bf16*>(q), *pp = static_cast<const bf16*>(pool);
   bf16* op = static_cast<bf16*>(out);
   if (hd == 64) {
-    attention_prefill_kernel<64><<<grid, FA_WARPS * 32, smem, stream>>>(qp, pp, block_table, max_pages, page_size,
+    snk_launch(attention_prefill_kernel<64>, dim3(grid), dim3(FA_WARPS * 32), smem, stream, qp, pp, block_table, max_pages, page_size,
                                                                         tiles, op, nh, nkv, window, scale_log2);
   } else {
     cudaFuncSetAttribute(attention_prefill_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    attention_prefill_kernel<128><<<grid, FA_WARPS * 32, smem, stream>>>(qp, pp, block_table, max_pages, page_size,
+    snk_launch(attention_prefill_kernel<128>, dim3(grid), dim3(FA_WARPS * 32), smem, stream, qp, pp, block_table, max_pages, page_size,
                                                                          tiles, op, nh, nkv, window, scale_log2);
   }
   SNK_LAUNCH_CHECK();
@@ -278,6 +279,7 @@ attention_decode_mma_kernel(const bf16* __restrict__ q, const bf16* __restrict__
                             const int* __restrict__ row_list, bf16* __restrict__ out,
                             float* __restrict__ part_o, float* __restrict__ part_ml, int nh, int nkv,
                             int window, int num_chunks, float scale_log2) {
+  pdl_begin();
   constexpr int CH = HD / 8, KT = HD / 16, NT = HD / 8;
   extern __shared__ __align__(16) unsigned char fd_smem[];
   const uint32_t sm_q = (uint32_t)__cvta_generic_to_shared(fd_smem);        // [16][HD]
@@ -471,12 +473,12 @@ SNK_API int snk_attention_decode_mma(const void* q, const void* pool, const int*
   bf16* op = static_cast<bf16*>(out);
   if (hd == 64) {
     cudaFuncSetAttribute(attention_decode_mma_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    attention_decode_mma_kernel<64><<<grid, FA_WARPS * 32, smem, stream>>>(
+    snk_launch(attention_decode_mma_kernel<64>, dim3(grid), dim3(FA_WARPS * 32), smem, stream, 
         qp, pp, block_table, max_pages, page_size, positions, row_seg, row_list, op, part_o, part_ml, nh, nkv,
         window, num_chunks, scale_log2);
   } else {
     cudaFuncSetAttribute(attention_decode_mma_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    attention_decode_mma_kernel<128><<<grid, FA_WARPS * 32, smem, stream>>>(
+    snk_launch(attention_decode_mma_kernel<128>, dim3(grid), dim3(FA_WARPS * 32), smem, stream, 
         qp, pp, block_table, max_pages, page_size, positions, row_seg, row_list, op, part_o, part_ml, nh, nkv,
         window, num_chunks, scale_log2);
   }

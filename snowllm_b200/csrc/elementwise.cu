@@ -13,6 +13,7 @@
 template <typename T>
 __global__ void embedding_kernel(const int* __restrict__ ids, const T* __restrict__ table,
                                  float* __restrict__ out, int H, int V) {
+  pdl_begin();
   const int m = blockIdx.x;
   int id = ids[m];
   const bool ok = id >= 0 && id < V;     // the host checks ids; a bad one reads nothing
@@ -25,7 +26,7 @@ SNK_API int snk_embedding(const int* ids, const void* table, float* out, int M, 
                           int dtype, cudaStream_t stream) {
   if (M <= 0) return 0;
   const int threads = H >= 1024 ? 256 : 128;
-  SNK_DISPATCH(dtype, embedding_kernel<T><<<M, threads, 0, stream>>>(
+  SNK_DISPATCH(dtype, snk_launch(embedding_kernel<T>, dim3(M), dim3(threads), 0, stream, 
                           ids, static_cast<const T*>(table), out, H, V));
   SNK_LAUNCH_CHECK();
   return 0;
@@ -51,6 +52,7 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ residual, const float* __
                                    const int* __restrict__ rows, int H, float eps, int vec4,
                                    const float* __restrict__ moe_y, const int* __restrict__ pair_pos,
                                    const float* __restrict__ topk_w, int k) {
+  pdl_begin();
   extern __shared__ __align__(16) float xs[];   // H floats + 33 for the reduction
   float* red = xs + ((H + 3) & ~3);
   const int r = blockIdx.x;
@@ -146,7 +148,7 @@ SNK_API int snk_add_rmsnorm(float* residual, const float* delta, const void* gam
     if (smem > 48 * 1024)
       cudaFuncSetAttribute(add_rmsnorm_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                            (int)smem);
-    add_rmsnorm_kernel<T><<<R, threads, smem, stream>>>(residual, delta, g,
+    snk_launch(add_rmsnorm_kernel<T>, dim3(R), dim3(threads), smem, stream, residual, delta, g,
                                                         static_cast<T*>(out), rows, H, eps, vec4, moe_y, pair_pos,
                                                         topk_w, k);
   });
@@ -157,13 +159,14 @@ SNK_API int snk_add_rmsnorm(float* residual, const float* delta, const void* gam
 // ---------------------------------------------------------------------------------------
 // Residual update without a norm: residual += delta (used where no norm follows).
 __global__ void add_kernel(float* __restrict__ residual, const float* __restrict__ delta, size_t n) {
+  pdl_begin();
   size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (i < n) residual[i] += delta[i];
 }
 
 SNK_API int snk_residual_add(float* residual, const float* delta, long long n, cudaStream_t stream) {
   if (n <= 0) return 0;
-  add_kernel<<<(unsigned)((n + 255) / 256), 256, 0, stream>>>(residual, delta, (size_t)n);
+  snk_launch(add_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, stream, residual, delta, (size_t)n);
   SNK_LAUNCH_CHECK();
   return 0;
 }
@@ -173,6 +176,7 @@ SNK_API int snk_residual_add(float* residual, const float* delta, long long n, c
 // 16 columns, 8 gate columns then the 8 up columns of the same features (what the fused products use).
 template <typename T>
 __global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ out, int I, size_t total, int interleaved) {
+  pdl_begin();
   size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (idx >= total) return;
   const size_t m = idx / I;
@@ -189,7 +193,7 @@ SNK_API int snk_swiglu(const void* gu, void* out, int M, int I, int interleaved,
   const size_t total = (size_t)M * I;
   if (total == 0) return 0;
   if (interleaved && I % 8) return SNK_ERR_SIZE;
-  SNK_DISPATCH(dtype, swiglu_kernel<T><<<(unsigned)((total + 255) / 256), 256, 0, stream>>>(
+  SNK_DISPATCH(dtype, snk_launch(swiglu_kernel<T>, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, stream, 
                           static_cast<const T*>(gu), static_cast<T*>(out), I, total, interleaved));
   SNK_LAUNCH_CHECK();
   return 0;

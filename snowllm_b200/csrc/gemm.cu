@@ -45,6 +45,7 @@ __global__ void __launch_bounds__(256)
 gemm_simt_kernel(const T* __restrict__ A, const T* __restrict__ W, OutT* __restrict__ C, int M,
                  int N, int K, const int* __restrict__ a_rows, int a_div,
                  const int* __restrict__ offsets, int vec) {
+  pdl_begin();
   __shared__ __align__(16) float As[BK][BM + 4];
   __shared__ __align__(16) float Ws[BK][BN + 4];
   int row_begin = 0, row_end = M;
@@ -127,11 +128,11 @@ SNK_API int snk_gemm_simt(const void* A, const void* W, void* C, int M, int N, i
   if (a_div <= 0) a_div = 1;
   SNK_DISPATCH(dtype, {
     if (out_f32 || dtype == SNK_F32)
-      gemm_simt_kernel<T, float><<<grid, 256, 0, stream>>>(
+      snk_launch(gemm_simt_kernel<T, float>, dim3(grid), dim3(256), 0, stream, 
           static_cast<const T*>(A), static_cast<const T*>(W), static_cast<float*>(C), M, N, K,
           a_rows, a_div, offsets, vec);
     else
-      gemm_simt_kernel<T, T><<<grid, 256, 0, stream>>>(
+      snk_launch(gemm_simt_kernel<T, T>, dim3(grid), dim3(256), 0, stream, 
           static_cast<const T*>(A), static_cast<const T*>(W), static_cast<T*>(C), M, N, K, a_rows,
           a_div, offsets, vec);
   });

@@ -47,6 +47,7 @@ __global__ void __launch_bounds__(SK_WARPS * 32)
 gemm_skinny_kernel(const bf16* __restrict__ A, const bf16* __restrict__ W, OutT* __restrict__ C, int M,
                    int N, int K, const int* __restrict__ a_rows, int a_div,
                    const int* __restrict__ offsets) {
+  pdl_begin();
   __shared__ float red[SK_WARPS][MT * 8][SK_ROWS + 1];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, t = lane & 3;
@@ -153,13 +154,13 @@ static int launch_skinny(const void* A, const void* W, void* C, int M, int N, in
   dim3 grid((N + SK_ROWS - 1) / SK_ROWS, offsets ? groups : 1);
   const bf16 *a = static_cast<const bf16*>(A), *w = static_cast<const bf16*>(W);
   if (swiglu)
-    gemm_skinny_kernel<MT, bf16, true><<<grid, SK_WARPS * 32, 0, stream>>>(a, w, static_cast<bf16*>(C), M, N, K,
+    snk_launch(gemm_skinny_kernel<MT, bf16, true>, dim3(grid), dim3(SK_WARPS * 32), 0, stream, a, w, static_cast<bf16*>(C), M, N, K,
                                                                            a_rows, a_div, offsets);
   else if (out_f32)
-    gemm_skinny_kernel<MT, float, false><<<grid, SK_WARPS * 32, 0, stream>>>(a, w, static_cast<float*>(C), M, N,
+    snk_launch(gemm_skinny_kernel<MT, float, false>, dim3(grid), dim3(SK_WARPS * 32), 0, stream, a, w, static_cast<float*>(C), M, N,
                                                                              K, a_rows, a_div, offsets);
   else
-    gemm_skinny_kernel<MT, bf16, false><<<grid, SK_WARPS * 32, 0, stream>>>(a, w, static_cast<bf16*>(C), M, N, K,
+    snk_launch(gemm_skinny_kernel<MT, bf16, false>, dim3(grid), dim3(SK_WARPS * 32), 0, stream, a, w, static_cast<bf16*>(C), M, N, K,
                                                                             a_rows, a_div, offsets);
   SNK_LAUNCH_CHECK();
   return 0;

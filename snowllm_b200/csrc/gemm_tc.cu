@@ -190,6 +190,7 @@ __global__ void __launch_bounds__(TC_THREADS)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
                OutT* __restrict__ C, int M, int N, int K, const int* __restrict__ offsets, int groups,
                int row_tiles_bound) {
+  pdl_begin();
   constexpr int STAGE_BYTES = (TC_BM + BN) * TC_BK * 2;
   constexpr int STAGES = TC_SMEM_TILES / STAGE_BYTES < TC_MAX_STAGES ? TC_SMEM_TILES / STAGE_BYTES : TC_MAX_STAGES;
   extern __shared__ unsigned char smem_raw[];
@@ -429,7 +430,7 @@ static int launch_tc(const CUtensorMap& map_a, const CUtensorMap& map_w, void* C
   }
   const long long tiles = (long long)row_tiles * ((N + BN - 1) / BN);
   const int blocks = (int)(tiles < sms ? tiles : sms);     // one block per SM (shared memory), persistent
-  gemm_tc_kernel<BN, OutT, SWIGLU><<<blocks, TC_THREADS, smem, stream>>>(map_a, map_w, static_cast<OutT*>(C), M, N, K,
+  snk_launch(gemm_tc_kernel<BN, OutT, SWIGLU>, dim3(blocks), dim3(TC_THREADS), smem, stream, map_a, map_w, static_cast<OutT*>(C), M, N, K,
                                                                  offsets, groups, row_tiles);
   SNK_LAUNCH_CHECK();
   return 0;
@@ -472,6 +473,7 @@ SNK_API int snk_gemm_tc_status() {
 // out[r, :] = in[rows[r] / div, :]  (bfloat16 rows of K elements, K a multiple of 8)
 __global__ void gather_rows_kernel(const uint4* __restrict__ in, uint4* __restrict__ out,
                                    const int* __restrict__ rows, int div, int vecs) {
+  pdl_begin();
   const uint4* src = in + (size_t)(rows[blockIdx.x] / div) * vecs;
   uint4* dst = out + (size_t)blockIdx.x * vecs;
   for (int i = threadIdx.x; i < vecs; i += blockDim.x) dst[i] = src[i];
@@ -481,7 +483,7 @@ SNK_API int snk_gather_rows_bf16(const void* in, void* out, const int* rows, int
                                  cudaStream_t stream) {
   if (R <= 0) return 0;
   if (K % 8 || ((uintptr_t)in % 16) || ((uintptr_t)out % 16)) return SNK_ERR_ALIGN;
-  gather_rows_kernel<<<R, 128, 0, stream>>>(static_cast<const uint4*>(in), static_cast<uint4*>(out), rows,
+  snk_launch(gather_rows_kernel, dim3(R), dim3(128), 0, stream, static_cast<const uint4*>(in), static_cast<uint4*>(out), rows,
                                             div <= 0 ? 1 : div, K / 8);
   SNK_LAUNCH_CHECK();
   return 0;

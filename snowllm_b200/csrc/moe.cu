@@ -63,6 +63,7 @@ template <typename T>
 __global__ void moe_route_kernel(const T* __restrict__ x, SmallVec wr, const float* __restrict__ bias,
                                  int* __restrict__ topk_ids, float* __restrict__ topk_w, int H, int E,
                                  int k, int norm_topk, float scaling) {
+  pdl_begin();
   extern __shared__ float sh[];
   float* xs = sh;                // H
   float* prob = xs + H;          // E
@@ -91,6 +92,7 @@ __global__ void moe_route_kernel(const T* __restrict__ x, SmallVec wr, const flo
 __global__ void moe_topk_kernel(const float* __restrict__ logits, const float* __restrict__ bias,
                                 int* __restrict__ topk_ids, float* __restrict__ topk_w, int M, int E, int k,
                                 int norm_topk, float scaling) {
+  pdl_begin();
   extern __shared__ float sh[];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarp = blockDim.x >> 5;
   const int m = blockIdx.x * nwarp + warp;
@@ -111,7 +113,7 @@ SNK_API int snk_moe_topk(const float* logits, const float* bias, int* topk_ids, 
   if (M <= 0) return 0;
   if (E <= 0 || E > ROUTE_MAX_EXPERTS || k <= 0 || k > E) return SNK_ERR_SIZE;
   const int warps = 4;
-  moe_topk_kernel<<<(M + warps - 1) / warps, warps * 32, (size_t)warps * 2 * E * sizeof(float), stream>>>(
+  snk_launch(moe_topk_kernel, dim3((M + warps - 1) / warps), dim3(warps * 32), (size_t)warps * 2 * E * sizeof(float), stream, 
       logits, bias, topk_ids, topk_w, M, E, k, norm_topk, scaling);
   SNK_LAUNCH_CHECK();
   return 0;
@@ -131,7 +133,7 @@ SNK_API int snk_moe_route(const void* x, const void* wr, int wr_is_f32, const fl
     // one warp per expert where it fits: the few rows of a decode step would otherwise leave most
     // of the GPU idle.  A dot product's order does not depend on the number of warps.
     const int threads = E >= 32 ? 1024 : (E >= 16 ? 512 : (E >= 8 ? 256 : ROUTE_THREADS));
-    moe_route_kernel<T><<<M, threads, smem, stream>>>(static_cast<const T*>(x), w, bias, topk_ids,
+    snk_launch(moe_route_kernel<T>, dim3(M), dim3(threads), smem, stream, static_cast<const T*>(x), w, bias, topk_ids,
                                                             topk_w, H, E, k, norm_topk, scaling);
   });
   SNK_LAUNCH_CHECK();
@@ -146,6 +148,7 @@ SNK_API int snk_moe_route(const void* x, const void* wr, int wr_is_f32, const fl
 __global__ void moe_sort_kernel(const int* __restrict__ topk_ids, int* __restrict__ offsets,
                                 int* __restrict__ pair_pos, int* __restrict__ sorted_pair, int pairs,
                                 int E) {
+  pdl_begin();
   extern __shared__ int cnt[];   // E counts, then E+1 offsets
   int* off = cnt + E;
   for (int e = threadIdx.x; e < E; e += blockDim.x) cnt[e] = 0;
@@ -177,7 +180,7 @@ SNK_API int snk_moe_sort(const int* topk_ids, int* offsets, int* pair_pos, int* 
   if (pairs <= 0) return 0;
   if (E <= 0 || E > 4096) return SNK_ERR_SIZE;
   const size_t smem = (size_t)(2 * E + 1) * sizeof(int);
-  moe_sort_kernel<<<1, 1024, smem, stream>>>(topk_ids, offsets, pair_pos, sorted_pair, pairs, E);
+  snk_launch(moe_sort_kernel, dim3(1), dim3(1024), smem, stream, topk_ids, offsets, pair_pos, sorted_pair, pairs, E);
   SNK_LAUNCH_CHECK();
   return 0;
 }
@@ -187,6 +190,7 @@ SNK_API int snk_moe_sort(const int* topk_ids, int* offsets, int* pair_pos, int* 
 __global__ void moe_combine_kernel(const float* __restrict__ y, const int* __restrict__ pair_pos,
                                    const float* __restrict__ topk_w, float* __restrict__ out, int H,
                                    int k) {
+  pdl_begin();
   const int m = blockIdx.x;
   for (int i = threadIdx.x; i < H; i += blockDim.x) {
     float acc = 0.f;
@@ -199,7 +203,7 @@ __global__ void moe_combine_kernel(const float* __restrict__ y, const int* __res
 SNK_API int snk_moe_combine(const float* y, const int* pair_pos, const float* topk_w, float* out,
                             int M, int H, int k, cudaStream_t stream) {
   if (M <= 0) return 0;
-  moe_combine_kernel<<<M, H >= 1024 ? 256 : 128, 0, stream>>>(y, pair_pos, topk_w, out, H, k);
+  snk_launch(moe_combine_kernel, dim3(M), dim3(H >= 1024 ? 256 : 128), 0, stream, y, pair_pos, topk_w, out, H, k);
   SNK_LAUNCH_CHECK();
   return 0;
 }

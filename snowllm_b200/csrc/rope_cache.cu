@@ -12,13 +12,16 @@
 
 #define ROPE_MAX_PER_LANE 16   // head_dim <= 512
 
-template <typename T>
+// PER: elements per lane, head_dim <= 32 * PER (a compile-time bound keeps the loops free of dead
+// iterations).
+template <typename T, int PER>
 __global__ void qk_norm_rope_cache_kernel(
     const T* __restrict__ qkv, SmallVec q_gamma, SmallVec k_gamma, int has_norm, float eps,
     const float* __restrict__ inv_freq, int rot_dim, const int* __restrict__ positions,
     const int* __restrict__ row_seg, const int* __restrict__ block_table, int max_pages,
     int page_size, T* __restrict__ pool, T* __restrict__ q_out, int nh, int nkv, int hd,
     int write_kv) {
+  pdl_begin();
   extern __shared__ float sh[];            // one head per warp: hd floats each; then cos, sin of the row
   const int warps = blockDim.x >> 5, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int m = blockIdx.x;
@@ -38,16 +41,13 @@ __global__ void qk_norm_rope_cache_kernel(
 
   const bool is_q = head < nh;
   const bool is_k = !is_q && head < nh + nkv;
-  float x[ROPE_MAX_PER_LANE];
-  const int per = (hd + 31) / 32;
+  float x[PER];
   float ss = 0.f;
 #pragma unroll
-  for (int j = 0; j < ROPE_MAX_PER_LANE; ++j) {
-    if (j < per) {
-      const int d = lane + 32 * j;
-      x[j] = d < hd ? to_f<T>(src[d]) : 0.f;
-      ss += x[j] * x[j];
-    }
+  for (int j = 0; j < PER; ++j) {
+    const int d = lane + 32 * j;
+    x[j] = d < hd ? to_f<T>(src[d]) : 0.f;
+    ss += x[j] * x[j];
   }
   if (is_q || is_k) {
     if (has_norm) {
@@ -55,32 +55,29 @@ __global__ void qk_norm_rope_cache_kernel(
       const float inv = rsqrtf(ss / (float)hd + eps);
       const SmallVec& g = is_q ? q_gamma : k_gamma;
 #pragma unroll
-      for (int j = 0; j < ROPE_MAX_PER_LANE; ++j)
-        if (j < per) {
-          const int d = lane + 32 * j;
-          if (d < hd) x[j] = x[j] * inv * g[d];
-        }
+      for (int j = 0; j < PER; ++j) {
+        const int d = lane + 32 * j;
+        if (d < hd) x[j] = x[j] * inv * g[d];
+      }
     }
     if (inv_freq != nullptr && rot_dim > 0) {
 #pragma unroll
-      for (int j = 0; j < ROPE_MAX_PER_LANE; ++j)
-        if (j < per) {
-          const int d = lane + 32 * j;
-          if (d < hd) buf[d] = x[j];
-        }
+      for (int j = 0; j < PER; ++j) {
+        const int d = lane + 32 * j;
+        if (d < hd) buf[d] = x[j];
+      }
       __syncwarp();
       const int half = rot_dim >> 1;
 #pragma unroll
-      for (int j = 0; j < ROPE_MAX_PER_LANE; ++j)
-        if (j < per) {
-          const int d = lane + 32 * j;
-          if (d < rot_dim) {
-            const int i = d < half ? d : d - half;
-            const float sn = sn_tab[i], cs = cs_tab[i];
-            const float other = d < half ? -buf[d + half] : buf[d - half];
-            x[j] = x[j] * cs + other * sn;
-          }
+      for (int j = 0; j < PER; ++j) {
+        const int d = lane + 32 * j;
+        if (d < rot_dim) {
+          const int i = d < half ? d : d - half;
+          const float sn = sn_tab[i], cs = cs_tab[i];
+          const float other = d < half ? -buf[d + half] : buf[d - half];
+          x[j] = x[j] * cs + other * sn;
         }
+      }
     }
   }
   T* dst;
@@ -93,11 +90,10 @@ __global__ void qk_norm_rope_cache_kernel(
     dst = pool + ((((size_t)page * 2 + (is_k ? 0 : 1)) * nkv + kvh) * page_size + pos % page_size) * hd;
   }
 #pragma unroll
-  for (int j = 0; j < ROPE_MAX_PER_LANE; ++j)
-    if (j < per) {
-      const int d = lane + 32 * j;
-      if (d < hd) dst[d] = from_f<T>(x[j]);
-    }
+  for (int j = 0; j < PER; ++j) {
+    const int d = lane + 32 * j;
+    if (d < hd) dst[d] = from_f<T>(x[j]);
+  }
   __syncwarp();                              // buf is reused by the warp's next head
   }
 }
@@ -114,10 +110,19 @@ SNK_API int snk_qk_norm_rope_cache(
   dim3 grid(M);
   const size_t smem = ((size_t)warps * hd + rot_dim) * sizeof(float);
   SmallVec qg{q_gamma, gamma_is_f32}, kg{k_gamma, gamma_is_f32};
-  SNK_DISPATCH(dtype, qk_norm_rope_cache_kernel<T><<<grid, warps * 32, smem, stream>>>(
-                          static_cast<const T*>(qkv), qg, kg, has_norm, eps, inv_freq, rot_dim,
-                          positions, row_seg, block_table, max_pages, page_size,
-                          static_cast<T*>(pool), static_cast<T*>(q_out), nh, nkv, hd, write_kv));
+#define ROPE_LAUNCH(PER_)                                                                            \
+  snk_launch(qk_norm_rope_cache_kernel<T, PER_>, dim3(grid), dim3(warps * 32), smem, stream,                             \
+      static_cast<const T*>(qkv), qg, kg, has_norm, eps, inv_freq, rot_dim, positions, row_seg,      \
+      block_table, max_pages, page_size, static_cast<T*>(pool), static_cast<T*>(q_out), nh, nkv, hd, \
+      write_kv)
+  SNK_DISPATCH(dtype, {
+    if (hd <= 32) ROPE_LAUNCH(1);
+    else if (hd <= 64) ROPE_LAUNCH(2);
+    else if (hd <= 128) ROPE_LAUNCH(4);
+    else if (hd <= 256) ROPE_LAUNCH(8);
+    else ROPE_LAUNCH(16);
+  });
+#undef ROPE_LAUNCH
   SNK_LAUNCH_CHECK();
   return 0;
 }

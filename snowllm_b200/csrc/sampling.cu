@@ -58,6 +58,7 @@ __device__ ArgPair block_argmax(const float* __restrict__ row, int V, ArgPair* r
 }
 
 __global__ void argmax_kernel(const float* __restrict__ logits, int* __restrict__ out, int V) {
+  pdl_begin();
   __shared__ ArgPair red[33];
   const ArgPair r = block_argmax(logits + (size_t)blockIdx.x * V, V, red);
   if (threadIdx.x == 0) out[blockIdx.x] = r.i;
@@ -66,7 +67,7 @@ __global__ void argmax_kernel(const float* __restrict__ logits, int* __restrict_
 SNK_API int snk_argmax(const float* logits, int* out, int B, int V, cudaStream_t stream) {
   if (B <= 0) return 0;
   if (V <= 0) return SNK_ERR_SIZE;
-  argmax_kernel<<<B, V >= 4096 ? 1024 : 256, 0, stream>>>(logits, out, V);
+  snk_launch(argmax_kernel, dim3(B), dim3(V >= 4096 ? 1024 : 256), 0, stream, logits, out, V);
   SNK_LAUNCH_CHECK();
   return 0;
 }
@@ -76,6 +77,7 @@ __global__ void penalties_kernel(float* __restrict__ logits, const int* __restri
                                  const int* __restrict__ ids, const int* __restrict__ counts,
                                  const float* __restrict__ presence, const float* __restrict__ frequency,
                                  const float* __restrict__ repetition, int V) {
+  pdl_begin();
   const int b = blockIdx.x;
   float* row = logits + (size_t)b * V;
   const float pp = presence[b], fp = frequency[b], rp = repetition[b];
@@ -96,7 +98,7 @@ SNK_API int snk_apply_penalties(float* logits, const int* row_offsets, const int
                                 const int* counts, const float* presence, const float* frequency,
                                 const float* repetition, int B, int V, cudaStream_t stream) {
   if (B <= 0) return 0;
-  penalties_kernel<<<B, 256, 0, stream>>>(logits, row_offsets, ids, counts, presence, frequency,
+  snk_launch(penalties_kernel, dim3(B), dim3(256), 0, stream, logits, row_offsets, ids, counts, presence, frequency,
                                           repetition, V);
   SNK_LAUNCH_CHECK();
   return 0;
@@ -126,6 +128,7 @@ __global__ void __launch_bounds__(SAMPLE_THREADS)
 sample_kernel(const float* __restrict__ logits, const float* __restrict__ temperature,
               const int* __restrict__ top_k, const float* __restrict__ top_p,
               const float* __restrict__ uniform, int* __restrict__ out, int V) {
+  pdl_begin();
   __shared__ ArgPair ared[33];
   __shared__ float fred[33];
   __shared__ int ired[33];
@@ -222,7 +225,7 @@ SNK_API int snk_sample(const float* logits, const float* temperature, const int*
                        cudaStream_t stream) {
   if (B <= 0) return 0;
   if (V <= 0) return SNK_ERR_SIZE;
-  sample_kernel<<<B, SAMPLE_THREADS, 0, stream>>>(logits, temperature, top_k, top_p, uniform, out, V);
+  snk_launch(sample_kernel, dim3(B), dim3(SAMPLE_THREADS), 0, stream, logits, temperature, top_k, top_p, uniform, out, V);
   SNK_LAUNCH_CHECK();
   return 0;
 }

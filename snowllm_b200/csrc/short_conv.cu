@@ -27,6 +27,7 @@ __global__ void short_conv_kernel(const T* __restrict__ bcx, SmallVec w, const T
                                   const int* __restrict__ cu_seqlens, const int* __restrict__ seg_start,
                                   const int* __restrict__ seg_slot, const int* __restrict__ row_seg,
                                   T* __restrict__ out, int M, int H, int L) {
+  pdl_begin();
   const int c = blockIdx.x * blockDim.x + threadIdx.x;
   if (c >= H) return;
   float taps[CONV_MAX_L];
@@ -60,6 +61,7 @@ __global__ void short_conv_state_kernel(const T* __restrict__ bcx, T* __restrict
                                         const int* __restrict__ cu_seqlens,
                                         const int* __restrict__ seg_start,
                                         const int* __restrict__ seg_slot, int H, int L) {
+  pdl_begin();
   const int c = blockIdx.x * blockDim.x + threadIdx.x;
   if (c >= H) return;
   const int seg = blockIdx.y;
@@ -126,6 +128,7 @@ __global__ void short_conv_strip_kernel(const T* __restrict__ bcx, SmallVec w, c
                                         const int* __restrict__ cu_seqlens, const int* __restrict__ seg_start,
                                         const int* __restrict__ seg_slot, const int* __restrict__ row_seg,
                                         T* __restrict__ out, int M, int H, int L) {
+  pdl_begin();
   constexpr int VEC = ConvVec<T>::N;
   const int c0 = (blockIdx.x * blockDim.x + threadIdx.x) * VEC;
   if (c0 >= H) return;
@@ -196,6 +199,7 @@ template <typename T>
 __global__ void short_conv_decode_kernel(const T* __restrict__ bcx, SmallVec w, T* __restrict__ state,
                                          const int* __restrict__ seg_start, const int* __restrict__ seg_slot,
                                          T* __restrict__ out, int H, int L) {
+  pdl_begin();
   const int c = blockIdx.x * blockDim.x + threadIdx.x;
   if (c >= H) return;
   const int seg = blockIdx.y;                        // = the row: one token per segment
@@ -228,7 +232,7 @@ SNK_API int snk_short_conv(const void* bcx, const void* w, int w_is_f32, void* s
   if (M == B && L > 1 && B <= 65535) {               // one token per segment
     dim3 dgrid((H + threads - 1) / threads, B);
     SmallVec dw{w, w_is_f32};
-    SNK_DISPATCH(dtype, short_conv_decode_kernel<T><<<dgrid, threads, 0, stream>>>(
+    SNK_DISPATCH(dtype, snk_launch(short_conv_decode_kernel<T>, dim3(dgrid), dim3(threads), 0, stream, 
                             static_cast<const T*>(bcx), dw, static_cast<T*>(state), seg_start, seg_slot,
                             static_cast<T*>(out), H, L));
     SNK_LAUNCH_CHECK();
@@ -241,20 +245,20 @@ SNK_API int snk_short_conv(const void* bcx, const void* w, int w_is_f32, void* s
   if (L >= 2 && L <= CONV_FAST_L && aligned && M >= 4 * CONV_STRIP) {
     dim3 sgrid((H / vec + threads - 1) / threads, (M + CONV_STRIP - 1) / CONV_STRIP);
     if (sgrid.y > 65535u) return SNK_ERR_SIZE;
-    SNK_DISPATCH(dtype, short_conv_strip_kernel<T><<<sgrid, threads, 0, stream>>>(
+    SNK_DISPATCH(dtype, snk_launch(short_conv_strip_kernel<T>, dim3(sgrid), dim3(threads), 0, stream, 
                             static_cast<const T*>(bcx), wv, static_cast<const T*>(state), cu_seqlens,
                             seg_start, seg_slot, row_seg, static_cast<T*>(out), M, H, L));
   } else {
     dim3 grid((H + threads - 1) / threads, (M + CONV_ROWS_PER_BLOCK - 1) / CONV_ROWS_PER_BLOCK);
     if (grid.y > 65535u) return SNK_ERR_SIZE;
-    SNK_DISPATCH(dtype, short_conv_kernel<T><<<grid, threads, 0, stream>>>(
+    SNK_DISPATCH(dtype, snk_launch(short_conv_kernel<T>, dim3(grid), dim3(threads), 0, stream, 
                             static_cast<const T*>(bcx), wv, static_cast<const T*>(state), cu_seqlens,
                             seg_start, seg_slot, row_seg, static_cast<T*>(out), M, H, L));
   }
   SNK_LAUNCH_CHECK();
   if (L > 1) {
     dim3 sgrid((H + threads - 1) / threads, B);
-    SNK_DISPATCH(dtype, short_conv_state_kernel<T><<<sgrid, threads, 0, stream>>>(
+    SNK_DISPATCH(dtype, snk_launch(short_conv_state_kernel<T>, dim3(sgrid), dim3(threads), 0, stream, 
                             static_cast<const T*>(bcx), static_cast<T*>(state), cu_seqlens,
                             seg_start, seg_slot, H, L));
     SNK_LAUNCH_CHECK();
