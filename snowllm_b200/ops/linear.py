@@ -1,7 +1,8 @@
 """Matrix products of the model: the one place that picks a kernel for a shape and dtype.
 
 float32: the CUDA-core kernel of csrc/gemm.cu (true 32-bit, sums in k order).
-bfloat16, up to 64 rows (decode): csrc/gemm_skinny.cu, which streams W once into mma.sync fragments.
+bfloat16, up to 16 rows (decode; grouped: up to 4 rows per group on average): csrc/gemm_skinny.cu, which
+streams W once into mma.sync fragments.
 bfloat16, more rows (prefill): csrc/gemm_tc.cu, 128 x 128 tiles on the tcgen05 tensor cores with TMA
 loads and the accumulator in tensor memory.
 bfloat16 operands that neither takes (K no multiple of 8, unaligned views): the CUDA-core kernel.
@@ -13,7 +14,8 @@ import torch
 
 from . import kernels
 
-SKINNY_MAX_ROWS = 64       # up to here the product is bound by the read of W: the few-rows kernel
+SKINNY_MAX_ROWS = 16       # measured crossover: up to here the few-rows kernel reads W faster than 128-row tiles
+SKINNY_MAX_GROUP_ROWS = 4  # grouped: mean rows per group up to which the few-rows kernel wins
 
 
 def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype | None = None,
@@ -26,11 +28,15 @@ def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype | None = Non
     return kernels.gemm_simt(x, w, out_dtype=out_dtype, out=out)
 
 
+def _few_rows_per_group(rows_out: int, groups: int) -> bool:
+    return rows_out <= SKINNY_MAX_GROUP_ROWS * groups
+
+
 def grouped_linear(x, w, offsets, rows_out, max_rows_per_group, a_rows=None, a_div=1, out_dtype=None):
     """Rows sorted by group: row r in [offsets[g], offsets[g+1]) is x[a_rows[r] // a_div] (or x[r])
     times w[g] [N, K]^T.  ``max_rows_per_group`` bounds the rows one group can own."""
     if kernels.gemm_skinny_ok(x, w):
-        if max_rows_per_group <= SKINNY_MAX_ROWS:
+        if _few_rows_per_group(rows_out, w.shape[0]):
             # a pass covers about twice the mean rows of a group; fuller groups take more passes
             hint = min(max_rows_per_group, max(8, 2 * -(-rows_out // w.shape[0])))
             return kernels.gemm_skinny(x, w, out_dtype=out_dtype, a_rows=a_rows, a_div=a_div, offsets=offsets,
@@ -63,7 +69,7 @@ def linear_swiglu(x: torch.Tensor, w13: torch.Tensor, interleaved: bool) -> torc
 def grouped_linear_swiglu(x, w13, offsets, rows_out, max_rows_per_group, a_rows, a_div, interleaved: bool):
     """The grouped form of ``linear_swiglu`` over rows sorted by group (w13 [G, 2I, K])."""
     if interleaved and kernels.gemm_skinny_ok(x, w13):
-        if max_rows_per_group <= SKINNY_MAX_ROWS:
+        if _few_rows_per_group(rows_out, w13.shape[0]):
             hint = min(max_rows_per_group, max(8, 2 * -(-rows_out // w13.shape[0])))
             return kernels.gemm_skinny(x, w13, a_rows=a_rows, a_div=a_div, offsets=offsets, rows_out=rows_out,
                                        rows_hint=hint, swiglu=True)
