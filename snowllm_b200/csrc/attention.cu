@@ -200,27 +200,52 @@ __global__ void paged_attention_kernel(
   }
 }
 
-// Merge the chunks of one (row, head) in chunk order.
+// Merge the chunks of one (row, head).  The first warp finds the running maximum and the normaliser
+// over the chunks (lanes take chunks in turns, then a butterfly).  The chunks are then cut into
+// MERGE_ZG runs; a thread sums one element of the output over one run in chunk order, and the runs'
+// sums are added in run order: many short chains of loads instead of one long one.
+#define MERGE_ZG 4
+
 template <typename T>
 __global__ void attention_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                        const int* __restrict__ positions, T* __restrict__ out, int nh,
                                        int hd, int window, int chunk, int num_chunks,
                                        const int* __restrict__ row_list) {
   pdl_begin();
+  extern __shared__ float merge_sh[];                      // [MERGE_ZG][hd]
+  __shared__ float s_mx, s_inv;
   const int m = row_list ? row_list[blockIdx.x] : blockIdx.x, head = blockIdx.y;
   const int pos = positions[m];
   const int lo = window > 0 ? max(0, pos - window + 1) : 0;
   const int n = pos / chunk - lo / chunk + 1;              // chunks this row really has
   const size_t base = ((size_t)blockIdx.x * nh + head) * num_chunks;
-  float mx = -INFINITY;
-  for (int z = 0; z < n; ++z) mx = fmaxf(mx, part_ml[(base + z) * 2]);
-  float l = 0.f;
-  for (int z = 0; z < n; ++z) l += part_ml[(base + z) * 2 + 1] * expf(part_ml[(base + z) * 2] - mx);
-  const float inv = 1.f / l;
-  for (int d = threadIdx.x; d < hd; d += blockDim.x) {
+  if (threadIdx.x < 32) {
+    const int lane = threadIdx.x;
+    float mx = -INFINITY;
+    for (int z = lane; z < n; z += 32) mx = fmaxf(mx, part_ml[(base + z) * 2]);
+    mx = warp_max(mx);
+    float l = 0.f;
+    for (int z = lane; z < n; z += 32) l += part_ml[(base + z) * 2 + 1] * expf(part_ml[(base + z) * 2] - mx);
+    l = warp_sum(l);
+    if (lane == 0) { s_mx = mx; s_inv = 1.f / l; }
+  }
+  __syncthreads();
+  const float mx = s_mx, inv = s_inv;
+  const int dthreads = blockDim.x / MERGE_ZG, zg = threadIdx.x / dthreads, dt = threadIdx.x % dthreads;
+  const int per = (n + MERGE_ZG - 1) / MERGE_ZG;
+  const int z0 = min(n, zg * per), z1 = min(n, z0 + per);
+  for (int d = dt; d < hd; d += dthreads) {
     float acc = 0.f;
-    for (int z = 0; z < n; ++z)
+#pragma unroll 8
+    for (int z = z0; z < z1; ++z)
       acc = fmaf(part_o[(base + z) * hd + d], expf(part_ml[(base + z) * 2] - mx), acc);
+    merge_sh[zg * hd + d] = acc;
+  }
+  __syncthreads();
+  for (int d = threadIdx.x; d < hd; d += blockDim.x) {
+    float acc = merge_sh[d];
+#pragma unroll
+    for (int r = 1; r < MERGE_ZG; ++r) acc += merge_sh[r * hd + d];
     out[((size_t)m * nh + head) * hd + d] = from_f<T>(acc * inv);
   }
 }
@@ -273,8 +298,9 @@ SNK_API int snk_paged_attention_rows(const void* q, const void* pool, const int*
   SNK_LAUNCH_CHECK();
   if (num_chunks > 1) {
     dim3 mgrid(M, nh);
-    const int threads = hd <= 32 ? 32 : (hd <= 64 ? 64 : 128);
-    SNK_DISPATCH(dtype, snk_launch(attention_merge_kernel<T>, dim3(mgrid), dim3(threads), 0, stream, 
+    const int threads = MERGE_ZG * (hd <= 32 ? 32 : (hd <= 64 ? 64 : 128));
+    SNK_DISPATCH(dtype, snk_launch(attention_merge_kernel<T>, dim3(mgrid), dim3(threads),
+                                   (size_t)MERGE_ZG * hd * sizeof(float), stream, 
                             part_o, part_ml, positions, static_cast<T*>(out), nh, hd, window,
                             chunk, num_chunks, row_list));
     SNK_LAUNCH_CHECK();
@@ -291,8 +317,9 @@ SNK_API int snk_attention_merge(const void* scratch, const int* positions, void*
   const float* part_o = static_cast<const float*>(scratch);
   const float* part_ml = part_o + (size_t)M * nh * num_chunks * hd;
   dim3 mgrid(M, nh);
-  const int threads = hd <= 32 ? 32 : (hd <= 64 ? 64 : 128);
-  SNK_DISPATCH(dtype, snk_launch(attention_merge_kernel<T>, dim3(mgrid), dim3(threads), 0, stream, 
+  const int threads = MERGE_ZG * (hd <= 32 ? 32 : (hd <= 64 ? 64 : 128));
+  SNK_DISPATCH(dtype, snk_launch(attention_merge_kernel<T>, dim3(mgrid), dim3(threads),
+                                 (size_t)MERGE_ZG * hd * sizeof(float), stream, 
                           part_o, part_ml, positions, static_cast<T*>(out), nh, hd, window, chunk, num_chunks,
                           row_list));
   SNK_LAUNCH_CHECK();

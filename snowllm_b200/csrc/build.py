@@ -29,6 +29,8 @@ NVCC_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "--shared", "-Xcompiler", "-fPIC
               "-Xcompiler", "-fvisibility=hidden"]
 LIBRARIES = ("elementwise", "rope_cache", "short_conv", "attention", "attention_mma", "gemm", "gemm_skinny", "gemm_tc", "moe", "sampling")
 EXTRA_LINK: dict[str, list[str]] = {}
+# more nvcc flags from the environment (-D switches of an experiment); they enter the library's hash
+ENV_FLAGS = os.environ.get("SNOWLLM_B200_NVCC_FLAGS", "").split()
 
 _loaded: dict[str, ctypes.CDLL] = {}
 _lock = threading.Lock()
@@ -66,7 +68,7 @@ def _digest(name: str) -> str:
     for f in sorted(HERE.glob("*.cuh")) + [HERE / f"{name}.cu"]:
         h.update(f.name.encode())
         h.update(f.read_bytes())
-    h.update(" ".join(ARCH_FLAGS + NVCC_FLAGS + EXTRA_LINK.get(name, [])).encode())
+    h.update(" ".join(ARCH_FLAGS + NVCC_FLAGS + ENV_FLAGS + EXTRA_LINK.get(name, [])).encode())
     return h.hexdigest()[:16]
 
 
@@ -79,7 +81,7 @@ def _compile(name: str, out: pathlib.Path) -> None:
     if not src.exists():
         raise KernelError(f"no CUDA source {src}")
     tmp = out.with_suffix(f".tmp{os.getpid()}.so")
-    cmd = [_nvcc(), *ARCH_FLAGS, *NVCC_FLAGS, "-I", str(HERE), "-o", str(tmp), str(src),
+    cmd = [_nvcc(), *ARCH_FLAGS, *NVCC_FLAGS, *ENV_FLAGS, "-I", str(HERE), "-o", str(tmp), str(src),
            *EXTRA_LINK.get(name, [])]
     print(f"[snowllm_b200] compiling {src.name} for sm_100a ...", file=sys.stderr, flush=True)
     t0 = time.time()

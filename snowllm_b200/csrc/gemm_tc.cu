@@ -190,7 +190,6 @@ __global__ void __launch_bounds__(TC_THREADS)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
                OutT* __restrict__ C, int M, int N, int K, const int* __restrict__ offsets, int groups,
                int row_tiles_bound) {
-  pdl_begin();
   constexpr int STAGE_BYTES = (TC_BM + BN) * TC_BK * 2;
   constexpr int STAGES = TC_SMEM_TILES / STAGE_BYTES < TC_MAX_STAGES ? TC_SMEM_TILES / STAGE_BYTES : TC_MAX_STAGES;
   extern __shared__ unsigned char smem_raw[];
@@ -200,15 +199,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int k_tiles = (K + TC_BK - 1) / TC_BK;
-  // number of row tiles: known for the plain product, counted from the offsets for the grouped one
-  int row_tiles = row_tiles_bound;
-  if (offsets) {
-    row_tiles = 0;
-    for (int e = 0; e < groups; ++e) row_tiles += (offsets[e + 1] - offsets[e] + TC_BM - 1) / TC_BM;
-  }
-  const int n_tiles = (N + BN - 1) / BN;
-  const int total = row_tiles * n_tiles;
 
+  // Barriers and tensor memory are set up before the wait for the kernel in front: none of it touches
+  // global memory, and it then overlaps with that kernel's tail.
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(&sh->full[s], 1);
@@ -232,6 +225,15 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   tc_fence_after();
   const uint32_t tmem_acc = sh->tmem_base;
   volatile int* aborted = &sh->aborted;
+  pdl_begin();
+  // number of row tiles: known for the plain product, counted from the offsets for the grouped one
+  int row_tiles = row_tiles_bound;
+  if (offsets) {
+    row_tiles = 0;
+    for (int e = 0; e < groups; ++e) row_tiles += (offsets[e + 1] - offsets[e] + TC_BM - 1) / TC_BM;
+  }
+  const int n_tiles = (N + BN - 1) / BN;
+  const int total = row_tiles * n_tiles;
 
   if (warp == 0) {
     if (lane == 0) {

@@ -59,24 +59,61 @@ __device__ __forceinline__ void select_topk(float* prob, float* score, int* ids,
   }
 }
 
+// Eight consecutive elements as floats, by 16-byte loads.
+template <typename T> __device__ __forceinline__ void load8(const T* p, float (&v)[8]);
+template <> __device__ __forceinline__ void load8<float>(const float* p, float (&v)[8]) {
+  const float4 a = __ldg(reinterpret_cast<const float4*>(p)), b = __ldg(reinterpret_cast<const float4*>(p) + 1);
+  v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+}
+template <> __device__ __forceinline__ void load8<bf16>(const bf16* p, float (&v)[8]) {
+  const uint4 u = __ldg(reinterpret_cast<const uint4*>(p));
+  const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    v[2 * i] = __uint_as_float(w[i] << 16);
+    v[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+  }
+}
+
+// x . w over H elements by one warp; every lane gets the sum.  Lane l owns the elements
+// [8l, 8l + 8) of every run of 256 and adds them in ascending order, then the lanes' sums meet in a
+// butterfly: the order depends on H alone, never on the launch.  vec: both rows are 16-byte aligned.
+template <typename T, typename W>
+__device__ __forceinline__ float warp_dot(const T* __restrict__ x, const W* __restrict__ w, int H, int lane,
+                                          bool vec) {
+  float acc = 0.f;
+  int done = 0;
+  if (vec) {
+    done = H & ~7;
+#pragma unroll 4
+    for (int i = lane * 8; i < done; i += 256) {
+      float xv[8], wv[8];
+      load8<T>(x + i, xv);
+      load8<W>(w + i, wv);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) acc = fmaf(xv[j], wv[j], acc);
+    }
+  }
+  for (int i = done + lane; i < H; i += 32) acc = fmaf(to_f<T>(x[i]), to_f<W>(w[i]), acc);
+  return warp_sum(acc);
+}
+
+// One block per token, one warp per expert (in turns when there are more experts than warps).
 template <typename T>
 __global__ void moe_route_kernel(const T* __restrict__ x, SmallVec wr, const float* __restrict__ bias,
                                  int* __restrict__ topk_ids, float* __restrict__ topk_w, int H, int E,
-                                 int k, int norm_topk, float scaling) {
+                                 int k, int norm_topk, float scaling, int vec) {
   pdl_begin();
   extern __shared__ float sh[];
-  float* xs = sh;                // H
-  float* prob = xs + H;          // E
+  float* prob = sh;              // E
   float* score = prob + E;       // E
   const int m = blockIdx.x;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarp = blockDim.x >> 5;
   const T* xr = x + (size_t)m * H;
-  for (int i = threadIdx.x; i < H; i += blockDim.x) xs[i] = to_f<T>(xr[i]);
-  __syncthreads();
   for (int e = warp; e < E; e += nwarp) {
-    float acc = 0.f;
-    for (int i = lane; i < H; i += 32) acc = fmaf(xs[i], wr[(size_t)e * H + i], acc);
-    acc = warp_sum(acc);
+    const float acc = wr.is_f32
+        ? warp_dot<T, float>(xr, static_cast<const float*>(wr.p) + (size_t)e * H, H, lane, vec)
+        : warp_dot<T, bf16>(xr, static_cast<const bf16*>(wr.p) + (size_t)e * H, H, lane, vec);
     if (lane == 0) {
       const float p = 1.f / (1.f + expf(-acc));
       prob[e] = p;
@@ -86,6 +123,24 @@ __global__ void moe_route_kernel(const T* __restrict__ x, SmallVec wr, const flo
   __syncthreads();
   if (warp != 0) return;
   select_topk(prob, score, topk_ids + (size_t)m * k, topk_w + (size_t)m * k, E, k, norm_topk, scaling, lane);
+}
+
+// logits[m, e] = x[m] . wr[e], one warp per (token, expert): the few tokens of a decode step spread
+// over many blocks, where one block per token would pull the whole router matrix through one SM.
+// The same dot product as moe_route_kernel's, so a token's logits do not depend on the path.
+template <typename T>
+__global__ void moe_logits_kernel(const T* __restrict__ x, SmallVec wr, float* __restrict__ logits, int H,
+                                  int E, int vec) {
+  pdl_begin();
+  const int m = blockIdx.x;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int e = blockIdx.y * (blockDim.x >> 5) + warp;
+  if (e >= E) return;
+  const T* xr = x + (size_t)m * H;
+  const float acc = wr.is_f32
+      ? warp_dot<T, float>(xr, static_cast<const float*>(wr.p) + (size_t)e * H, H, lane, vec)
+      : warp_dot<T, bf16>(xr, static_cast<const bf16*>(wr.p) + (size_t)e * H, H, lane, vec);
+  if (lane == 0) logits[(size_t)m * E + e] = acc;
 }
 
 // One warp per token: probabilities and selection from float logits [M, E] that a matrix product left.
@@ -124,17 +179,17 @@ SNK_API int snk_moe_route(const void* x, const void* wr, int wr_is_f32, const fl
                           float scaling, int dtype, cudaStream_t stream) {
   if (M <= 0) return 0;
   if (E <= 0 || E > ROUTE_MAX_EXPERTS || k <= 0 || k > E) return SNK_ERR_SIZE;
-  const size_t smem = (size_t)(H + 2 * E) * sizeof(float);
-  if (smem > 200 * 1024) return SNK_ERR_SIZE;
+  const size_t smem = (size_t)(2 * E) * sizeof(float);
   SmallVec w{wr, wr_is_f32};
+  const size_t xsz = dtype == SNK_F32 ? 4 : 2, wsz = wr_is_f32 ? 4 : 2;
+  const int vec = ((uintptr_t)x % 16 == 0) && ((uintptr_t)wr % 16 == 0) && ((H * xsz) % 16 == 0) &&
+                  ((H * wsz) % 16 == 0);
   SNK_DISPATCH(dtype, {
-    if (smem > 48 * 1024)
-      cudaFuncSetAttribute(moe_route_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     // one warp per expert where it fits: the few rows of a decode step would otherwise leave most
     // of the GPU idle.  A dot product's order does not depend on the number of warps.
     const int threads = E >= 32 ? 1024 : (E >= 16 ? 512 : (E >= 8 ? 256 : ROUTE_THREADS));
     snk_launch(moe_route_kernel<T>, dim3(M), dim3(threads), smem, stream, static_cast<const T*>(x), w, bias, topk_ids,
-                                                            topk_w, H, E, k, norm_topk, scaling);
+                                                            topk_w, H, E, k, norm_topk, scaling, vec);
   });
   SNK_LAUNCH_CHECK();
   return 0;
@@ -145,12 +200,10 @@ SNK_API int snk_moe_route(const void* x, const void* wr, int wr_is_f32, const fl
 // expert; pair_pos[p]: sorted row of pair p = m*k + j; sorted_pair[r]: the pair at row r.
 // Where a pair lands inside its expert's rows may vary from run to run; no value depends
 // on it, since each row is computed on its own.
-__global__ void moe_sort_kernel(const int* __restrict__ topk_ids, int* __restrict__ offsets,
-                                int* __restrict__ pair_pos, int* __restrict__ sorted_pair, int pairs,
-                                int E) {
-  pdl_begin();
-  extern __shared__ int cnt[];   // E counts, then E+1 offsets
-  int* off = cnt + E;
+__device__ __forceinline__ void sort_pairs(const int* __restrict__ topk_ids, int* __restrict__ offsets,
+                                           int* __restrict__ pair_pos, int* __restrict__ sorted_pair, int pairs,
+                                           int E, int* cnt) {
+  int* off = cnt + E;            // cnt: E counts, then E+1 offsets
   for (int e = threadIdx.x; e < E; e += blockDim.x) cnt[e] = 0;
   __syncthreads();
   for (int p = threadIdx.x; p < pairs; p += blockDim.x) {
@@ -175,12 +228,74 @@ __global__ void moe_sort_kernel(const int* __restrict__ topk_ids, int* __restric
   }
 }
 
+__global__ void moe_sort_kernel(const int* __restrict__ topk_ids, int* __restrict__ offsets,
+                                int* __restrict__ pair_pos, int* __restrict__ sorted_pair, int pairs,
+                                int E) {
+  pdl_begin();
+  extern __shared__ int cnt[];
+  sort_pairs(topk_ids, offsets, pair_pos, sorted_pair, pairs, E, cnt);
+}
+
+// Selection and sort in one block, for the few tokens of a decode step: a warp per token selects from
+// the logits, then the block sorts the pairs.
+__global__ void moe_topk_sort_kernel(const float* __restrict__ logits, const float* __restrict__ bias,
+                                     int* __restrict__ topk_ids, float* __restrict__ topk_w,
+                                     int* __restrict__ offsets, int* __restrict__ pair_pos,
+                                     int* __restrict__ sorted_pair, int M, int E, int k, int norm_topk,
+                                     float scaling) {
+  pdl_begin();
+  extern __shared__ float sh[];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarp = blockDim.x >> 5;
+  float* prob = sh + (size_t)warp * 2 * E;
+  float* score = prob + E;
+  for (int m = warp; m < M; m += nwarp) {
+    for (int e = lane; e < E; e += 32) {
+      const float p = 1.f / (1.f + expf(-logits[(size_t)m * E + e]));
+      prob[e] = p;
+      score[e] = bias ? p + bias[e] : p;
+    }
+    __syncwarp();
+    select_topk(prob, score, topk_ids + (size_t)m * k, topk_w + (size_t)m * k, E, k, norm_topk, scaling, lane);
+    __syncwarp();
+  }
+  __syncthreads();               // the ids of every token are written (same block: visible after the barrier)
+  sort_pairs(topk_ids, offsets, pair_pos, sorted_pair, M * k, E, reinterpret_cast<int*>(sh));
+}
+
 SNK_API int snk_moe_sort(const int* topk_ids, int* offsets, int* pair_pos, int* sorted_pair,
                          int pairs, int E, cudaStream_t stream) {
   if (pairs <= 0) return 0;
   if (E <= 0 || E > 4096) return SNK_ERR_SIZE;
   const size_t smem = (size_t)(2 * E + 1) * sizeof(int);
   snk_launch(moe_sort_kernel, dim3(1), dim3(1024), smem, stream, topk_ids, offsets, pair_pos, sorted_pair, pairs, E);
+  SNK_LAUNCH_CHECK();
+  return 0;
+}
+
+// Few rows: logits by one warp per (token, expert), then selection and sort in one block.
+// logits: float scratch [M, E].  Refuses (SNK_ERR_SIZE) what does not fit one block's shared memory;
+// the caller then takes snk_moe_route and snk_moe_sort.
+SNK_API int snk_moe_route_sort(const void* x, const void* wr, int wr_is_f32, const float* bias, float* logits,
+                               int* topk_ids, float* topk_w, int* offsets, int* pair_pos, int* sorted_pair,
+                               int M, int H, int E, int k, int norm_topk, float scaling, int dtype,
+                               cudaStream_t stream) {
+  if (M <= 0) return 0;
+  if (E <= 0 || E > ROUTE_MAX_EXPERTS || k <= 0 || k > E || M > 1024) return SNK_ERR_SIZE;
+  const int warps = M < 32 ? M : 32;
+  size_t smem = (size_t)warps * 2 * E * sizeof(float);
+  const size_t sort_smem = (size_t)(2 * E + 1) * sizeof(int);
+  if (smem < sort_smem) smem = sort_smem;
+  if (smem > 48 * 1024) return SNK_ERR_SIZE;
+  SmallVec w{wr, wr_is_f32};
+  const size_t xsz = dtype == SNK_F32 ? 4 : 2, wsz = wr_is_f32 ? 4 : 2;
+  const int vec = ((uintptr_t)x % 16 == 0) && ((uintptr_t)wr % 16 == 0) && ((H * xsz) % 16 == 0) &&
+                  ((H * wsz) % 16 == 0);
+  const int lw = 4;              // experts per block of the logits kernel
+  SNK_DISPATCH(dtype, snk_launch(moe_logits_kernel<T>, dim3(M, (E + lw - 1) / lw), dim3(lw * 32), 0, stream,
+                                 static_cast<const T*>(x), w, logits, H, E, vec));
+  SNK_LAUNCH_CHECK();
+  snk_launch(moe_topk_sort_kernel, dim3(1), dim3(warps * 32), smem, stream, logits, bias, topk_ids, topk_w,
+             offsets, pair_pos, sorted_pair, M, E, k, norm_topk, scaling);
   SNK_LAUNCH_CHECK();
   return 0;
 }

@@ -33,7 +33,7 @@ __global__ void qk_norm_rope_cache_kernel(
     for (int i = threadIdx.x; i < (rot_dim >> 1); i += blockDim.x) sincosf(posf * inv_freq[i], &sn_tab[i], &cs_tab[i]);
   }
   __syncthreads();
-  for (int head = warp; head < total_heads; head += warps) {
+  for (int head = blockIdx.y * warps + warp; head < total_heads; head += warps * gridDim.y) {
   float* buf = sh + (size_t)warp * hd;
   // A layer that reads another layer's cache projects q only: its rows hold no k, v.
   const int row_width = (write_kv ? nh + 2 * nkv : nh) * hd;
@@ -107,7 +107,8 @@ SNK_API int snk_qk_norm_rope_cache(
   if (hd <= 0 || hd > 32 * ROPE_MAX_PER_LANE || rot_dim > hd || (rot_dim & 1)) return SNK_ERR_SIZE;
   const int total_heads = write_kv ? nh + 2 * nkv : nh;
   const int warps = total_heads >= 8 ? 8 : (total_heads >= 4 ? 4 : 2);
-  dim3 grid(M);
+  // few rows (decode): the heads of a row spread over several blocks, one head per warp
+  dim3 grid(M, M < 64 ? (total_heads + warps - 1) / warps : 1);
   const size_t smem = ((size_t)warps * hd + rot_dim) * sizeof(float);
   SmallVec qg{q_gamma, gamma_is_f32}, kg{k_gamma, gamma_is_f32};
 #define ROPE_LAUNCH(PER_)                                                                            \

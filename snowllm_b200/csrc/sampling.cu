@@ -32,7 +32,19 @@ __device__ __forceinline__ ArgPair better(ArgPair a, ArgPair b) {
 
 __device__ ArgPair block_argmax(const float* __restrict__ row, int V, ArgPair* red) {
   ArgPair best{-INFINITY, 0x7fffffff};
-  for (int i = threadIdx.x; i < V; i += blockDim.x) best = better(best, ArgPair{clean(row[i]), i});
+  int done = 0;
+  if ((uintptr_t)row % 16 == 0) {          // four values a load; a thread still meets its indices in ascending order
+    done = V & ~3;
+#pragma unroll 4
+    for (int i = threadIdx.x * 4; i < done; i += blockDim.x * 4) {
+      const float4 v = *reinterpret_cast<const float4*>(row + i);
+      best = better(best, ArgPair{clean(v.x), i});
+      best = better(best, ArgPair{clean(v.y), i + 1});
+      best = better(best, ArgPair{clean(v.z), i + 2});
+      best = better(best, ArgPair{clean(v.w), i + 3});
+    }
+  }
+  for (int i = done + threadIdx.x; i < V; i += blockDim.x) best = better(best, ArgPair{clean(row[i]), i});
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) {
     ArgPair other{__shfl_xor_sync(0xffffffffu, best.v, o), __shfl_xor_sync(0xffffffffu, best.i, o)};

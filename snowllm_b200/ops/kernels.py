@@ -55,6 +55,7 @@ _SIGNATURES = {
     "moe": {
         "snk_moe_route": [P, P, I, P, P, P, I, I, I, I, I, F, I, P],
         "snk_moe_topk": [P, P, P, P, I, I, I, I, F, P],
+        "snk_moe_route_sort": [P, P, I, P, P, P, P, P, P, P, I, I, I, I, I, F, I, P],
         "snk_moe_sort": [P, P, P, P, I, I, P],
         "snk_moe_combine": [P, P, P, P, I, I, I, P],
     },
@@ -578,6 +579,38 @@ def moe_route(x, router_w, bias, top_k, norm_topk_prob, scaling):
                               top_k, int(bool(norm_topk_prob)), float(scaling), code_of(dtype), _stream()),
           "moe_route")
     return ids, wts
+
+
+ROUTE_FUSED_MAX_ROWS = 32      # up to here: logits spread over the GPU, selection and sort in one block
+
+
+def moe_route_sort(x, router_w, bias, top_k, norm_topk_prob, scaling):
+    """Routing and the sort by expert together: (ids, weights, offsets, pair_pos, sorted_pair) as
+    `moe_route` and `moe_sort` give them.  The few rows of a decode step take two launches made for
+    them; a row's logits are the same numbers on every path but the tensor-core one."""
+    M, H = x.shape
+    E = router_w.shape[0]
+    if M > ROUTE_FUSED_MAX_ROWS or 8 * E * min(M, 32) > 48 * 1024:
+        ids, wts = moe_route(x, router_w, bias, top_k, norm_topk_prob, scaling)
+        return (ids, wts) + moe_sort(ids, E)
+    dtype = x.dtype
+    _chk(x, "router input", (torch.float32, torch.bfloat16))
+    w32 = _small(router_w, "router weight", dtype)
+    _chk(router_w, "router weight", shape=(E, H))
+    if bias is not None:
+        _chk(bias, "expert bias", torch.float32, (E,))
+    dev = x.device
+    ints = torch.empty(M * top_k * 3 + E + 1, dtype=torch.int32, device=dev)
+    floats = torch.empty(M * E + M * top_k, dtype=torch.float32, device=dev)
+    pairs = M * top_k
+    ids, pair_pos, sorted_pair = ints[:pairs].view(M, top_k), ints[pairs:2 * pairs], ints[2 * pairs:3 * pairs]
+    offsets = ints[3 * pairs:]
+    logits, wts = floats[:M * E], floats[M * E:].view(M, top_k)
+    check(fn("snk_moe_route_sort")(_ptr(x), _ptr(router_w), w32, _ptr(bias), _ptr(logits), _ptr(ids), _ptr(wts),
+                                   _ptr(offsets), _ptr(pair_pos), _ptr(sorted_pair), M, H, E, top_k,
+                                   int(bool(norm_topk_prob)), float(scaling), code_of(dtype), _stream()),
+          "moe_route_sort", launches=2)
+    return ids, wts, offsets, pair_pos, sorted_pair
 
 
 def moe_sort(topk_ids, num_experts):

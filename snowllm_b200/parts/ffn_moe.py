@@ -67,10 +67,10 @@ class SigmoidMoE(Part):
 
     def forward(self, ctx, x):
         M, k = x.shape[0], self.top_k
-        ids, weights = self.route(x)
+        ids, weights, offsets, pair_pos, sorted_pair = kernels.moe_route_sort(
+            x, self.router, self.bias, self.top_k, self.norm_topk_prob, self.routed_scaling_factor)
         if ctx is not None:
             ctx.tap("moe_route", ids)
-        offsets, pair_pos, sorted_pair = kernels.moe_sort(ids, self.num_experts)
         cap = min(M, M * k)          # an expert gets a token at most once
         act = grouped_linear_swiglu(x, self.w13, offsets, M * k, cap, sorted_pair, k, self.interleaved)
         y = grouped_linear(act, self.w2, offsets, M * k, cap, out_dtype=torch.float32)

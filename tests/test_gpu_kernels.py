@@ -387,6 +387,29 @@ def test_moe_route_ties_go_to_the_lower_index_and_bias_only_selects(K):
     assert ids.cpu().tolist() == [[1, 3, 5]] * 2 and torch.allclose(wts.cpu(), torch.full((2, 3), 1.0))
 
 
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("M,E,k,H", [(1, 8, 2, 64), (8, 32, 4, 2048), (13, 5, 3, 80), (32, 40, 6, 104), (9, 7, 7, 50)])
+def test_moe_route_sort_few_rows_is_the_same_routing_and_a_valid_sort(K, dtype, M, E, k, H):
+    torch.manual_seed(13)
+    x, wr = dev(rnd(dtype, M, H), dtype), dev(rnd(dtype, E, H, scale=H ** -0.5), dtype)
+    bias = dev(torch.randn(E) * 0.1)
+    ids, wts, offsets, pair_pos, sorted_pair = K.moe_route_sort(x, wr, bias, k, True, 1.5)
+    # bit for bit what the one-block-per-token kernel selects: a token's routing does not depend on the path
+    big_x = torch.cat([x, dev(rnd(dtype, 64 - M, H), dtype)])        # more rows than the few-rows path takes
+    ids2, wts2 = K.moe_route(big_x, wr, bias, k, True, 1.5)
+    assert torch.equal(ids, ids2[:M]) and torch.equal(wts, wts2[:M])
+    ids3, wts3, *_ = K.moe_route_sort(big_x, wr, bias, k, True, 1.5)
+    assert torch.equal(ids3, ids2) and torch.equal(wts3, wts2)
+    flat = ids.cpu().reshape(-1).long()
+    offsets, pair_pos, sorted_pair = offsets.cpu(), pair_pos.cpu(), sorted_pair.cpu()
+    assert offsets[0] == 0 and offsets[-1] == M * k
+    assert torch.equal(offsets[1:] - offsets[:-1], torch.bincount(flat, minlength=E).int())
+    assert sorted(sorted_pair.tolist()) == list(range(M * k))
+    for p_ in range(M * k):
+        r = int(pair_pos[p_])
+        assert int(sorted_pair[r]) == p_ and offsets[flat[p_]] <= r < offsets[flat[p_] + 1]
+
+
 def test_moe_sort_and_combine(K):
     torch.manual_seed(12)
     M, k, E, H = 37, 3, 9, 70
