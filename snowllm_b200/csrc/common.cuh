@@ -102,20 +102,34 @@ inline int snk_pdl_enabled() {
   return on;
 }
 
+// cluster_z > 1: thread-block clusters of that many blocks along z (grid.z a multiple of it).
 template <typename... KArgs, typename... Args>
-inline cudaError_t snk_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
-                              Args&&... args) {
+inline cudaError_t snk_launch_cluster(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                                      cudaStream_t stream, int cluster_z, Args&&... args) {
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = grid;
   cfg.blockDim = block;
   cfg.dynamicSmemBytes = smem;
   cfg.stream = stream;
-  cudaLaunchAttribute attr[1];
+  cudaLaunchAttribute attr[2];
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr[0].val.programmaticStreamSerializationAllowed = snk_pdl_enabled();
   cfg.attrs = attr;
   cfg.numAttrs = 1;
+  if (cluster_z > 1) {
+    attr[1].id = cudaLaunchAttributeClusterDimension;
+    attr[1].val.clusterDim.x = 1;
+    attr[1].val.clusterDim.y = 1;
+    attr[1].val.clusterDim.z = (unsigned)cluster_z;
+    cfg.numAttrs = 2;
+  }
   return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t snk_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                              Args&&... args) {
+  return snk_launch_cluster(kernel, grid, block, smem, stream, 1, static_cast<Args&&>(args)...);
 }
 
 #define SNK_LAUNCH_CHECK()                       \

@@ -12,6 +12,10 @@
 // two MMAs see a permutation of the 32 k-values, the same one for both operands, which a dot
 // product does not mind.  So every global load is a full 16-byte vector and no shuffle is needed.
 //
+// Few output features (N/16 blocks would leave SMs idle): a thread-block cluster of S blocks along z
+// shares one 16-row strip of W and splits K S ways more; the S partial sums meet in the first block
+// through distributed shared memory, added in rank order.  S depends on N and K alone.
+//
 // Grouped form (routed experts): rows are sorted by group; group e owns rows
 // [offsets[e], offsets[e+1]) and uses W + e*N*K; a_rows gathers A (row r reads A[a_rows[r] / a_div]).
 // A group with more than 64 rows is walked in passes of 64 (W is then re-read from L2).
@@ -19,15 +23,32 @@
 // at decode shapes)
 #include "common.cuh"
 
+#ifndef SK_WARPS
 #define SK_WARPS 8
+#endif
 #define SK_ROWS 16
 #define SK_KBLOCK 32
+#ifndef SK_UNROLL
 #define SK_UNROLL 4
+#endif
 
 __device__ __forceinline__ uint4 ldg_stream(const void* p) {
   uint4 v;
   asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
                : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+  return v;
+}
+
+__device__ __forceinline__ void cluster_sync() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// The float at the same shared-memory address in block `rank` of this cluster.
+__device__ __forceinline__ float ld_cluster_f32(const float* local, uint32_t rank) {
+  uint32_t remote;
+  float v;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;"
+               : "=r"(remote) : "r"((uint32_t)__cvta_generic_to_shared(local)), "r"(rank));
+  asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(remote) : "memory");
   return v;
 }
 
@@ -64,6 +85,8 @@ gemm_skinny_kernel(const bf16* __restrict__ A, const bf16* __restrict__ W, OutT*
   const bf16* w_lo = Wg + (size_t)min(n0 + g, N - 1) * K + 8 * t;
   const bf16* w_hi = Wg + (size_t)min(n0 + g + 8, N - 1) * K + 8 * t;
   const int kblocks = (K + SK_KBLOCK - 1) / SK_KBLOCK;
+  const int split = gridDim.z, rank = blockIdx.z;         // the cluster spans z: S blocks split K further
+  const int vwarp = rank * SK_WARPS + warp, vwarps = split * SK_WARPS;
 
   for (int m0 = row_begin; m0 < row_end; m0 += MT * 8) {
     const bf16* a_ptr[MT];
@@ -81,11 +104,11 @@ gemm_skinny_kernel(const bf16* __restrict__ A, const bf16* __restrict__ W, OutT*
 #pragma unroll
       for (int j = 0; j < 4; ++j) acc[i][j] = 0.f;
 
-    for (int kb0 = warp; kb0 < kblocks; kb0 += SK_WARPS * SK_UNROLL) {
+    for (int kb0 = vwarp; kb0 < kblocks; kb0 += vwarps * SK_UNROLL) {
       uint4 wl[SK_UNROLL], wh[SK_UNROLL];
 #pragma unroll
       for (int u = 0; u < SK_UNROLL; ++u) {
-        const int kb = kb0 + u * SK_WARPS;
+        const int kb = kb0 + u * vwarps;
         const int k = kb * SK_KBLOCK + 8 * t;
         if (kb < kblocks && k < K) {              // K is a multiple of 8: a lane's 8 values are all in or all out
           wl[u] = ldg_stream(w_lo + (size_t)kb * SK_KBLOCK);
@@ -97,7 +120,7 @@ gemm_skinny_kernel(const bf16* __restrict__ A, const bf16* __restrict__ W, OutT*
       }
 #pragma unroll
       for (int u = 0; u < SK_UNROLL; ++u) {
-        const int kb = kb0 + u * SK_WARPS;
+        const int kb = kb0 + u * vwarps;
         const int k = kb * SK_KBLOCK + 8 * t;
         const bool k_ok = kb < kblocks && k < K;
 #pragma unroll
@@ -119,6 +142,44 @@ gemm_skinny_kernel(const bf16* __restrict__ A, const bf16* __restrict__ W, OutT*
       red[warp][i * 8 + 2 * t + 1][g + 8] = acc[i][3];
     }
     __syncthreads();
+    if (split > 1) {
+      // this block's sum over its warps goes to red[0]; the first block then adds the blocks' sums in rank order
+      for (int idx = threadIdx.x; idx < MT * 8 * SK_ROWS; idx += SK_WARPS * 32) {
+        const int tok = idx / SK_ROWS, r = idx % SK_ROWS;
+        float sum = 0.f;
+#pragma unroll
+        for (int w = 0; w < SK_WARPS; ++w) sum += red[w][tok][r];
+        red[0][tok][r] = sum;                               // read and written by this thread alone
+      }
+      cluster_sync();
+      if (rank == 0) {
+        for (int idx = threadIdx.x; idx < MT * 8 * SK_ROWS; idx += SK_WARPS * 32) {
+          const int tok = idx / SK_ROWS, r = idx % SK_ROWS;
+          float sum = red[0][tok][r];
+          for (int q = 1; q < split; ++q) sum += ld_cluster_f32(&red[0][tok][r], q);
+          red[1][tok][r] = sum;
+        }
+        __syncthreads();
+        if constexpr (SWIGLU) {
+          for (int idx = threadIdx.x; idx < MT * 8 * (SK_ROWS / 2); idx += SK_WARPS * 32) {
+            const int tok = idx / (SK_ROWS / 2), r = idx % (SK_ROWS / 2);
+            const int m = m0 + tok, n = n0 + r;
+            if (m < row_end && n + 8 < N) {
+              const float gate = red[1][tok][r], up = red[1][tok][r + 8];
+              C[(size_t)m * (N / 2) + n0 / 2 + r] = from_f<OutT>(gate / (1.f + expf(-gate)) * up);
+            }
+          }
+        } else {
+          for (int idx = threadIdx.x; idx < MT * 8 * SK_ROWS; idx += SK_WARPS * 32) {
+            const int tok = idx / SK_ROWS, r = idx % SK_ROWS;
+            const int m = m0 + tok, n = n0 + r;
+            if (m < row_end && n < N) C[(size_t)m * N + n] = from_f<OutT>(red[1][tok][r]);
+          }
+        }
+      }
+      cluster_sync();                                       // the others' shared memory lives until it has been read
+      continue;
+    }
     if constexpr (SWIGLU) {
       for (int idx = threadIdx.x; idx < MT * 8 * (SK_ROWS / 2); idx += SK_WARPS * 32) {
         const int tok = idx / (SK_ROWS / 2), r = idx % (SK_ROWS / 2);
@@ -150,20 +211,40 @@ gemm_skinny_kernel(const bf16* __restrict__ A, const bf16* __restrict__ W, OutT*
 
 template <int MT>
 static int launch_skinny(const void* A, const void* W, void* C, int M, int N, int K, const int* a_rows,
-                         int a_div, const int* offsets, int groups, int out_f32, int swiglu, cudaStream_t stream) {
-  dim3 grid((N + SK_ROWS - 1) / SK_ROWS, offsets ? groups : 1);
+                         int a_div, const int* offsets, int groups, int out_f32, int swiglu, int split,
+                         cudaStream_t stream) {
+  dim3 grid((N + SK_ROWS - 1) / SK_ROWS, offsets ? groups : 1, split);
+  const dim3 block(SK_WARPS * 32);
   const bf16 *a = static_cast<const bf16*>(A), *w = static_cast<const bf16*>(W);
   if (swiglu)
-    snk_launch(gemm_skinny_kernel<MT, bf16, true>, dim3(grid), dim3(SK_WARPS * 32), 0, stream, a, w, static_cast<bf16*>(C), M, N, K,
-                                                                           a_rows, a_div, offsets);
+    snk_launch_cluster(gemm_skinny_kernel<MT, bf16, true>, grid, block, 0, stream, split, a, w,
+                       static_cast<bf16*>(C), M, N, K, a_rows, a_div, offsets);
   else if (out_f32)
-    snk_launch(gemm_skinny_kernel<MT, float, false>, dim3(grid), dim3(SK_WARPS * 32), 0, stream, a, w, static_cast<float*>(C), M, N,
-                                                                             K, a_rows, a_div, offsets);
+    snk_launch_cluster(gemm_skinny_kernel<MT, float, false>, grid, block, 0, stream, split, a, w,
+                       static_cast<float*>(C), M, N, K, a_rows, a_div, offsets);
   else
-    snk_launch(gemm_skinny_kernel<MT, bf16, false>, dim3(grid), dim3(SK_WARPS * 32), 0, stream, a, w, static_cast<bf16*>(C), M, N, K,
-                                                                            a_rows, a_div, offsets);
+    snk_launch_cluster(gemm_skinny_kernel<MT, bf16, false>, grid, block, 0, stream, split, a, w,
+                       static_cast<bf16*>(C), M, N, K, a_rows, a_div, offsets);
   SNK_LAUNCH_CHECK();
   return 0;
+}
+
+// How many blocks share one strip of W (a cluster along z).  A plain product with fewer strips than
+// the GPU has SMs is split 4 ways, as long as every warp of the cluster keeps two k-blocks of its own.
+// Measured in a replayed chain of launches at 8 rows: 2048 x 2048 6.8 -> 5.1 us, 2048 x 7168 20.6 -> 9.2 us;
+// with 384 strips (6144 x 2048) any split lost (8.1 -> 11.0 us), and so did 8 ways everywhere.
+// Depends on N and K alone, so a row's sum has the same order whatever else the launch holds.
+#define SK_SPLIT 4
+#define SK_SPLIT_MAX_STRIPS 148
+static int skinny_split(int N, int K, const int* offsets) {
+  static int off = -1;                                     // SNOWLLM_B200_SKINNY_SPLIT=0 in the environment: never split
+  if (off < 0) {
+    const char* e = getenv("SNOWLLM_B200_SKINNY_SPLIT");
+    off = (e && e[0] == '0') ? 1 : 0;
+  }
+  if (offsets || off) return 1;                            // grouped: the groups already multiply the blocks
+  const int strips = (N + SK_ROWS - 1) / SK_ROWS, kblocks = (K + SK_KBLOCK - 1) / SK_KBLOCK;
+  return (strips <= SK_SPLIT_MAX_STRIPS && kblocks >= 2 * SK_SPLIT * SK_WARPS) ? SK_SPLIT : 1;
 }
 
 // rows_hint: the most rows one group (or the whole product) is expected to hold; picks how many
@@ -178,8 +259,9 @@ SNK_API int snk_gemm_skinny(const void* A, const void* W, void* C, int M, int N,
   if (((uintptr_t)A % 16) || ((uintptr_t)W % 16)) return SNK_ERR_ALIGN;
   if (groups > 65535) return SNK_ERR_SIZE;
   if (a_div <= 0) a_div = 1;
-  if (rows_hint <= 8) return launch_skinny<1>(A, W, C, M, N, K, a_rows, a_div, offsets, groups, out_f32, swiglu, stream);
-  if (rows_hint <= 16) return launch_skinny<2>(A, W, C, M, N, K, a_rows, a_div, offsets, groups, out_f32, swiglu, stream);
-  if (rows_hint <= 32) return launch_skinny<4>(A, W, C, M, N, K, a_rows, a_div, offsets, groups, out_f32, swiglu, stream);
-  return launch_skinny<8>(A, W, C, M, N, K, a_rows, a_div, offsets, groups, out_f32, swiglu, stream);
+  const int split = skinny_split(N, K, offsets);
+  if (rows_hint <= 8) return launch_skinny<1>(A, W, C, M, N, K, a_rows, a_div, offsets, groups, out_f32, swiglu, split, stream);
+  if (rows_hint <= 16) return launch_skinny<2>(A, W, C, M, N, K, a_rows, a_div, offsets, groups, out_f32, swiglu, split, stream);
+  if (rows_hint <= 32) return launch_skinny<4>(A, W, C, M, N, K, a_rows, a_div, offsets, groups, out_f32, swiglu, split, stream);
+  return launch_skinny<8>(A, W, C, M, N, K, a_rows, a_div, offsets, groups, out_f32, swiglu, split, stream);
 }
