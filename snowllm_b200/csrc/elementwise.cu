@@ -10,24 +10,27 @@
 #include "common.cuh"
 
 // ---------------------------------------------------------------------------------------
+// A negative id -(i + 1) stands for pending[i]: a token that an earlier launch sampled and that the host
+// has not read yet (the step that follows a sampled token can then be launched before the token is known).
 template <typename T>
-__global__ void embedding_kernel(const int* __restrict__ ids, const T* __restrict__ table,
-                                 float* __restrict__ out, int H, int V) {
+__global__ void embedding_kernel(const int* __restrict__ ids, const int* __restrict__ pending, int num_pending,
+                                 const T* __restrict__ table, float* __restrict__ out, int H, int V) {
   pdl_begin();
   const int m = blockIdx.x;
   int id = ids[m];
+  if (id < 0 && pending != nullptr && -(id + 1) < num_pending) id = pending[-(id + 1)];
   const bool ok = id >= 0 && id < V;     // the host checks ids; a bad one reads nothing
   const T* row = table + (size_t)(ok ? id : 0) * H;
   float* o = out + (size_t)m * H;
   for (int i = threadIdx.x; i < H; i += blockDim.x) o[i] = ok ? to_f<T>(row[i]) : 0.f;
 }
 
-SNK_API int snk_embedding(const int* ids, const void* table, float* out, int M, int H, int V,
-                          int dtype, cudaStream_t stream) {
+SNK_API int snk_embedding(const int* ids, const int* pending, int num_pending, const void* table, float* out,
+                          int M, int H, int V, int dtype, cudaStream_t stream) {
   if (M <= 0) return 0;
   const int threads = H >= 1024 ? 256 : 128;
-  SNK_DISPATCH(dtype, snk_launch(embedding_kernel<T>, dim3(M), dim3(threads), 0, stream, 
-                          ids, static_cast<const T*>(table), out, H, V));
+  SNK_DISPATCH(dtype, snk_launch(embedding_kernel<T>, dim3(M), dim3(threads), 0, stream,
+                          ids, pending, num_pending, static_cast<const T*>(table), out, H, V));
   SNK_LAUNCH_CHECK();
   return 0;
 }

@@ -40,6 +40,7 @@ class StepContext:
     _split: tuple | None = None
     fixed_chunks: int | None = None  # a captured step: the key-chunk count its launches were built for
     taps: list | None = None       # when a list: parts append (name, tensor) of chosen intermediates
+    pending_tokens: torch.Tensor | None = None   # int32 on the device: a token id -(i + 1) stands for entry i
 
     def tap(self, name: str, tensor) -> None:
         if self.taps is not None:

@@ -70,7 +70,8 @@ class Engine:
                  max_model_len: int = 8192, stop_token_ids=(), seed: int | None = None,
                  enforce_eager: bool = False, prefill_chunk: int = DEFAULT_PREFILL_CHUNK,
                  gpu_memory_utilization: float = DEFAULT_GPU_UTIL, preempt: bool = True,
-                 exact_stats: bool = False, page_size: int = DEFAULT_PAGE_SIZE, device="cuda"):
+                 exact_stats: bool = False, page_size: int = DEFAULT_PAGE_SIZE, device="cuda",
+                 overlap_steps: bool = True):
         if not 1 <= max_num_seqs <= MAX_NUM_SEQS:
             raise SnowLLMError(f"max_num_seqs must lie in 1..{MAX_NUM_SEQS}")
         self.model, self.device = model, torch.device(device)
@@ -94,6 +95,11 @@ class Engine:
         self.sampler = Sampler(stop_token_ids, seed, self.device)
         self.acct = StepAccounting()
         self.steps = 0
+        self.overlap_steps = overlap_steps
+        self._arrivals = 0
+        self._flight = None                # (requests, pinned host tokens, event) of the step not yet read back
+        self._landing = [torch.empty(MAX_NUM_SEQS, dtype=torch.int32).pin_memory() for _ in range(2)]
+        self._landing_turn = 0
 
     # -- the reference's names ------------------------------------------------------------
     @property
@@ -117,7 +123,8 @@ class Engine:
         return self.sampler.stop_token_ids
 
     def add(self, prompt, params: SamplingParams | None = None) -> Request:
-        r = Request(prompt=[int(t) for t in prompt], params=params or SamplingParams())
+        r = Request(prompt=[int(t) for t in prompt], params=params or SamplingParams(), arrival=self._arrivals)
+        self._arrivals += 1
         V = self.model.vocab_size
         if any(not 0 <= t < V for t in r.prompt):
             raise SnowLLMError(f"prompt holds a token id outside [0, {V})")
@@ -125,24 +132,44 @@ class Engine:
         return r
 
     def abort(self, r: Request) -> None:
+        self._land()
+        r.in_flight = -1
         self.scheduler.abort(r)
 
     def step(self) -> str:
-        """One scheduling round and one model step: "prefill", "decode", "mixed" or "idle"."""
+        """One scheduling round and one model step: "prefill", "decode", "mixed" or "idle" ("drain" when
+        the round only read back the tokens of the step before).
+
+        Overlapped steps (``overlap_steps``): the sampled tokens stay on the device, where the next step's
+        embedding finds them, and reach the host one step late.  So the host plans and launches step k + 1
+        while step k still runs; a request that ended on a stop token is found out one step late too, and
+        the row it was given in between is thrown away.  Steps whose sampling looks at the generated tokens
+        (penalties, n-gram bans), and steps in which pages could run out, first read everything back."""
         t0 = time.perf_counter()
+        if self._flight is not None and self.cache.min_free_pages() < len(self.scheduler.running) + 1:
+            self._land()                   # a decoding request might be preempted: its tokens must be known
         self.scheduler.retire_finished()
         plan = self.scheduler.schedule()
         if not plan:
-            return "idle"
+            if self._flight is None:
+                return "idle"
+            self._land()
+            return "drain"
         entries = [StepEntry(s.request.cache, s.tokens, [s.count - 1] if s.wants_logits else [])
                    for s in plan]
         decode = sum(1 for s in plan if s.count == 1 and s.start >= len(s.request.prompt))
         logits = self.runner.step(entries)
-        sampled = [s.request for s in plan if s.wants_logits]
         for s in plan:
             s.request.num_computed += s.count
-        for r, tok in zip(sampled, self.sampler.sample(logits, sampled)):
-            self.sampler.append(r, tok)
+        self._land()                       # the step before: its tokens are on the host by now, or soon
+        sampled = [s.request for s in plan if s.wants_logits]
+        if sampled:
+            if self.overlap_steps and not self.sampler.needs_history(sampled):
+                self._take_off(logits, sampled)
+            else:
+                for r, tok in zip(sampled, self.sampler.sample(logits, sampled)):
+                    if not r.done:
+                        self.sampler.append(r, tok)
         if self.exact_stats:
             torch.cuda.synchronize(self.device)
         prefill = sum(s.count for s in plan) - decode
@@ -150,10 +177,38 @@ class Engine:
         self.steps += 1
         return "mixed" if prefill and decode else ("prefill" if prefill else "decode")
 
+    def _take_off(self, logits, sampled) -> None:
+        """Sample on the device into the runner's pending tokens and start their copy to the host."""
+        n = len(sampled)
+        self.sampler.sample_on_device(logits, sampled, out=self.runner.pending_tokens[:n])
+        host = self._landing[self._landing_turn]
+        self._landing_turn ^= 1
+        host[:n].copy_(self.runner.pending_tokens[:n], non_blocking=True)
+        event = torch.cuda.Event()
+        event.record()
+        for i, r in enumerate(sampled):
+            if not r.done:                 # found out at the landing just before: the row is thrown away
+                r.in_flight = i
+        self._flight = (sampled, host, event)
+
+    def _land(self) -> None:
+        """Read back the tokens of the step in flight, if any, and record them."""
+        if self._flight is None:
+            return
+        sampled, host, event = self._flight
+        self._flight = None
+        event.synchronize()
+        tokens = host[:len(sampled)].tolist()
+        for i, (r, tok) in enumerate(zip(sampled, tokens)):
+            if r.in_flight == i and not r.done:
+                r.in_flight = -1
+                self.sampler.append(r, tok)
+
     def run(self) -> None:
         while self.scheduler.has_work():
             if self.step() == "idle":
                 break
+        self._land()
         self.scheduler.retire_finished()
 
     def generate(self, prompts, params: SamplingParams | None = None) -> list:

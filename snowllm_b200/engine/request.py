@@ -37,15 +37,35 @@ class Request:
     done: bool = False
     finish_reason: str | None = None    # "stop", "length", "abort", "error"
     preemptions: int = 0
+    arrival: int = 0                    # the engine's count of requests when this one was added
+    in_flight: int = -1                 # >= 0: the last sampled token is still on the device, at this place
+                                        # of the runner's pending tokens; the host has not read it yet
 
     @property
     def tokens(self) -> list:
+        """Prompt and generated tokens; a token the host has not read yet appears as -(place + 1)."""
+        if self.in_flight >= 0:
+            return self.prompt + self.out + [-(self.in_flight + 1)]
         return self.prompt + self.out
+
+    @property
+    def generated(self) -> int:
+        """Tokens sampled so far, the one in flight included."""
+        return len(self.out) + (self.in_flight >= 0)
+
+    @property
+    def num_tokens(self) -> int:
+        return len(self.prompt) + self.generated
 
     @property
     def pending(self) -> int:
         """Tokens not yet run: the rest of the prompt, or the last sampled token."""
-        return len(self.prompt) + len(self.out) - self.num_computed
+        return self.num_tokens - self.num_computed
+
+    @property
+    def at_length(self) -> bool:
+        """The token in flight is the last one this request may generate: nothing more to schedule."""
+        return self.generated >= self.params.max_new_tokens
 
     @property
     def last(self) -> int:

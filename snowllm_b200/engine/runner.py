@@ -13,6 +13,7 @@ import numpy as np
 import torch
 
 from ..cache import CacheManager, RequestCache
+from ..config.engine import MAX_NUM_SEQS
 from ..errors import CapacityError, KernelError, SnowLLMError
 from ..ops import kernels
 from .context import ATTENTION_CHUNK, HostStaging, StepContext
@@ -37,6 +38,9 @@ class ModelRunner:
         self.model, self.cache = model, cache
         self.device = torch.device(device)
         self.staging = HostStaging(self.device)
+        # Tokens that were sampled on the device and that the host may not have read yet.  An entry's
+        # token -(i + 1) stands for pending_tokens[i] (see the Engine's overlapped steps).
+        self.pending_tokens = torch.zeros(MAX_NUM_SEQS, dtype=torch.int32, device=self.device)
         kernels.libraries_for(model.libraries())
         self.steps = 0
         self.tokens = 0
@@ -70,7 +74,8 @@ class ModelRunner:
 
     def build_context(self, entries: Sequence[StepEntry], **kw) -> StepContext:
         return build_context(entries, self.cache, self.model.dtype, self.device, self.staging,
-                             self.model.vocab_size, self.model.spec.max_position, self.taps, **kw)
+                             self.model.vocab_size, self.model.spec.max_position, self.taps,
+                             pending_tokens=self.pending_tokens, **kw)
 
     # -- decode steps as CUDA graphs ------------------------------------------------------------
     def _graph_step(self, entries) -> torch.Tensor:
@@ -136,7 +141,8 @@ class CapturedDecode:
 
 def build_context(entries: Sequence[StepEntry], cache: CacheManager, dtype, device, staging: HostStaging,
                   vocab_size: int, max_position: int = 1 << 30, taps=None, max_pages: int | None = None,
-                  into: torch.Tensor | None = None, host_only: bool = False, fixed_chunks: int | None = None):
+                  into: torch.Tensor | None = None, host_only: bool = False, fixed_chunks: int | None = None,
+                  pending_tokens: torch.Tensor | None = None):
     """Turn a step's entries into the flat batch on the device (one host-to-device copy).
     ``max_pages`` fixes the block-table width; ``into`` is a device buffer that already holds the
     packed metadata (no copy is made); ``host_only`` returns the packed host array instead."""
@@ -164,7 +170,9 @@ def build_context(entries: Sequence[StepEntry], cache: CacheManager, dtype, devi
                 if any(p < 0 for p in table[first:need]):
                     raise CapacityError("the step was given tokens whose pages were not taken")
     ids = np.fromiter((t for e in entries for t in e.tokens), dtype=np.int64, count=M)
-    if M and (ids.min() < 0 or ids.max() >= V):
+    # a negative id -(i + 1) names a token the device still holds (pending_tokens[i])
+    lowest = -pending_tokens.numel() if pending_tokens is not None else 0
+    if M and (ids.min() < lowest or ids.max() >= V):
         raise SnowLLMError(f"token id outside [0, {V})")
     cu = np.zeros(B + 1, dtype=np.int64)
     np.cumsum(lens, out=cu[1:])
@@ -206,4 +214,4 @@ def build_context(entries: Sequence[StepEntry], cache: CacheManager, dtype, devi
         row_seg=view(2), cu_seqlens=view(3), seg_start=view(4), seg_slot=view(5), logit_rows=view(6),
         num_logit_rows=len(logit_rows), block_tables={key: tab[g] for g, key in enumerate(groups)},
         page_size=P, host_positions=positions.astype(np.int64), host_seg_start=list(starts),
-        host_seg_len=list(lens), taps=taps)
+        host_seg_len=list(lens), taps=taps, pending_tokens=pending_tokens, fixed_chunks=fixed_chunks)

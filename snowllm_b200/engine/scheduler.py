@@ -93,7 +93,7 @@ class Scheduler:
         i = 0
         while i < len(self.running) and budget > 0:
             r = self.running[i]
-            if r.done or r.pending != 1 or not r.out:
+            if r.done or r.at_length or r.pending != 1 or not r.generated:
                 i += 1
                 continue
             while not self.cache.ensure(r.cache, r.num_computed + 1):
@@ -118,10 +118,10 @@ class Scheduler:
         for r in self.running:
             if budget <= 0:
                 break
-            if r.done or any(s.request is r for s in plan) or r.pending < 1 or (r.pending == 1 and r.out):
+            if r.done or any(s.request is r for s in plan) or r.pending < 1 or (r.pending == 1 and r.generated):
                 continue
             n = min(r.pending, budget)
-            plan.append(Segment(r, r.num_computed, n, r.num_computed + n == len(r.prompt) + len(r.out)))
+            plan.append(Segment(r, r.num_computed, n, r.num_computed + n == r.num_tokens))
             budget -= n
         # 3. admissions
         while budget > 0 and self.waiting and len(self.running) < self.max_num_seqs:

@@ -20,7 +20,7 @@ _DTYPE_CODE = {torch.float32: F32, torch.bfloat16: BF16}
 P, I, F, LL = c_void_p, c_int, c_float, c_longlong
 _SIGNATURES = {
     "elementwise": {
-        "snk_embedding": [P, P, P, I, I, I, I, P],
+        "snk_embedding": [P, P, I, P, P, I, I, I, I, P],
         "snk_add_rmsnorm": [P, P, P, I, P, P, I, I, F, I, P, P, P, I, P],
         "snk_residual_add": [P, P, LL, P],
         "snk_swiglu": [P, P, I, I, I, I, P],
@@ -158,17 +158,21 @@ def _small(t: torch.Tensor, what: str, compute: torch.dtype) -> int:
 
 # --- elementwise -----------------------------------------------------------------------
 
-def embedding(ids: torch.Tensor, table: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
-    """Float rows of ``table`` (compute dtype) at int32 ``ids``: the start of the residual stream."""
+def embedding(ids: torch.Tensor, table: torch.Tensor, out: torch.Tensor | None = None,
+              pending: torch.Tensor | None = None) -> torch.Tensor:
+    """Float rows of ``table`` (compute dtype) at int32 ``ids``: the start of the residual stream.
+    An id -(i + 1) reads its token from ``pending[i]`` (int32, on the device)."""
     M = ids.numel()
     V, H = table.shape
     _chk(ids, "embedding ids", torch.int32)
+    if pending is not None:
+        _chk(pending, "pending tokens", torch.int32)
     _chk(table, "embedding table", (torch.float32, torch.bfloat16))
     if out is None:
         out = torch.empty(M, H, dtype=torch.float32, device=table.device)
     _chk(out, "embedding output", torch.float32, (M, H))
-    check(fn("snk_embedding")(_ptr(ids), _ptr(table), _ptr(out), M, H, V, code_of(table.dtype),
-                              _stream()), "embedding")
+    check(fn("snk_embedding")(_ptr(ids), _ptr(pending), pending.numel() if pending is not None else 0,
+                              _ptr(table), _ptr(out), M, H, V, code_of(table.dtype), _stream()), "embedding")
     return out
 
 

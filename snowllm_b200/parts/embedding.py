@@ -26,7 +26,7 @@ class Embedding(Part):
 
     def forward(self, ctx):
         """The float residual stream [M, H] of the step's tokens."""
-        return kernels.embedding(ctx.token_ids, self.weight)
+        return kernels.embedding(ctx.token_ids, self.weight, pending=ctx.pending_tokens)
 
 
 class LinearHead(Part):

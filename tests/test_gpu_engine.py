@@ -119,6 +119,50 @@ def test_stop_tokens_and_limits(model_dirs):
     assert len(full.out) == 8
 
 
+def test_overlapped_steps_give_the_tokens_of_steps_read_back_one_by_one(model_dirs):
+    """Tokens that stay on the device for a step (overlap_steps) change nothing: the same requests with
+    stop tokens, with mixed lengths, with a seeded draw, and through a preemption."""
+    from snowllm_b200.engine import SamplingParams
+    d = model_dirs("tiny_a", "float32")
+    prompts = [random_prompt(256, n, 30 + n) for n in (5, 23, 40, 17)]
+    free = engine_for(d, max_num_seqs=4, overlap_steps=False).generate(
+        prompts, SamplingParams(temperature=0, max_new_tokens=20))
+    stops = (free[0][6], free[2][11])
+
+    def run(overlap, **kw):
+        eng = engine_for(d, max_num_seqs=4, prefill_chunk=16, seed=5, overlap_steps=overlap, **kw)
+        pages = eng.stats().free_kv_blocks
+        reqs = [eng.add(p, SamplingParams(temperature=0, max_new_tokens=20, stop_token_ids=stops)) for p in prompts[:3]]
+        reqs.append(eng.add(prompts[3], SamplingParams(temperature=0.9, top_k=20, max_new_tokens=9)))
+        eng.run()
+        assert all(r.done and r.in_flight < 0 for r in reqs)
+        assert eng.stats().running == 0 and eng.stats().free_slots == 4 and eng.stats().free_kv_blocks == pages
+        return [(r.out, r.finish_reason) for r in reqs], eng
+    one_by_one, _ = run(False)
+    overlapped, eng = run(True)
+    assert overlapped == one_by_one
+    assert one_by_one[0][1] == "stop" and one_by_one[0][0] == free[0][:free[0].index(stops[0]) + 1]
+    # few pages: a request is preempted while tokens are in flight
+    params = SamplingParams(temperature=0, max_new_tokens=40)
+    long = [random_prompt(256, 90, s) for s in (1, 2)]
+    calm = engine_for(d, max_num_seqs=2, max_model_len=256, overlap_steps=False).generate(long, params)
+    tight = engine_for(d, max_num_seqs=2, max_model_len=256, num_kv_blocks=13, overlap_steps=True)
+    assert tight.generate(long, params) == calm and tight.stats().preemptions > 0
+
+
+def test_graph_steps_follow_launch_by_launch_steps_across_key_chunks(model_dirs):
+    """Decoding from 500 to 830 tokens crosses several 256-key chunks inside one captured graph's range
+    (the chunk count is rounded up to a power of two): the captured steps must look at every chunk."""
+    from snowllm_b200.engine import SamplingParams
+    d = model_dirs("tiny_e", "float32")
+    prompts = [random_prompt(ALL["tiny_e"]["vocab_size"], n, n) for n in (500, 300)]
+    params = SamplingParams(temperature=0, max_new_tokens=330)
+    eager = engine_for(d, max_num_seqs=2, max_model_len=2048, enforce_eager=True).generate(prompts, params)
+    eng = engine_for(d, max_num_seqs=2, max_model_len=2048)
+    assert eng.generate(prompts, params) == eager
+    assert eng.runner.graph_replays > 300
+
+
 def test_sampling_is_seeded_and_penalties_bite(model_dirs):
     from snowllm_b200.engine import SamplingParams
     d = model_dirs("tiny_a", "float32", flavour="baseline")
