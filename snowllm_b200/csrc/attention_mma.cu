@@ -18,7 +18,7 @@
 // The tile order is fixed by positions alone, so a row's result does not depend on what else the
 // launch holds.  Head sizes 64 and 128; other sizes and float32 go through csrc/attention.cu.
 // Pool layout: [page, 2 (k, v), kv head, page_size, head_dim].
-#include "common.cuh"
+#include "tma.cuh"
 
 #define FA_BQ 64
 #define FA_BK 64
@@ -484,4 +484,279 @@ SNK_API int snk_attention_decode_mma(const void* q, const void* pool, const int*
   }
   SNK_LAUNCH_CHECK();
   return 0;
+}
+
+// ---------------------------------------------------------------------------------------------
+// The same kernel with the chunk's keys and values brought in by TMA: the cache pool is one 2-D tensor
+// [pages * 2 * kv heads * page_size rows, head_dim] whose map has a box of page_size rows x 64 elements
+// and the 128-byte swizzle, so one instruction of one lane lands a page's keys (or values) of this kv
+// head in shared memory in the layout ldmatrix wants (a head of 128 elements is two such panels side by
+// side).  The 128 threads no longer compute addresses and issue 16-byte copies; they wait on one
+// mbarrier.  Pages are loaded whole: rows outside the chunk's valid keys hold whatever the page (or
+// the shared memory before) held, so their scores are replaced, never computed with, and their value
+// rows are zeroed before use.  For page sizes that divide 256 and are multiples of 8.
+// The wait is bounded by wall time; when it runs out the block records it (snk_attention_decode_status)
+// and goes on without the data.
+#define FD_WAIT_NS 1000000000ull
+__device__ int g_fd_status;
+
+template <int HD>
+__global__ void __launch_bounds__(FA_WARPS * 32)
+attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_kv, const bf16* __restrict__ q,
+                            const int* __restrict__ block_table, int max_pages, int page_size,
+                            const int* __restrict__ positions, const int* __restrict__ row_seg,
+                            const int* __restrict__ row_list, bf16* __restrict__ out,
+                            float* __restrict__ part_o, float* __restrict__ part_ml, int nh, int nkv,
+                            int window, int num_chunks, float scale_log2) {
+  // the map is a kernel parameter: fetching it does not have to wait for the kernel in front
+  if (threadIdx.x == 0)
+    asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_kv)) : "memory");
+  pdl_begin();
+  constexpr int CH = HD / 8, KT = HD / 16, NT = HD / 8, PANELS = HD / 64;
+  constexpr uint32_t PANEL = FD_CHUNK * 128;              // bytes of one 64-element panel of the chunk's rows
+  extern __shared__ unsigned char fd_raw[];
+  unsigned char* fd_smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(fd_raw) + 1023) & ~uintptr_t(1023));
+  const uint32_t sm_k = (uint32_t)__cvta_generic_to_shared(fd_smem);        // [PANELS][256][64]
+  const uint32_t sm_v = sm_k + PANELS * PANEL;
+  const uint32_t sm_q = sm_v + PANELS * PANEL;                              // [16][HD], swz<CH>
+  float* merge = reinterpret_cast<float*>(fd_smem);                         // reuses the key tile afterwards
+  __shared__ uint64_t bar;
+
+  const int m = row_list ? row_list[blockIdx.x] : blockIdx.x;
+  const int kvh = blockIdx.y;
+  const int group = nh / nkv;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int g = lane >> 2, t = lane & 3;
+  const int pos = positions[m];
+  const int lo = window > 0 ? max(0, pos - window + 1) : 0;
+  const int c = lo / FD_CHUNK + blockIdx.z;
+  if ((long long)c * FD_CHUNK > pos) return;
+  const int k0 = c * FD_CHUNK;
+  const int k_begin = max(lo, k0), k_end = min(pos + 1, k0 + FD_CHUNK);
+  const int* bt = block_table + (size_t)row_seg[m] * max_pages;
+
+  if (threadIdx.x == 0) {
+    mbar_init(&bar, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  for (int v = threadIdx.x; v < 16 * CH; v += FA_WARPS * 32) {
+    const int r = v / CH, cc = v % CH;
+    fa_cp_async16(sm_q + swz<CH>(r, cc), q + ((size_t)m * nh + kvh * group + min(r, group - 1)) * HD + cc * 8,
+                  r < group);
+  }
+  fa_commit();
+  __syncthreads();                                        // the barrier is initialised
+  const int first_page = k_begin / page_size;
+  const int n_pages = (k_end - 1) / page_size - first_page + 1;
+  if (warp == 0) {
+    if (lane == 0) mbar_expect_tx(&bar, (uint32_t)n_pages * page_size * 128u * 2u * PANELS);
+    __syncwarp();
+    for (int i = lane; i < n_pages; i += 32) {
+      const int page = bt[first_page + i];
+      const int row = (first_page + i) * page_size - k0;                    // the page's first row in the chunk
+      const int y_k = ((page * 2) * nkv + kvh) * page_size, y_v = ((page * 2 + 1) * nkv + kvh) * page_size;
+#pragma unroll
+      for (int p = 0; p < PANELS; ++p) {
+        tma_load_2d(fd_smem + p * PANEL + row * 128, &map_kv, &bar, p * 64, y_k);
+        tma_load_2d(fd_smem + (PANELS + p) * PANEL + row * 128, &map_kv, &bar, p * 64, y_v);
+      }
+    }
+  }
+  fa_wait<0>();
+  if (!mbar_try_wait(&bar, 0)) {
+    const uint64_t start = global_ns();
+    while (!mbar_try_wait(&bar, 0)) {
+      if (global_ns() - start > FD_WAIT_NS) {
+        atomicCAS(&g_fd_status, 0, 1);
+        break;
+      }
+    }
+  }
+  if (k_begin > k0 || k_end < k0 + FD_CHUNK) {            // value rows outside the valid keys: zero, whatever they held
+    for (int r = threadIdx.x; r < FD_CHUNK; r += FA_WARPS * 32) {
+      const int kp = k0 + r;
+      if (kp < k_begin || kp >= k_end) {
+#pragma unroll
+        for (int p = 0; p < PANELS; ++p) {
+          uint4* row = reinterpret_cast<uint4*>(fd_smem + (PANELS + p) * PANEL + r * 128);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) row[i] = make_uint4(0, 0, 0, 0);
+        }
+      }
+    }
+  }
+  __syncthreads();
+  // byte offset of 16-byte chunk cc of row r in a [PANELS][256][64] tile written by TMA
+  auto tile_off = [](int r, int cc) -> uint32_t {
+    return (uint32_t)(cc >> 3) * PANEL + (uint32_t)r * 128u + (uint32_t)(((cc & 7) ^ (r & 7)) << 4);
+  };
+
+  float acc_o[NT][4];
+#pragma unroll
+  for (int i = 0; i < NT; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) acc_o[i][j] = 0.f;
+  float row_max[2] = {-INFINITY, -INFINITY}, row_sum[2] = {0.f, 0.f};
+  const int w0 = k0 + warp * FA_BK;                       // first key of this warp's 64
+  if (w0 < k_end && w0 + FA_BK > k_begin) {
+    uint32_t qf[KT][4];
+#pragma unroll
+    for (int k = 0; k < KT; ++k) {
+      const int r = (lane & 7) + 8 * ((lane >> 3) & 1), cc = 2 * k + (lane >> 4);
+      ldmatrix_x4(sm_q + swz<CH>(r, cc), qf[k][0], qf[k][1], qf[k][2], qf[k][3]);
+    }
+    float s[FA_BK / 8][4];
+#pragma unroll
+    for (int i = 0; i < FA_BK / 8; ++i)
+#pragma unroll
+      for (int j = 0; j < 4; ++j) s[i][j] = 0.f;
+#pragma unroll
+    for (int k = 0; k < KT; ++k) {
+#pragma unroll
+      for (int n = 0; n < FA_BK / 16; ++n) {
+        uint32_t b0, b1, b2, b3;
+        const int r = warp * FA_BK + n * 16 + (lane & 7) + 8 * (lane >> 4), cc = 2 * k + ((lane >> 3) & 1);
+        ldmatrix_x4(sm_k + tile_off(r, cc), b0, b1, b2, b3);
+        fa_mma(s[2 * n], qf[k][0], qf[k][1], qf[k][2], qf[k][3], b0, b1);
+        fa_mma(s[2 * n + 1], qf[k][0], qf[k][1], qf[k][2], qf[k][3], b2, b3);
+      }
+    }
+    float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+    for (int i = 0; i < FA_BK / 8; ++i) {
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int kp = w0 + 8 * i + 2 * t + (j & 1);
+        s[i][j] = (kp >= k_begin && kp < k_end) ? s[i][j] * scale_log2 : -INFINITY;
+        mx[j >> 1] = fmaxf(mx[j >> 1], s[i][j]);
+      }
+    }
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 1));
+      mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 2));
+      row_max[h] = mx[h];
+    }
+    uint32_t pf[FA_BK / 16][4];
+#pragma unroll
+    for (int i = 0; i < FA_BK / 8; ++i) {
+      const float p0 = exp2f(s[i][0] - mx[0]), p1 = exp2f(s[i][1] - mx[0]);
+      const float p2 = exp2f(s[i][2] - mx[1]), p3 = exp2f(s[i][3] - mx[1]);
+      row_sum[0] += p0 + p1;
+      row_sum[1] += p2 + p3;
+      pf[i >> 1][(i & 1) * 2] = pack_bf16(p0, p1);
+      pf[i >> 1][(i & 1) * 2 + 1] = pack_bf16(p2, p3);
+    }
+#pragma unroll
+    for (int kk = 0; kk < FA_BK / 16; ++kk) {
+#pragma unroll
+      for (int n = 0; n < NT / 2; ++n) {
+        uint32_t b0, b1, b2, b3;
+        const int r = warp * FA_BK + kk * 16 + (lane & 7) + 8 * ((lane >> 3) & 1), cc = 2 * n + (lane >> 4);
+        ldmatrix_x4_trans(sm_v + tile_off(r, cc), b0, b1, b2, b3);
+        fa_mma(acc_o[2 * n], pf[kk][0], pf[kk][1], pf[kk][2], pf[kk][3], b0, b1);
+        fa_mma(acc_o[2 * n + 1], pf[kk][0], pf[kk][1], pf[kk][2], pf[kk][3], b2, b3);
+      }
+    }
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      row_sum[h] += __shfl_xor_sync(0xffffffffu, row_sum[h], 1);
+      row_sum[h] += __shfl_xor_sync(0xffffffffu, row_sum[h], 2);
+    }
+  }
+  __syncthreads();                                        // all warps are done with the key tile: reuse it
+  float* ml = merge;
+  float* mo = merge + FA_WARPS * 16 * 2;
+  if (t == 0) {
+    ml[(warp * 16 + g) * 2] = row_max[0];
+    ml[(warp * 16 + g) * 2 + 1] = row_sum[0];
+    ml[(warp * 16 + g + 8) * 2] = row_max[1];
+    ml[(warp * 16 + g + 8) * 2 + 1] = row_sum[1];
+  }
+#pragma unroll
+  for (int i = 0; i < NT; ++i) {
+    const int d = 8 * i + 2 * t;
+    mo[(warp * 16 + g) * HD + d] = acc_o[i][0];
+    mo[(warp * 16 + g) * HD + d + 1] = acc_o[i][1];
+    mo[(warp * 16 + g + 8) * HD + d] = acc_o[i][2];
+    mo[(warp * 16 + g + 8) * HD + d + 1] = acc_o[i][3];
+  }
+  __syncthreads();
+  for (int idx = threadIdx.x; idx < group * HD; idx += FA_WARPS * 32) {
+    const int r = idx / HD, d = idx % HD;
+    float mxl = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < FA_WARPS; ++w) mxl = fmaxf(mxl, ml[(w * 16 + r) * 2]);
+    float l = 0.f, o = 0.f;
+#pragma unroll
+    for (int w = 0; w < FA_WARPS; ++w) {                  // warps in key order
+      const float f = exp2f(ml[(w * 16 + r) * 2] - mxl);  // a warp without keys: exp2(-inf) = 0
+      l += ml[(w * 16 + r) * 2 + 1] * f;
+      o = fmaf(mo[(w * 16 + r) * HD + d], f, o);
+    }
+    const int head = kvh * group + r;
+    if (num_chunks == 1) {
+      out[((size_t)m * nh + head) * HD + d] = __float2bfloat16_rn(o / l);
+    } else {
+      const size_t slot = ((size_t)blockIdx.x * nh + head) * num_chunks + blockIdx.z;
+      part_o[slot * HD + d] = o;
+      if (d == 0) {
+        part_ml[slot * 2] = mxl * 0.6931471805599453f;
+        part_ml[slot * 2 + 1] = l;
+      }
+    }
+  }
+}
+
+// Whether the TMA kernel takes this page size.
+static bool decode_tma_page_ok(int page_size) {
+  return page_size >= 8 && page_size <= FD_CHUNK && page_size % 8 == 0 && FD_CHUNK % page_size == 0;
+}
+
+// num_pages: pages in the pool (it is [num_pages, 2, nkv, page_size, hd]).  Page sizes the TMA kernel does
+// not take give SNK_ERR_SIZE (the caller then uses snk_attention_decode_mma).
+SNK_API int snk_attention_decode_tma(const void* q, const void* pool, long long num_pages, const int* block_table,
+                                     int max_pages, int page_size, const int* positions, const int* row_seg,
+                                     const int* row_list, void* out, void* scratch, int M, int nh, int nkv,
+                                     int hd, int window, int num_chunks, float scale, cudaStream_t stream) {
+  if (M <= 0) return 0;
+  if (nkv <= 0 || nh % nkv || nh / nkv > 16 || nkv > 65535 || num_chunks < 1 || num_chunks > 65535)
+    return SNK_ERR_SIZE;
+  if ((hd != 64 && hd != 128) || !decode_tma_page_ok(page_size) || num_pages <= 0) return SNK_ERR_SIZE;
+  if (num_pages * 2 * nkv * page_size >= (1ll << 31)) return SNK_ERR_SIZE;       // row coordinates are 32-bit
+  if (num_chunks > 1 && scratch == nullptr) return SNK_ERR_SIZE;
+  if (((uintptr_t)q % 16) || ((uintptr_t)pool % 16)) return SNK_ERR_ALIGN;
+  CUtensorMap map;
+  const int rc = tensor_map(pool, num_pages * 2 * nkv * page_size, hd, page_size, 64, &map);
+  if (rc) return rc;
+  const float scale_log2 = scale * 1.4426950408889634f;
+  dim3 grid(M, nkv, num_chunks);
+  const size_t smem = 1024 + (size_t)2 * (hd / 64) * FD_CHUNK * 128 + (size_t)16 * hd * 2;
+  float* part_o = static_cast<float*>(scratch);
+  float* part_ml = part_o ? part_o + (size_t)M * nh * num_chunks * hd : nullptr;
+  const bf16* qp = static_cast<const bf16*>(q);
+  bf16* op = static_cast<bf16*>(out);
+  if (hd == 64) {
+    cudaFuncSetAttribute(attention_decode_tma_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    snk_launch(attention_decode_tma_kernel<64>, dim3(grid), dim3(FA_WARPS * 32), smem, stream, map, qp, block_table,
+               max_pages, page_size, positions, row_seg, row_list, op, part_o, part_ml, nh, nkv, window, num_chunks,
+               scale_log2);
+  } else {
+    cudaFuncSetAttribute(attention_decode_tma_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    snk_launch(attention_decode_tma_kernel<128>, dim3(grid), dim3(FA_WARPS * 32), smem, stream, map, qp, block_table,
+               max_pages, page_size, positions, row_seg, row_list, op, part_o, part_ml, nh, nkv, window, num_chunks,
+               scale_log2);
+  }
+  SNK_LAUNCH_CHECK();
+  return 0;
+}
+
+// 0, or 1 when a block of an earlier launch gave up waiting for its keys; reading clears it.
+// Synchronises the device.
+SNK_API int snk_attention_decode_status() {
+  int v = 0, zero = 0;
+  if (cudaMemcpyFromSymbol(&v, g_fd_status, sizeof(int)) != cudaSuccess) return -1;
+  if (v) cudaMemcpyToSymbol(g_fd_status, &zero, sizeof(int));
+  return v;
 }

@@ -27,12 +27,7 @@
 // tensor memory and returns.
 // (the role of snowllm/ops/gemm.py:33-41 and the expert products of snowllm/ops/inference.py:60-76
 // at prefill shapes)
-#include <cuda.h>
-
-#include <mutex>
-#include <unordered_map>
-
-#include "common.cuh"
+#include "tma.cuh"
 
 #define TC_BM 128
 #define TC_BK 64
@@ -44,27 +39,6 @@ enum { TC_ERR_WAIT_FULL = 1, TC_ERR_WAIT_EMPTY = 2, TC_ERR_WAIT_ACC = 3, TC_ERR_
 
 __device__ int g_tc_status;            // 0, or the first error code a block recorded
 
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ uint64_t global_ns() {
-  uint64_t t;
-  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-  return t;
-}
-
-__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
-}
-__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
-  uint32_t ok;
-  asm volatile(
-      "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}"
-      : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
-  return ok != 0;
-}
 // Wait for a phase, for TC_WAIT_NS at most.  `aborted` (shared) short-cuts every later wait of the block.
 __device__ __forceinline__ void mbar_wait(uint64_t* bar, uint32_t parity, volatile int* aborted, int code) {
   if (*aborted) return;
@@ -78,13 +52,6 @@ __device__ __forceinline__ void mbar_wait(uint64_t* bar, uint32_t parity, volati
       return;
     }
   }
-}
-
-__device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* map, uint64_t* bar, int x, int y) {
-  asm volatile(
-      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
-      ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar)), "r"(x), "r"(y)
-      : "memory");
 }
 
 // Shared-memory matrix descriptor of a K-major tile whose rows are 128 bytes, written by TMA with the
@@ -103,9 +70,6 @@ __device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t smem_addr) {
 // Instruction descriptor of kind::f16: D float, A and B bfloat16, both K-major, M 128, N n.
 __device__ __forceinline__ uint32_t instr_desc_bf16(int n) {
   return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(TC_BM >> 4) << 24);
-}
-__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
-  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
 
 __device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
@@ -358,65 +322,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   }
 }
 
-// ---------------------------------------------------------------------------------------------
-// Tensor maps: 2-D, bfloat16, inner dimension K, box 64 x (128 or 256) rows, 128-byte swizzle.  Built through the
-// driver entry point (no link against the driver library) and cached by (pointer, rows, K).
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
-                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-static EncodeTiledFn encode_fn() {
-  static EncodeTiledFn fn = nullptr;
-  static std::once_flag once;
-  std::call_once(once, [] {
-    void* p = nullptr;
-    cudaDriverEntryPointQueryResult q;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
-        q == cudaDriverEntryPointSuccess)
-      fn = reinterpret_cast<EncodeTiledFn>(p);
-  });
-  return fn;
-}
-
-struct MapKey {
-  const void* ptr;
-  long long rows, k;
-  int box_rows;
-  bool operator==(const MapKey& o) const {
-    return ptr == o.ptr && rows == o.rows && k == o.k && box_rows == o.box_rows;
-  }
-};
-struct MapKeyHash {
-  size_t operator()(const MapKey& m) const {
-    return std::hash<const void*>()(m.ptr) ^ (std::hash<long long>()(m.rows) * 1315423911u) ^
-           (std::hash<long long>()(m.k) * 2654435761u) ^ (size_t)m.box_rows;
-  }
-};
-
-static int tensor_map(const void* ptr, long long rows, long long k, int box_rows, CUtensorMap* out) {
-  static std::unordered_map<MapKey, CUtensorMap, MapKeyHash> cache;
-  static std::mutex mu;
-  std::lock_guard<std::mutex> lock(mu);
-  const MapKey key{ptr, rows, k, box_rows};
-  auto it = cache.find(key);
-  if (it != cache.end()) { *out = it->second; return 0; }
-  EncodeTiledFn fn = encode_fn();
-  if (!fn) return SNK_ERR_SIZE + 100;
-  const cuuint64_t dims[2] = {(cuuint64_t)k, (cuuint64_t)rows};
-  const cuuint64_t strides[1] = {(cuuint64_t)k * 2};
-  const cuuint32_t box[2] = {TC_BK, (cuuint32_t)box_rows};
-  const cuuint32_t estr[2] = {1, 1};
-  CUtensorMap m;
-  const CUresult r = fn(&m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
-                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  if (r != CUDA_SUCCESS) return 30000 + (int)r;
-  if (cache.size() > 8192) cache.clear();
-  cache.emplace(key, m);
-  *out = m;
-  return 0;
-}
-
 template <int BN, typename OutT, bool SWIGLU>
 static int launch_tc(const CUtensorMap& map_a, const CUtensorMap& map_w, void* C, int M, int N, int K,
                      const int* offsets, int groups, int row_tiles, cudaStream_t stream) {
@@ -451,9 +356,9 @@ SNK_API int snk_gemm_tc(const void* A, const void* W, void* C, int M, int N, int
   // wide tiles where they still give every SM work; narrow ones otherwise
   const bool wide = (long long)((M + TC_BM - 1) / TC_BM) * ((N + 255) / 256) >= 120;
   CUtensorMap map_a, map_w;
-  int rc = tensor_map(A, M, K, TC_BM, &map_a);
+  int rc = tensor_map(A, M, K, TC_BM, TC_BK, &map_a);
   if (rc) return rc;
-  rc = tensor_map(W, (long long)(offsets ? groups : 1) * N, K, wide ? 256 : 128, &map_w);
+  rc = tensor_map(W, (long long)(offsets ? groups : 1) * N, K, wide ? 256 : 128, TC_BK, &map_w);
   if (rc) return rc;
 #define TC_GO(BN_, T_, S_) launch_tc<BN_, T_, S_>(map_a, map_w, C, M, N, K, offsets, groups, row_tiles, stream)
   if (swiglu) return wide ? TC_GO(256, bf16, true) : TC_GO(128, bf16, true);

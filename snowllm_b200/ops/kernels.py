@@ -7,6 +7,7 @@ or a library that cannot be built, is an error (the role of snowllm/ops/_common.
 from __future__ import annotations
 
 import ctypes
+import os
 from ctypes import c_float, c_int, c_longlong, c_void_p
 
 import torch
@@ -40,6 +41,8 @@ _SIGNATURES = {
     "attention_mma": {
         "snk_attention_prefill": [P, P, P, I, I, P, I, P, I, I, I, I, F, P],
         "snk_attention_decode_mma": [P, P, P, I, I, P, P, P, P, P, I, I, I, I, I, I, F, P],
+        "snk_attention_decode_tma": [P, P, LL, P, I, I, P, P, P, P, P, I, I, I, I, I, I, F, P],
+        "snk_attention_decode_status": [],
     },
     "gemm": {
         "snk_gemm_simt": [P, P, P, I, I, I, P, I, P, I, I, I, I, P],
@@ -366,10 +369,25 @@ def attention_decode_mma_ok(q, num_kv_heads: int) -> bool:
             and q.shape[1] // num_kv_heads <= DECODE_MMA_MAX_GROUP)
 
 
+def decode_tma_page_ok(page_size: int) -> bool:
+    """Page sizes whose pages a TMA box brings in whole (csrc/attention_mma.cu)."""
+    return 8 <= page_size <= DECODE_MMA_CHUNK and page_size % 8 == 0 and DECODE_MMA_CHUNK % page_size == 0
+
+
+DECODE_TMA = os.environ.get("SNOWLLM_B200_DECODE_TMA", "1") != "0"
+
+
+def attention_decode_status() -> int:
+    """0, or 1 when a block of the TMA decode kernel gave up waiting for its keys (clears it)."""
+    return int(fn("snk_attention_decode_status")())
+
+
 def attention_decode_mma(q, pool, block_table, page_size, positions, row_seg, scale, num_chunks, out,
-                         window=None, scratch=None, rows=None):
+                         window=None, scratch=None, rows=None, tma=None):
     """Tensor-core attention for rows with long runs of keys (decoded tokens): keys in chunks of 256, the
-    q heads of a kv head as the rows of the MMA; chunks merged in order when there is more than one."""
+    q heads of a kv head as the rows of the MMA; chunks merged in order when there is more than one.
+    ``tma``: bring keys and values in by TMA (default: wherever the page size allows); both ways give the
+    same bits."""
     M, nh, hd = q.shape
     _chk(q, "q", torch.bfloat16)
     _chk(pool, "kv pool", torch.bfloat16)
@@ -388,10 +406,18 @@ def attention_decode_mma(q, pool, block_table, page_size, positions, row_seg, sc
         _chk(scratch, "attention scratch", torch.uint8)
         if scratch.numel() < need:
             raise KernelError(f"attention scratch holds {scratch.numel()} bytes, needs {need}")
-    check(fn("snk_attention_decode_mma")(
-        _ptr(q), _ptr(pool), _ptr(block_table), block_table.shape[1], page_size, _ptr(positions), _ptr(row_seg),
-        _ptr(rows), _ptr(out), _ptr(scratch), served, nh, pool.shape[2], hd, int(window or 0), int(num_chunks),
-        float(scale), _stream()), "attention_decode_mma")
+    if tma is None:
+        tma = DECODE_TMA and decode_tma_page_ok(page_size)
+    if tma:
+        check(fn("snk_attention_decode_tma")(
+            _ptr(q), _ptr(pool), pool.shape[0], _ptr(block_table), block_table.shape[1], page_size, _ptr(positions),
+            _ptr(row_seg), _ptr(rows), _ptr(out), _ptr(scratch), served, nh, pool.shape[2], hd, int(window or 0),
+            int(num_chunks), float(scale), _stream()), "attention_decode_tma")
+    else:
+        check(fn("snk_attention_decode_mma")(
+            _ptr(q), _ptr(pool), _ptr(block_table), block_table.shape[1], page_size, _ptr(positions), _ptr(row_seg),
+            _ptr(rows), _ptr(out), _ptr(scratch), served, nh, pool.shape[2], hd, int(window or 0), int(num_chunks),
+            float(scale), _stream()), "attention_decode_mma")
     if num_chunks > 1:
         check(fn("snk_attention_merge")(_ptr(scratch), _ptr(positions), _ptr(out), served, nh, hd, int(window or 0),
                                         DECODE_MMA_CHUNK, int(num_chunks), BF16, _ptr(rows), _stream()),

@@ -711,7 +711,8 @@ def test_products_with_swiglu_store(K, M, I, K_):
 
 # ---------------------------------------------------------------------------------------------
 @pytest.mark.parametrize("nh,nkv,hd,P,window", [(4, 1, 64, 16, None), (32, 8, 64, 16, None), (16, 1, 128, 64, None),
-                                                (6, 2, 128, 8, None), (8, 2, 64, 16, 300), (3, 3, 64, 16, 37)])
+                                                (6, 2, 128, 8, None), (8, 2, 64, 16, 300), (3, 3, 64, 16, 37),
+                                                (4, 2, 64, 4, None), (2, 1, 128, 32, 520)])
 def test_attention_decode_mma(K, nh, nkv, hd, P, window):
     """The tensor-core kernel for decoded rows: requests of very different lengths (one chunk, a chunk
     edge, many chunks), scattered pages, unwritten cache entries NaN, a row list, windows."""
@@ -745,6 +746,12 @@ def test_attention_decode_mma(K, nh, nkv, hd, P, window):
                                n_chunks + extra, out, window=window)
         assert out.isfinite().all(), "an unwritten (NaN) cache entry was read, or a row was not written"
         close(out, want, dtype)
+    if K.decode_tma_page_ok(P):                    # keys brought in by TMA or by 16-byte copies: the same bits
+        by_copies = torch.full((B, nh * hd), float("nan"), dtype=dtype, device="cuda")
+        K.attention_decode_mma(dev(q, dtype), pool, bt, P, i32(positions), i32(list(range(B))), scale,
+                               n_chunks, by_copies, window=window, tma=False)
+        assert torch.equal(by_copies, out)
+        assert K.attention_decode_status() == 0
     some = [5, 0, 3]
     out = torch.zeros(B, nh * hd, dtype=dtype, device="cuda")
     K.attention_decode_mma(dev(q, dtype), pool, bt, P, i32(positions), i32(list(range(B))), scale, n_chunks, out,
