@@ -263,6 +263,285 @@ SNK_API int snk_attention_prefill(const void* q, const void* pool, const int* bl
 
 
 // ---------------------------------------------------------------------------------------------
+// The prompt kernel with keys and values brought in by TMA (see the decode kernel below for the map: a
+// box is one page's rows of one kv head, 64 elements wide, 128-byte swizzle).  A ring of FP_STAGES key
+// tiles: lanes of warp 0 issue the loads of tile kt + FP_STAGES - 1 while the warps work on tile kt, each
+// stage with an mbarrier that counts its bytes.  Pages are loaded whole, so in the first and the last
+// tile rows outside [key_lo, last_pos] hold whatever was there: their scores are replaced, never used,
+// and their value rows are zeroed before use.  Only tiles that cross a row's causal or window edge apply
+// masks.  Blocks take the tiles from the last (most keys) to the first.  For page sizes 8, 16, 32, 64.
+#ifndef FP_STAGES
+#define FP_STAGES 3
+#endif
+#ifndef FP_MIN_BLOCKS
+#define FP_MIN_BLOCKS 1
+#endif
+#define FP_WAIT_NS 1000000000ull
+
+__device__ int g_fa_status;
+
+template <int HD>
+__global__ void __launch_bounds__(FA_WARPS * 32, FP_MIN_BLOCKS)
+attention_prefill_tma_kernel(const __grid_constant__ CUtensorMap map_kv, const bf16* __restrict__ q,
+                             const int* __restrict__ block_table, int max_pages, int page_size,
+                             const int* __restrict__ tiles, int n_tiles, bf16* __restrict__ out, int nh, int nkv,
+                             int window, float scale_log2) {
+  if (threadIdx.x == 0)
+    asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_kv)) : "memory");
+  pdl_begin();
+  constexpr int CH = HD / 8, KT = HD / 16, NT = HD / 8, PANELS = HD / 64;
+  constexpr uint32_t PANEL = FA_BK * 128;                 // bytes of one 64-element panel of a key tile
+  constexpr uint32_t STAGE = 2 * PANELS * PANEL;          // keys, then values
+  extern __shared__ unsigned char fp_raw[];
+  unsigned char* fp_smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(fp_raw) + 1023) & ~uintptr_t(1023));
+  const uint32_t sm_kv = (uint32_t)__cvta_generic_to_shared(fp_smem);       // [FP_STAGES][k | v][PANELS][64][64]
+  const uint32_t sm_q = sm_kv + FP_STAGES * STAGE;                          // [64][HD], swz<CH>
+  __shared__ uint64_t full[FP_STAGES];
+
+  const int* tile = tiles + (size_t)(n_tiles - 1 - blockIdx.x) * 4;
+  const int seg = tile[0], row0 = tile[1], rows = tile[2], pos0 = tile[3];
+  const int head = blockIdx.y;
+  const int kvh = head / (nh / nkv);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int g = lane >> 2, t = lane & 3;
+  const int* bt = block_table + (size_t)seg * max_pages;
+
+  const int last_pos = pos0 + rows - 1;
+  const int key_lo = window > 0 ? max(0, pos0 - window + 1) : 0;
+  const int k_first = (key_lo / FA_BK) * FA_BK;
+  const int n_kt = (last_pos - k_first) / FA_BK + 1;
+
+  if (threadIdx.x == 0) {
+#pragma unroll
+    for (int i = 0; i < FP_STAGES; ++i) mbar_init(&full[i], 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  for (int v = threadIdx.x; v < FA_BQ * CH; v += FA_WARPS * 32) {
+    const int r = v / CH, c = v % CH;
+    fa_cp_async16(sm_q + swz<CH>(r, c), q + ((size_t)(row0 + min(r, rows - 1)) * nh + head) * HD + c * 8, r < rows);
+  }
+  fa_commit();
+  __syncthreads();                                        // the barriers are initialised
+
+  // warp 0 issues tile kt's pages: those that hold a key of [key_lo, last_pos]
+  auto issue = [&](int kt) {
+    if (warp != 0 || kt >= n_kt) return;
+    const int k0 = k_first + kt * FA_BK;
+    const int first_page = max(k0, key_lo) / page_size;
+    const int n_pages = min(k0 + FA_BK - 1, last_pos) / page_size - first_page + 1;
+    unsigned char* stage = fp_smem + (size_t)(kt % FP_STAGES) * STAGE;
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");     // rows zeroed by threads before: ordered before the loads
+    if (lane == 0) mbar_expect_tx(&full[kt % FP_STAGES], (uint32_t)n_pages * page_size * 128u * 2u * PANELS);
+    __syncwarp();
+    for (int i = lane; i < n_pages; i += 32) {
+      const int page = bt[first_page + i];
+      const int row = (first_page + i) * page_size - k0;
+      const int y_k = ((page * 2) * nkv + kvh) * page_size, y_v = ((page * 2 + 1) * nkv + kvh) * page_size;
+#pragma unroll
+      for (int p = 0; p < PANELS; ++p) {
+        tma_load_2d(stage + p * PANEL + row * 128, &map_kv, &full[kt % FP_STAGES], p * 64, y_k);
+        tma_load_2d(stage + (PANELS + p) * PANEL + row * 128, &map_kv, &full[kt % FP_STAGES], p * 64, y_v);
+      }
+    }
+  };
+  auto tile_off = [](int r, int cc) -> uint32_t {
+    return (uint32_t)(cc >> 3) * PANEL + (uint32_t)r * 128u + (uint32_t)(((cc & 7) ^ (r & 7)) << 4);
+  };
+#pragma unroll
+  for (int i = 0; i < FP_STAGES - 1; ++i) issue(i);
+
+  float acc_o[NT][4];
+#pragma unroll
+  for (int i = 0; i < NT; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) acc_o[i][j] = 0.f;
+  float row_max[2] = {-INFINITY, -INFINITY}, row_sum[2] = {0.f, 0.f};
+  uint32_t qf[KT][4];
+  const int r_lo = warp * 16 + g, r_hi = r_lo + 8;
+  const int p_lo = pos0 + r_lo, p_hi = pos0 + r_hi;
+  const int lo_lo = window > 0 ? max(0, p_lo - window + 1) : 0;
+  const int lo_hi = window > 0 ? max(0, p_hi - window + 1) : 0;
+  const int warp_first_pos = pos0 + warp * 16, warp_last_pos = min(warp_first_pos + 15, last_pos);
+  const int warp_lo = window > 0 ? max(0, warp_first_pos - window + 1) : 0;          // lower bound of the warp's first row
+  const int warp_lo_last = window > 0 ? max(0, warp_last_pos - window + 1) : 0;      // and of its last row
+  fa_wait<0>();
+  __syncthreads();                                        // Q is in shared memory
+#pragma unroll
+  for (int k = 0; k < KT; ++k) {
+    const int r = warp * 16 + (lane & 7) + 8 * ((lane >> 3) & 1), c = 2 * k + (lane >> 4);
+    ldmatrix_x4(sm_q + swz<CH>(r, c), qf[k][0], qf[k][1], qf[k][2], qf[k][3]);
+  }
+
+  for (int kt = 0; kt < n_kt; ++kt) {
+    issue(kt + FP_STAGES - 1);                            // into the stage that tile kt - 1 left
+    const int st = kt % FP_STAGES;
+    const uint32_t parity = (uint32_t)(kt / FP_STAGES) & 1u;
+    if (!mbar_try_wait(&full[st], parity)) {
+      const uint64_t start = global_ns();
+      while (!mbar_try_wait(&full[st], parity)) {
+        if (global_ns() - start > FP_WAIT_NS) {
+          atomicCAS(&g_fa_status, 0, 1);
+          break;
+        }
+      }
+    }
+    const int k0 = k_first + kt * FA_BK;
+    const uint32_t ks = sm_kv + (uint32_t)st * STAGE, vs = ks + PANELS * PANEL;
+    if (k0 < key_lo || k0 + FA_BK - 1 > last_pos) {       // an edge tile: value rows outside the keys anyone sees
+      if (threadIdx.x < FA_BK) {
+        const int kp = k0 + (int)threadIdx.x;
+        if (kp < key_lo || kp > last_pos) {
+#pragma unroll
+          for (int p = 0; p < PANELS; ++p) {
+            uint4* row = reinterpret_cast<uint4*>(fp_smem + (size_t)st * STAGE + (PANELS + p) * PANEL + threadIdx.x * 128);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) row[i] = make_uint4(0, 0, 0, 0);
+          }
+        }
+      }
+      __syncthreads();
+    }
+    const bool active = warp * 16 < rows && k0 <= warp_last_pos && k0 + FA_BK > warp_lo;
+    if (active) {
+      float s[FA_BK / 8][4];
+#pragma unroll
+      for (int i = 0; i < FA_BK / 8; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) s[i][j] = 0.f;
+#pragma unroll
+      for (int k = 0; k < KT; ++k) {
+#pragma unroll
+        for (int n = 0; n < FA_BK / 16; ++n) {
+          uint32_t b0, b1, b2, b3;
+          const int r = n * 16 + (lane & 7) + 8 * (lane >> 4), c = 2 * k + ((lane >> 3) & 1);
+          ldmatrix_x4(ks + tile_off(r, c), b0, b1, b2, b3);
+          fa_mma(s[2 * n], qf[k][0], qf[k][1], qf[k][2], qf[k][3], b0, b1);
+          fa_mma(s[2 * n + 1], qf[k][0], qf[k][1], qf[k][2], qf[k][3], b2, b3);
+        }
+      }
+      float mx[2] = {row_max[0], row_max[1]};
+      // every row of the warp sees every key of the tile: no masks
+      const bool all_visible = k0 + FA_BK - 1 <= warp_first_pos && k0 >= warp_lo_last;
+      if (all_visible) {
+#pragma unroll
+        for (int i = 0; i < FA_BK / 8; ++i) {
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            s[i][j] *= scale_log2;
+            mx[j >> 1] = fmaxf(mx[j >> 1], s[i][j]);
+          }
+        }
+      } else {
+#pragma unroll
+        for (int i = 0; i < FA_BK / 8; ++i) {
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const int kp = k0 + 8 * i + 2 * t + (j & 1);
+            const bool hi = j >= 2;
+            const bool ok = hi ? (kp <= p_hi && kp >= lo_hi) : (kp <= p_lo && kp >= lo_lo);
+            s[i][j] = ok ? s[i][j] * scale_log2 : -INFINITY;
+            mx[hi] = fmaxf(mx[hi], s[i][j]);
+          }
+        }
+      }
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 1));
+        mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 2));
+      }
+      float alpha[2], base[2];
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        base[h] = mx[h] == -INFINITY ? 0.f : mx[h];
+        alpha[h] = exp2f(row_max[h] - base[h]);
+        row_max[h] = mx[h];
+        row_sum[h] *= alpha[h];
+      }
+#pragma unroll
+      for (int i = 0; i < NT; ++i) {
+        acc_o[i][0] *= alpha[0]; acc_o[i][1] *= alpha[0];
+        acc_o[i][2] *= alpha[1]; acc_o[i][3] *= alpha[1];
+      }
+      uint32_t pf[FA_BK / 16][4];
+#pragma unroll
+      for (int i = 0; i < FA_BK / 8; ++i) {
+        const float p0 = exp2f(s[i][0] - base[0]), p1 = exp2f(s[i][1] - base[0]);
+        const float p2 = exp2f(s[i][2] - base[1]), p3 = exp2f(s[i][3] - base[1]);
+        row_sum[0] += p0 + p1;
+        row_sum[1] += p2 + p3;
+        pf[i >> 1][(i & 1) * 2] = pack_bf16(p0, p1);
+        pf[i >> 1][(i & 1) * 2 + 1] = pack_bf16(p2, p3);
+      }
+#pragma unroll
+      for (int kk = 0; kk < FA_BK / 16; ++kk) {
+#pragma unroll
+        for (int n = 0; n < NT / 2; ++n) {
+          uint32_t b0, b1, b2, b3;
+          const int r = kk * 16 + (lane & 7) + 8 * ((lane >> 3) & 1), c = 2 * n + (lane >> 4);
+          ldmatrix_x4_trans(vs + tile_off(r, c), b0, b1, b2, b3);
+          fa_mma(acc_o[2 * n], pf[kk][0], pf[kk][1], pf[kk][2], pf[kk][3], b0, b1);
+          fa_mma(acc_o[2 * n + 1], pf[kk][0], pf[kk][1], pf[kk][2], pf[kk][3], b2, b3);
+        }
+      }
+    }
+    __syncthreads();                                      // the stage is free for tile kt + FP_STAGES
+  }
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    row_sum[h] += __shfl_xor_sync(0xffffffffu, row_sum[h], 1);
+    row_sum[h] += __shfl_xor_sync(0xffffffffu, row_sum[h], 2);
+  }
+  const float inv_lo = 1.f / row_sum[0], inv_hi = 1.f / row_sum[1];
+#pragma unroll
+  for (int i = 0; i < NT; ++i) {
+    const int d = 8 * i + 2 * t;
+    if (r_lo < rows)
+      *reinterpret_cast<uint32_t*>(out + ((size_t)(row0 + r_lo) * nh + head) * HD + d) =
+          pack_bf16(acc_o[i][0] * inv_lo, acc_o[i][1] * inv_lo);
+    if (r_hi < rows)
+      *reinterpret_cast<uint32_t*>(out + ((size_t)(row0 + r_hi) * nh + head) * HD + d) =
+          pack_bf16(acc_o[i][2] * inv_hi, acc_o[i][3] * inv_hi);
+  }
+}
+
+static bool prefill_tma_page_ok(int page_size) {
+  return page_size >= 8 && page_size <= FA_BK && page_size % 8 == 0 && FA_BK % page_size == 0;
+}
+
+// num_pages: pages in the pool.  Page sizes the TMA kernel does not take give SNK_ERR_SIZE (the caller
+// then uses snk_attention_prefill).
+SNK_API int snk_attention_prefill_tma(const void* q, const void* pool, long long num_pages, const int* block_table,
+                                      int max_pages, int page_size, const int* tiles, int n_tiles, void* out, int nh,
+                                      int nkv, int hd, int window, float scale, cudaStream_t stream) {
+  if (n_tiles <= 0) return 0;
+  if (nkv <= 0 || nh % nkv || nh > 65535) return SNK_ERR_SIZE;
+  if ((hd != 64 && hd != 128) || !prefill_tma_page_ok(page_size) || num_pages <= 0) return SNK_ERR_SIZE;
+  if (num_pages * 2 * nkv * page_size >= (1ll << 31)) return SNK_ERR_SIZE;
+  if (((uintptr_t)q % 16) || ((uintptr_t)pool % 16) || ((uintptr_t)out % 4)) return SNK_ERR_ALIGN;
+  CUtensorMap map;
+  const int rc = tensor_map(pool, num_pages * 2 * nkv * page_size, hd, page_size, 64, &map);
+  if (rc) return rc;
+  const float scale_log2 = scale * 1.4426950408889634f;
+  dim3 grid(n_tiles, nh);
+  const size_t smem = 1024 + (size_t)FP_STAGES * 2 * (hd / 64) * FA_BK * 128 + (size_t)FA_BQ * hd * 2;
+  const bf16* qp = static_cast<const bf16*>(q);
+  bf16* op = static_cast<bf16*>(out);
+  if (hd == 64) {
+    cudaFuncSetAttribute(attention_prefill_tma_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    snk_launch(attention_prefill_tma_kernel<64>, dim3(grid), dim3(FA_WARPS * 32), smem, stream, map, qp, block_table,
+               max_pages, page_size, tiles, n_tiles, op, nh, nkv, window, scale_log2);
+  } else {
+    cudaFuncSetAttribute(attention_prefill_tma_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    snk_launch(attention_prefill_tma_kernel<128>, dim3(grid), dim3(FA_WARPS * 32), smem, stream, map, qp, block_table,
+               max_pages, page_size, tiles, n_tiles, op, nh, nkv, window, scale_log2);
+  }
+  SNK_LAUNCH_CHECK();
+  return 0;
+}
+
+
+// ---------------------------------------------------------------------------------------------
 // Rows of decoded tokens (one row per request, a long run of keys each).  One block takes one row, one
 // kv head and one chunk of 256 keys.  The q heads that share the kv head are the rows of the MMA (up to
 // 16), so the chunk's keys and values are read once for all of them.  Each of the 4 warps multiplies
@@ -752,11 +1031,13 @@ SNK_API int snk_attention_decode_tma(const void* q, const void* pool, long long 
   return 0;
 }
 
-// 0, or 1 when a block of an earlier launch gave up waiting for its keys; reading clears it.
-// Synchronises the device.
+// 0, or bit 0 / bit 1 when a block of an earlier decode / prompt launch gave up waiting for its keys;
+// reading clears it.  Synchronises the device.
 SNK_API int snk_attention_decode_status() {
-  int v = 0, zero = 0;
+  int v = 0, w = 0, zero = 0;
   if (cudaMemcpyFromSymbol(&v, g_fd_status, sizeof(int)) != cudaSuccess) return -1;
+  if (cudaMemcpyFromSymbol(&w, g_fa_status, sizeof(int)) != cudaSuccess) return -1;
   if (v) cudaMemcpyToSymbol(g_fd_status, &zero, sizeof(int));
-  return v;
+  if (w) cudaMemcpyToSymbol(g_fa_status, &zero, sizeof(int));
+  return v | (w << 1);
 }

@@ -41,6 +41,7 @@ _SIGNATURES = {
     "attention_mma": {
         "snk_attention_prefill": [P, P, P, I, I, P, I, P, I, I, I, I, F, P],
         "snk_attention_decode_mma": [P, P, P, I, I, P, P, P, P, P, I, I, I, I, I, I, F, P],
+        "snk_attention_prefill_tma": [P, P, LL, P, I, I, P, I, P, I, I, I, I, F, P],
         "snk_attention_decode_tma": [P, P, LL, P, I, I, P, P, P, P, P, I, I, I, I, I, I, F, P],
         "snk_attention_decode_status": [],
     },
@@ -342,9 +343,19 @@ def attention_prefill_ok(q) -> bool:
     return q.dtype == torch.bfloat16 and q.shape[2] in PREFILL_HEAD_DIMS
 
 
-def attention_prefill(q, pool, block_table, page_size, tiles, scale, out, window=None):
+def prefill_tma_page_ok(page_size: int) -> bool:
+    """Page sizes whose pages a TMA box brings into a 64-key tile whole (csrc/attention_mma.cu)."""
+    return page_size in (8, 16, 32, 64)
+
+
+PREFILL_TMA = os.environ.get("SNOWLLM_B200_PREFILL_TMA", "1") != "0"
+
+
+def attention_prefill(q, pool, block_table, page_size, tiles, scale, out, window=None, tma=None):
     """Tensor-core causal attention for prompt portions: ``tiles`` int32 [n, 4] = (segment, first row,
-    rows <= 64, position of the first row); writes those rows of ``out`` [M, heads*head_dim]."""
+    rows <= 64, position of the first row); writes those rows of ``out`` [M, heads*head_dim].
+    ``tma``: bring keys and values in by TMA (default: wherever the page size allows); both ways give the
+    same bits."""
     M, nh, hd = q.shape
     _chk(q, "q", torch.bfloat16)
     _chk(pool, "kv pool", torch.bfloat16)
@@ -353,9 +364,17 @@ def attention_prefill(q, pool, block_table, page_size, tiles, scale, out, window
     _chk(out, "attention output", torch.bfloat16, (M, nh * hd))
     if tiles.dim() != 2 or tiles.shape[1] != 4:
         raise KernelError("attention tiles must be [n, 4]")
-    check(fn("snk_attention_prefill")(
-        _ptr(q), _ptr(pool), _ptr(block_table), block_table.shape[1], page_size, _ptr(tiles), tiles.shape[0],
-        _ptr(out), nh, pool.shape[2], hd, int(window or 0), float(scale), _stream()), "attention_prefill")
+    if tma is None:
+        tma = PREFILL_TMA and prefill_tma_page_ok(page_size)
+    if tma:
+        check(fn("snk_attention_prefill_tma")(
+            _ptr(q), _ptr(pool), pool.shape[0], _ptr(block_table), block_table.shape[1], page_size, _ptr(tiles),
+            tiles.shape[0], _ptr(out), nh, pool.shape[2], hd, int(window or 0), float(scale), _stream()),
+            "attention_prefill_tma")
+    else:
+        check(fn("snk_attention_prefill")(
+            _ptr(q), _ptr(pool), _ptr(block_table), block_table.shape[1], page_size, _ptr(tiles), tiles.shape[0],
+            _ptr(out), nh, pool.shape[2], hd, int(window or 0), float(scale), _stream()), "attention_prefill")
     return out
 
 

@@ -618,7 +618,8 @@ def test_gemm_tc_grouped_after_gather(K):
 
 # ---------------------------------------------------------------------------------------------
 @pytest.mark.parametrize("nh,nkv,hd,P,window", [(4, 2, 64, 16, None), (6, 1, 128, 16, None), (2, 2, 64, 64, None),
-                                                (4, 2, 64, 16, 100), (3, 1, 128, 8, 37)])
+                                                (4, 2, 64, 16, 100), (3, 1, 128, 8, 37), (2, 1, 64, 4, None),
+                                                (2, 2, 64, 32, 70)])
 def test_attention_prefill_tiles(K, nh, nkv, hd, P, window):
     """The tensor-core prompt kernel: a portion from position 0, one in the middle of a long request
     (not aligned to tiles or pages), a short one; pages scattered; unwritten cache entries are NaN."""
@@ -648,6 +649,11 @@ def test_attention_prefill_tiles(K, nh, nkv, hd, P, window):
     out = torch.full((M, nh * hd), float("nan"), dtype=dtype, device="cuda")
     K.attention_prefill(dev(q, dtype), pool, bt, P, i32(tiles), hd ** -0.5, out, window=window)
     assert out.isfinite().all(), "a row was not written, or an unwritten cache entry was read"
+    if K.prefill_tma_page_ok(P):                   # keys brought in by TMA or by 16-byte copies: the same bits
+        by_copies = torch.full((M, nh * hd), float("nan"), dtype=dtype, device="cuda")
+        K.attention_prefill(dev(q, dtype), pool, bt, P, i32(tiles), hd ** -0.5, by_copies, window=window, tma=False)
+        assert torch.equal(by_copies, out)
+        assert K.attention_decode_status() == 0
     first = 0
     for b in range(3):
         rows = list(range(starts[b], totals[b]))
