@@ -58,7 +58,7 @@ _SIGNATURES = {
     },
     "moe": {
         "snk_moe_route": [P, P, I, P, P, P, I, I, I, I, I, F, I, P],
-        "snk_moe_topk": [P, P, P, P, I, I, I, I, F, P],
+        "snk_moe_topk": [P, P, P, P, I, I, I, I, F, I, P],
         "snk_moe_route_sort": [P, P, I, P, P, P, P, P, P, P, I, I, I, I, I, F, I, P],
         "snk_moe_sort": [P, P, P, P, I, I, P],
         "snk_moe_combine": [P, P, P, P, I, I, I, P],
@@ -618,11 +618,13 @@ def moe_route(x, router_w, bias, top_k, norm_topk_prob, scaling):
         _chk(bias, "expert bias", torch.float32, (E,))
     ids = torch.empty(M, top_k, dtype=torch.int32, device=x.device)
     wts = torch.empty(M, top_k, dtype=torch.float32, device=x.device)
-    if M > ROUTE_GEMM_MIN_ROWS and router_w.dtype == torch.bfloat16 and gemm_tc_ok(x, router_w):
-        # many rows: the logits are a tensor-core product with float accumulation and float output
-        logits = gemm_tc(x, router_w, out_dtype=torch.float32)
+    if M > ROUTE_GEMM_MIN_ROWS and router_w.dtype == torch.bfloat16 and gemm_skinny_ok(router_w, x):
+        # many rows: the logits are a tensor-core product with float accumulation and float output.  The few
+        # router rows take the place of the tokens in the few-rows kernel, which then streams x once and
+        # leaves the logits transposed, [E, M].
+        logits = gemm_skinny(router_w, x, out_dtype=torch.float32, rows_hint=min(E, 64))
         check(fn("snk_moe_topk")(_ptr(logits), _ptr(bias), _ptr(ids), _ptr(wts), M, E, top_k,
-                                 int(bool(norm_topk_prob)), float(scaling), _stream()), "moe_topk")
+                                 int(bool(norm_topk_prob)), float(scaling), 1, _stream()), "moe_topk")
         return ids, wts
     check(fn("snk_moe_route")(_ptr(x), _ptr(router_w), w32, _ptr(bias), _ptr(ids), _ptr(wts), M, H, E,
                               top_k, int(bool(norm_topk_prob)), float(scaling), code_of(dtype), _stream()),

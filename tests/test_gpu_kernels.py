@@ -614,6 +614,20 @@ def test_gemm_tc_grouped_after_gather(K):
         r = slice(offsets[e], offsets[e + 1])
         if counts[e]:
             close(out[r], x[r] @ w[e].T, torch.float32, scale=16)
+    # the same groups through the store that applies SwiGLU, and to bfloat16 (tiles of 60, 20, 1 and 1 rows
+    # are multiplied the other way round)
+    from snowllm_b200.ops import interleave_gate_up
+    I = 552
+    gate, up = rnd(dtype, E, I, K_, scale=K_ ** -0.5), rnd(dtype, E, I, K_, scale=K_ ** -0.5)
+    w13 = interleave_gate_up(dev(gate, dtype), dev(up, dtype))
+    act = K.gemm_tc(dev(x, dtype), w13, offsets=i32(offsets), swiglu=True)
+    half = K.gemm_tc(dev(x, dtype), dev(w, dtype), offsets=i32(offsets))
+    assert K.gemm_tc_status() == 0 and act.shape == (offsets[-1], I)
+    for e in range(E):
+        r = slice(offsets[e], offsets[e + 1])
+        if counts[e]:
+            close(act[r], F.silu(x[r] @ gate[e].T) * (x[r] @ up[e].T), dtype, scale=4)
+            close(half[r], x[r] @ w[e].T, dtype, scale=16)
 
 
 # ---------------------------------------------------------------------------------------------
@@ -694,7 +708,8 @@ def test_attention_prefill_far_key_and_diagonal(K):
 
 
 # ---------------------------------------------------------------------------------------------
-@pytest.mark.parametrize("M,I,K_", [(5, 24, 48), (64, 1792, 256), (65, 56, 72), (2000, 2048, 64)])
+@pytest.mark.parametrize("M,I,K_", [(5, 24, 48), (64, 1792, 256), (65, 56, 72), (2000, 2048, 64),
+                                    (300, 120, 136), (1930, 2056, 72), (129, 1032, 64)])   # the last three end in a tile of few rows
 def test_products_with_swiglu_store(K, M, I, K_):
     """Gate and up rows interleaved by 8: the few-rows and the tcgen05 products store silu(gate) * up,
     and the stand-alone kernel reads the same layout."""
