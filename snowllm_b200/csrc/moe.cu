@@ -41,7 +41,7 @@ __device__ __forceinline__ void select_topk(float* prob, float* score, int* ids,
     if (lane == 0) score[best_e] = -INFINITY;
     __syncwarp();
     if (lane == (j & 31)) { my_w = p; my_id = best_e; }
-    if ((j & 31) == 31 || j == k - 1) {
+    if (k > 32 && ((j & 31) == 31 || j == k - 1)) {
       // flush this round of up to 32 picks; the normaliser is applied in a second pass
       const int base = j & ~31;
       if (base + lane <= j) {
@@ -50,8 +50,15 @@ __device__ __forceinline__ void select_topk(float* prob, float* score, int* ids,
       }
     }
   }
-  __syncwarp();
   const float mul = (norm_topk ? 1.f / (wsum + 1e-6f) : 1.f);
+  if (k <= 32) {                   // one round: every pick is in a lane's registers; written once, normalised
+    if (lane < k) {
+      ids[lane] = my_id;
+      wts[lane] = (norm_topk ? my_w * mul : my_w) * scaling;
+    }
+    return;
+  }
+  __syncwarp();
   for (int j = lane; j < k; j += 32) {
     float w = wts[j];
     w = norm_topk ? w * mul : w;
@@ -239,7 +246,8 @@ __global__ void moe_sort_kernel(const int* __restrict__ topk_ids, int* __restric
 }
 
 // Selection and sort in one block, for the few tokens of a decode step: a warp per token selects from
-// the logits, then the block sorts the pairs.
+// the logits, then the block sorts the pairs.  The picks and their places stay in shared memory until
+// the end (each trip through global memory would cost more than the arithmetic between two of them).
 __global__ void moe_topk_sort_kernel(const float* __restrict__ logits, const float* __restrict__ bias,
                                      int* __restrict__ topk_ids, float* __restrict__ topk_w,
                                      int* __restrict__ offsets, int* __restrict__ pair_pos,
@@ -248,7 +256,11 @@ __global__ void moe_topk_sort_kernel(const float* __restrict__ logits, const flo
   pdl_begin();
   extern __shared__ float sh[];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarp = blockDim.x >> 5;
-  float* prob = sh + (size_t)warp * 2 * E;
+  const int pairs = M * k;
+  int* ids_s = reinterpret_cast<int*>(sh);              // [pairs]
+  int* pos_s = ids_s + pairs;                           // [pairs]
+  float* work = reinterpret_cast<float*>(pos_s + pairs);
+  float* prob = work + (size_t)warp * 2 * E;
   float* score = prob + E;
   for (int m = warp; m < M; m += nwarp) {
     for (int e = lane; e < E; e += 32) {
@@ -257,11 +269,16 @@ __global__ void moe_topk_sort_kernel(const float* __restrict__ logits, const flo
       score[e] = bias ? p + bias[e] : p;
     }
     __syncwarp();
-    select_topk(prob, score, topk_ids + (size_t)m * k, topk_w + (size_t)m * k, E, k, norm_topk, scaling, lane);
+    select_topk(prob, score, ids_s + (size_t)m * k, topk_w + (size_t)m * k, E, k, norm_topk, scaling, lane);
     __syncwarp();
   }
-  __syncthreads();               // the ids of every token are written (same block: visible after the barrier)
-  sort_pairs(topk_ids, offsets, pair_pos, sorted_pair, M * k, E, reinterpret_cast<int*>(sh));
+  __syncthreads();
+  sort_pairs(ids_s, offsets, pos_s, sorted_pair, pairs, E, reinterpret_cast<int*>(work));
+  __syncthreads();
+  for (int p = threadIdx.x; p < pairs; p += blockDim.x) {
+    topk_ids[p] = ids_s[p];
+    pair_pos[p] = pos_s[p];
+  }
 }
 
 SNK_API int snk_moe_sort(const int* topk_ids, int* offsets, int* pair_pos, int* sorted_pair,
@@ -287,6 +304,7 @@ SNK_API int snk_moe_route_sort(const void* x, const void* wr, int wr_is_f32, con
   size_t smem = (size_t)warps * 2 * E * sizeof(float);
   const size_t sort_smem = (size_t)(2 * E + 1) * sizeof(int);
   if (smem < sort_smem) smem = sort_smem;
+  smem += (size_t)2 * M * k * sizeof(int);               // the picks and their places
   if (smem > 48 * 1024) return SNK_ERR_SIZE;
   SmallVec w{wr, wr_is_f32};
   const size_t xsz = dtype == SNK_F32 ? 4 : 2, wsz = wr_is_f32 ? 4 : 2;

@@ -641,7 +641,7 @@ def moe_route_sort(x, router_w, bias, top_k, norm_topk_prob, scaling):
     them; a row's logits are the same numbers on every path but the tensor-core one."""
     M, H = x.shape
     E = router_w.shape[0]
-    if M > ROUTE_FUSED_MAX_ROWS or 8 * E * min(M, 32) > 48 * 1024:
+    if M > ROUTE_FUSED_MAX_ROWS or 8 * E * min(M, 32) + 8 * M * top_k > 48 * 1024:
         ids, wts = moe_route(x, router_w, bias, top_k, norm_topk_prob, scaling)
         return (ids, wts) + moe_sort(ids, E)
     dtype = x.dtype
