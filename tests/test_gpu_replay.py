@@ -120,7 +120,7 @@ def plain_routes(cfg, tensors, toks, forced):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["tiny_a", "tiny_b", "tiny_c", "tiny_dense", "tiny_e"])
+@pytest.mark.parametrize("name", ["tiny_a", "tiny_b", "tiny_c", "tiny_dense", "tiny_e", "tiny_f"])
 @pytest.mark.parametrize("cut", list(CUTS))
 def test_cuts_match_the_plain_implementation(model_dirs, name, dtype, cut):
     d = model_dirs(name, dtype)

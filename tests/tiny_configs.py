@@ -58,9 +58,21 @@ TINY_E = {   # head size 64 (the tensor-core attention kernels), one kv head for
     "max_position_embeddings": 4096,
 }
 
+TINY_F = {   # head size 128 (two 64-element panels in the tensor-core attention kernels), three q heads on one kv head
+    "architectures": ["Lfm2MoeForCausalLM"], "model_type": "lfm2_moe",
+    "vocab_size": 272, "hidden_size": 192, "num_hidden_layers": 3,
+    "layer_types": ["full_attention", "conv", "full_attention"],
+    "num_attention_heads": 3, "num_key_value_heads": 1, "head_dim": 128, "conv_L_cache": 4, "conv_bias": False,
+    "num_dense_layers": 1, "intermediate_size": 160,
+    "num_experts": 6, "num_experts_per_tok": 2, "moe_intermediate_size": 40,
+    "norm_topk_prob": True, "use_expert_bias": False, "routed_scaling_factor": 1.0,
+    "rope_theta": 50000.0, "norm_eps": 1e-6, "tie_word_embeddings": False,
+    "max_position_embeddings": 4096,
+}
+
 TINY_CONV_ONLY = dict(TINY_DENSE, layer_types=["conv", "conv", "conv"], conv_L_cache=5)   # no paged cache at all
 TINY_ATTN_ONLY = dict(TINY_A, layer_types=["full_attention"] * 4, num_dense_layers=0,    # no state slots in use
                       hidden_size=104, num_attention_heads=1, num_key_value_heads=1, head_dim=24,
                       moe_intermediate_size=20, vocab_size=250)
 
-ALL = {"tiny_conv_only": TINY_CONV_ONLY, "tiny_attn_only": TINY_ATTN_ONLY, "tiny_e": TINY_E, "tiny_a": TINY_A, "tiny_b": TINY_B, "tiny_c": TINY_C, "tiny_dense": TINY_DENSE}
+ALL = {"tiny_conv_only": TINY_CONV_ONLY, "tiny_attn_only": TINY_ATTN_ONLY, "tiny_e": TINY_E, "tiny_f": TINY_F, "tiny_a": TINY_A, "tiny_b": TINY_B, "tiny_c": TINY_C, "tiny_dense": TINY_DENSE}
