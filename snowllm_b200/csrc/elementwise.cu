@@ -39,16 +39,6 @@ SNK_API int snk_embedding(const int* ids, const int* pending, int num_pending, c
 // One block per output row.  rows == nullptr: row r is residual row r; delta (if any) is
 // added into the residual and the sum is written back.  rows != nullptr: output row r
 // normalises residual[rows[r]] + delta[rows[r]] and nothing is written back.
-template <typename T> __device__ __forceinline__ void store4(T* p, float a, float b, float c, float d);
-template <> __device__ __forceinline__ void store4<float>(float* p, float a, float b, float c, float d) {
-  *reinterpret_cast<float4*>(p) = make_float4(a, b, c, d);
-}
-template <> __device__ __forceinline__ void store4<bf16>(bf16* p, float a, float b, float c, float d) {
-  const __nv_bfloat162 lo = __floats2bfloat162_rn(a, b), hi = __floats2bfloat162_rn(c, d);
-  *reinterpret_cast<uint2*>(p) = make_uint2(*reinterpret_cast<const uint32_t*>(&lo),
-                                            *reinterpret_cast<const uint32_t*>(&hi));
-}
-
 template <typename T>
 __global__ void add_rmsnorm_kernel(float* __restrict__ residual, const float* __restrict__ delta,
                                    SmallVec gamma, T* __restrict__ out,

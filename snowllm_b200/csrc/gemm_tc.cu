@@ -153,7 +153,7 @@ template <int BN, typename OutT, bool SWIGLU>
 __global__ void __launch_bounds__(TC_THREADS)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
                OutT* __restrict__ C, int M, int N, int K, const int* __restrict__ offsets, int groups,
-               int row_tiles_bound) {
+               int row_tiles_bound, int splits) {
   constexpr int STAGE_BYTES = (TC_BM + BN) * TC_BK * 2;
   constexpr int STAGES = TC_SMEM_TILES / STAGE_BYTES < TC_MAX_STAGES ? TC_SMEM_TILES / STAGE_BYTES : TC_MAX_STAGES;
   extern __shared__ unsigned char smem_raw[];
@@ -198,14 +198,19 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   }
   const int n_tiles = (N + BN - 1) / BN;
   const int total = row_tiles * n_tiles;
+  // splits > 1 (plain products with few tiles): work item w is tile w % total over the k-blocks of part
+  // w / total, and the partial product goes to plane w / total of C, which then is float [splits, M, N]
+  const int items = total * splits;
+  const int k_per = (k_tiles + splits - 1) / splits;
 
   if (warp == 0) {
     if (lane == 0) {
       int it = 0;                                        // k-blocks issued so far, over all tiles
-      for (int tile = blockIdx.x; tile < total; tile += gridDim.x) {
-        const TcTile t = tc_tile(tile, row_tiles, M, N, BN, offsets, groups);
+      for (int item = blockIdx.x; item < items; item += gridDim.x) {
+        const TcTile t = tc_tile(item % total, row_tiles, M, N, BN, offsets, groups);
         if (!t.valid) continue;
-        for (int kt = 0; kt < k_tiles; ++kt, ++it) {
+        const int kt_begin = (item / total) * k_per, kt_end = min(k_tiles, kt_begin + k_per);
+        for (int kt = kt_begin; kt < kt_end; ++kt, ++it) {
           const int s = it % STAGES;
           mbar_wait(&sh->empty[s], ((it / STAGES) & 1) ^ 1, aborted, TC_ERR_WAIT_EMPTY);
           mbar_expect_tx(&sh->full[s], STAGE_BYTES);
@@ -219,14 +224,15 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     if (lane == 0) {
       const uint32_t idesc = instr_desc_bf16(BN);
       int it = 0, local = 0;
-      for (int tile = blockIdx.x; tile < total; tile += gridDim.x) {
-        const TcTile t = tc_tile(tile, row_tiles, M, N, BN, offsets, groups);
+      for (int item = blockIdx.x; item < items; item += gridDim.x) {
+        const TcTile t = tc_tile(item % total, row_tiles, M, N, BN, offsets, groups);
         if (!t.valid) continue;
+        const int kt_begin = (item / total) * k_per, kt_end = min(k_tiles, kt_begin + k_per);
         const int buf = local & 1;
         mbar_wait(&sh->acc_empty[buf], ((local >> 1) & 1) ^ 1, aborted, TC_ERR_WAIT_ACC_FREE);
         tc_fence_after();
         const uint32_t d_tmem = tmem_acc + (uint32_t)(buf * BN);
-        for (int kt = 0; kt < k_tiles; ++kt, ++it) {
+        for (int kt = kt_begin; kt < kt_end; ++kt, ++it) {
           const int s = it % STAGES;
           mbar_wait(&sh->full[s], (it / STAGES) & 1, aborted, TC_ERR_WAIT_FULL);
           tc_fence_after();
@@ -236,7 +242,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
           for (int k = 0; k < TC_BK / 16; ++k) {
             // 16 k-values = 32 bytes further along the swizzled 128-byte rows
             umma_bf16(d_tmem, smem_desc_sw128(a_addr + k * 32), smem_desc_sw128(w_addr + k * 32), idesc,
-                      (kt > 0 || k > 0) ? 1u : 0u);
+                      (kt > kt_begin || k > 0) ? 1u : 0u);
           }
           umma_commit(&sh->empty[s]);                    // the stage is free once these MMAs have read it
         }
@@ -248,9 +254,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     const int lane_group = warp & 3;                     // a warp reads the 32 tensor-memory lanes 32*(warp%4)..
     const bool vec_ok = (N % 8) == 0;
     int local = 0;
-    for (int tile = blockIdx.x; tile < total; tile += gridDim.x) {
-      const TcTile t = tc_tile(tile, row_tiles, M, N, BN, offsets, groups);
+    for (int item = blockIdx.x; item < items; item += gridDim.x) {
+      const TcTile t = tc_tile(item % total, row_tiles, M, N, BN, offsets, groups);
       if (!t.valid) continue;
+      OutT* Cp = C + (size_t)(item / total) * M * N;        // the part's plane (C itself without a split)
       const int buf = local & 1;
       mbar_wait(&sh->acc_full[buf], (local >> 1) & 1, aborted, TC_ERR_WAIT_ACC);
       tc_fence_after();
@@ -266,7 +273,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         }
         if constexpr (SWIGLU) {
           if (row < t.row_end && !*aborted) {
-            OutT* dst = C + (size_t)row * (N / 2) + (t.n0 + c0) / 2;
+            OutT* dst = Cp + (size_t)row * (N / 2) + (t.n0 + c0) / 2;
 #pragma unroll
             for (int blk = 0; blk < 2; ++blk) {
               if (t.n0 + c0 + blk * 16 + 16 <= N) {
@@ -284,7 +291,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             }
           }
         } else if (row < t.row_end && !*aborted) {
-          OutT* dst = C + (size_t)row * N + t.n0 + c0;
+          OutT* dst = Cp + (size_t)row * N + t.n0 + c0;
           if (vec_ok && t.n0 + c0 + 32 <= N) {
             if constexpr (sizeof(OutT) == 4) {
 #pragma unroll
@@ -324,7 +331,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 
 template <int BN, typename OutT, bool SWIGLU>
 static int launch_tc(const CUtensorMap& map_a, const CUtensorMap& map_w, void* C, int M, int N, int K,
-                     const int* offsets, int groups, int row_tiles, cudaStream_t stream) {
+                     const int* offsets, int groups, int row_tiles, int splits, cudaStream_t stream) {
   constexpr int STAGE_BYTES = (TC_BM + BN) * TC_BK * 2;
   constexpr int STAGES = TC_SMEM_TILES / STAGE_BYTES < TC_MAX_STAGES ? TC_SMEM_TILES / STAGE_BYTES : TC_MAX_STAGES;
   const size_t smem = 1024 + (size_t)STAGES * STAGE_BYTES + sizeof(TcShared);
@@ -335,18 +342,91 @@ static int launch_tc(const CUtensorMap& map_a, const CUtensorMap& map_w, void* C
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
     cudaFuncSetAttribute(gemm_tc_kernel<BN, OutT, SWIGLU>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   }
-  const long long tiles = (long long)row_tiles * ((N + BN - 1) / BN);
+  const long long tiles = (long long)row_tiles * ((N + BN - 1) / BN) * splits;
   const int blocks = (int)(tiles < sms ? tiles : sms);     // one block per SM (shared memory), persistent
   snk_launch(gemm_tc_kernel<BN, OutT, SWIGLU>, dim3(blocks), dim3(TC_THREADS), smem, stream, map_a, map_w, static_cast<OutT*>(C), M, N, K,
-                                                                 offsets, groups, row_tiles);
+                                                                 offsets, groups, row_tiles, splits);
   SNK_LAUNCH_CHECK();
   return 0;
 }
 
+// ---------------------------------------------------------------------------------------------
+// Products with few tiles (one row tile, a narrow N: the projections of a 64-row decode step) would leave
+// most SMs idle behind a long serial walk over K.  They are split along K into parts that run side by
+// side; each part leaves its float partial product in a plane of scratch, and a second kernel adds the
+// planes in part order and stores C (converted, or through SwiGLU).
+template <typename OutT, bool SWIGLU>
+__global__ void splitk_reduce_kernel(const float* __restrict__ parts, OutT* __restrict__ C, int M, int N, int splits) {
+  pdl_begin();
+  const size_t plane = (size_t)M * N;
+  if constexpr (SWIGLU) {
+    // blocks of 16 columns: 8 gate columns, then the 8 up columns of the same features
+    const size_t blocks = plane / 16;
+    const size_t b = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (b >= blocks) return;
+    float g[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f}, u[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    for (int p = 0; p < splits; ++p) {
+      const float4* src = reinterpret_cast<const float4*>(parts + (size_t)p * plane + b * 16);
+      const float4 g0 = src[0], g1 = src[1], u0 = src[2], u1 = src[3];
+      g[0] += g0.x; g[1] += g0.y; g[2] += g0.z; g[3] += g0.w; g[4] += g1.x; g[5] += g1.y; g[6] += g1.z; g[7] += g1.w;
+      u[0] += u0.x; u[1] += u0.y; u[2] += u0.z; u[3] += u0.w; u[4] += u1.x; u[5] += u1.y; u[6] += u1.z; u[7] += u1.w;
+    }
+    uint32_t o[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const __nv_bfloat162 v = __floats2bfloat162_rn(g[2 * j] / (1.f + expf(-g[2 * j])) * u[2 * j],
+                                                     g[2 * j + 1] / (1.f + expf(-g[2 * j + 1])) * u[2 * j + 1]);
+      o[j] = *reinterpret_cast<const uint32_t*>(&v);
+    }
+    *reinterpret_cast<uint4*>(C + b * 8) = make_uint4(o[0], o[1], o[2], o[3]);   // row m, features 8*(b % (N/16))..
+  } else {
+    const size_t vecs = plane / 4;
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= vecs) return;
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int p = 0; p < splits; ++p) {
+      const float4 v = reinterpret_cast<const float4*>(parts + (size_t)p * plane)[i];
+      acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+    }
+    store4<OutT>(C + 4 * i, acc.x, acc.y, acc.z, acc.w);
+  }
+}
+
+// How many parts along K a plain product of these sizes is split into (1: none).
+static int tc_splits(int M, int N, int K, const int* offsets) {
+  static int sms = 0;
+  static int off = -1;
+  if (sms == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    const char* e = getenv("SNOWLLM_B200_TC_SPLIT");
+    off = (e && e[0] == '0') ? 1 : 0;
+  }
+  if (offsets || off || N % 16) return 1;
+  const int k_tiles = (K + TC_BK - 1) / TC_BK;
+  const int tiles = ((M + TC_BM - 1) / TC_BM) * ((N + 127) / 128);
+  int splits = sms / tiles;                                   // parts that still find an SM each
+  if (splits > 8) splits = 8;
+  if (splits > k_tiles / 4) splits = k_tiles / 4;             // a part walks at least four k-blocks
+  if (splits < 2) return 1;
+  const int k_per = (k_tiles + splits - 1) / splits;
+  return (k_tiles + k_per - 1) / k_per;                       // no part without k-blocks
+}
+
+// Bytes of scratch snk_gemm_tc wants for these sizes (0: none).
+SNK_API long long snk_gemm_tc_scratch_bytes(int M, int N, int K, int grouped) {
+  if (grouped) return 0;
+  const int splits = tc_splits(M, N, K, nullptr);
+  return splits > 1 ? (long long)splits * M * N * (long long)sizeof(float) : 0;
+}
+
 // M: rows of A (all groups together).  Grouped: offsets[groups+1] on the device, W = [groups, N, K];
 // max_row_tiles bounds the number of 128-row tiles over all groups (M/128 + groups is always enough).
+// scratch: snk_gemm_tc_scratch_bytes of device memory (may be null when that is 0).
 SNK_API int snk_gemm_tc(const void* A, const void* W, void* C, int M, int N, int K, const int* offsets,
-                        int groups, int max_row_tiles, int out_f32, int swiglu, cudaStream_t stream) {
+                        int groups, int max_row_tiles, int out_f32, int swiglu, void* scratch,
+                        cudaStream_t stream) {
   if (M <= 0 || N <= 0) return 0;
   if (K <= 0 || K % 8) return SNK_ERR_SIZE;                   // TMA: the row pitch is a multiple of 16 bytes
   if (swiglu && (N % 16 || out_f32)) return SNK_ERR_SIZE;
@@ -355,12 +435,26 @@ SNK_API int snk_gemm_tc(const void* A, const void* W, void* C, int M, int N, int
   if (row_tiles <= 0) return SNK_ERR_SIZE;
   // wide tiles where they still give every SM work; narrow ones otherwise
   const bool wide = (long long)((M + TC_BM - 1) / TC_BM) * ((N + 255) / 256) >= 120;
+  const int splits = wide ? 1 : tc_splits(M, N, K, offsets);
+  if (splits > 1 && (scratch == nullptr || ((uintptr_t)scratch % 16))) return SNK_ERR_ALIGN;
   CUtensorMap map_a, map_w;
   int rc = tensor_map(A, M, K, TC_BM, TC_BK, &map_a);
   if (rc) return rc;
   rc = tensor_map(W, (long long)(offsets ? groups : 1) * N, K, wide ? 256 : 128, TC_BK, &map_w);
   if (rc) return rc;
-#define TC_GO(BN_, T_, S_) launch_tc<BN_, T_, S_>(map_a, map_w, C, M, N, K, offsets, groups, row_tiles, stream)
+  if (splits > 1) {
+    rc = launch_tc<128, float, false>(map_a, map_w, scratch, M, N, K, nullptr, 1, row_tiles, splits, stream);
+    if (rc) return rc;
+    const float* parts = static_cast<const float*>(scratch);
+    const size_t work = swiglu ? (size_t)M * N / 16 : (size_t)M * N / 4;
+    const dim3 grid((unsigned)((work + 255) / 256)), block(256);
+    if (swiglu) snk_launch(splitk_reduce_kernel<bf16, true>, grid, block, 0, stream, parts, static_cast<bf16*>(C), M, N, splits);
+    else if (out_f32) snk_launch(splitk_reduce_kernel<float, false>, grid, block, 0, stream, parts, static_cast<float*>(C), M, N, splits);
+    else snk_launch(splitk_reduce_kernel<bf16, false>, grid, block, 0, stream, parts, static_cast<bf16*>(C), M, N, splits);
+    SNK_LAUNCH_CHECK();
+    return 0;
+  }
+#define TC_GO(BN_, T_, S_) launch_tc<BN_, T_, S_>(map_a, map_w, C, M, N, K, offsets, groups, row_tiles, 1, stream)
   if (swiglu) return wide ? TC_GO(256, bf16, true) : TC_GO(128, bf16, true);
   if (wide) return out_f32 ? TC_GO(256, float, false) : TC_GO(256, bf16, false);
   return out_f32 ? TC_GO(128, float, false) : TC_GO(128, bf16, false);

@@ -52,7 +52,8 @@ _SIGNATURES = {
         "snk_gemm_skinny": [P, P, P, I, I, I, P, I, P, I, I, I, I, P],
     },
     "gemm_tc": {
-        "snk_gemm_tc": [P, P, P, I, I, I, P, I, I, I, I, P],
+        "snk_gemm_tc": [P, P, P, I, I, I, P, I, I, I, I, P, P],
+        "snk_gemm_tc_scratch_bytes": [I, I, I, I],
         "snk_gemm_tc_status": [],
         "snk_gather_rows_bf16": [P, P, P, I, I, I, P],
     },
@@ -69,7 +70,7 @@ _SIGNATURES = {
         "snk_sample": [P, P, P, P, P, P, I, I, P],
     },
 }
-_RESTYPES = {"snk_paged_attention_scratch_bytes": LL}
+_RESTYPES = {"snk_paged_attention_scratch_bytes": LL, "snk_gemm_tc_scratch_bytes": LL}
 _functions: dict[str, object] = {}
 _library_of = {fn: lib for lib, fns in _SIGNATURES.items() for fn in fns}
 
@@ -577,9 +578,19 @@ def gemm_tc(a, w, out_dtype=None, out=None, offsets=None, swiglu=False):
     if out_dtype not in (torch.bfloat16, torch.float32) or (swiglu and out_dtype != torch.bfloat16):
         raise KernelError("gemm output is bfloat16 or float32 (bfloat16 with swiglu)")
     row_tiles = -(-M // TC_TILE) + (G if grouped else 0)
+    # few tiles: the product is split along K, and the parts' float planes need a place
+    need = int(fn("snk_gemm_tc_scratch_bytes")(M, N, K, int(grouped)))
+    scratch = torch.empty(need, dtype=torch.uint8, device=a.device) if need else None
     check(fn("snk_gemm_tc")(_ptr(a), _ptr(w), _ptr(out), M, N, K, _ptr(offsets), G, row_tiles,
-                            int(out_dtype == torch.float32), int(swiglu), _stream()), "gemm_tc")
+                            int(out_dtype == torch.float32), int(swiglu), _ptr(scratch), _stream()), "gemm_tc",
+          launches=2 if need else 1)
     return out
+
+
+def gemm_tc_is_split(M: int, N: int, K: int) -> bool:
+    """Whether a plain tcgen05 product of these sizes is split along K (few tiles): its sums then have
+    another order than the unsplit product's, so the same row may differ by rounding between the two."""
+    return int(fn("snk_gemm_tc_scratch_bytes")(M, N, K, 0)) > 0
 
 
 def gemm_tc_status() -> int:
