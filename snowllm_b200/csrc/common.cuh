@@ -87,6 +87,21 @@ __device__ __forceinline__ float block_sum(float v, float* red) {
   return red[32];
 }
 
+// Thread-block clusters: a barrier over all threads of the cluster's blocks, and the shared memory of
+// another block of the cluster (distributed shared memory) by the address the same variable has here.
+__device__ __forceinline__ void cluster_sync() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// The float at the same shared-memory address in block `rank` of this cluster.
+__device__ __forceinline__ float ld_cluster_f32(const float* local, uint32_t rank) {
+  uint32_t remote;
+  float v;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;"
+               : "=r"(remote) : "r"((uint32_t)__cvta_generic_to_shared(local)), "r"(rank));
+  asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(remote) : "memory");
+  return v;
+}
+
 // Programmatic dependent launch.  pdl_wait() holds a kernel until the kernels before it have completed
 // and their writes are visible; before it a kernel touches no memory.  pdl_trigger() lets the next
 // kernel of the stream be scheduled while this one still runs, so that its launch latency hides behind
@@ -113,10 +128,11 @@ inline int snk_pdl_enabled() {
   return on;
 }
 
-// cluster_z > 1: thread-block clusters of that many blocks along z (grid.z a multiple of it).
+// Thread-block clusters of cluster.x x cluster.y x cluster.z blocks (each grid dimension a multiple of the
+// cluster's); all ones: no clusters.
 template <typename... KArgs, typename... Args>
-inline cudaError_t snk_launch_cluster(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
-                                      cudaStream_t stream, int cluster_z, Args&&... args) {
+inline cudaError_t snk_launch_cluster3(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                                       cudaStream_t stream, dim3 cluster, Args&&... args) {
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = grid;
   cfg.blockDim = block;
@@ -127,14 +143,22 @@ inline cudaError_t snk_launch_cluster(void (*kernel)(KArgs...), dim3 grid, dim3 
   attr[0].val.programmaticStreamSerializationAllowed = snk_pdl_enabled();
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  if (cluster_z > 1) {
+  if (cluster.x * cluster.y * cluster.z > 1) {
     attr[1].id = cudaLaunchAttributeClusterDimension;
-    attr[1].val.clusterDim.x = 1;
-    attr[1].val.clusterDim.y = 1;
-    attr[1].val.clusterDim.z = (unsigned)cluster_z;
+    attr[1].val.clusterDim.x = cluster.x;
+    attr[1].val.clusterDim.y = cluster.y;
+    attr[1].val.clusterDim.z = cluster.z;
     cfg.numAttrs = 2;
   }
   return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
+// cluster_z > 1: clusters of that many blocks along z.
+template <typename... KArgs, typename... Args>
+inline cudaError_t snk_launch_cluster(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                                      cudaStream_t stream, int cluster_z, Args&&... args) {
+  return snk_launch_cluster3(kernel, grid, block, smem, stream, dim3(1, 1, (unsigned)(cluster_z > 1 ? cluster_z : 1)),
+                             static_cast<Args&&>(args)...);
 }
 
 template <typename... KArgs, typename... Args>

@@ -28,6 +28,7 @@
 // (the role of snowllm/ops/gemm.py:33-41 and the expert products of snowllm/ops/inference.py:60-76
 // at prefill shapes)
 #include "tma.cuh"
+#include "tcgen05.cuh"
 
 #define TC_BM 128
 #define TC_BK 64
@@ -54,59 +55,16 @@ __device__ __forceinline__ void mbar_wait(uint64_t* bar, uint32_t parity, volati
   }
 }
 
-// Shared-memory matrix descriptor of a K-major tile whose rows are 128 bytes, written by TMA with the
-// 128-byte swizzle: 8-row groups lie 1024 bytes apart (stride byte offset); the leading byte offset is
-// not used by swizzled K-major layouts; descriptor version 1; layout type 2 = 128-byte swizzle.
-__device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t smem_addr) {
-  uint64_t d = 0;
-  d |= (uint64_t)((smem_addr & 0x3ffff) >> 4);          // start address, bits [0, 14)
-  d |= (uint64_t)1 << 16;                               // leading byte offset (unused), bits [16, 30)
-  d |= (uint64_t)(1024 >> 4) << 32;                     // stride byte offset, bits [32, 46)
-  d |= (uint64_t)1 << 46;                               // version, bits [46, 48)
-  d |= (uint64_t)2 << 61;                               // layout type, bits [61, 64)
-  return d;
-}
-
-// Instruction descriptor of kind::f16: D float, A and B bfloat16, both K-major, M 128, N n.
-__device__ __forceinline__ uint32_t instr_desc_bf16(int n) {
-  return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(TC_BM >> 4) << 24);
-}
-
-__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
-                                          uint32_t accumulate) {
-  asm volatile(
-      "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n"
-      " tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}"
-      ::"r"(tmem_d), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
-}
-__device__ __forceinline__ void umma_commit(uint64_t* bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
-               : "memory");
-}
-__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
-        "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
-        "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-      : "r"(taddr));
-  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-}
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-
 #define TC_MAX_STAGES 6
 
-struct __align__(8) TcShared {
+struct __align__(16) TcShared {
   uint64_t full[TC_MAX_STAGES];
   uint64_t empty[TC_MAX_STAGES];
   uint64_t acc_full[2];
   uint64_t acc_empty[2];
   uint32_t tmem_base;
   int aborted;
+  __align__(16) float stage_out[4][TC_STAGE_FLOATS];    // one staging tile per epilogue warp (tc_store_piece)
 };
 
 // Rows of C and rows of W that tile `tile` covers.  Plain: tiles = row_tiles * n_tiles, row tile fastest.
@@ -222,7 +180,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     }
   } else if (warp == 1) {
     if (lane == 0) {
-      const uint32_t idesc = instr_desc_bf16(BN);
+      const uint32_t idesc = instr_desc_bf16(TC_BM, BN);
       int it = 0, local = 0;
       for (int item = blockIdx.x; item < items; item += gridDim.x) {
         const TcTile t = tc_tile(item % total, row_tiles, M, N, BN, offsets, groups);
@@ -252,7 +210,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     }
   } else {
     const int lane_group = warp & 3;                     // a warp reads the 32 tensor-memory lanes 32*(warp%4)..
-    const bool vec_ok = (N % 8) == 0;
+    float* stage_out = sh->stage_out[warp - 2];
     int local = 0;
     for (int item = blockIdx.x; item < items; item += gridDim.x) {
       const TcTile t = tc_tile(item % total, row_tiles, M, N, BN, offsets, groups);
@@ -261,7 +219,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       const int buf = local & 1;
       mbar_wait(&sh->acc_full[buf], (local >> 1) & 1, aborted, TC_ERR_WAIT_ACC);
       tc_fence_after();
-      const int row = t.row0 + lane_group * 32 + lane;
 #pragma unroll 1
       for (int c0 = 0; c0 < BN; c0 += 32) {
         uint32_t r[32];
@@ -271,51 +228,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
           __syncwarp();
           if (lane == 0) mbar_arrive(&sh->acc_empty[buf]);
         }
-        if constexpr (SWIGLU) {
-          if (row < t.row_end && !*aborted) {
-            OutT* dst = Cp + (size_t)row * (N / 2) + (t.n0 + c0) / 2;
-#pragma unroll
-            for (int blk = 0; blk < 2; ++blk) {
-              if (t.n0 + c0 + blk * 16 + 16 <= N) {
-                uint32_t p[4];
-#pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                  const float g0 = __uint_as_float(r[blk * 16 + 2 * j]), g1 = __uint_as_float(r[blk * 16 + 2 * j + 1]);
-                  const float u0 = __uint_as_float(r[blk * 16 + 8 + 2 * j]), u1 = __uint_as_float(r[blk * 16 + 9 + 2 * j]);
-                  const __nv_bfloat162 v = __floats2bfloat162_rn(g0 / (1.f + expf(-g0)) * u0,
-                                                                 g1 / (1.f + expf(-g1)) * u1);
-                  p[j] = *reinterpret_cast<const uint32_t*>(&v);
-                }
-                *reinterpret_cast<uint4*>(dst + blk * 8) = make_uint4(p[0], p[1], p[2], p[3]);
-              }
-            }
-          }
-        } else if (row < t.row_end && !*aborted) {
-          OutT* dst = Cp + (size_t)row * N + t.n0 + c0;
-          if (vec_ok && t.n0 + c0 + 32 <= N) {
-            if constexpr (sizeof(OutT) == 4) {
-#pragma unroll
-              for (int i = 0; i < 32; i += 4)
-                *reinterpret_cast<uint4*>(dst + i) = make_uint4(r[i], r[i + 1], r[i + 2], r[i + 3]);
-            } else {
-#pragma unroll
-              for (int i = 0; i < 32; i += 8) {
-                uint32_t p[4];
-#pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                  const __nv_bfloat162 v = __floats2bfloat162_rn(__uint_as_float(r[i + 2 * j]),
-                                                                 __uint_as_float(r[i + 2 * j + 1]));
-                  p[j] = *reinterpret_cast<const uint32_t*>(&v);
-                }
-                *reinterpret_cast<uint4*>(dst + i) = make_uint4(p[0], p[1], p[2], p[3]);
-              }
-            }
-          } else {
-#pragma unroll
-            for (int i = 0; i < 32; ++i)
-              if (t.n0 + c0 + i < N) dst[i] = from_f<OutT>(__uint_as_float(r[i]));
-          }
-        }
+        if (!*aborted)
+          tc_store_piece<OutT, SWIGLU>(r, stage_out, lane, Cp, t.row0 + lane_group * 32, t.row_end, t.n0 + c0, N);
       }
       ++local;
     }

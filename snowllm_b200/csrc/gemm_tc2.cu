@@ -1,0 +1,278 @@
+// C[M,N] = A[M,K] . W[N,K]^T in bfloat16 on the tcgen05 tensor cores with PAIRS of SMs (cta_group::2), for
+// many rows (prefill).  The one-SM kernel of gemm_tc.cu is bound by what L2 feeds an SM: 48 KB of operands per
+// k-block of a 128 x 256 tile.  Here a cluster of two blocks owns a 256 x 256 tile of C: each block loads its own
+// 128 rows of A and HALF of the 256 rows of W (32 KB per k-block), the leader block issues one MMA of M 256 for
+// both, and the tensor cores of the two SMs read the other block's half of W across the pair.  A third less
+// operand traffic per product.
+//
+//   warp 0, one lane   TMA producer (both blocks): 128x64 of A and 128x64 of W into this block's stage ring; the
+//                      bytes of both blocks count towards the LEADER's stage barrier (cta_group::2 loads)
+//   warp 1, one lane   leader only: waits for the stage, issues four tcgen05.mma.cta_group::2; a multicast commit
+//                      frees the stage in both blocks and, after the last k-block, hands the accumulator to both
+//                      epilogues
+//   warps 2..5         epilogue (both blocks): tcgen05.ld of this block's 128 accumulator rows, stores; then an
+//                      arrival on the leader's accumulator-free barrier (remote from the peer)
+//
+// Row tiles are 256 rows; a grouped product counts them per group.  Every mbarrier wait is bounded by wall
+// time (see snk_gemm_tc2_status).  No TMA load is multicast: each block loads what it owns.
+#include "tcgen05.cuh"
+
+#define T2_BM 128                     // rows of A per block (256 per pair)
+#define T2_BN 256                     // columns of C per pair; each block loads T2_BN / 2 rows of W
+#define T2_BK 64
+#define T2_THREADS 192
+#define T2_STAGE_BYTES ((T2_BM + T2_BN / 2) * T2_BK * 2)
+#ifndef T2_STAGES
+#define T2_STAGES 6
+#endif
+#define T2_WAIT_NS 1500000000ull
+#ifndef T2_ACC_BUFFERS
+#define T2_ACC_BUFFERS 2              // accumulators in tensor memory: the epilogue of a tile overlaps the next tile's products
+#endif
+
+enum { T2_ERR_FULL = 1, T2_ERR_EMPTY = 2, T2_ERR_ACC = 3, T2_ERR_ACC_FREE = 4, T2_ERR_PEER = 5 };
+
+__device__ int g_t2_status;
+__device__ unsigned int g_t2_tmem[2];  // the tensor-memory base addresses the two blocks of cluster 0 were given (a probe)
+
+__device__ __forceinline__ void t2_wait(uint64_t* bar, uint32_t parity, volatile int* aborted, int code) {
+  if (*aborted) return;
+  if (mbar_try_wait(bar, parity)) return;
+  const uint64_t start = global_ns();
+  while (!mbar_try_wait(bar, parity)) {
+    if (*aborted) return;
+    if (global_ns() - start > T2_WAIT_NS) {
+      *aborted = 1;
+      atomicCAS(&g_t2_status, 0, code);
+      return;
+    }
+  }
+}
+
+struct __align__(16) T2Shared {
+  uint64_t full[T2_STAGES];         // (leader) both blocks' stages hold their operands
+  uint64_t empty[T2_STAGES];        // the MMAs that read the stage have completed (both blocks)
+  uint64_t acc_full[2];             // the tile's products have completed (both blocks)
+  uint64_t acc_empty[2];            // (leader) both epilogues have read the accumulator: 8 arrivals
+  uint32_t tmem_base;
+  int aborted;
+  __align__(16) float stage_out[4][TC_STAGE_FLOATS];    // one staging tile per epilogue warp (tc_store_piece)
+};
+
+struct T2Tile {
+  int row0, row_end, w_row0, n0;
+  bool valid;
+};
+
+// Pair tile `tile`: 256 rows x 256 columns; row tiles fastest; grouped: counted group by group.
+__device__ __forceinline__ T2Tile t2_tile(int tile, int row_tiles, int M, int N, const int* offsets, int groups) {
+  T2Tile t;
+  const int rt = tile % row_tiles, nt = tile / row_tiles;
+  t.n0 = nt * T2_BN;
+  t.valid = t.n0 < N;
+  if (!offsets) {
+    t.row0 = rt * 2 * T2_BM;
+    t.row_end = M;
+    t.w_row0 = 0;
+    return t;
+  }
+  int left = rt;
+  t.valid = false;
+  t.row0 = t.row_end = t.w_row0 = 0;
+  if (t.n0 >= N) return t;
+  for (int e = 0; e < groups; ++e) {
+    const int begin = offsets[e], cnt = offsets[e + 1] - begin;
+    const int tiles_e = (cnt + 2 * T2_BM - 1) / (2 * T2_BM);
+    if (left < tiles_e) {
+      t.row0 = begin + left * 2 * T2_BM;
+      t.row_end = begin + cnt;
+      t.w_row0 = e * N;
+      t.valid = true;
+      return t;
+    }
+    left -= tiles_e;
+  }
+  return t;
+}
+
+template <typename OutT, bool SWIGLU>
+__global__ void __launch_bounds__(T2_THREADS)
+gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
+                OutT* __restrict__ C, int M, int N, int K, const int* __restrict__ offsets, int groups,
+                int row_tiles_bound) {
+  extern __shared__ unsigned char smem_raw[];
+  unsigned char* tiles = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  T2Shared* sh = reinterpret_cast<T2Shared*>(tiles + (size_t)T2_STAGES * T2_STAGE_BYTES);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();               // 0: leader, 1: peer
+  const int pair = blockIdx.x >> 1, pairs = gridDim.x >> 1;     // pairs lie along x
+  const int k_tiles = (K + T2_BK - 1) / T2_BK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < T2_STAGES; ++s) {
+      mbar_init(&sh->full[s], 1);
+      mbar_init(&sh->empty[s], 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&sh->acc_full[b], 1);
+      mbar_init(&sh->acc_empty[b], 8);                   // four epilogue warps of each block
+    }
+    sh->aborted = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;"
+                 ::"r"(smem_u32(&sh->tmem_base)), "r"((uint32_t)(T2_ACC_BUFFERS * T2_BN)) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  cluster_sync();                                        // both blocks' barriers and tensor memory are set up
+  tc_fence_after();
+  // the accumulator's address is the leader's: the MMA writes rows 128..255 at the same columns of the peer
+  const uint32_t tmem_acc = rank == 0 ? sh->tmem_base : ld_cluster_u32(&sh->tmem_base, 0);
+  if (pair == 0 && threadIdx.x == 0) g_t2_tmem[rank] = sh->tmem_base;
+  volatile int* aborted = &sh->aborted;
+  pdl_begin();
+  int row_tiles = row_tiles_bound;
+  if (offsets) {
+    row_tiles = 0;
+    for (int e = 0; e < groups; ++e) row_tiles += (offsets[e + 1] - offsets[e] + 2 * T2_BM - 1) / (2 * T2_BM);
+  }
+  const int n_tiles = (N + T2_BN - 1) / T2_BN;
+  const int total = row_tiles * n_tiles;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      int it = 0;
+      for (int tile = pair; tile < total; tile += pairs) {
+        const T2Tile t = t2_tile(tile, row_tiles, M, N, offsets, groups);
+        if (!t.valid) continue;
+        for (int kt = 0; kt < k_tiles; ++kt, ++it) {
+          const int s = it % T2_STAGES;
+          t2_wait(&sh->empty[s], ((it / T2_STAGES) & 1) ^ 1, aborted, T2_ERR_EMPTY);
+          // both blocks' bytes count towards the leader's barrier: it is the leader that issues the MMAs
+          if (rank == 0) mbar_expect_tx(&sh->full[s], 2 * T2_STAGE_BYTES);
+          const uint32_t bar = cluster_addr(&sh->full[s], 0);
+          unsigned char* stage = tiles + (size_t)s * T2_STAGE_BYTES;
+          tma2_load_2d(stage, &map_a, bar, kt * T2_BK, t.row0 + (int)rank * T2_BM);
+          tma2_load_2d(stage + T2_BM * T2_BK * 2, &map_w, bar, kt * T2_BK, t.w_row0 + t.n0 + (int)rank * (T2_BN / 2));
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0 && rank == 0) {                        // the leader issues for the pair; the peer's warp rests
+      const uint32_t idesc = instr_desc_bf16(2 * T2_BM, T2_BN);
+      int it = 0, local = 0;
+      for (int tile = pair; tile < total; tile += pairs) {
+        const T2Tile t = t2_tile(tile, row_tiles, M, N, offsets, groups);
+        if (!t.valid) continue;
+        const int buf = local % T2_ACC_BUFFERS;
+        const int use = local / T2_ACC_BUFFERS;          // how often this accumulator was used before
+        t2_wait(&sh->acc_empty[buf], (use & 1) ^ 1, aborted, T2_ERR_ACC_FREE);
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_acc + (uint32_t)(buf * T2_BN);
+        for (int kt = 0; kt < k_tiles; ++kt, ++it) {
+          const int s = it % T2_STAGES;
+          t2_wait(&sh->full[s], (it / T2_STAGES) & 1, aborted, T2_ERR_FULL);   // both blocks' stage s
+          tc_fence_after();
+          const uint32_t a_addr = smem_u32(tiles + (size_t)s * T2_STAGE_BYTES);
+          const uint32_t w_addr = a_addr + T2_BM * T2_BK * 2;
+#pragma unroll
+          for (int k = 0; k < T2_BK / 16; ++k)
+            umma2_bf16(d_tmem, smem_desc_sw128(a_addr + k * 32), smem_desc_sw128(w_addr + k * 32), idesc,
+                       (kt > 0 || k > 0) ? 1u : 0u);
+          umma2_commit(&sh->empty[s], 3);                // the stage is free in both blocks once these MMAs have read it
+        }
+        umma2_commit(&sh->acc_full[buf], 3);
+        ++local;
+      }
+    }
+  } else {
+    const int lane_group = warp & 3;
+    float* stage_out = sh->stage_out[warp - 2];
+    int local = 0;
+    for (int tile = pair; tile < total; tile += pairs) {
+      const T2Tile t = t2_tile(tile, row_tiles, M, N, offsets, groups);
+      if (!t.valid) continue;
+      const int buf = local % T2_ACC_BUFFERS;
+      const int use = local / T2_ACC_BUFFERS;
+      t2_wait(&sh->acc_full[buf], use & 1, aborted, T2_ERR_ACC);
+      tc_fence_after();
+#pragma unroll 1
+      for (int c0 = 0; c0 < T2_BN; c0 += 32) {
+        uint32_t r[32];
+        tmem_ld32(tmem_acc + ((uint32_t)(lane_group * 32) << 16) + (uint32_t)(buf * T2_BN + c0), r);
+        if (c0 + 32 >= T2_BN) {                          // everything of this accumulator is in registers
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0 && !*aborted) {
+            if (rank == 0) mbar_arrive(&sh->acc_empty[buf]);
+            else mbar_arrive_remote(&sh->acc_empty[buf], 0);
+          }
+        }
+        if (!*aborted)
+          tc_store_piece<OutT, SWIGLU>(r, stage_out, lane, C, t.row0 + (int)rank * T2_BM + lane_group * 32, t.row_end,
+                                       t.n0 + c0, N);
+      }
+      ++local;
+    }
+  }
+  tc_fence_before();
+  cluster_sync();                                        // nobody of the pair touches tensor memory or barriers any more
+  if (warp == 1) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;"
+                 ::"r"(sh->tmem_base), "r"((uint32_t)(T2_ACC_BUFFERS * T2_BN)) : "memory");
+  }
+}
+
+template <typename OutT, bool SWIGLU>
+static int launch_tc2(const CUtensorMap& map_a, const CUtensorMap& map_w, void* C, int M, int N, int K,
+                      const int* offsets, int groups, int row_tiles, cudaStream_t stream) {
+  const size_t smem = 1024 + (size_t)T2_STAGES * T2_STAGE_BYTES + sizeof(T2Shared);
+  static int sms = 0;
+  if (sms == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    cudaFuncSetAttribute(gemm_tc2_kernel<OutT, SWIGLU>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  }
+  const long long tiles = (long long)row_tiles * ((N + T2_BN - 1) / T2_BN);
+  const int pairs = (int)(tiles < sms / 2 ? tiles : sms / 2);
+  snk_launch_cluster3(gemm_tc2_kernel<OutT, SWIGLU>, dim3(2 * pairs), dim3(T2_THREADS), smem, stream, dim3(2, 1, 1),
+                      map_a, map_w, static_cast<OutT*>(C), M, N, K, offsets, groups, row_tiles);
+  SNK_LAUNCH_CHECK();
+  return 0;
+}
+
+// M: rows of A (all groups together).  Grouped: offsets[groups+1] on the device, W = [groups, N, K];
+// max_row_tiles bounds the number of 256-row tiles over all groups (M/256 + groups is always enough).
+SNK_API int snk_gemm_tc2(const void* A, const void* W, void* C, int M, int N, int K, const int* offsets,
+                         int groups, int max_row_tiles, int out_f32, int swiglu, cudaStream_t stream) {
+  if (M <= 0 || N <= 0) return 0;
+  if (K <= 0 || K % 8) return SNK_ERR_SIZE;
+  if (swiglu && (N % 16 || out_f32)) return SNK_ERR_SIZE;
+  if (((uintptr_t)A % 16) || ((uintptr_t)W % 16) || ((uintptr_t)C % 16)) return SNK_ERR_ALIGN;
+  const int row_tiles = offsets ? max_row_tiles : (M + 2 * T2_BM - 1) / (2 * T2_BM);
+  if (row_tiles <= 0) return SNK_ERR_SIZE;
+  CUtensorMap map_a, map_w;
+  int rc = tensor_map(A, M, K, T2_BM, T2_BK, &map_a);
+  if (rc) return rc;
+  rc = tensor_map(W, (long long)(offsets ? groups : 1) * N, K, T2_BN / 2, T2_BK, &map_w);
+  if (rc) return rc;
+  if (swiglu) return launch_tc2<bf16, true>(map_a, map_w, C, M, N, K, offsets, groups, row_tiles, stream);
+  if (out_f32) return launch_tc2<float, false>(map_a, map_w, C, M, N, K, offsets, groups, row_tiles, stream);
+  return launch_tc2<bf16, false>(map_a, map_w, C, M, N, K, offsets, groups, row_tiles, stream);
+}
+
+// 0, or the first error a block of any earlier launch recorded (a wait that ran out); reading clears it.
+// tmem (may be null): the tensor-memory addresses the two blocks of the first pair were given.  Synchronises.
+SNK_API int snk_gemm_tc2_status(unsigned int* tmem) {
+  int v = 0, zero = 0;
+  if (cudaMemcpyFromSymbol(&v, g_t2_status, sizeof(int)) != cudaSuccess) return -1;
+  if (v) cudaMemcpyToSymbol(g_t2_status, &zero, sizeof(int));
+  if (tmem && cudaMemcpyFromSymbol(tmem, g_t2_tmem, 2 * sizeof(unsigned int)) != cudaSuccess) return -1;
+  return v;
+}

@@ -57,6 +57,10 @@ _SIGNATURES = {
         "snk_gemm_tc_status": [],
         "snk_gather_rows_bf16": [P, P, P, I, I, I, P],
     },
+    "gemm_tc2": {
+        "snk_gemm_tc2": [P, P, P, I, I, I, P, I, I, I, I, P],
+        "snk_gemm_tc2_status": [P],
+    },
     "moe": {
         "snk_moe_route": [P, P, I, P, P, P, I, I, I, I, I, F, I, P],
         "snk_moe_topk": [P, P, P, P, I, I, I, I, F, I, P],
@@ -585,6 +589,41 @@ def gemm_tc(a, w, out_dtype=None, out=None, offsets=None, swiglu=False):
                             int(out_dtype == torch.float32), int(swiglu), _ptr(scratch), _stream()), "gemm_tc",
           launches=2 if need else 1)
     return out
+
+
+def gemm_tc2(a, w, out_dtype=None, out=None, offsets=None, swiglu=False):
+    """As ``gemm_tc``, on pairs of SMs (cta_group::2): 256 x 256 tiles of C, each block of a pair loading
+    its 128 rows of ``a`` and half of the tile's rows of ``w``."""
+    _chk(a, "gemm a", torch.bfloat16)
+    _chk(w, "gemm w", torch.bfloat16)
+    M, K = a.shape
+    grouped = offsets is not None
+    if grouped:
+        G, N, Kw = w.shape
+        _chk(offsets, "group offsets", torch.int32, (G + 1,))
+    else:
+        G = 1
+        N, Kw = w.shape
+    if Kw != K:
+        raise KernelError(f"gemm: a has K={K}, w has K={Kw}")
+    out_dtype = out_dtype or torch.bfloat16
+    cols = N // 2 if swiglu else N
+    if out is None:
+        out = torch.empty(M, cols, dtype=out_dtype, device=a.device)
+    _chk(out, "gemm out", out_dtype, (M, cols))
+    if out_dtype not in (torch.bfloat16, torch.float32) or (swiglu and out_dtype != torch.bfloat16):
+        raise KernelError("gemm output is bfloat16 or float32 (bfloat16 with swiglu)")
+    row_tiles = -(-M // (2 * TC_TILE)) + (G if grouped else 0)
+    check(fn("snk_gemm_tc2")(_ptr(a), _ptr(w), _ptr(out), M, N, K, _ptr(offsets), G, row_tiles,
+                             int(out_dtype == torch.float32), int(swiglu), _stream()), "gemm_tc2")
+    return out
+
+
+def gemm_tc2_status():
+    """(0 or the code of a wait that ran out inside the pair kernel since the last call, the tensor-memory
+    addresses the two blocks of the first pair were given); synchronises the device."""
+    addr = (ctypes.c_uint * 2)()
+    return int(fn("snk_gemm_tc2_status")(addr)), (int(addr[0]), int(addr[1]))
 
 
 def gemm_tc_is_split(M: int, N: int, K: int) -> bool:

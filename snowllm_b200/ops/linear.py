@@ -3,16 +3,35 @@
 float32: the CUDA-core kernel of csrc/gemm.cu (true 32-bit, sums in k order).
 bfloat16, up to 16 rows (decode; grouped: up to 4 rows per group on average): csrc/gemm_skinny.cu, which
 streams W once into mma.sync fragments.
-bfloat16, more rows (prefill): csrc/gemm_tc.cu, 128 x 128 tiles on the tcgen05 tensor cores with TMA
-loads and the accumulator in tensor memory.
+bfloat16, more rows (prefill): csrc/gemm_tc.cu, 128 x 256 tiles on the tcgen05 tensor cores with TMA
+loads and the accumulator in tensor memory; from 4,096 rows on csrc/gemm_tc2.cu, the same on pairs of SMs.
 bfloat16 operands that neither takes (K no multiple of 8, unaligned views): the CUDA-core kernel.
 (the role of snowllm/models/projection.py:27-35)
 """
 from __future__ import annotations
 
+import os
+
 import torch
 
 from . import kernels
+
+# Products of very many rows run on pairs of SMs (csrc/gemm_tc2.cu: 256 x 256 tiles, a third less operand traffic).
+# Measured against the one-SM kernel: 2,048 rows no gain (the launch is short; tile rounds and the epilogue
+# decide), 4,096 rows +6 %, 8,192 rows +7 %, 32,768 sorted rows over 32 experts +7 %.
+TC_PAIRS = os.environ.get("SNOWLLM_B200_TC_PAIRS", "1") != "0"
+PAIRS_MIN_ROWS = 4096             # plain products
+PAIRS_MIN_GROUP_ROWS = 512        # grouped: rows per group on average (a group's rows are cut into 256-row tiles)
+
+
+def _tc(x, w, **kw):
+    """The tcgen05 product: on pairs of SMs where there are rows enough."""
+    offsets = kw.get("offsets")
+    rows = x.shape[0]
+    if TC_PAIRS and rows >= PAIRS_MIN_ROWS and (offsets is None or rows >= PAIRS_MIN_GROUP_ROWS * w.shape[0]):
+        return kernels.gemm_tc2(x, w, **kw)
+    return kernels.gemm_tc(x, w, **kw)
+
 
 SKINNY_MAX_ROWS = 16       # measured crossover: up to here the few-rows kernel reads W faster than 128-row tiles
 SKINNY_MAX_GROUP_ROWS = 4  # grouped: mean rows per group up to which the few-rows kernel wins
@@ -24,7 +43,7 @@ def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype | None = Non
     if kernels.gemm_skinny_ok(x, w):
         if x.shape[0] <= SKINNY_MAX_ROWS:
             return kernels.gemm_skinny(x, w, out_dtype=out_dtype, out=out)
-        return kernels.gemm_tc(x, w, out_dtype=out_dtype, out=out)
+        return _tc(x, w, out_dtype=out_dtype, out=out)
     return kernels.gemm_simt(x, w, out_dtype=out_dtype, out=out)
 
 
@@ -43,7 +62,7 @@ def grouped_linear(x, w, offsets, rows_out, max_rows_per_group, a_rows=None, a_d
                                        rows_out=rows_out, rows_hint=hint)
         # TMA reads whole tiles of contiguous rows: bring the rows into sorted order first
         xs = kernels.gather_rows(x, a_rows, a_div) if a_rows is not None else x
-        return kernels.gemm_tc(xs, w, out_dtype=out_dtype, offsets=offsets)
+        return _tc(xs, w, out_dtype=out_dtype, offsets=offsets)
     return kernels.gemm_simt(x, w, out_dtype=out_dtype, a_rows=a_rows, a_div=a_div, offsets=offsets,
                              rows_out=rows_out, max_rows_per_group=max_rows_per_group)
 
@@ -62,7 +81,7 @@ def linear_swiglu(x: torch.Tensor, w13: torch.Tensor, interleaved: bool) -> torc
     if interleaved and kernels.gemm_skinny_ok(x, w13):
         if x.shape[0] <= SKINNY_MAX_ROWS:
             return kernels.gemm_skinny(x, w13, swiglu=True)
-        return kernels.gemm_tc(x, w13, swiglu=True)
+        return _tc(x, w13, swiglu=True)
     return kernels.swiglu(linear(x, w13), interleaved=interleaved)
 
 
@@ -74,6 +93,6 @@ def grouped_linear_swiglu(x, w13, offsets, rows_out, max_rows_per_group, a_rows,
             return kernels.gemm_skinny(x, w13, a_rows=a_rows, a_div=a_div, offsets=offsets, rows_out=rows_out,
                                        rows_hint=hint, swiglu=True)
         xs = kernels.gather_rows(x, a_rows, a_div) if a_rows is not None else x
-        return kernels.gemm_tc(xs, w13, offsets=offsets, swiglu=True)
+        return _tc(xs, w13, offsets=offsets, swiglu=True)
     h = grouped_linear(x, w13, offsets, rows_out, max_rows_per_group, a_rows=a_rows, a_div=a_div)
     return kernels.swiglu(h, interleaved=interleaved)

@@ -69,20 +69,20 @@ def gemm_skinny(a):
 def gemm_tc(a):
     gen = torch.Generator(device="cuda").manual_seed(0)
     G = a.groups
+    product = kernels.gemm_tc2 if a.pairs else kernels.gemm_tc      # --pairs: the kernel on pairs of SMs
     if G > 1:
         w = bf16(G, a.n, a.k, scale=a.k ** -0.5, gen=gen)
         per = a.m // G
         offsets = torch.arange(0, G + 1, dtype=torch.int32, device="cuda") * per
         x = bf16(per * G, a.k, gen=gen)
-        fn = lambda: kernels.gemm_tc(x, w, offsets=offsets, out_dtype=torch.float32 if a.f32 else None,
-                                     swiglu=a.swiglu)
+        fn = lambda: product(x, w, offsets=offsets, out_dtype=torch.float32 if a.f32 else None, swiglu=a.swiglu)
         flops = 2.0 * per * G * a.n * a.k
     else:
         w, x = bf16(a.n, a.k, scale=a.k ** -0.5, gen=gen), bf16(a.m, a.k, gen=gen)
-        fn = lambda: kernels.gemm_tc(x, w, out_dtype=torch.float32 if a.f32 else None, swiglu=a.swiglu)
+        fn = lambda: product(x, w, out_dtype=torch.float32 if a.f32 else None, swiglu=a.swiglu)
         flops = 2.0 * a.m * a.n * a.k
     us = timed(fn, a.iters)
-    assert kernels.gemm_tc_status() == 0
+    assert kernels.gemm_tc_status() == 0 and (not a.pairs or kernels.gemm_tc2_status()[0] == 0)
     return {"us": us, "TFLOP/s": flops / us / 1e6, "flops": flops}
 
 
@@ -144,6 +144,7 @@ def main(argv=None) -> int:
     ap.add_argument("--active", type=int, default=0, help="groups that own rows (gemm_skinny)")
     ap.add_argument("--f32", action="store_true", help="float32 output")
     ap.add_argument("--swiglu", action="store_true", help="SwiGLU at the store (w rows interleaved by 8)")
+    ap.add_argument("--pairs", action="store_true", help="gemm_tc: the kernel on pairs of SMs (cta_group::2)")
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--context", type=int, default=8192)
     ap.add_argument("--tokens", type=int, default=2048)

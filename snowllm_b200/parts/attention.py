@@ -20,7 +20,7 @@ from .spec import INIT_ONES, KEEP_SMALL, PagedKVSpec, TensorSpec
 
 
 class Attention(Part):
-    libraries = ("gemm", "gemm_skinny", "gemm_tc", "rope_cache", "attention", "attention_mma")
+    libraries = ("gemm", "gemm_skinny", "gemm_tc", "gemm_tc2", "rope_cache", "attention", "attention_mma")
 
     def __init__(self, dtype, names, *, hidden_size: int, num_heads: int, num_kv_heads: int,
                  head_dim: int, qk_norm_eps: float | None, position: dict, window: int | None = None,

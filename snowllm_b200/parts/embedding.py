@@ -31,7 +31,7 @@ class Embedding(Part):
 
 class LinearHead(Part):
     """logits = x . W^T in float.  ``tied``: W is the embedding table, and no tensor is declared."""
-    libraries = ("gemm", "gemm_skinny", "gemm_tc")
+    libraries = ("gemm", "gemm_skinny", "gemm_tc", "gemm_tc2")
 
     def __init__(self, dtype, names, *, vocab_size: int, hidden_size: int, tied: bool):
         super().__init__(dtype, names)

@@ -12,7 +12,7 @@ from .spec import TensorSpec
 
 
 class SwiGLU(Part):
-    libraries = ("gemm", "gemm_skinny", "gemm_tc", "elementwise")
+    libraries = ("gemm", "gemm_skinny", "gemm_tc", "gemm_tc2", "elementwise")
 
     def __init__(self, dtype, names, *, hidden_size: int, intermediate_size: int):
         super().__init__(dtype, names)

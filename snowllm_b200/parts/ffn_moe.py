@@ -16,7 +16,7 @@ from .spec import INIT_BIAS, KEEP_F32, KEEP_SMALL, TensorSpec
 
 
 class SigmoidMoE(Part):
-    libraries = ("gemm", "gemm_skinny", "gemm_tc", "moe", "elementwise")
+    libraries = ("gemm", "gemm_skinny", "gemm_tc", "gemm_tc2", "moe", "elementwise")
 
     def __init__(self, dtype, names, *, hidden_size: int, intermediate_size: int, num_experts: int,
                  top_k: int, norm_topk_prob: bool, use_expert_bias: bool, routed_scaling_factor: float):

@@ -13,7 +13,7 @@ from .spec import INIT_CONV, KEEP_SMALL, SlotStateSpec, TensorSpec
 
 
 class ShortConv(Part):
-    libraries = ("gemm", "gemm_skinny", "gemm_tc", "short_conv")
+    libraries = ("gemm", "gemm_skinny", "gemm_tc", "gemm_tc2", "short_conv")
 
     def __init__(self, dtype, names, *, hidden_size: int, kernel_size: int):
         super().__init__(dtype, names)

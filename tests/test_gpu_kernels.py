@@ -589,6 +589,38 @@ def test_gemm_tc(K, M, N, K_):
         assert torch.allclose(part, out[rows], rtol=1e-5, atol=1e-5 * math.sqrt(K_))
 
 
+@pytest.mark.parametrize("M,N,K_", [(256, 256, 64), (300, 520, 200), (1000, 96, 48), (2000, 4000, 72), (513, 264, 2048)])
+def test_gemm_tc2_pairs_of_sms(K, M, N, K_):
+    """The product on pairs of SMs (cta_group::2) against the float product, to float and to bfloat16, with
+    SwiGLU at the store, and grouped with ragged groups."""
+    from snowllm_b200.ops import interleave_gate_up
+    torch.manual_seed(33)
+    dtype = torch.bfloat16
+    a, w = rnd(dtype, M, K_), rnd(dtype, N, K_)
+    want = a @ w.T
+    close(K.gemm_tc2(dev(a, dtype), dev(w, dtype), out_dtype=torch.float32), want, torch.float32, scale=math.sqrt(K_))
+    close(K.gemm_tc2(dev(a, dtype), dev(w, dtype)), want, dtype, scale=math.sqrt(K_) / 4)
+    status, tmem = K.gemm_tc2_status()
+    assert status == 0 and tmem[0] == tmem[1]            # the pair holds one accumulator address
+    I = (N // 16) * 8
+    if I:
+        gate, up = rnd(dtype, I, K_, scale=K_ ** -0.5), rnd(dtype, I, K_, scale=K_ ** -0.5)
+        act = K.gemm_tc2(dev(a, dtype), interleave_gate_up(dev(gate, dtype), dev(up, dtype)), swiglu=True)
+        close(act, F.silu(a @ gate.T) * (a @ up.T), dtype, scale=2)
+    counts = [M // 3, 0, 1, M - M // 3 - 1 - 257, 257]
+    if min(counts) >= 0:
+        offsets = [0]
+        for c in counts:
+            offsets.append(offsets[-1] + c)
+        wg = rnd(dtype, len(counts), N, K_)
+        out = K.gemm_tc2(dev(a, dtype), dev(wg, dtype), out_dtype=torch.float32, offsets=i32(offsets))
+        for e, c in enumerate(counts):
+            r = slice(offsets[e], offsets[e + 1])
+            if c:
+                close(out[r], a[r] @ wg[e].T, torch.float32, scale=math.sqrt(K_))
+    assert K.gemm_tc2_status()[0] == 0
+
+
 def test_gemm_tc_grouped_after_gather(K):
     torch.manual_seed(31)
     dtype = torch.bfloat16
