@@ -386,20 +386,29 @@ SNK_API int snk_gemm_tc_status() {
 
 // ---------------------------------------------------------------------------------------------
 // out[r, :] = in[rows[r] / div, :]  (bfloat16 rows of K elements, K a multiple of 8)
+#define GATHER_ROWS_PER_BLOCK 8
 __global__ void gather_rows_kernel(const uint4* __restrict__ in, uint4* __restrict__ out,
-                                   const int* __restrict__ rows, int div, int vecs) {
+                                   const int* __restrict__ rows, int div, int vecs, int R) {
   pdl_begin();
-  const uint4* src = in + (size_t)(rows[blockIdx.x] / div) * vecs;
-  uint4* dst = out + (size_t)blockIdx.x * vecs;
-  for (int i = threadIdx.x; i < vecs; i += blockDim.x) dst[i] = src[i];
+  // a block copies GATHER_ROWS_PER_BLOCK rows; every thread has one vector of each row in flight
+  const int r0 = blockIdx.x * GATHER_ROWS_PER_BLOCK;
+  for (int i = threadIdx.x; i < vecs; i += blockDim.x) {
+    uint4 v[GATHER_ROWS_PER_BLOCK];
+#pragma unroll
+    for (int j = 0; j < GATHER_ROWS_PER_BLOCK; ++j)
+      if (r0 + j < R) v[j] = in[(size_t)(rows[r0 + j] / div) * vecs + i];
+#pragma unroll
+    for (int j = 0; j < GATHER_ROWS_PER_BLOCK; ++j)
+      if (r0 + j < R) out[(size_t)(r0 + j) * vecs + i] = v[j];
+  }
 }
 
 SNK_API int snk_gather_rows_bf16(const void* in, void* out, const int* rows, int div, int R, int K,
                                  cudaStream_t stream) {
   if (R <= 0) return 0;
   if (K % 8 || ((uintptr_t)in % 16) || ((uintptr_t)out % 16)) return SNK_ERR_ALIGN;
-  snk_launch(gather_rows_kernel, dim3(R), dim3(128), 0, stream, static_cast<const uint4*>(in), static_cast<uint4*>(out), rows,
-                                            div <= 0 ? 1 : div, K / 8);
+  snk_launch(gather_rows_kernel, dim3((R + GATHER_ROWS_PER_BLOCK - 1) / GATHER_ROWS_PER_BLOCK), dim3(256), 0, stream,
+             static_cast<const uint4*>(in), static_cast<uint4*>(out), rows, div <= 0 ? 1 : div, K / 8, R);
   SNK_LAUNCH_CHECK();
   return 0;
 }

@@ -87,7 +87,9 @@ __global__ void short_conv_state_kernel(const T* __restrict__ bcx, T* __restrict
 // Many rows (prompt portions): a thread owns VEC consecutive channels (one 16-byte vector) and walks
 // CONV_STRIP consecutive rows, keeping the last L-1 values of g in registers, so B, C and x of a row
 // are read once, as vectors.  Up to 4 taps; the state is brought up to date by the second kernel.
+#ifndef CONV_STRIP
 #define CONV_STRIP 8
+#endif
 #define CONV_FAST_L 4
 
 template <typename T> struct ConvVec;

@@ -668,6 +668,13 @@ def moe_route(x, router_w, bias, top_k, norm_topk_prob, scaling):
         _chk(bias, "expert bias", torch.float32, (E,))
     ids = torch.empty(M, top_k, dtype=torch.int32, device=x.device)
     wts = torch.empty(M, top_k, dtype=torch.float32, device=x.device)
+    if (M > ROUTE_GEMM_MIN_ROWS and router_w.dtype == torch.bfloat16 and gemm_tc_ok(x, router_w)
+            and gemm_tc_is_split(M, E, H)):
+        # many rows, few experts: a tcgen05 product split along K (float accumulation, float output)
+        logits = gemm_tc(x, router_w, out_dtype=torch.float32)
+        check(fn("snk_moe_topk")(_ptr(logits), _ptr(bias), _ptr(ids), _ptr(wts), M, E, top_k,
+                                 int(bool(norm_topk_prob)), float(scaling), 0, _stream()), "moe_topk")
+        return ids, wts
     if M > ROUTE_GEMM_MIN_ROWS and router_w.dtype == torch.bfloat16 and gemm_skinny_ok(router_w, x):
         # many rows: the logits are a tensor-core product with float accumulation and float output.  The few
         # router rows take the place of the tokens in the few-rows kernel, which then streams x once and
