@@ -150,3 +150,36 @@ def test_finished_requests_pages_serve_the_next_request_in_the_next_step():
     s.retire_finished()
     plan = s.schedule()
     assert plan[0].request is b and sorted(b.cache.tables[("paged", None)]) == [0, 1]
+
+
+def test_tokens_in_flight_count_as_generated_and_appear_as_references():
+    """Overlapped steps: a sampled token that the host has not read yet (``in_flight``: its place among the
+    device's pending tokens) is scheduled like a known token, appears in the segment as -(place + 1), and a
+    request whose token in flight is its last is not scheduled again."""
+    cm, s = make(budget=32)
+    a, b = req(5, new=3), req(6, new=1)
+    s.add(a)
+    s.add(b)
+    plan = s.schedule()                               # both prompts whole, logits wanted
+    assert [(x.start, x.count, x.wants_logits) for x in plan] == [(0, 5, True), (0, 6, True)]
+    for i, x in enumerate(plan):                      # the step ran; its tokens stay on the device
+        cm.commit(x.request.cache, x.count)
+        x.request.num_computed += x.count
+        x.request.in_flight = i
+    assert a.generated == 1 and a.pending == 1 and not a.at_length
+    assert b.generated == 1 and b.at_length           # its only new token is the one in flight
+    plan = s.schedule()
+    assert [x.request for x in plan] == [a]           # b waits for its token to land, it is not run again
+    assert plan[0].tokens == [-1] and plan[0].start == 5 and plan[0].wants_logits
+    # the tokens land: b is done, a goes on with a known token and a new one in flight
+    a.in_flight, b.in_flight = -1, -1
+    a.out.append(11)
+    b.out.append(12)
+    b.done, b.finish_reason = True, "length"
+    cm.commit(a.cache, 6)
+    a.num_computed += 1
+    a.in_flight = 0
+    s.retire_finished()
+    assert b.cache is None and s.running == [a]
+    plan = s.schedule()
+    assert plan[0].tokens == [-1] and plan[0].start == 6 and a.tokens[-2:] == [11, -1]
