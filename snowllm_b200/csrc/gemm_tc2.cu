@@ -25,6 +25,9 @@
 #ifndef T2_STAGES
 #define T2_STAGES 6
 #endif
+#ifndef T2_BAND
+#define T2_BAND 8
+#endif
 #define T2_WAIT_NS 1500000000ull
 #ifndef T2_ACC_BUFFERS
 #define T2_ACC_BUFFERS 2              // accumulators in tensor memory: the epilogue of a tile overlaps the next tile's products
@@ -64,10 +67,17 @@ struct T2Tile {
   bool valid;
 };
 
-// Pair tile `tile`: 256 rows x 256 columns; row tiles fastest; grouped: counted group by group.
+// Pair tile `tile`: 256 rows x 256 columns; grouped: row tiles counted group by group.
 __device__ __forceinline__ T2Tile t2_tile(int tile, int row_tiles, int M, int N, const int* offsets, int groups) {
   T2Tile t;
-  const int rt = tile % row_tiles, nt = tile / row_tiles;
+  // bands of up to T2_BAND n-tiles, the n-tile fastest inside a band, then the row tile (as in gemm_tc.cu)
+  const int n_tiles = (N + T2_BN - 1) / T2_BN;
+  const int bands = (n_tiles + T2_BAND - 1) / T2_BAND;
+  const int band_w = (n_tiles + bands - 1) / bands;
+  const int per_band = row_tiles * band_w;
+  const int band = tile / per_band, in_band = tile % per_band;
+  const int w_here = min(band_w, n_tiles - band * band_w);
+  const int rt = in_band / w_here, nt = band * band_w + in_band % w_here;
   t.n0 = nt * T2_BN;
   t.valid = t.n0 < N;
   if (!offsets) {
