@@ -84,9 +84,11 @@ __global__ void short_conv_state_kernel(const T* __restrict__ bcx, T* __restrict
     if (i < L - 1) st[(size_t)i * H + c] = from_f<T>(next[i]);
 }
 
-// Many rows (prompt portions): a thread owns VEC consecutive channels (one 16-byte vector) and walks
-// CONV_STRIP consecutive rows, keeping the last L-1 values of g in registers, so B, C and x of a row
-// are read once, as vectors.  Up to 4 taps; the state is brought up to date by the second kernel.
+// Many rows (prompt portions): a thread owns VEC consecutive channels (one vector) and walks CONV_STRIP
+// consecutive rows, keeping the last L-1 values of g in registers, so B, C and x of a row are read
+// once.  Every load of the strip, and of the L-1 rows before it, is issued before the first value is
+// used: the loads do not wait for the segment look-ups, and a thread has the whole strip in flight.
+// Up to 4 taps (L is a template parameter); the state is brought up to date by the second kernel.
 #ifndef CONV_STRIP
 #define CONV_STRIP 8
 #endif
@@ -95,103 +97,111 @@ __global__ void short_conv_state_kernel(const T* __restrict__ bcx, T* __restrict
 template <typename T> struct ConvVec;
 template <> struct ConvVec<float> {
   static constexpr int N = 4;
-  static __device__ __forceinline__ void load(const float* p, float (&v)[4]) {
-    const float4 t = *reinterpret_cast<const float4*>(p);
+  using Raw = float4;
+  static __device__ __forceinline__ void unpack(const Raw& t, float (&v)[4]) {
     v[0] = t.x; v[1] = t.y; v[2] = t.z; v[3] = t.w;
   }
-  static __device__ __forceinline__ void store(float* p, const float (&v)[4]) {
-    *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
-  }
+  static __device__ __forceinline__ Raw pack(const float (&v)[4]) { return make_float4(v[0], v[1], v[2], v[3]); }
 };
 template <> struct ConvVec<bf16> {
-  static constexpr int N = 8;
-  static __device__ __forceinline__ void load(const bf16* p, float (&v)[8]) {
-    const uint4 t = *reinterpret_cast<const uint4*>(p);
-    const uint32_t w[4] = {t.x, t.y, t.z, t.w};
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      v[2 * i] = __uint_as_float(w[i] << 16);
-      v[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
-    }
+  static constexpr int N = 4;
+  using Raw = uint2;
+  static __device__ __forceinline__ void unpack(const Raw& t, float (&v)[4]) {
+    v[0] = __uint_as_float(t.x << 16); v[1] = __uint_as_float(t.x & 0xffff0000u);
+    v[2] = __uint_as_float(t.y << 16); v[3] = __uint_as_float(t.y & 0xffff0000u);
   }
-  static __device__ __forceinline__ void store(bf16* p, const float (&v)[8]) {
-    uint32_t w[4];
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      const __nv_bfloat162 h = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
-      w[i] = *reinterpret_cast<const uint32_t*>(&h);
-    }
-    *reinterpret_cast<uint4*>(p) = make_uint4(w[0], w[1], w[2], w[3]);
+  static __device__ __forceinline__ Raw pack(const float (&v)[4]) {
+    const __nv_bfloat162 lo = __floats2bfloat162_rn(v[0], v[1]), hi = __floats2bfloat162_rn(v[2], v[3]);
+    return make_uint2(*reinterpret_cast<const uint32_t*>(&lo), *reinterpret_cast<const uint32_t*>(&hi));
   }
 };
 
-template <typename T>
-__global__ void short_conv_strip_kernel(const T* __restrict__ bcx, SmallVec w, const T* __restrict__ state,
-                                        const int* __restrict__ cu_seqlens, const int* __restrict__ seg_start,
-                                        const int* __restrict__ seg_slot, const int* __restrict__ row_seg,
-                                        T* __restrict__ out, int M, int H, int L) {
+template <typename T, int L>
+__global__ void __launch_bounds__(128)
+short_conv_strip_kernel(const T* __restrict__ bcx, SmallVec w, const T* __restrict__ state,
+                        const int* __restrict__ cu_seqlens, const int* __restrict__ seg_start,
+                        const int* __restrict__ seg_slot, const int* __restrict__ row_seg,
+                        T* __restrict__ out, int M, int H) {
   pdl_begin();
   constexpr int VEC = ConvVec<T>::N;
+  using Raw = typename ConvVec<T>::Raw;
   const int c0 = (blockIdx.x * blockDim.x + threadIdx.x) * VEC;
   if (c0 >= H) return;
-  float taps[CONV_FAST_L][VEC];
+  const int m_begin = blockIdx.y * CONV_STRIP;
+  const size_t pitch = 3 * (size_t)H;
+  Raw rb[CONV_STRIP], rc[CONV_STRIP], rx[CONV_STRIP], pb[L - 1], px[L - 1];
+  int sgs[CONV_STRIP];
 #pragma unroll
-  for (int j = 0; j < CONV_FAST_L; ++j)
+  for (int r = 0; r < CONV_STRIP; ++r) {
+    if (m_begin + r < M) {
+      const T* row = bcx + (size_t)(m_begin + r) * pitch + c0;
+      rb[r] = *reinterpret_cast<const Raw*>(row);
+      rc[r] = *reinterpret_cast<const Raw*>(row + H);
+      rx[r] = *reinterpret_cast<const Raw*>(row + 2 * H);
+      sgs[r] = row_seg[m_begin + r];
+    }
+  }
 #pragma unroll
-    for (int e = 0; e < VEC; ++e) taps[j][e] = j < L ? w[(size_t)(c0 + e) * L + j] : 0.f;
-  float hist[CONV_FAST_L - 1][VEC];                  // hist[0] is the oldest of the L-1 values before the row
-  const int m_begin = blockIdx.y * CONV_STRIP, m_end = min(M, m_begin + CONV_STRIP);
+  for (int i = 0; i < L - 1; ++i) {                  // the rows before the strip: used if they are of its segment
+    const int mm = m_begin - (L - 1) + i;
+    if (mm >= 0) {
+      const T* row = bcx + (size_t)mm * pitch + c0;
+      pb[i] = *reinterpret_cast<const Raw*>(row);
+      px[i] = *reinterpret_cast<const Raw*>(row + 2 * H);
+    }
+  }
+  float taps[L][VEC];
+#pragma unroll
+  for (int j = 0; j < L; ++j)
+#pragma unroll
+    for (int e = 0; e < VEC; ++e) taps[j][e] = w[(size_t)(c0 + e) * L + j];
+  float hist[L - 1][VEC];                            // hist[0] is the oldest of the L-1 values before the row
   int seg = -1;
-  for (int m = m_begin; m < m_end; ++m) {
-    const int sg = row_seg[m];
-    const int first = cu_seqlens[sg];
-    const int t = m - first;
-    if (m == m_begin || sg != seg) {                 // (re)build the window: rows of this step, else the state
-      seg = sg;
-      const bool has_state = seg_start[sg] > 0;
-      const T* st = state + (size_t)seg_slot[sg] * (L - 1) * H;
 #pragma unroll
-      for (int i = 0; i < CONV_FAST_L - 1; ++i) {
-        if (i < L - 1) {
+  for (int r = 0; r < CONV_STRIP; ++r) {
+    const int m = m_begin + r;
+    if (m < M) {
+      const int sg = sgs[r];
+      if (r == 0 || sg != seg) {                     // (re)build the window: rows of this step, else the state
+        seg = sg;
+        const int t = m - cu_seqlens[sg];            // > 0 only at r == 0: a new segment starts at t == 0
+        const bool has_state = seg_start[sg] > 0;
+        const T* st = state + (size_t)seg_slot[sg] * (L - 1) * H;
+#pragma unroll
+        for (int i = 0; i < L - 1; ++i) {
           const int s = t - (L - 1) + i;             // index into this step's rows; < 0: history
-          if (s >= 0) {
+          if (s >= 0) {                              // then r == 0 and the row is m_begin - (L-1) + i
             float b[VEC], x[VEC];
-            ConvVec<T>::load(bcx + (size_t)(first + s) * 3 * H + c0, b);
-            ConvVec<T>::load(bcx + (size_t)(first + s) * 3 * H + 2 * H + c0, x);
+            ConvVec<T>::unpack(pb[i], b);
+            ConvVec<T>::unpack(px[i], x);
 #pragma unroll
             for (int e = 0; e < VEC; ++e) hist[i][e] = round_f<T>(b[e] * x[e]);
           } else if (has_state) {
-            ConvVec<T>::load(st + (size_t)(s + L - 1) * H + c0, hist[i]);
+            ConvVec<T>::unpack(*reinterpret_cast<const Raw*>(st + (size_t)(s + L - 1) * H + c0), hist[i]);
           } else {
 #pragma unroll
             for (int e = 0; e < VEC; ++e) hist[i][e] = 0.f;
           }
         }
       }
-    }
-    float b[VEC], cg[VEC], x[VEC], y[VEC];
-    const T* row = bcx + (size_t)m * 3 * H + c0;
-    ConvVec<T>::load(row, b);
-    ConvVec<T>::load(row + H, cg);
-    ConvVec<T>::load(row + 2 * H, x);
+      float b[VEC], cg[VEC], x[VEC], y[VEC];
+      ConvVec<T>::unpack(rb[r], b);
+      ConvVec<T>::unpack(rc[r], cg);
+      ConvVec<T>::unpack(rx[r], x);
 #pragma unroll
-    for (int e = 0; e < VEC; ++e) {
-      const float g = round_f<T>(b[e] * x[e]);
-      float acc = 0.f;                               // taps in order: oldest first, the current token last
+      for (int e = 0; e < VEC; ++e) {
+        const float g = round_f<T>(b[e] * x[e]);
+        float acc = 0.f;                             // taps in order: oldest first, the current token last
 #pragma unroll
-      for (int i = 0; i < CONV_FAST_L - 1; ++i)
-        if (i < L - 1) acc = fmaf(taps[i][e], hist[i][e], acc);
+        for (int i = 0; i < L - 1; ++i) acc = fmaf(taps[i][e], hist[i][e], acc);
+        acc = fmaf(taps[L - 1][e], g, acc);
+        y[e] = cg[e] * acc;
 #pragma unroll
-      for (int j = 0; j < CONV_FAST_L; ++j)
-        if (j == L - 1) acc = fmaf(taps[j][e], g, acc);    // compile-time indices keep the arrays in registers
-      y[e] = cg[e] * acc;
-#pragma unroll
-      for (int i = 0; i < CONV_FAST_L - 1; ++i) {
-        if (i < L - 2) hist[i][e] = hist[i + 1][e];
-        else if (i == L - 2) hist[i][e] = g;
+        for (int i = 0; i < L - 2; ++i) hist[i][e] = hist[i + 1][e];
+        hist[L - 2][e] = g;
       }
+      *reinterpret_cast<Raw*>(out + (size_t)m * H + c0) = ConvVec<T>::pack(y);
     }
-    ConvVec<T>::store(out + (size_t)m * H + c0, y);
   }
 }
 
@@ -241,15 +251,23 @@ SNK_API int snk_short_conv(const void* bcx, const void* w, int w_is_f32, void* s
     return 0;
   }
   SmallVec wv{w, w_is_f32};
-  const int vec = dtype == SNK_F32 ? 4 : 8;
-  const bool aligned = H % vec == 0 && (uintptr_t)bcx % 16 == 0 && (uintptr_t)state % 16 == 0 &&
-                       (uintptr_t)out % 16 == 0;
+  const int vec = 4;                                 // channels per thread: 16 bytes of float, 8 of bfloat16
+  const size_t vbytes = dtype == SNK_F32 ? 16 : 8;
+  const bool aligned = H % vec == 0 && (uintptr_t)bcx % vbytes == 0 && (uintptr_t)state % vbytes == 0 &&
+                       (uintptr_t)out % vbytes == 0;
   if (L >= 2 && L <= CONV_FAST_L && aligned && M >= 4 * CONV_STRIP) {
     dim3 sgrid((H / vec + threads - 1) / threads, (M + CONV_STRIP - 1) / CONV_STRIP);
     if (sgrid.y > 65535u) return SNK_ERR_SIZE;
-    SNK_DISPATCH(dtype, snk_launch(short_conv_strip_kernel<T>, dim3(sgrid), dim3(threads), 0, stream, 
-                            static_cast<const T*>(bcx), wv, static_cast<const T*>(state), cu_seqlens,
-                            seg_start, seg_slot, row_seg, static_cast<T*>(out), M, H, L));
+#define CONV_STRIP_LAUNCH(L_)                                                                          \
+    snk_launch(short_conv_strip_kernel<T, L_>, dim3(sgrid), dim3(threads), 0, stream,                  \
+               static_cast<const T*>(bcx), wv, static_cast<const T*>(state), cu_seqlens, seg_start,    \
+               seg_slot, row_seg, static_cast<T*>(out), M, H)
+    SNK_DISPATCH(dtype, {
+      if (L == 2) CONV_STRIP_LAUNCH(2);
+      else if (L == 3) CONV_STRIP_LAUNCH(3);
+      else CONV_STRIP_LAUNCH(4);
+    });
+#undef CONV_STRIP_LAUNCH
   } else {
     dim3 grid((H + threads - 1) / threads, (M + CONV_ROWS_PER_BLOCK - 1) / CONV_ROWS_PER_BLOCK);
     if (grid.y > 65535u) return SNK_ERR_SIZE;

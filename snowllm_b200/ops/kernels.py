@@ -593,7 +593,9 @@ def gemm_tc(a, w, out_dtype=None, out=None, offsets=None, swiglu=False):
 
 def gemm_tc2(a, w, out_dtype=None, out=None, offsets=None, swiglu=False):
     """As ``gemm_tc``, on pairs of SMs (cta_group::2): 256 x 256 tiles of C, each block of a pair loading
-    its 128 rows of ``a`` and half of the tile's rows of ``w``."""
+    its 128 rows of ``a`` and half of the tile's rows of ``w``.  Grouped (``offsets``): the operands change
+    places, each block loads 128 rows of the group's ``w`` and half of up to 256 of its rows of ``a``, and
+    a group's last tile is as wide as its rows need (a multiple of 16); at most 256 groups."""
     _chk(a, "gemm a", torch.bfloat16)
     _chk(w, "gemm w", torch.bfloat16)
     M, K = a.shape

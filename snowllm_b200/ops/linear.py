@@ -4,7 +4,8 @@ float32: the CUDA-core kernel of csrc/gemm.cu (true 32-bit, sums in k order).
 bfloat16, up to 16 rows (decode; grouped: up to 4 rows per group on average): csrc/gemm_skinny.cu, which
 streams W once into mma.sync fragments.
 bfloat16, more rows (prefill): csrc/gemm_tc.cu, 128 x 256 tiles on the tcgen05 tensor cores with TMA
-loads and the accumulator in tensor memory; from 4,096 rows on csrc/gemm_tc2.cu, the same on pairs of SMs.
+loads and the accumulator in tensor memory; from 4,096 rows on, and for all grouped products, csrc/gemm_tc2.cu
+on pairs of SMs (grouped: W is the 256-row operand and a group's rows the N side, in steps of 16).
 bfloat16 operands that neither takes (K no multiple of 8, unaligned views): the CUDA-core kernel.
 (the role of snowllm/models/projection.py:27-35)
 """
@@ -18,17 +19,18 @@ from . import kernels
 
 # Products of very many rows run on pairs of SMs (csrc/gemm_tc2.cu: 256 x 256 tiles, a third less operand traffic).
 # Measured against the one-SM kernel: 2,048 rows no gain (the launch is short; tile rounds and the epilogue
-# decide), 4,096 rows +6 %, 8,192 rows +7 %, 32,768 sorted rows over 32 experts +7 %.
+# decide), 4,096 rows +6 %, 8,192 rows +7 %.  Grouped (32 experts, top 4): the 2,048-token prefill step
+# 9.78 -> 9.38 ms, the 64-request decode step 5.90 -> 5.58 ms against the one-SM kernel's 128-row tiles.
 TC_PAIRS = os.environ.get("SNOWLLM_B200_TC_PAIRS", "1") != "0"
 PAIRS_MIN_ROWS = 4096             # plain products
-PAIRS_MIN_GROUP_ROWS = 512        # grouped: rows per group on average (a group's rows are cut into 256-row tiles)
+PAIRS_MAX_GROUPS = 256            # grouped products always run on pairs (a group's rows are the N side of the MMA)
 
 
 def _tc(x, w, **kw):
     """The tcgen05 product: on pairs of SMs where there are rows enough."""
     offsets = kw.get("offsets")
     rows = x.shape[0]
-    if TC_PAIRS and rows >= PAIRS_MIN_ROWS and (offsets is None or rows >= PAIRS_MIN_GROUP_ROWS * w.shape[0]):
+    if TC_PAIRS and (rows >= PAIRS_MIN_ROWS if offsets is None else w.shape[0] <= PAIRS_MAX_GROUPS):
         return kernels.gemm_tc2(x, w, **kw)
     return kernels.gemm_tc(x, w, **kw)
 

@@ -4,6 +4,8 @@
     python -m snowllm_b200.ops.microbench gemm_tc --m 2048 --n 6144 --k 2048
     python -m snowllm_b200.ops.microbench attention_decode --batch 8 --context 8192
     python -m snowllm_b200.ops.microbench attention_prefill --tokens 2048
+    python -m snowllm_b200.ops.microbench short_conv --tokens 2048 --n 2048
+    python -m snowllm_b200.ops.microbench qk_norm_rope --tokens 2048
 
 Prints one JSON line: microseconds per launch (CUDA events around ``--iters`` launches after 3 warm-up
 launches, a buffer larger than L2 written between launches) and the achieved GB/s or TFLOP/s from the
@@ -73,7 +75,11 @@ def gemm_tc(a):
     if G > 1:
         w = bf16(G, a.n, a.k, scale=a.k ** -0.5, gen=gen)
         per = a.m // G
-        offsets = torch.arange(0, G + 1, dtype=torch.int32, device="cuda") * per
+        if a.ragged:                              # rows dealt to the groups at random, as a router does
+            counts = torch.bincount(torch.randint(0, G, (per * G,), generator=torch.Generator().manual_seed(1)), minlength=G)
+            offsets = torch.cat((torch.zeros(1, dtype=torch.int64), counts.cumsum(0))).to(torch.int32).cuda()
+        else:
+            offsets = torch.arange(0, G + 1, dtype=torch.int32, device="cuda") * per
         x = bf16(per * G, a.k, gen=gen)
         fn = lambda: product(x, w, offsets=offsets, out_dtype=torch.float32 if a.f32 else None, swiglu=a.swiglu)
         flops = 2.0 * per * G * a.n * a.k
@@ -130,7 +136,46 @@ def attention_prefill(a):
     return {"us": us, "TFLOP/s": flops / us / 1e6, "flops": flops}
 
 
-KINDS = {"gemm_skinny": gemm_skinny, "gemm_tc": gemm_tc, "attention_decode": attention_decode,
+def short_conv(a):
+    """The gated short convolution over one fresh segment of --tokens rows, hidden size --n, --taps taps."""
+    gen = torch.Generator(device="cuda").manual_seed(0)
+    M, H, L = a.tokens, a.n, a.taps
+    sets = 6                                              # distinct inputs in turn: each launch reads cold rows
+    bcx = [bf16(M, 3 * H, gen=gen) for _ in range(sets)]
+    w = bf16(H, L, gen=gen)
+    state = torch.zeros(2, L - 1, H, dtype=torch.bfloat16, device="cuda")
+    i32 = lambda v: torch.tensor(v, dtype=torch.int32, device="cuda")
+    cu, start, slot, row_seg = i32([0, M]), i32([0]), i32([0]), torch.zeros(M, dtype=torch.int32, device="cuda")
+    out = torch.empty(M, H, dtype=torch.bfloat16, device="cuda")
+    turn = [0]
+
+    def fn():
+        turn[0] += 1
+        kernels.short_conv(bcx[turn[0] % sets], w, state, cu, start, slot, row_seg, out=out)
+    nbytes = M * H * 2 * 4
+    us = timed(fn, a.iters)
+    return {"us": us, "GB/s": nbytes / us / 1e3, "bytes": nbytes}
+
+
+def qk_norm_rope(a):
+    """Per-head q/k RMSNorm, rotary encoding and the cache write over --tokens rows of one fresh request."""
+    gen = torch.Generator(device="cuda").manual_seed(0)
+    M, nh, nkv, hd, P = a.tokens, a.heads, a.kv_heads, a.head_dim, a.page_size
+    qkv = bf16(M, (nh + 2 * nkv) * hd, gen=gen)
+    g = torch.ones(hd, dtype=torch.bfloat16, device="cuda")
+    inv = 1.0 / (10000.0 ** (torch.arange(0, hd, 2, dtype=torch.float32, device="cuda") / hd))
+    pages = -(-M // P)
+    pool = torch.zeros(pages, 2, nkv, P, hd, dtype=torch.bfloat16, device="cuda")
+    bt = torch.arange(pages, dtype=torch.int32, device="cuda").view(1, pages)
+    pos = torch.arange(M, dtype=torch.int32, device="cuda")
+    seg = torch.zeros(M, dtype=torch.int32, device="cuda")
+    fn = lambda: kernels.qk_norm_rope_cache(qkv, g, g, 1e-5, inv, hd, pos, seg, bt, P, pool, nh, nkv, hd)
+    nbytes = M * (nh + 2 * nkv) * hd * 2 * 2
+    us = timed(fn, a.iters)
+    return {"us": us, "GB/s": nbytes / us / 1e3, "bytes": nbytes}
+
+
+KINDS = {"short_conv": short_conv, "qk_norm_rope": qk_norm_rope, "gemm_skinny": gemm_skinny, "gemm_tc": gemm_tc, "attention_decode": attention_decode,
          "attention_prefill": attention_prefill}
 
 
@@ -144,10 +189,12 @@ def main(argv=None) -> int:
     ap.add_argument("--active", type=int, default=0, help="groups that own rows (gemm_skinny)")
     ap.add_argument("--f32", action="store_true", help="float32 output")
     ap.add_argument("--swiglu", action="store_true", help="SwiGLU at the store (w rows interleaved by 8)")
+    ap.add_argument("--ragged", action="store_true", help="gemm_tc with --groups: random rows per group, not m / groups")
     ap.add_argument("--pairs", action="store_true", help="gemm_tc: the kernel on pairs of SMs (cta_group::2)")
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--context", type=int, default=8192)
     ap.add_argument("--tokens", type=int, default=2048)
+    ap.add_argument("--taps", type=int, default=3, help="short_conv: kernel length")
     ap.add_argument("--heads", type=int, default=32)
     ap.add_argument("--kv-heads", type=int, default=8)
     ap.add_argument("--head-dim", type=int, default=64)

@@ -91,7 +91,8 @@ def make_pool(dtype, pages, nkv, P, hd):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("nh,nkv,hd,rot", [(5, 5, 48, 48), (6, 2, 80, 80), (3, 1, 128, 64), (2, 1, 16, 16)])
+@pytest.mark.parametrize("nh,nkv,hd,rot", [(5, 5, 48, 48), (6, 2, 80, 80), (3, 1, 128, 64), (2, 1, 16, 16),
+                                           (7, 2, 64, 64), (4, 2, 128, 128), (3, 1, 256, 256), (9, 3, 32, 32)])
 def test_qk_norm_rope_cache(K, dtype, nh, nkv, hd, rot):
     torch.manual_seed(3)
     P, pages, eps, theta = 8, 16, 1e-6, 1234.5
@@ -142,6 +143,27 @@ def test_qk_norm_rope_without_norm_or_rope_and_q_only(K):
     q2 = K.qk_norm_rope_cache(dev(qkv[:, :nh * hd].contiguous()), None, None, 0.0, None, 0, i32([0, 1, 2]),
                               i32([0, 0, 0]), i32([[1]]), P, pool, nh, nkv, hd, write_kv=False)
     assert torch.equal(q2.cpu(), q.cpu()) and torch.equal(pool, before)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("nh,nkv,hd", [(7, 2, 64), (5, 5, 48)])
+def test_qk_norm_rope_rows_do_not_depend_on_the_batch(K, dtype, nh, nkv, hd):
+    """A portion of 90 rows (one block per row) and the same rows three at a time (a row's heads spread over
+    blocks) give the same bits: q, and the keys and values in the pages."""
+    torch.manual_seed(4)
+    M, P, eps = 90, 16, 1e-5
+    qkv = dev(rnd(dtype, M, (nh + 2 * nkv) * hd), dtype)
+    qg, kg = dev(rnd(dtype, hd) + 1.0, dtype), dev(rnd(dtype, hd) + 1.0, dtype)
+    inv_freq = dev(1.0 / (1e6 ** (torch.arange(0, hd, 2, dtype=torch.float32) / hd)))
+    positions = list(range(1000, 1000 + M))
+    pages = (1000 + M) // P + 1
+    table = i32([list(range(pages))[::-1]])
+    pool_a, pool_b = make_pool(dtype, pages, nkv, P, hd), make_pool(dtype, pages, nkv, P, hd)
+    seg = i32([0] * M)
+    qa = K.qk_norm_rope_cache(qkv, qg, kg, eps, inv_freq, hd, i32(positions), seg, table, P, pool_a, nh, nkv, hd)
+    qb = torch.cat([K.qk_norm_rope_cache(qkv[i:i + 3].contiguous(), qg, kg, eps, inv_freq, hd, i32(positions[i:i + 3]),
+                                         i32([0] * 3), table, P, pool_b, nh, nkv, hd) for i in range(0, M, 3)])
+    assert torch.equal(qa, qb) and torch.equal(pool_a, pool_b)
 
 
 # ---------------------------------------------------------------------------------------------
@@ -618,6 +640,34 @@ def test_gemm_tc2_pairs_of_sms(K, M, N, K_):
             r = slice(offsets[e], offsets[e + 1])
             if c:
                 close(out[r], a[r] @ wg[e].T, torch.float32, scale=math.sqrt(K_))
+    assert K.gemm_tc2_status()[0] == 0
+
+
+@pytest.mark.parametrize("N,K_", [(256, 64), (520, 200), (96, 2048), (1792, 72)])
+def test_gemm_tc2_grouped_rows_on_the_n_side(K, N, K_):
+    """The grouped product on pairs of SMs, where a group's rows are the N side of the MMA in steps of 16:
+    groups of no, one, 16, 17, 255, 256, 257 and 530 rows; to float, to bfloat16 and with SwiGLU at the store."""
+    from snowllm_b200.ops import interleave_gate_up
+    torch.manual_seed(35)
+    dtype = torch.bfloat16
+    counts = [270, 0, 1, 16, 17, 255, 0, 256, 257, 530, 100, 31]
+    offsets = [0]
+    for c in counts:
+        offsets.append(offsets[-1] + c)
+    M, G = offsets[-1], len(counts)
+    a, wg = rnd(dtype, M, K_), rnd(dtype, G, N, K_)
+    want = torch.cat([a[offsets[e]:offsets[e + 1]] @ wg[e].T for e in range(G)])
+    out = torch.full((M, N), float("nan"), dtype=torch.float32, device="cuda")
+    K.gemm_tc2(dev(a, dtype), dev(wg, dtype), out_dtype=torch.float32, offsets=i32(offsets), out=out)
+    assert K.gemm_tc2_status()[0] == 0
+    close(out, want, torch.float32, scale=math.sqrt(K_))
+    close(K.gemm_tc2(dev(a, dtype), dev(wg, dtype), offsets=i32(offsets)), want, dtype, scale=math.sqrt(K_) / 4)
+    I = (N // 16) * 8
+    gate, up = rnd(dtype, G, I, K_, scale=K_ ** -0.5), rnd(dtype, G, I, K_, scale=K_ ** -0.5)
+    act = K.gemm_tc2(dev(a, dtype), interleave_gate_up(dev(gate, dtype), dev(up, dtype)), offsets=i32(offsets), swiglu=True)
+    want_act = torch.cat([F.silu(a[offsets[e]:offsets[e + 1]] @ gate[e].T) * (a[offsets[e]:offsets[e + 1]] @ up[e].T)
+                          for e in range(G)])
+    close(act, want_act, dtype, scale=2)
     assert K.gemm_tc2_status()[0] == 0
 
 
