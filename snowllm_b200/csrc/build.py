@@ -27,7 +27,7 @@ HERE = pathlib.Path(__file__).resolve().parent
 ARCH_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a"]
 NVCC_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "--shared", "-Xcompiler", "-fPIC",
               "-Xcompiler", "-fvisibility=hidden"]
-LIBRARIES = ("elementwise", "rope_cache", "short_conv", "attention", "attention_mma", "gemm", "gemm_skinny", "gemm_tc", "gemm_tc2", "moe", "sampling")
+LIBRARIES = ("elementwise", "rope_cache", "short_conv", "attention", "attention_mma", "attention_tc", "gemm", "gemm_skinny", "gemm_tc", "gemm_tc2", "moe", "sampling")
 EXTRA_LINK: dict[str, list[str]] = {}
 # more nvcc flags from the environment (-D switches of an experiment); they enter the library's hash
 ENV_FLAGS = os.environ.get("SNOWLLM_B200_NVCC_FLAGS", "").split()

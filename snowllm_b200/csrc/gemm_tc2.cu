@@ -68,8 +68,8 @@ struct T2Tile {
   bool valid;
 };
 
-// Pair tile `tile`: 256 rows x 256 columns; grouped: row tiles counted group by group.
-__device__ __forceinline__ T2Tile t2_tile(int tile, int row_tiles, int M, int N, const int* offsets, int groups) {
+// Pair tile `tile`: 256 rows x 256 columns.
+__device__ __forceinline__ T2Tile t2_tile(int tile, int row_tiles, int M, int N) {
   T2Tile t;
   // bands of up to T2_BAND n-tiles, the n-tile fastest inside a band, then the row tile (as in gemm_tc.cu)
   const int n_tiles = (N + T2_BN - 1) / T2_BN;
@@ -81,36 +81,16 @@ __device__ __forceinline__ T2Tile t2_tile(int tile, int row_tiles, int M, int N,
   const int rt = in_band / w_here, nt = band * band_w + in_band % w_here;
   t.n0 = nt * T2_BN;
   t.valid = t.n0 < N;
-  if (!offsets) {
-    t.row0 = rt * 2 * T2_BM;
-    t.row_end = M;
-    t.w_row0 = 0;
-    return t;
-  }
-  int left = rt;
-  t.valid = false;
-  t.row0 = t.row_end = t.w_row0 = 0;
-  if (t.n0 >= N) return t;
-  for (int e = 0; e < groups; ++e) {
-    const int begin = offsets[e], cnt = offsets[e + 1] - begin;
-    const int tiles_e = (cnt + 2 * T2_BM - 1) / (2 * T2_BM);
-    if (left < tiles_e) {
-      t.row0 = begin + left * 2 * T2_BM;
-      t.row_end = begin + cnt;
-      t.w_row0 = e * N;
-      t.valid = true;
-      return t;
-    }
-    left -= tiles_e;
-  }
+  t.row0 = rt * 2 * T2_BM;
+  t.row_end = M;
+  t.w_row0 = 0;
   return t;
 }
 
 template <typename OutT, bool SWIGLU>
 __global__ void __launch_bounds__(T2_THREADS)
 gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
-                OutT* __restrict__ C, int M, int N, int K, const int* __restrict__ offsets, int groups,
-                int row_tiles_bound) {
+                OutT* __restrict__ C, int M, int N, int K, int row_tiles) {
   extern __shared__ unsigned char smem_raw[];
   unsigned char* tiles = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   T2Shared* sh = reinterpret_cast<T2Shared*>(tiles + (size_t)T2_STAGES * T2_STAGE_BYTES);
@@ -146,11 +126,6 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
   if (pair == 0 && threadIdx.x == 0) g_t2_tmem[rank] = sh->tmem_base;
   volatile int* aborted = &sh->aborted;
   pdl_begin();
-  int row_tiles = row_tiles_bound;
-  if (offsets) {
-    row_tiles = 0;
-    for (int e = 0; e < groups; ++e) row_tiles += (offsets[e + 1] - offsets[e] + 2 * T2_BM - 1) / (2 * T2_BM);
-  }
   const int n_tiles = (N + T2_BN - 1) / T2_BN;
   const int total = row_tiles * n_tiles;
 
@@ -158,7 +133,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     if (lane == 0) {
       int it = 0;
       for (int tile = pair; tile < total; tile += pairs) {
-        const T2Tile t = t2_tile(tile, row_tiles, M, N, offsets, groups);
+        const T2Tile t = t2_tile(tile, row_tiles, M, N);
         if (!t.valid) continue;
         for (int kt = 0; kt < k_tiles; ++kt, ++it) {
           const int s = it % T2_STAGES;
@@ -177,7 +152,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
       const uint32_t idesc = instr_desc_bf16(2 * T2_BM, T2_BN);
       int it = 0, local = 0;
       for (int tile = pair; tile < total; tile += pairs) {
-        const T2Tile t = t2_tile(tile, row_tiles, M, N, offsets, groups);
+        const T2Tile t = t2_tile(tile, row_tiles, M, N);
         if (!t.valid) continue;
         const int buf = local % T2_ACC_BUFFERS;
         const int use = local / T2_ACC_BUFFERS;          // how often this accumulator was used before
@@ -205,7 +180,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     float* stage_out = sh->stage_out[warp - 2];
     int local = 0;
     for (int tile = pair; tile < total; tile += pairs) {
-      const T2Tile t = t2_tile(tile, row_tiles, M, N, offsets, groups);
+      const T2Tile t = t2_tile(tile, row_tiles, M, N);
       if (!t.valid) continue;
       const int buf = local % T2_ACC_BUFFERS;
       const int use = local / T2_ACC_BUFFERS;
@@ -241,7 +216,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
 
 template <typename OutT, bool SWIGLU>
 static int launch_tc2(const CUtensorMap& map_a, const CUtensorMap& map_w, void* C, int M, int N, int K,
-                      const int* offsets, int groups, int row_tiles, cudaStream_t stream) {
+                      int row_tiles, cudaStream_t stream) {
   const size_t smem = 1024 + (size_t)T2_STAGES * T2_STAGE_BYTES + sizeof(T2Shared);
   static int sms = 0;
   if (sms == 0) {
@@ -253,7 +228,7 @@ static int launch_tc2(const CUtensorMap& map_a, const CUtensorMap& map_w, void* 
   const long long tiles = (long long)row_tiles * ((N + T2_BN - 1) / T2_BN);
   const int pairs = (int)(tiles < sms / 2 ? tiles : sms / 2);
   snk_launch_cluster3(gemm_tc2_kernel<OutT, SWIGLU>, dim3(2 * pairs), dim3(T2_THREADS), smem, stream, dim3(2, 1, 1),
-                      map_a, map_w, static_cast<OutT*>(C), M, N, K, offsets, groups, row_tiles);
+                      map_a, map_w, static_cast<OutT*>(C), M, N, K, row_tiles);
   SNK_LAUNCH_CHECK();
   return 0;
 }
@@ -494,10 +469,9 @@ static int launch_tc2_grouped(const T2GMaps& maps, const CUtensorMap& map_w, voi
   return 0;
 }
 
-// M: rows of A (all groups together).  Grouped: offsets[groups+1] on the device, W = [groups, N, K];
-// max_row_tiles bounds the number of 256-row tiles over all groups (M/256 + groups is always enough).
+// M: rows of A (all groups together).  Grouped: offsets[groups+1] on the device, W = [groups, N, K].
 SNK_API int snk_gemm_tc2(const void* A, const void* W, void* C, int M, int N, int K, const int* offsets,
-                         int groups, int max_row_tiles, int out_f32, int swiglu, cudaStream_t stream) {
+                         int groups, int out_f32, int swiglu, cudaStream_t stream) {
   if (M <= 0 || N <= 0) return 0;
   if (K <= 0 || K % 8) return SNK_ERR_SIZE;
   if (swiglu && (N % 16 || out_f32)) return SNK_ERR_SIZE;
@@ -516,16 +490,16 @@ SNK_API int snk_gemm_tc2(const void* A, const void* W, void* C, int M, int N, in
     if (out_f32) return launch_tc2_grouped<float, false>(maps, gw, C, M, N, K, offsets, groups, stream);
     return launch_tc2_grouped<bf16, false>(maps, gw, C, M, N, K, offsets, groups, stream);
   }
-  const int row_tiles = offsets ? max_row_tiles : (M + 2 * T2_BM - 1) / (2 * T2_BM);
+  const int row_tiles = (M + 2 * T2_BM - 1) / (2 * T2_BM);
   if (row_tiles <= 0) return SNK_ERR_SIZE;
   CUtensorMap map_a, map_w;
   int rc = tensor_map(A, M, K, T2_BM, T2_BK, &map_a);
   if (rc) return rc;
-  rc = tensor_map(W, (long long)(offsets ? groups : 1) * N, K, T2_BN / 2, T2_BK, &map_w);
+  rc = tensor_map(W, N, K, T2_BN / 2, T2_BK, &map_w);
   if (rc) return rc;
-  if (swiglu) return launch_tc2<bf16, true>(map_a, map_w, C, M, N, K, offsets, groups, row_tiles, stream);
-  if (out_f32) return launch_tc2<float, false>(map_a, map_w, C, M, N, K, offsets, groups, row_tiles, stream);
-  return launch_tc2<bf16, false>(map_a, map_w, C, M, N, K, offsets, groups, row_tiles, stream);
+  if (swiglu) return launch_tc2<bf16, true>(map_a, map_w, C, M, N, K, row_tiles, stream);
+  if (out_f32) return launch_tc2<float, false>(map_a, map_w, C, M, N, K, row_tiles, stream);
+  return launch_tc2<bf16, false>(map_a, map_w, C, M, N, K, row_tiles, stream);
 }
 
 // 0, or the first error a block of any earlier launch recorded (a wait that ran out); reading clears it.

@@ -37,7 +37,7 @@ class StepContext:
     host_seg_start: list = field(default_factory=list)
     host_seg_len: list = field(default_factory=list)
     _plans: dict = field(default_factory=dict)
-    _split: tuple | None = None
+    _split: dict = field(default_factory=dict)   # tile rows -> (tiles, other rows, host list of them)
     fixed_chunks: int | None = None  # a captured step: the key-chunk count its launches were built for
     taps: list | None = None       # when a list: parts append (name, tensor) of chosen intermediates
     pending_tokens: torch.Tensor | None = None   # int32 on the device: a token id -(i + 1) stands for entry i
@@ -53,7 +53,7 @@ class StepContext:
     def attention_split(self, tile_rows: int):
         """(tiles int32 [n, 4] | None, other rows int32 [m] | None, host list of the other rows) for
         the prompt kernel and the row-wise kernel; uploaded once per step."""
-        if self._split is None:
+        if tile_rows not in self._split:
             tiles, rows = prefill_tiles(self.host_seg_start, self.host_seg_len, tile_rows)
             dev_tiles = dev_rows = None
             if tiles:
@@ -62,8 +62,8 @@ class StepContext:
                 both = both.pin_memory().to(self.device, non_blocking=True)
                 dev_tiles = both[:flat.numel()].view(-1, 4)
                 dev_rows = both[flat.numel():] if rows else None
-            self._split = (dev_tiles, dev_rows, rows)
-        return self._split
+            self._split[tile_rows] = (dev_tiles, dev_rows, rows)
+        return self._split[tile_rows]
 
     def attention_chunks(self, window=None, rows=None, chunk: int = ATTENTION_CHUNK) -> int:
         """The most chunks of ``chunk`` keys that a row (of ``rows``, or of the step) spans."""

@@ -45,6 +45,10 @@ _SIGNATURES = {
         "snk_attention_decode_tma": [P, P, LL, P, I, I, P, P, P, P, P, I, I, I, I, I, I, F, P],
         "snk_attention_decode_status": [],
     },
+    "attention_tc": {
+        "snk_attention_prefill_tc": [P, LL, P, LL, P, I, I, P, I, P, I, I, I, I, F, P],
+        "snk_attention_tc_status": [],
+    },
     "gemm": {
         "snk_gemm_simt": [P, P, P, I, I, I, P, I, P, I, I, I, I, P],
     },
@@ -58,7 +62,7 @@ _SIGNATURES = {
         "snk_gather_rows_bf16": [P, P, P, I, I, I, P],
     },
     "gemm_tc2": {
-        "snk_gemm_tc2": [P, P, P, I, I, I, P, I, I, I, I, P],
+        "snk_gemm_tc2": [P, P, P, I, I, I, P, I, I, I, P],
         "snk_gemm_tc2_status": [P],
     },
     "moe": {
@@ -383,6 +387,40 @@ def attention_prefill(q, pool, block_table, page_size, tiles, scale, out, window
     return out
 
 
+PREFILL_TC_TILE_ROWS = 128
+PREFILL_TC = os.environ.get("SNOWLLM_B200_PREFILL_TC", "1") != "0"
+
+
+def attention_prefill_tc_ok(q, page_size: int) -> bool:
+    """Whether the tcgen05 prompt kernel (csrc/attention_tc.cu) takes this q [M, heads, head_dim] and page size."""
+    return (PREFILL_TC and q.dtype == torch.bfloat16 and q.shape[2] == 64
+            and page_size in (8, 16, 32, 64, 128))
+
+
+def attention_prefill_tc(q, pool, block_table, page_size, tiles, scale, out, window=None):
+    """Causal attention for prompt portions on the tcgen05 tensor cores: ``tiles`` int32 [n, 4] = (segment,
+    first row, rows <= 128, position of the first row); writes those rows of ``out`` [M, heads*64]."""
+    M, nh, hd = q.shape
+    _chk(q, "q", torch.bfloat16)
+    _chk(pool, "kv pool", torch.bfloat16)
+    _chk(tiles, "attention tiles", torch.int32)
+    _chk(block_table, "block table", torch.int32)
+    _chk(out, "attention output", torch.bfloat16, (M, nh * hd))
+    if tiles.dim() != 2 or tiles.shape[1] != 4:
+        raise KernelError("attention tiles must be [n, 4]")
+    check(fn("snk_attention_prefill_tc")(
+        _ptr(q), M, _ptr(pool), pool.shape[0], _ptr(block_table), block_table.shape[1], page_size, _ptr(tiles),
+        tiles.shape[0], _ptr(out), nh, pool.shape[2], hd, int(window or 0), float(scale), _stream()),
+        "attention_prefill_tc")
+    return out
+
+
+def attention_tc_status() -> int:
+    """0, or the code of a wait that ran out inside the tcgen05 prompt kernel since the last call (clears it;
+    synchronises the device)."""
+    return int(fn("snk_attention_tc_status")())
+
+
 DECODE_MMA_CHUNK = 256
 DECODE_MMA_MAX_GROUP = 16
 
@@ -615,8 +653,7 @@ def gemm_tc2(a, w, out_dtype=None, out=None, offsets=None, swiglu=False):
     _chk(out, "gemm out", out_dtype, (M, cols))
     if out_dtype not in (torch.bfloat16, torch.float32) or (swiglu and out_dtype != torch.bfloat16):
         raise KernelError("gemm output is bfloat16 or float32 (bfloat16 with swiglu)")
-    row_tiles = -(-M // (2 * TC_TILE)) + (G if grouped else 0)
-    check(fn("snk_gemm_tc2")(_ptr(a), _ptr(w), _ptr(out), M, N, K, _ptr(offsets), G, row_tiles,
+    check(fn("snk_gemm_tc2")(_ptr(a), _ptr(w), _ptr(out), M, N, K, _ptr(offsets), G,
                              int(out_dtype == torch.float32), int(swiglu), _stream()), "gemm_tc2")
     return out
 

@@ -127,10 +127,14 @@ def attention_prefill(a):
     from ..engine.context import prefill_tiles
     pool, bt, gen = _cache(a, a.tokens, 1)
     q = bf16(a.tokens, a.heads, a.head_dim, gen=gen)
-    tiles, _ = prefill_tiles([0], [a.tokens], kernels.PREFILL_TILE_ROWS)
+    tc = not a.rowwise and kernels.attention_prefill_tc_ok(q, a.page_size)       # --rowwise: the mma.sync kernel
+    tiles, _ = prefill_tiles([0], [a.tokens], kernels.PREFILL_TC_TILE_ROWS if tc else kernels.PREFILL_TILE_ROWS)
     tiles = torch.tensor(tiles, dtype=torch.int32, device="cuda")
     out = torch.empty(a.tokens, a.heads * a.head_dim, dtype=torch.bfloat16, device="cuda")
-    fn = lambda: kernels.attention_prefill(q, pool, bt, a.page_size, tiles, a.head_dim ** -0.5, out)
+    if tc:
+        fn = lambda: kernels.attention_prefill_tc(q, pool, bt, a.page_size, tiles, a.head_dim ** -0.5, out)
+    else:
+        fn = lambda: kernels.attention_prefill(q, pool, bt, a.page_size, tiles, a.head_dim ** -0.5, out)
     flops = 4.0 * a.heads * a.head_dim * a.tokens * (a.tokens + 1) / 2
     us = timed(fn, a.iters)
     return {"us": us, "TFLOP/s": flops / us / 1e6, "flops": flops}
@@ -200,7 +204,7 @@ def main(argv=None) -> int:
     ap.add_argument("--head-dim", type=int, default=64)
     ap.add_argument("--page-size", type=int, default=16)
     ap.add_argument("--chunk", type=int, default=256)
-    ap.add_argument("--rowwise", action="store_true", help="attention_decode: the CUDA-core kernel")
+    ap.add_argument("--rowwise", action="store_true", help="attention_decode: the CUDA-core kernel; attention_prefill: the mma.sync kernel")
     ap.add_argument("--iters", type=int, default=20)
     a = ap.parse_args(argv)
     out = {"kernel": a.kind, **{k: v for k, v in vars(a).items() if k != "kind"}}

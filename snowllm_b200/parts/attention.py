@@ -20,7 +20,7 @@ from .spec import INIT_ONES, KEEP_SMALL, PagedKVSpec, TensorSpec
 
 
 class Attention(Part):
-    libraries = ("gemm", "gemm_skinny", "gemm_tc", "gemm_tc2", "rope_cache", "attention", "attention_mma")
+    libraries = ("gemm", "gemm_skinny", "gemm_tc", "gemm_tc2", "rope_cache", "attention", "attention_mma", "attention_tc")
 
     def __init__(self, dtype, names, *, hidden_size: int, num_heads: int, num_kv_heads: int,
                  head_dim: int, qk_norm_eps: float | None, position: dict, window: int | None = None,
@@ -72,9 +72,14 @@ class Attention(Part):
         rows = rows_host = None
         if kernels.attention_prefill_ok(q) and max(ctx.host_seg_len) >= PREFILL_MIN_ROWS:
             # prompt portions on the tensor cores; rows of short segments (decoded tokens) row by row
-            tiles, rows, rows_host = ctx.attention_split(kernels.PREFILL_TILE_ROWS)
-            kernels.attention_prefill(q, cache.pool, cache.block_table, cache.page_size, tiles, self.scale, o,
-                                      window=self.window)
+            if kernels.attention_prefill_tc_ok(q, cache.page_size):
+                tiles, rows, rows_host = ctx.attention_split(kernels.PREFILL_TC_TILE_ROWS)
+                kernels.attention_prefill_tc(q, cache.pool, cache.block_table, cache.page_size, tiles, self.scale,
+                                             o, window=self.window)
+            else:
+                tiles, rows, rows_host = ctx.attention_split(kernels.PREFILL_TILE_ROWS)
+                kernels.attention_prefill(q, cache.pool, cache.block_table, cache.page_size, tiles, self.scale, o,
+                                          window=self.window)
             if not rows_host:
                 return linear(o, self.wo, out_dtype=torch.float32)
         served = ctx.M if rows_host is None else len(rows_host)

@@ -773,6 +773,77 @@ def test_attention_prefill_tiles(K, nh, nkv, hd, P, window):
     assert float(other[untouched].abs().max()) == 0.0
 
 
+@pytest.mark.parametrize("nh,nkv,P,window", [(4, 2, 16, None), (2, 2, 64, None), (4, 2, 16, 100), (3, 1, 8, 37),
+                                             (2, 1, 128, None), (2, 2, 32, 170), (6, 3, 16, 300)])
+def test_attention_prefill_tc_tiles(K, nh, nkv, P, window):
+    """The tcgen05 prompt kernel (head size 64): a portion from position 0, one in the middle of a long request
+    (not aligned to tiles or pages), a short one; pages scattered; unwritten cache entries are NaN."""
+    from snowllm_b200.engine.context import prefill_tiles
+    torch.manual_seed(42)
+    dtype, hd = torch.bfloat16, 64
+    starts, lens = [0, 333, 700], [300, 150, 17]
+    totals = [s + n for s, n in zip(starts, lens)]
+    pages = sum(-(-n // P) for n in totals) + 2
+    perm = torch.randperm(pages).tolist()
+    pool = torch.full((pages, 2, nkv, P, hd), float("nan"), dtype=dtype, device="cuda")
+    tables, ks, vs = [], [], []
+    for n in totals:
+        need = -(-n // P)
+        table, perm = perm[:need], perm[need:]
+        k, v = rnd(dtype, n, nkv, hd), rnd(dtype, n, nkv, hd)
+        scatter_kv(pool, k, v, table, P)
+        tables.append(table)
+        ks.append(k)
+        vs.append(v)
+    width = max(len(t) for t in tables)
+    bt = i32([t + [0] * (width - len(t)) for t in tables])
+    tiles, rest = prefill_tiles(starts, lens, K.PREFILL_TC_TILE_ROWS)
+    assert not rest and len(tiles) == 3 + 2 + 1
+    M = sum(lens)
+    q = rnd(dtype, M, nh, hd)
+    out = torch.full((M, nh * hd), float("nan"), dtype=dtype, device="cuda")
+    assert K.attention_prefill_tc_ok(dev(q, dtype), P)
+    K.attention_prefill_tc(dev(q, dtype), pool, bt, P, i32(tiles), hd ** -0.5, out, window=window)
+    assert K.attention_tc_status() == 0
+    assert out.isfinite().all(), "a row was not written, or an unwritten cache entry was read"
+    first = 0
+    for b in range(3):
+        rows = list(range(starts[b], totals[b]))
+        want = ref_attention(q[first:first + lens[b]], ks[b], vs[b], rows, hd ** -0.5, window)
+        close(out[first:first + lens[b]], want, dtype)
+        first += lens[b]
+    # rows do not depend on the tile they are in: the same rows in tiles of other sizes give the same bits
+    other_tiles = [[b, f + r, min(48, n - r), s + r] for b, (f, n, s) in enumerate(zip([0, 300, 450], lens, starts))
+                   for r in range(0, n, 48)]
+    again = torch.full((M, nh * hd), float("nan"), dtype=dtype, device="cuda")
+    K.attention_prefill_tc(dev(q, dtype), pool, bt, P, i32(other_tiles), hd ** -0.5, again, window=window)
+    assert torch.equal(again, out)
+    assert K.attention_tc_status() == 0
+
+
+def test_attention_prefill_tc_far_key_and_diagonal(K):
+    """As the next test, on the tcgen05 kernel: a key far back stands out for the last row, every row's own key
+    for itself."""
+    torch.manual_seed(41)
+    dtype, nh, nkv, hd, P, T = torch.bfloat16, 2, 1, 64, 16, 640
+    k, v = rnd(dtype, T, nkv, hd, scale=0.05), rnd(dtype, T, nkv, hd)
+    q = rnd(dtype, T, nh, hd, scale=0.05)
+    direction = F.normalize(torch.randn(hd), dim=0)
+    k[7, 0] = (direction * 16).to(dtype).float()
+    q[T - 1] = (direction * 16).to(dtype).float()
+    table = torch.randperm(T // P).tolist()
+    pool = make_pool(dtype, len(table), nkv, P, hd)
+    scatter_kv(pool, k, v, table, P)
+    tiles = [[0, r, min(128, T - r), r] for r in range(0, T, 128)]
+    out = torch.zeros(T, nh * hd, dtype=dtype, device="cuda")
+    K.attention_prefill_tc(dev(q, dtype), pool, i32([table]), P, i32(tiles), hd ** -0.5, out)
+    assert K.attention_tc_status() == 0
+    got = out.float().cpu()
+    assert (got[T - 1] - v[7, 0].repeat(nh)).abs().max() < 0.02
+    close(got, ref_attention(q, k, v, list(range(T)), hd ** -0.5, None), dtype)
+    assert torch.allclose(got[0], v[0, 0].repeat(nh), atol=1e-2)     # the first row sees its own key only
+
+
 def test_attention_prefill_far_key_and_diagonal(K):
     """A key far back is made to stand out for the last row of a portion, and every row's own key for
     itself: the far key must win in the one row, the diagonal in all others (the causal edge)."""
