@@ -8,7 +8,7 @@
 // One block takes 128 rows of one request and one q head and walks the keys in tiles of 128:
 //   warp 0        TMA: the block's rows of q once, then per key tile the pages that hold its keys and
 //                 values (a box is one page's rows of one kv head, 64 elements wide, 128-byte swizzle)
-//                 into two rings of AT_STAGES slots, one for keys and one for values
+//                 into two rings, AT_KSTAGES slots of keys and AT_VSTAGES slots of values
 //   warp 1        one lane issues the MMAs: S[j] = Q K[j]^T (M 128, N 128, four k-steps) into tensor
 //                 memory, then, once the softmax warps have written P[j] to shared memory,
 //                 O += P[j] V[j] (M 128, N 64, eight k-steps; V is the MN-major operand: its rows are keys
@@ -29,19 +29,25 @@
 // P is zero, but zero times stale bits is not), and scores there are masked.
 // A row's sums do not depend on the block it is in: key tiles start at multiples of 128 counted from
 // the window's first tile, and a tile in which the row sees no key leaves its state as it is.
-// Measured on 8,192 tokens of 32 heads (501 us, 548 TFLOP/s; the mma.sync kernel 1,122 us): without the
-// MMAs and without the softmax arithmetic the same launch still takes 450 us, so what bounds a block is the
+// q is the A operand from tensor memory (the softmax warps move each row there once, two bfloat16 to a
+// column): the 16 KB it held in shared memory are a third slot of keys.
+// Measured on 8,192 tokens of 32 heads (470 us, 585 TFLOP/s; the mma.sync kernel 1,122 us): without the MMAs
+// and without the softmax arithmetic the launch still took 450 of 501 us, so what bounds a block is the
 // chain of hand-overs per tile (loads, Q K^T, softmax, P V, each waiting for the one before), not a pipe;
 // two blocks per SM give two such chains.  Keys and values in one ring cost 654 us, one block per SM with
-// two score buffers 1,635 us.
+// two score buffers 1,635 us; the third slot of keys brought 499 -> 467 us, keys issued a tile ahead of the
+// values nothing more.
 // Every wait is bounded by wall time; a block that gives up sets a status word (snk_attention_tc_status).
 #include "tcgen05.cuh"
 
 #define AT_BQ 128
 #define AT_BK 128
 #define AT_HD 64
-#ifndef AT_STAGES
-#define AT_STAGES 2
+#ifndef AT_KSTAGES
+#define AT_KSTAGES 3                                    // slots of keys
+#endif
+#ifndef AT_VSTAGES
+#define AT_VSTAGES 2                                    // slots of values
 #endif
 #define AT_THREADS 192
 #define AT_WAIT_NS 1000000000ull
@@ -50,6 +56,7 @@
 #define AT_P_BYTES (AT_BQ * AT_BK * 2)                  // two panels of 64 keys
 #define AT_TMEM_COLS 256
 #define AT_TMEM_O 128                                   // S at column 0, O at 128
+#define AT_TMEM_Q 192                                   // the rows of q, two bfloat16 to a column: 32 columns
 #define AT_RESCALE_STEP 8.f                             // the reference maximum follows the row's maximum in steps of more than this
 
 enum { AT_ERR_Q = 1, AT_ERR_KV = 2, AT_ERR_KV_FREE = 3, AT_ERR_S = 4, AT_ERR_S_FREE = 5, AT_ERR_P = 6, AT_ERR_PV = 7 };
@@ -58,10 +65,11 @@ __device__ int g_at_status;
 
 struct __align__(16) AtShared {
   uint64_t q_full;
-  uint64_t k_full[AT_STAGES];       // the slot's pages of keys have landed
-  uint64_t k_empty[AT_STAGES];      // Q K^T of the tile that used the slot has completed
-  uint64_t v_full[AT_STAGES];       // the same for the values
-  uint64_t v_empty[AT_STAGES];      // P V of the tile that used the slot has completed
+  uint64_t q_ready;                 // the softmax warps have moved q into tensor memory
+  uint64_t k_full[AT_KSTAGES];      // the slot's pages of keys have landed
+  uint64_t k_empty[AT_KSTAGES];     // Q K^T of the tile that used the slot has completed
+  uint64_t v_full[AT_VSTAGES];      // the same for the values
+  uint64_t v_empty[AT_VSTAGES];     // P V of the tile that used the slot has completed
   uint64_t s_full;                  // Q K^T of a tile has completed
   uint64_t s_empty;                 // the four softmax warps hold the scores in registers
   uint64_t p_full;                  // P is in shared memory, O is rescaled, stale value rows are zeroed
@@ -113,6 +121,15 @@ __device__ __forceinline__ void tmem_ld32_nowait(uint32_t taddr, uint32_t (&r)[3
       : "r"(taddr));
 }
 
+// D += A B with A in tensor memory (lane = row, a column = two consecutive bfloat16 of the row) and B by descriptor.
+__device__ __forceinline__ void umma_bf16_ta(uint32_t tmem_d, uint32_t tmem_a, uint64_t b_desc, uint32_t idesc,
+                                             uint32_t accumulate) {
+  asm volatile(
+      "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n"
+      " tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n}"
+      ::"r"(tmem_d), "r"(tmem_a), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+}
+
 __device__ __forceinline__ uint32_t at_pack(float a, float b) {
   const __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
   return *reinterpret_cast<const uint32_t*>(&h);
@@ -130,10 +147,10 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                             const int* __restrict__ tiles, int n_tiles, bf16* __restrict__ out, int nh, int nkv,
                             int window, float scale_log2) {
   extern __shared__ __align__(1024) unsigned char smem[];
-  unsigned char* sm_q = smem;                                             // [128 rows][64], swizzled by TMA
-  unsigned char* sm_k = sm_q + AT_Q_BYTES;                                // [AT_STAGES][128 keys][64]
-  unsigned char* sm_v = sm_k + (size_t)AT_STAGES * AT_KV_BYTES;           // [AT_STAGES][128 keys][64]
-  unsigned char* sm_p = sm_v + (size_t)AT_STAGES * AT_KV_BYTES;           // [2 panels][128 rows][64 keys]
+  unsigned char* sm_k = smem;                                             // [AT_KSTAGES][128 keys][64], swizzled by TMA
+  unsigned char* sm_v = sm_k + (size_t)AT_KSTAGES * AT_KV_BYTES;          // [AT_VSTAGES][128 keys][64]
+  unsigned char* sm_p = sm_v + (size_t)AT_VSTAGES * AT_KV_BYTES;          // [2 panels][128 rows][64 keys]
+  unsigned char* sm_q = sm_p;                                             // q lands in P's place and moves on to tensor memory
   AtShared* sh = reinterpret_cast<AtShared*>(sm_p + AT_P_BYTES);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -141,9 +158,12 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_q)) : "memory");
     asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_kv)) : "memory");
     mbar_init(&sh->q_full, 1);
-    for (int i = 0; i < AT_STAGES; ++i) {
+    mbar_init(&sh->q_ready, 4);
+    for (int i = 0; i < AT_KSTAGES; ++i) {
       mbar_init(&sh->k_full[i], 1);
       mbar_init(&sh->k_empty[i], 1);
+    }
+    for (int i = 0; i < AT_VSTAGES; ++i) {
       mbar_init(&sh->v_full[i], 1);
       mbar_init(&sh->v_empty[i], 1);
     }
@@ -190,61 +210,65 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
       first_page = max(k0, key_lo) / page_size;
       n_pages = min(k0 + AT_BK - 1, last_pos) / page_size - first_page + 1;
     };
-    int first_page, n_pages;
-    tile_pages(0, first_page, n_pages);
-    int page_next = lane < n_pages ? bt[first_page + lane] : 0;
-    for (int j = 0; j < n_kt; ++j) {
-      const int st = j % AT_STAGES;
-      const uint32_t free_parity = ((j / AT_STAGES) & 1) ^ 1;
-      const int k0 = k_first + j * AT_BK;
-      tile_pages(j, first_page, n_pages);
-      const int page = page_next;
-      const bool mine = lane < n_pages;
-      if (j + 1 < n_kt) {
+    // The keys run one tile ahead of the values (K[0], K[1], V[0], K[2], V[1], ...): a slot of values is
+    // free late, and keys asked for behind that wait would be late too.
+    int fp_k, np_k, fp_v = 0, np_v = 0;
+    tile_pages(0, fp_k, np_k);
+    int page_k = lane < np_k ? bt[fp_k + lane] : 0, page_v = 0, page_next = 0;
+    for (int t = 0; t <= n_kt; ++t) {
+      if (t + 1 < n_kt) {                                                 // the look-up for the keys of the next round
         int fp, np;
-        tile_pages(j + 1, fp, np);
+        tile_pages(t + 1, fp, np);
         page_next = lane < np ? bt[fp + lane] : 0;
       }
-      const uint32_t bytes = (uint32_t)n_pages * page_size * 128u;
-      const int row = (first_page + lane) * page_size - k0;               // the page's first row in the tile
-      at_wait(&sh->k_empty[st], free_parity, aborted, AT_ERR_KV_FREE);
-      if (lane == 0) mbar_expect_tx(&sh->k_full[st], bytes);
-      __syncwarp();
-      if (mine)
-        tma_load_2d(sm_k + (size_t)st * AT_KV_BYTES + row * 128, &map_kv, &sh->k_full[st], 0,
-                    ((page * 2) * nkv + kvh) * page_size);
-      at_wait(&sh->v_empty[st], free_parity, aborted, AT_ERR_KV_FREE);
-      if (lane == 0) mbar_expect_tx(&sh->v_full[st], bytes);
-      __syncwarp();
-      if (mine)
-        tma_load_2d(sm_v + (size_t)st * AT_KV_BYTES + row * 128, &map_kv, &sh->v_full[st], 0,
-                    ((page * 2 + 1) * nkv + kvh) * page_size);
+      if (t < n_kt) {
+        const int ks = t % AT_KSTAGES;
+        const int k0 = k_first + t * AT_BK;
+        tile_pages(t, fp_k, np_k);
+        at_wait(&sh->k_empty[ks], ((t / AT_KSTAGES) & 1) ^ 1, aborted, AT_ERR_KV_FREE);
+        if (lane == 0) mbar_expect_tx(&sh->k_full[ks], (uint32_t)np_k * page_size * 128u);
+        __syncwarp();
+        if (lane < np_k)
+          tma_load_2d(sm_k + (size_t)ks * AT_KV_BYTES + ((fp_k + lane) * page_size - k0) * 128, &map_kv,
+                      &sh->k_full[ks], 0, ((page_k * 2) * nkv + kvh) * page_size);
+      }
+      if (t >= 1) {
+        const int j = t - 1, vs = j % AT_VSTAGES;
+        const int k0 = k_first + j * AT_BK;
+        at_wait(&sh->v_empty[vs], ((j / AT_VSTAGES) & 1) ^ 1, aborted, AT_ERR_KV_FREE);
+        if (lane == 0) mbar_expect_tx(&sh->v_full[vs], (uint32_t)np_v * page_size * 128u);
+        __syncwarp();
+        if (lane < np_v)
+          tma_load_2d(sm_v + (size_t)vs * AT_KV_BYTES + ((fp_v + lane) * page_size - k0) * 128, &map_kv,
+                      &sh->v_full[vs], 0, ((page_v * 2 + 1) * nkv + kvh) * page_size);
+      }
+      fp_v = fp_k; np_v = np_k; page_v = page_k;                          // this round's keys are the next round's values
+      page_k = page_next;
       __syncwarp();
     }
   } else if (warp == 1) {
     if (lane == 0) {
       const uint32_t idesc_s = instr_desc_bf16(AT_BQ, AT_BK);
       const uint32_t idesc_o = instr_desc_bf16(AT_BQ, AT_HD) | (1u << 16);     // B (values) is MN-major
-      const uint32_t q_addr = smem_u32(sm_q);
-      at_wait(&sh->q_full, 0, aborted, AT_ERR_Q);
+      at_wait(&sh->q_ready, 0, aborted, AT_ERR_Q);
       auto scores = [&](int j) {
-        const int st = j % AT_STAGES;
-        at_wait(&sh->k_full[st], (j / AT_STAGES) & 1, aborted, AT_ERR_KV);
+        const int st = j % AT_KSTAGES;
+        at_wait(&sh->k_full[st], (j / AT_KSTAGES) & 1, aborted, AT_ERR_KV);
         at_wait(&sh->s_empty, (j & 1) ^ 1, aborted, AT_ERR_S_FREE);
         tc_fence_after();
         const uint32_t k_addr = smem_u32(sm_k + (size_t)st * AT_KV_BYTES);
 #pragma unroll
-        for (int k = 0; k < AT_HD / 16; ++k)
-          umma_bf16(tmem, smem_desc_sw128(q_addr + k * 32), smem_desc_sw128(k_addr + k * 32), idesc_s, k > 0 ? 1u : 0u);
+        for (int k = 0; k < AT_HD / 16; ++k)                 // 16 elements of q = 8 columns of tensor memory
+          umma_bf16_ta(tmem, tmem + AT_TMEM_Q + k * 8, smem_desc_sw128(k_addr + k * 32), idesc_s, k > 0 ? 1u : 0u);
         umma_commit(&sh->k_empty[st]);
         umma_commit(&sh->s_full);
       };
       scores(0);
       for (int j = 0; j < n_kt; ++j) {
         if (j + 1 < n_kt) scores(j + 1);
-        const int st = j % AT_STAGES;
+        const int st = j % AT_VSTAGES;
         at_wait(&sh->p_full, j & 1, aborted, AT_ERR_P);
-        at_wait(&sh->v_full[st], (j / AT_STAGES) & 1, aborted, AT_ERR_KV);
+        at_wait(&sh->v_full[st], (j / AT_VSTAGES) & 1, aborted, AT_ERR_KV);
         tc_fence_after();
         const uint32_t p_addr = smem_u32(sm_p);
         const uint32_t v_addr = smem_u32(sm_v + (size_t)st * AT_KV_BYTES);
@@ -264,9 +288,22 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     const int pos = pos0 + row;
     const int lo = window > 0 ? max(0, pos - window + 1) : 0;
     const int lo_last = window > 0 ? max(0, last_pos - window + 1) : 0;   // the last row's lowest key
+    {                                                    // this row of q: shared memory -> tensor memory
+      at_wait(&sh->q_full, 0, aborted, AT_ERR_Q);
+      uint32_t qr[32];
+#pragma unroll
+      for (int c = 0; c < 8; ++c) {
+        const uint4 v = *reinterpret_cast<const uint4*>(sm_q + row * 128 + ((c ^ (row & 7)) << 4));
+        qr[4 * c] = v.x; qr[4 * c + 1] = v.y; qr[4 * c + 2] = v.z; qr[4 * c + 3] = v.w;
+      }
+      tmem_st32(tmem + t_lane + AT_TMEM_Q, qr);
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&sh->q_ready);
+    }
     float m_ref = -INFINITY, l = 0.f;                    // the maximum the exponentials are taken against (scaled), the sum
     for (int j = 0; j < n_kt; ++j) {
-      const int st = j % AT_STAGES;
+      const int st = j % AT_VSTAGES;
       const int k0 = k_first + j * AT_BK;
       at_wait(&sh->s_full, j & 1, aborted, AT_ERR_S);
       tc_fence_after();
@@ -342,7 +379,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
               make_uint4(r[c][4 * q8], r[c][4 * q8 + 1], r[c][4 * q8 + 2], r[c][4 * q8 + 3]);
         }
       if (k0 < key_lo || k0 + AT_BK - 1 > last_pos) {    // value rows no row sees: zero, whatever they held
-        at_wait(&sh->v_full[st], (j / AT_STAGES) & 1, aborted, AT_ERR_KV);
+        at_wait(&sh->v_full[st], (j / AT_VSTAGES) & 1, aborted, AT_ERR_KV);
         const int kp = k0 + row;
         if (kp < key_lo || kp > last_pos) {
           uint4* v_row = reinterpret_cast<uint4*>(sm_v + (size_t)st * AT_KV_BYTES + row * 128);
@@ -414,7 +451,7 @@ SNK_API int snk_attention_prefill_tc(const void* q, long long M, const void* poo
   if (rc) return rc;
   rc = tensor_map(pool, num_pages * 2 * nkv * page_size, hd, page_size, 64, &map_kv);
   if (rc) return rc;
-  const size_t smem = AT_Q_BYTES + (size_t)AT_STAGES * 2 * AT_KV_BYTES + AT_P_BYTES + sizeof(AtShared);
+  const size_t smem = (size_t)(AT_KSTAGES + AT_VSTAGES) * AT_KV_BYTES + AT_P_BYTES + sizeof(AtShared);
   static bool configured = false;
   if (!configured) {
     cudaFuncSetAttribute(attention_prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
