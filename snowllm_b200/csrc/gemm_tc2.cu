@@ -248,10 +248,7 @@ static int launch_tc2(const CUtensorMap& map_a, const CUtensorMap& map_w, void* 
 // tokens, as pairs side by side then read far-apart memory; items drawn from a counter as pairs get free,
 // 159 us; L2 prefetch of an item's rows of W in one piece, 184 to 198 us.)
 #define T2G_MAX_GROUPS 256
-#ifndef T2G_X_ROWS
-#define T2G_X_ROWS 128
-#endif
-#define T2G_STAGE_BYTES ((T2_BM + T2G_X_ROWS) * T2_BK * 2)
+#define T2G_STAGE_BYTES ((T2_BM + T2_BM) * T2_BK * 2)  // 128 rows of W and up to 128 of the tile's rows of A
 #define T2G_BOXES 5                  // tensor maps of A with boxes of 128, 64, 32, 16 and 8 rows
 
 struct T2GMaps {
@@ -265,7 +262,7 @@ struct T2GItem {
 
 // first[e]: the number of items before group e (shared memory, groups + 1 entries)
 __device__ __forceinline__ T2GItem t2g_item(int item, const int* first, const int* __restrict__ offsets, int groups,
-                                            int N, int n_tiles) {
+                                            int N) {
   T2GItem t;
   t.valid = false;
   int lo = 0, hi = groups;                               // the group e with first[e] <= item < first[e + 1]
@@ -285,7 +282,6 @@ __device__ __forceinline__ T2GItem t2g_item(int item, const int* first, const in
   t.w_row0 = lo * N;
   t.f0 = ft * T2_BN;
   t.valid = true;
-  (void)n_tiles;
   return t;
 }
 
@@ -347,7 +343,7 @@ gemm_tc2_grouped_kernel(const __grid_constant__ T2GMaps maps, const __grid_const
 
   int it = 0;                                            // k-blocks so far (producer and MMA thread)
   auto issue_loads = [&](int item) {
-    const T2GItem t = t2g_item(item, first, offsets, groups, N, n_tiles);
+    const T2GItem t = t2g_item(item, first, offsets, groups, N);
     const int half = t.nt >> 1, box = t2g_box(half);
     const uint32_t bytes = (uint32_t)(T2_BM * T2_BK * 2 + (128 >> box) * T2_BK * 2);
     for (int kt = 0; kt < k_tiles; ++kt, ++it) {
@@ -368,7 +364,7 @@ gemm_tc2_grouped_kernel(const __grid_constant__ T2GMaps maps, const __grid_const
     if (lane == 0 && rank == 0) {
       int local = 0;
       for (int item = pair; item < total; item += pairs, ++local) {
-        const T2GItem t = t2g_item(item, first, offsets, groups, N, n_tiles);
+        const T2GItem t = t2g_item(item, first, offsets, groups, N);
         const uint32_t idesc = instr_desc_bf16(2 * T2_BM, t.nt);
         const int buf = local % T2_ACC_BUFFERS;
         const int use = local / T2_ACC_BUFFERS;
@@ -395,7 +391,7 @@ gemm_tc2_grouped_kernel(const __grid_constant__ T2GMaps maps, const __grid_const
     float* stage_out = sh->stage_out[warp - 2];
     int local = 0;
     for (int item = pair; item < total; item += pairs, ++local) {
-      const T2GItem t = t2g_item(item, first, offsets, groups, N, n_tiles);
+      const T2GItem t = t2g_item(item, first, offsets, groups, N);
       const int buf = local % T2_ACC_BUFFERS;
       const int use = local / T2_ACC_BUFFERS;
       t2_wait(&sh->acc_full[buf], use & 1, aborted, T2_ERR_ACC);
