@@ -215,10 +215,27 @@ __device__ __forceinline__ void sort_pairs(const int* __restrict__ topk_ids, int
   int* off = cnt + E;            // cnt: E counts, then E+1 offsets
   for (int e = threadIdx.x; e < E; e += blockDim.x) cnt[e] = 0;
   __syncthreads();
-  for (int p = threadIdx.x; p < pairs; p += blockDim.x) {
-    int e = topk_ids[p];
-    e = e < 0 ? 0 : (e >= E ? E - 1 : e);
-    pair_pos[p] = atomicAdd(&cnt[e], 1);
+  // Up to SORT_KEEP pairs per thread stay in registers between the two passes, and their ids are all asked
+  // for before the first is used: one trip to memory instead of one per pair and pass.
+  constexpr int SORT_KEEP = 8;
+  int ids[SORT_KEEP], place[SORT_KEEP];
+  const bool keep = pairs <= SORT_KEEP * (int)blockDim.x;
+  if (keep) {
+#pragma unroll
+    for (int i = 0; i < SORT_KEEP; ++i) {
+      const int p = threadIdx.x + i * blockDim.x;
+      int e = p < pairs ? topk_ids[p] : 0;
+      ids[i] = e < 0 ? 0 : (e >= E ? E - 1 : e);
+    }
+#pragma unroll
+    for (int i = 0; i < SORT_KEEP; ++i)
+      if ((int)(threadIdx.x + i * blockDim.x) < pairs) place[i] = atomicAdd(&cnt[ids[i]], 1);
+  } else {
+    for (int p = threadIdx.x; p < pairs; p += blockDim.x) {
+      int e = topk_ids[p];
+      e = e < 0 ? 0 : (e >= E ? E - 1 : e);
+      pair_pos[p] = atomicAdd(&cnt[e], 1);
+    }
   }
   __syncthreads();
   if (threadIdx.x == 0) {
@@ -228,6 +245,18 @@ __device__ __forceinline__ void sort_pairs(const int* __restrict__ topk_ids, int
   }
   __syncthreads();
   for (int e = threadIdx.x; e <= E; e += blockDim.x) offsets[e] = off[e];
+  if (keep) {
+#pragma unroll
+    for (int i = 0; i < SORT_KEEP; ++i) {
+      const int p = threadIdx.x + i * blockDim.x;
+      if (p < pairs) {
+        const int r = off[ids[i]] + place[i];
+        pair_pos[p] = r;
+        sorted_pair[r] = p;
+      }
+    }
+    return;
+  }
   for (int p = threadIdx.x; p < pairs; p += blockDim.x) {
     int e = topk_ids[p];
     e = e < 0 ? 0 : (e >= E ? E - 1 : e);
