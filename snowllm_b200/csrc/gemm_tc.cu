@@ -388,6 +388,25 @@ SNK_API int snk_gemm_tc(const void* A, const void* W, void* C, int M, int N, int
 #undef TC_GO
 }
 
+// The product split along K with the sum left to the caller: `parts` receives the float planes
+// [splits][M][N], to be added in plane order (what splitk_reduce_kernel does).  Returns the number of planes
+// through *splits_out; products that are not split (see snk_gemm_tc_scratch_bytes) give SNK_ERR_SIZE.
+SNK_API int snk_gemm_tc_parts(const void* A, const void* W, void* parts, int M, int N, int K, int* splits_out,
+                              cudaStream_t stream) {
+  if (M <= 0 || N <= 0 || K <= 0 || K % 8) return SNK_ERR_SIZE;
+  if (((uintptr_t)A % 16) || ((uintptr_t)W % 16) || parts == nullptr || ((uintptr_t)parts % 16)) return SNK_ERR_ALIGN;
+  const bool wide = (long long)((M + TC_BM - 1) / TC_BM) * ((N + 255) / 256) >= 120;
+  const int splits = wide ? 1 : tc_splits(M, N, K, nullptr);
+  if (splits <= 1) return SNK_ERR_SIZE;
+  CUtensorMap map_a, map_w;
+  int rc = tensor_map(A, M, K, TC_BM, TC_BK, &map_a);
+  if (rc) return rc;
+  rc = tensor_map(W, N, K, 128, TC_BK, &map_w);
+  if (rc) return rc;
+  *splits_out = splits;
+  return launch_tc<128, float, false>(map_a, map_w, parts, M, N, K, nullptr, 1, (M + TC_BM - 1) / TC_BM, splits, stream);
+}
+
 // 0, or the first error a block of any earlier launch recorded (a wait that ran out); reading clears
 // it.  Synchronises the device.
 SNK_API int snk_gemm_tc_status() {

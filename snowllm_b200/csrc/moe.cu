@@ -152,9 +152,11 @@ __global__ void moe_logits_kernel(const T* __restrict__ x, SmallVec wr, float* _
 
 // One warp per token: probabilities and selection from float logits that a matrix product left, [M, E]
 // or (transposed) [E, M].
+// planes > 1: the logits are the sum of that many planes of [M, E] (a product split along K), added here in
+// plane order.
 __global__ void moe_topk_kernel(const float* __restrict__ logits, const float* __restrict__ bias,
                                 int* __restrict__ topk_ids, float* __restrict__ topk_w, int M, int E, int k,
-                                int norm_topk, float scaling, int transposed) {
+                                int norm_topk, float scaling, int transposed, int planes) {
   pdl_begin();
   extern __shared__ float sh[];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarp = blockDim.x >> 5;
@@ -163,7 +165,11 @@ __global__ void moe_topk_kernel(const float* __restrict__ logits, const float* _
   float* prob = sh + (size_t)warp * 2 * E;
   float* score = prob + E;
   for (int e = lane; e < E; e += 32) {
-    const float x = transposed ? logits[(size_t)e * M + m] : logits[(size_t)m * E + e];
+    float x = transposed ? logits[(size_t)e * M + m] : logits[(size_t)m * E + e];
+    if (planes > 1) {
+      x += 0.f;                                          // the sum starts from zero, as the product's own sum does
+      for (int q = 1; q < planes; ++q) x += logits[(size_t)q * M * E + (size_t)m * E + e];
+    }
     const float p = 1.f / (1.f + expf(-x));
     prob[e] = p;
     score[e] = bias ? p + bias[e] : p;
@@ -173,12 +179,12 @@ __global__ void moe_topk_kernel(const float* __restrict__ logits, const float* _
 }
 
 SNK_API int snk_moe_topk(const float* logits, const float* bias, int* topk_ids, float* topk_w, int M, int E,
-                         int k, int norm_topk, float scaling, int transposed, cudaStream_t stream) {
+                         int k, int norm_topk, float scaling, int transposed, int planes, cudaStream_t stream) {
   if (M <= 0) return 0;
-  if (E <= 0 || E > ROUTE_MAX_EXPERTS || k <= 0 || k > E) return SNK_ERR_SIZE;
+  if (E <= 0 || E > ROUTE_MAX_EXPERTS || k <= 0 || k > E || planes < 1 || (planes > 1 && transposed)) return SNK_ERR_SIZE;
   const int warps = 4;
   snk_launch(moe_topk_kernel, dim3((M + warps - 1) / warps), dim3(warps * 32), (size_t)warps * 2 * E * sizeof(float), stream, 
-      logits, bias, topk_ids, topk_w, M, E, k, norm_topk, scaling, transposed);
+      logits, bias, topk_ids, topk_w, M, E, k, norm_topk, scaling, transposed, planes);
   SNK_LAUNCH_CHECK();
   return 0;
 }

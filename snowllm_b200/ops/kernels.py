@@ -59,6 +59,7 @@ _SIGNATURES = {
         "snk_gemm_tc": [P, P, P, I, I, I, P, I, I, I, I, P, P],
         "snk_gemm_tc_scratch_bytes": [I, I, I, I],
         "snk_gemm_tc_status": [],
+        "snk_gemm_tc_parts": [P, P, P, I, I, I, P, P],
         "snk_gather_rows_bf16": [P, P, P, I, I, I, P],
     },
     "gemm_tc2": {
@@ -67,7 +68,7 @@ _SIGNATURES = {
     },
     "moe": {
         "snk_moe_route": [P, P, I, P, P, P, I, I, I, I, I, F, I, P],
-        "snk_moe_topk": [P, P, P, P, I, I, I, I, F, I, P],
+        "snk_moe_topk": [P, P, P, P, I, I, I, I, F, I, I, P],
         "snk_moe_route_sort": [P, P, I, P, P, P, P, P, P, P, I, I, I, I, I, F, I, P],
         "snk_moe_sort": [P, P, P, P, I, I, P],
         "snk_moe_combine": [P, P, P, P, I, I, I, P],
@@ -710,9 +711,14 @@ def moe_route(x, router_w, bias, top_k, norm_topk_prob, scaling):
     if (M > ROUTE_GEMM_MIN_ROWS and router_w.dtype == torch.bfloat16 and gemm_tc_ok(x, router_w)
             and gemm_tc_is_split(M, E, H)):
         # many rows, few experts: a tcgen05 product split along K (float accumulation, float output)
-        logits = gemm_tc(x, router_w, out_dtype=torch.float32)
-        check(fn("snk_moe_topk")(_ptr(logits), _ptr(bias), _ptr(ids), _ptr(wts), M, E, top_k,
-                                 int(bool(norm_topk_prob)), float(scaling), 0, _stream()), "moe_topk")
+        # whose partial sums the selection adds itself, in the order the product's own sum has
+        nbytes = int(fn("snk_gemm_tc_scratch_bytes")(M, E, H, 0))
+        parts = torch.empty(nbytes, dtype=torch.uint8, device=x.device)
+        planes = ctypes.c_int(0)
+        check(fn("snk_gemm_tc_parts")(_ptr(x), _ptr(router_w), _ptr(parts), M, E, H, ctypes.byref(planes),
+                                      _stream()), "gemm_tc_parts")
+        check(fn("snk_moe_topk")(_ptr(parts), _ptr(bias), _ptr(ids), _ptr(wts), M, E, top_k,
+                                 int(bool(norm_topk_prob)), float(scaling), 0, planes.value, _stream()), "moe_topk")
         return ids, wts
     if M > ROUTE_GEMM_MIN_ROWS and router_w.dtype == torch.bfloat16 and gemm_skinny_ok(router_w, x):
         # many rows: the logits are a tensor-core product with float accumulation and float output.  The few
@@ -720,7 +726,7 @@ def moe_route(x, router_w, bias, top_k, norm_topk_prob, scaling):
         # leaves the logits transposed, [E, M].
         logits = gemm_skinny(router_w, x, out_dtype=torch.float32, rows_hint=min(E, 64))
         check(fn("snk_moe_topk")(_ptr(logits), _ptr(bias), _ptr(ids), _ptr(wts), M, E, top_k,
-                                 int(bool(norm_topk_prob)), float(scaling), 1, _stream()), "moe_topk")
+                                 int(bool(norm_topk_prob)), float(scaling), 1, 1, _stream()), "moe_topk")
         return ids, wts
     check(fn("snk_moe_route")(_ptr(x), _ptr(router_w), w32, _ptr(bias), _ptr(ids), _ptr(wts), M, H, E,
                               top_k, int(bool(norm_topk_prob)), float(scaling), code_of(dtype), _stream()),
