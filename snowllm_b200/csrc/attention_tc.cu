@@ -36,7 +36,8 @@
 // chain of hand-overs per tile (loads, Q K^T, softmax, P V, each waiting for the one before), not a pipe;
 // two blocks per SM give two such chains.  Keys and values in one ring cost 654 us, one block per SM with
 // two score buffers 1,635 us; the third slot of keys brought 499 -> 467 us, keys issued a tile ahead of the
-// values nothing more.
+// values nothing more.  P in tensor memory as well, in the scores' place (256 columns hold no second place),
+// gave 600 us: the next tile's Q K^T must then wait for P V.
 // Every wait is bounded by wall time; a block that gives up sets a status word (snk_attention_tc_status).
 #include "tcgen05.cuh"
 
