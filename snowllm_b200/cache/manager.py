@@ -2,11 +2,13 @@
 
 A *group* is a set of layers with the same need: ("paged", None) keeps every key,
 ("paged", W) keeps a window of W positions.  Each group has pages of its own (its own pool of
-page ids and, per layer of the group, its own device tensor [pages, 2, kv heads, page_size,
-head_dim]) and each request has one block table per group: entry i is the page that holds
+page ids and, per layer of the group, device tensors of its own in the layout its spec chooses:
+[pages, 2, kv heads, page_size, head_dim] for keys and values of one width) and each request has
+one block table per group: entry i is the page that holds
 positions [i*page_size, (i+1)*page_size), or -1 once a window has passed it and the page was
 given back.  Beside the pages, every request holds one slot: layers with state of fixed size
-keep a tensor [slots + 1, *shape] each, indexed by that slot.
+keep a tensor [slots + 1, *shape] each, indexed by that slot.  A mixer may ask for several of these
+at once (pages and a state of fixed size): its ``cache_spec()`` is then a tuple, and so is its view.
 
 What is given back when: a window group's pages as soon as no later query can reach them (at the
 end of the step that passed them); everything at ``free``.  The step function never allocates:
@@ -36,9 +38,10 @@ class RequestCache:
 
 @dataclass
 class PagedView:
-    pool: torch.Tensor
+    pool: torch.Tensor                 # the first (for keys and values of one width: the only) pool tensor
     block_table: torch.Tensor
     page_size: int
+    pools: tuple = ()                  # every pool tensor of the spec, in the order of ``pool_shapes``
 
 
 @dataclass
@@ -50,56 +53,88 @@ def pages_for(tokens: int, page_size: int) -> int:
     return -(-tokens // page_size)
 
 
+_CACHE_DTYPES = {"float32": torch.float32, "bfloat16": torch.bfloat16}
+
+
+def _as_tuple(spec) -> tuple:
+    return tuple(spec) if isinstance(spec, (tuple, list)) else (spec,)
+
+
 class CacheManager:
     def __init__(self, cache_specs, page_size: int, num_pages, max_seqs: int,
                  dtype: torch.dtype = torch.float32, device=None):
-        """``cache_specs``: {entry index -> PagedKVSpec | SlotStateSpec} for the run entries that own
-        a cache.  ``num_pages``: an int for every group, or {group key -> int}.  ``device`` None
-        keeps the book-keeping only (no tensors): what the CPU tests and sizing code use."""
+        """``cache_specs``: {entry index -> PagedKVSpec | SlotStateSpec | a tuple of them} for the run
+        entries that own a cache.  ``num_pages``: an int for every group, or {group key -> int}.
+        ``device`` None keeps the book-keeping only (no tensors): what the CPU tests and sizing code use."""
         if page_size <= 0:
             raise ValueError("page_size must be positive")
         self.page_size, self.max_seqs, self.dtype, self.device = page_size, max_seqs, dtype, device
         self.specs = dict(cache_specs)
         self.groups: dict[tuple, PagePool] = {}
-        self.group_of: dict[int, tuple] = {}
-        for idx, spec in self.specs.items():
-            if isinstance(spec, PagedKVSpec):
-                key = ("paged", spec.window)
-                self.group_of[idx] = key
-                if key not in self.groups:
-                    n = num_pages[key] if isinstance(num_pages, dict) else num_pages
-                    self.groups[key] = PagePool(int(n))
-            elif not isinstance(spec, SlotStateSpec):
-                raise TypeError(f"run entry {idx}: unknown cache spec {spec!r}")
+        for idx, entry in self.specs.items():
+            for spec in _as_tuple(entry):
+                if isinstance(spec, PagedKVSpec):
+                    key = ("paged", spec.window)
+                    if key not in self.groups:
+                        n = num_pages[key] if isinstance(num_pages, dict) else num_pages
+                        self.groups[key] = PagePool(int(n))
+                    if spec.cache_dtype is not None and spec.cache_dtype not in _CACHE_DTYPES:
+                        raise TypeError(f"run entry {idx}: cache dtype {spec.cache_dtype!r} "
+                                        f"(known: {', '.join(_CACHE_DTYPES)})")
+                elif not isinstance(spec, SlotStateSpec):
+                    raise TypeError(f"run entry {idx}: unknown cache spec {spec!r}")
         self.slots = StateSlots(max_seqs)
-        self.pools: dict[int, torch.Tensor] = {}
-        self.states: dict[int, list] = {}
+        self._tensors: dict[int, tuple] = {}       # entry index -> per spec of the entry: its tensors
         if device is not None:
             self._allocate()
 
     # -- device tensors -------------------------------------------------------------------
     def _allocate(self) -> None:
-        for idx, spec in self.specs.items():
-            if isinstance(spec, PagedKVSpec):
-                n = self.groups[self.group_of[idx]].total
-                self.pools[idx] = torch.zeros(max(n, 1), 2, spec.num_kv_heads, self.page_size, spec.head_dim,
-                                              dtype=self.dtype, device=self.device)
-            else:
-                kinds = spec.dtypes or ("compute",) * len(spec.shapes)
-                self.states[idx] = [
-                    torch.zeros(self.max_seqs + 1, *shape, device=self.device,
-                                dtype=self.dtype if kind == "compute" else torch.float32)
-                    for shape, kind in zip(spec.shapes, kinds)]
+        for idx, entry in self.specs.items():
+            made = []
+            for spec in _as_tuple(entry):
+                if isinstance(spec, PagedKVSpec):
+                    n = max(self.groups[("paged", spec.window)].total, 1)
+                    dtype = _CACHE_DTYPES[spec.cache_dtype] if spec.cache_dtype else self.dtype
+                    made.append(tuple(torch.zeros(shape, dtype=dtype, device=self.device)
+                                      for shape in spec.pool_shapes(n, self.page_size)))
+                else:
+                    kinds = spec.dtypes or ("compute",) * len(spec.shapes)
+                    made.append(tuple(
+                        torch.zeros(self.max_seqs + 1, *shape, device=self.device,
+                                    dtype=self.dtype if kind == "compute" else torch.float32)
+                        for shape, kind in zip(spec.shapes, kinds)))
+            self._tensors[idx] = tuple(made)
+
+    def _each(self, kind):
+        for idx, entry in self.specs.items():
+            for spec, tensors in zip(_as_tuple(entry), self._tensors.get(idx, ())):
+                if isinstance(spec, kind):
+                    yield idx, spec, tensors
+
+    def paged_tensors(self) -> list:
+        """Every pool tensor (first dimension: pages), over all run entries."""
+        return [t for _, _, ts in self._each(PagedKVSpec) for t in ts]
+
+    def state_tensors(self) -> list:
+        """Every tensor of fixed-size state (first dimension: slots + 1), over all run entries."""
+        return [t for _, _, ts in self._each(SlotStateSpec) for t in ts]
+
+    def bytes_per_token(self) -> int:
+        """Bytes one cached position costs over all paged layers (pools as allocated)."""
+        return sum(t[0].numel() * t.element_size() for t in self.paged_tensors()) // self.page_size
 
     @staticmethod
     def bytes_per_page(cache_specs, page_size: int, dtype: torch.dtype) -> dict:
         """{group key -> bytes one page id costs over all layers of the group}."""
-        esz = torch.empty((), dtype=dtype).element_size()
         out: dict[tuple, int] = {}
-        for spec in cache_specs.values():
-            if isinstance(spec, PagedKVSpec):
-                key = ("paged", spec.window)
-                out[key] = out.get(key, 0) + 2 * spec.num_kv_heads * page_size * spec.head_dim * esz
+        for entry in cache_specs.values():
+            for spec in _as_tuple(entry):
+                if isinstance(spec, PagedKVSpec):
+                    key = ("paged", spec.window)
+                    esz = torch.empty((), dtype=_CACHE_DTYPES[spec.cache_dtype] if spec.cache_dtype
+                                      else dtype).element_size()
+                    out[key] = out.get(key, 0) + spec.elements_per_page(page_size) * esz
         return out
 
     # -- requests -------------------------------------------------------------------------
@@ -132,6 +167,12 @@ class CacheManager:
             need[key] = max(0, want - max(have, first)) + sum(
                 1 for i in range(first, min(have, want)) if table[i] < 0)
         return need
+
+    def pages_for_life(self, total_tokens: int) -> dict:
+        """{group key -> pages a request of ``total_tokens`` can hold at once}: what a pool must have for the
+        request to run alone.  (A window group holds fewer while it decodes, but a request that is admitted
+        again after a preemption takes pages for all it has so far.)"""
+        return {key: pages_for(total_tokens, self.page_size) for key in self.groups}
 
     def can_ensure(self, rc: RequestCache, total_tokens: int) -> bool:
         return all(n <= self.groups[k].free_count for k, n in self.missing_pages(rc, total_tokens).items())
@@ -193,10 +234,16 @@ class CacheManager:
         return min((p.free_count for p in self.groups.values()), default=1 << 30)
 
     def view(self, idx: int, block_tables: dict):
-        """What the mixer of run entry ``idx`` gets: its pool and the step's block table of its
-        group, or its state tensors."""
-        if idx in self.pools:
-            return PagedView(self.pools[idx], block_tables[self.group_of[idx]], self.page_size)
-        if idx in self.states:
-            return SlotView(self.states[idx])
-        return None
+        """What the mixer of run entry ``idx`` gets: for a PagedKVSpec its pools and the step's block
+        table of its group, for a SlotStateSpec its state tensors; a tuple of these, in the spec's
+        order, when the mixer's ``cache_spec()`` is a tuple; None when it asked for nothing."""
+        entry = self.specs.get(idx)
+        if entry is None or idx not in self._tensors:
+            return None
+        views = []
+        for spec, tensors in zip(_as_tuple(entry), self._tensors[idx]):
+            if isinstance(spec, PagedKVSpec):
+                views.append(PagedView(tensors[0], block_tables[("paged", spec.window)], self.page_size, tensors))
+            else:
+                views.append(SlotView(list(tensors)))
+        return tuple(views) if isinstance(entry, (tuple, list)) else views[0]

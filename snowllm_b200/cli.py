@@ -88,6 +88,10 @@ def parser() -> argparse.ArgumentParser:
     g = p.add_argument_group("diagnostics")
     g.add_argument("--enforce-eager", action="store_true", help="Disable GPU graph execution.")
     g.add_argument("--stats-exact", action="store_true", help="Synchronize each step for GPU timing.")
+    g.add_argument("--enable-profiler", action="store_true",
+                   help="Run under torch.profiler with named spans and write a Chrome trace.")
+    g.add_argument("--profiler-dir", "--profile-dir", dest="profile_dir", default="~/.cache/snowllm_b200/profiler",
+                   metavar="DIR", help="Where --enable-profiler writes trace.json.")
     return p
 
 
@@ -127,16 +131,16 @@ def _tokenizer(path):
 
 def build(a):
     """(engine, tokenizer or None) from parsed arguments (the role of snowllm/cli.py:87-358)."""
+    from .config.engine import EngineConfig
     from .engine.engine import Engine
     from .loader import load
     model = load(a.model, a.dtype)
     limit = min(a.max_model_len, model.spec.max_position)
-    engine = Engine(model, num_kv_blocks=a.num_kv_blocks, max_num_seqs=a.max_num_seqs,
-                    max_model_len=limit, stop_token_ids=a.stop_token_ids, seed=a.seed,
-                    enforce_eager=a.enforce_eager, prefill_chunk=a.max_num_batched_tokens,
-                    gpu_memory_utilization=a.max_gpu_mem_util, exact_stats=a.stats_exact,
-                    page_size=a.kv_block_size)
-    return engine, _tokenizer(a.model)
+    config = EngineConfig(page_size=a.kv_block_size, num_kv_blocks=a.num_kv_blocks, max_num_seqs=a.max_num_seqs,
+                          max_model_len=limit, max_num_batched_tokens=a.max_num_batched_tokens,
+                          gpu_memory_utilization=a.max_gpu_mem_util, enforce_eager=a.enforce_eager,
+                          seed=a.seed, stop_token_ids=tuple(a.stop_token_ids), exact_stats=a.stats_exact)
+    return Engine(model, config), _tokenizer(a.model)
 
 
 def main(argv=None) -> int:
@@ -163,12 +167,19 @@ def main(argv=None) -> int:
             frequency_penalty=a.frequency_penalty, repetition_penalty=a.repetition_penalty,
             no_repeat_ngram_size=a.no_repeat_ngram_size)
         requests = [engine.add(p, params) for p in prompts]
-        engine.run()
+        if a.enable_profiler:
+            from .trace import profile_to
+            with profile_to(a.profile_dir):
+                engine.run()
+        else:
+            engine.run()
     except SnowLLMError as e:
         print(f"snowllm_b200: {e}", file=sys.stderr)
         return 1
     for r in requests:
         line = {"prompt_tokens": len(r.prompt), "tokens": r.out, "finish_reason": r.finish_reason}
+        if r.error:
+            line["error"] = r.error
         if tok is not None:
             line["text"] = tok.decode(r.out)
         print(json.dumps(line))

@@ -1031,6 +1031,14 @@ SNK_API int snk_attention_decode_tma(const void* q, const void* pool, long long 
   return 0;
 }
 
+// Queue copies of the two status words (decode, prompt) into ``host`` (pinned host memory, two ints) on
+// ``stream`` without waiting for them and without clearing them.  Not for use inside a stream capture.
+SNK_API int snk_attention_decode_status_peek(int* host, void* stream) {
+  cudaError_t e = cudaMemcpyFromSymbolAsync(host, g_fd_status, sizeof(int), 0, cudaMemcpyDeviceToHost, (cudaStream_t)stream);
+  if (e != cudaSuccess) return (int)e;
+  return (int)cudaMemcpyFromSymbolAsync(host + 1, g_fa_status, sizeof(int), 0, cudaMemcpyDeviceToHost, (cudaStream_t)stream);
+}
+
 // 0, or bit 0 / bit 1 when a block of an earlier decode / prompt launch gave up waiting for its keys;
 // reading clears it.  Synchronises the device.
 SNK_API int snk_attention_decode_status() {

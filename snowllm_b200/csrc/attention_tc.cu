@@ -3,7 +3,7 @@
 //   S = Q K^T * scale; key kp is seen by the row at position p when lo(p) <= kp <= p, lo(p) = 0 or
 //   p - window + 1; P = softmax(S) in float (base-2 exponentials of scores scaled by log2 e), rounded to
 //   bfloat16 for P V; O = P V / sum(P) accumulated in float
-//   (snowllm/ops/attention.py:14-38; snowllm/models/lfm2/layers.py:60-71)
+//   (snowllm/ops/attention_full.py:14-38; snowllm/models/lfm2/layers.py:60-71)
 //
 // One block takes 128 rows of one request and one q head and walks the keys in tiles of 128:
 //   warp 0        TMA: the block's rows of q once, then per key tile the pages that hold its keys and
@@ -463,6 +463,13 @@ SNK_API int snk_attention_prefill_tc(const void* q, long long M, const void* poo
              scale * 1.4426950408889634f);
   SNK_LAUNCH_CHECK();
   return 0;
+}
+
+// Queue a copy of the status word into ``host`` (pinned host memory, one int) on ``stream`` without waiting
+// for it and without clearing it: a caller that synchronises with the stream anyway (an event, a read-back)
+// learns of a wait that ran out at no cost.  Not for use inside a stream capture.
+SNK_API int snk_attention_tc_status_peek(int* host, void* stream) {
+  return (int)cudaMemcpyFromSymbolAsync(host, g_at_status, sizeof(int), 0, cudaMemcpyDeviceToHost, (cudaStream_t)stream);
 }
 
 // 0, or the code of the first wait that ran out in a block of an earlier launch; reading clears it.  Synchronises.

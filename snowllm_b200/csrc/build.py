@@ -65,7 +65,7 @@ def _build_dir() -> pathlib.Path:
 
 def _digest(name: str) -> str:
     h = hashlib.sha256()
-    for f in sorted(HERE.glob("*.cuh")) + [HERE / f"{name}.cu"]:
+    for f in sorted(HERE.glob("*.cuh")) + sorted(HERE.glob("*.h")) + [HERE / f"{name}.cu"]:
         h.update(f.name.encode())
         h.update(f.read_bytes())
     h.update(" ".join(ARCH_FLAGS + NVCC_FLAGS + ENV_FLAGS + EXTRA_LINK.get(name, [])).encode())
@@ -132,6 +132,11 @@ def build(names=LIBRARIES, parallel: bool = True) -> list[pathlib.Path]:
         for n, p in missing:
             _compile(n, p)
     return [p for _, p in todo]
+
+
+def is_loaded(name: str) -> bool:
+    """Whether this process has loaded the library of ``<name>.cu``."""
+    return name in _loaded
 
 
 def load(name: str) -> ctypes.CDLL:

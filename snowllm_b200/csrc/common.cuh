@@ -118,15 +118,22 @@ __device__ __forceinline__ void pdl_begin() {
   pdl_trigger();
 }
 
-// Launch with the programmatic-serialization attribute (off with SNOWLLM_B200_PDL=0 in the environment).
-inline int snk_pdl_enabled() {
+// Launch with the programmatic-serialization attribute (off with SNOWLLM_B200_PDL=0 in the environment, or
+// at run time through snk_pdl_set, which every library exports: a measurement that wants each kernel's own
+// duration switches it off, since a kernel launched early spends the wait inside its measured time).
+inline int& snk_pdl_flag() {
   static int on = -1;
+  return on;
+}
+inline int snk_pdl_enabled() {
+  int& on = snk_pdl_flag();
   if (on < 0) {
     const char* e = getenv("SNOWLLM_B200_PDL");
     on = (e && e[0] == '0') ? 0 : 1;
   }
   return on;
 }
+SNK_API void snk_pdl_set(int on) { snk_pdl_flag() = on ? 1 : 0; }
 
 // Thread-block clusters of cluster.x x cluster.y x cluster.z blocks (each grid dimension a multiple of the
 // cluster's); all ones: no clusters.

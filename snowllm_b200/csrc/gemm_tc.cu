@@ -407,6 +407,13 @@ SNK_API int snk_gemm_tc_parts(const void* A, const void* W, void* parts, int M, 
   return launch_tc<128, float, false>(map_a, map_w, parts, M, N, K, nullptr, 1, (M + TC_BM - 1) / TC_BM, splits, stream);
 }
 
+// Queue a copy of the status word into ``host`` (pinned host memory, one int) on ``stream`` without waiting
+// for it and without clearing it: a caller that synchronises with the stream anyway (an event, a read-back)
+// learns of a wait that ran out at no cost.  Not for use inside a stream capture.
+SNK_API int snk_gemm_tc_status_peek(int* host, void* stream) {
+  return (int)cudaMemcpyFromSymbolAsync(host, g_tc_status, sizeof(int), 0, cudaMemcpyDeviceToHost, (cudaStream_t)stream);
+}
+
 // 0, or the first error a block of any earlier launch recorded (a wait that ran out); reading clears
 // it.  Synchronises the device.
 SNK_API int snk_gemm_tc_status() {

@@ -498,6 +498,13 @@ SNK_API int snk_gemm_tc2(const void* A, const void* W, void* C, int M, int N, in
   return launch_tc2<bf16, false>(map_a, map_w, C, M, N, K, row_tiles, stream);
 }
 
+// Queue a copy of the status word into ``host`` (pinned host memory, one int) on ``stream`` without waiting
+// for it and without clearing it: a caller that synchronises with the stream anyway (an event, a read-back)
+// learns of a wait that ran out at no cost.  Not for use inside a stream capture.
+SNK_API int snk_gemm_tc2_status_peek(int* host, void* stream) {
+  return (int)cudaMemcpyFromSymbolAsync(host, g_t2_status, sizeof(int), 0, cudaMemcpyDeviceToHost, (cudaStream_t)stream);
+}
+
 // 0, or the first error a block of any earlier launch recorded (a wait that ran out); reading clears it.
 // tmem (may be null): the tensor-memory addresses the two blocks of the first pair were given.  Synchronises.
 SNK_API int snk_gemm_tc2_status(unsigned int* tmem) {

@@ -12,10 +12,6 @@ from dataclasses import dataclass, field
 import numpy as np
 import torch
 
-ATTENTION_CHUNK = 256          # keys per block along the sequence when rows are few
-ATTENTION_ROWS_ENOUGH = 128    # from this many rows on, rows alone fill the GPU: one chunk
-ATTENTION_TILE = 32
-
 
 @dataclass
 class StepContext:
@@ -36,9 +32,8 @@ class StepContext:
     host_positions: np.ndarray     # the same facts on the host, for launch decisions
     host_seg_start: list = field(default_factory=list)
     host_seg_len: list = field(default_factory=list)
-    _plans: dict = field(default_factory=dict)
-    _split: dict = field(default_factory=dict)   # tile rows -> (tiles, other rows, host list of them)
-    fixed_chunks: int | None = None  # a captured step: the key-chunk count its launches were built for
+    memo: dict = field(default_factory=dict)     # what parts worked out for this step (launch plans, uploaded lists)
+    capture_max_len: int | None = None           # a captured step: its launches must serve sequences up to this length
     taps: list | None = None       # when a list: parts append (name, tensor) of chosen intermediates
     pending_tokens: torch.Tensor | None = None   # int32 on the device: a token id -(i + 1) stands for entry i
 
@@ -49,69 +44,6 @@ class StepContext:
     def scratch(self, nbytes: int) -> torch.Tensor:
         """Scratch bytes for one kernel launch (stream-ordered, from torch's caching allocator)."""
         return torch.empty(max(int(nbytes), 1), dtype=torch.uint8, device=self.device)
-
-    def attention_split(self, tile_rows: int):
-        """(tiles int32 [n, 4] | None, other rows int32 [m] | None, host list of the other rows) for
-        the prompt kernel and the row-wise kernel; uploaded once per step."""
-        if tile_rows not in self._split:
-            tiles, rows = prefill_tiles(self.host_seg_start, self.host_seg_len, tile_rows)
-            dev_tiles = dev_rows = None
-            if tiles:
-                flat = torch.tensor(tiles, dtype=torch.int32).reshape(-1)
-                both = torch.cat((flat, torch.tensor(rows, dtype=torch.int32)))
-                both = both.pin_memory().to(self.device, non_blocking=True)
-                dev_tiles = both[:flat.numel()].view(-1, 4)
-                dev_rows = both[flat.numel():] if rows else None
-            self._split[tile_rows] = (dev_tiles, dev_rows, rows)
-        return self._split[tile_rows]
-
-    def attention_chunks(self, window=None, rows=None, chunk: int = ATTENTION_CHUNK) -> int:
-        """The most chunks of ``chunk`` keys that a row (of ``rows``, or of the step) spans."""
-        if self.fixed_chunks is not None:
-            return self.fixed_chunks
-        pos = self.host_positions if rows is None else self.host_positions[np.asarray(rows, dtype=np.int64)]
-        if len(pos) == 0:
-            return 1
-        lo = np.maximum(0, pos - window + 1) if window else np.zeros_like(pos)
-        return int((pos // chunk - lo // chunk).max()) + 1
-
-    def attention_plan(self, window=None, rows=None) -> tuple[int, int]:
-        """(chunk, num_chunks) for the attention kernel: with many rows one chunk per row, else
-        chunks of ATTENTION_CHUNK keys so that long sequences spread over the GPU."""
-        key = (window, None if rows is None else len(rows))
-        plan = self._plans.get(key)
-        if plan is None and self.fixed_chunks is not None:
-            whole = (1 << 30) - ((1 << 30) % ATTENTION_TILE)
-            plan = (ATTENTION_CHUNK, self.fixed_chunks)     # a captured step: always chunks of fixed count
-            self._plans[key] = plan
-        if plan is None:
-            whole = (1 << 30) - ((1 << 30) % ATTENTION_TILE)
-            pos = self.host_positions if rows is None else self.host_positions[np.asarray(rows, dtype=np.int64)]
-            if len(pos) >= ATTENTION_ROWS_ENOUGH or int(pos.max(initial=0)) < 2 * ATTENTION_CHUNK:
-                plan = (whole, 1)
-            else:
-                lo = np.maximum(0, pos - window + 1) if window else np.zeros_like(pos)
-                n = int((pos // ATTENTION_CHUNK - lo // ATTENTION_CHUNK).max()) + 1
-                plan = (ATTENTION_CHUNK, n) if n > 1 else (whole, 1)
-            self._plans[key] = plan
-        return plan
-
-
-PREFILL_MIN_ROWS = 16          # portions of at least this many rows go to the tensor-core prompt kernel
-
-
-def prefill_tiles(seg_start, seg_len, tile_rows: int, min_rows: int = PREFILL_MIN_ROWS):
-    """Split a step's rows between the prompt kernel and the row-wise kernel.  Returns
-    (tiles [[segment, first row, rows, first position], ...], other rows [row, ...])."""
-    tiles, rows, first = [], [], 0
-    for b, (start, n) in enumerate(zip(seg_start, seg_len)):
-        if n >= min_rows:
-            for r in range(0, n, tile_rows):
-                tiles.append([b, first + r, min(tile_rows, n - r), start + r])
-        else:
-            rows.extend(range(first, first + n))
-        first += n
-    return tiles, rows
 
 
 class HostStaging:

@@ -16,10 +16,11 @@ from dataclasses import asdict, dataclass, field
 import torch
 
 from ..cache import CacheManager, pages_for
-from ..config.engine import (DEFAULT_GPU_UTIL, DEFAULT_MAX_NUM_SEQS, DEFAULT_PAGE_SIZE,
-                             DEFAULT_PREFILL_CHUNK, MAX_NUM_SEQS)
-from ..errors import CapacityError, SnowLLMError
+from ..config.engine import MAX_NUM_SEQS, EngineConfig
+from ..errors import CapacityError, KernelError, SnowLLMError
+from ..ops import kernels
 from ..sampling import Sampler
+from ..trace import span
 from .request import Request, SamplingParams
 from .runner import ModelRunner, StepEntry
 from .scheduler import Scheduler
@@ -63,42 +64,61 @@ class EngineStats:
     preemptions: int
     steps: int
     accounting: dict = field(default_factory=dict)
+    step_errors: int = 0
+    failed_requests: int = 0
+    graphs: dict = field(default_factory=dict)
 
 
 class Engine:
-    def __init__(self, model, num_kv_blocks: int | None = None, max_num_seqs: int = DEFAULT_MAX_NUM_SEQS,
-                 max_model_len: int = 8192, stop_token_ids=(), seed: int | None = None,
-                 enforce_eager: bool = False, prefill_chunk: int = DEFAULT_PREFILL_CHUNK,
-                 gpu_memory_utilization: float = DEFAULT_GPU_UTIL, preempt: bool = True,
-                 exact_stats: bool = False, page_size: int = DEFAULT_PAGE_SIZE, device="cuda",
-                 overlap_steps: bool = True):
-        if not 1 <= max_num_seqs <= MAX_NUM_SEQS:
-            raise SnowLLMError(f"max_num_seqs must lie in 1..{MAX_NUM_SEQS}")
+    def __init__(self, model, config: EngineConfig | None = None, device="cuda", runner=None, sampler=None,
+                 status=None, **settings):
+        """``config``, or the same settings as keyword arguments under SnowLLM's names (``max_num_seqs``,
+        ``max_model_len``, ``prefill_chunk``, ``num_kv_blocks``, ``stop_token_ids``, ``seed``,
+        ``enforce_eager``, ``gpu_memory_utilization``, ``preempt``, ``exact_stats``, ``page_size``,
+        ``overlap_steps``, ``max_graphs``).  ``runner`` / ``sampler`` / ``status``: stand-ins for the step
+        function, the sampler and the kernels' status words; with a ``runner`` given the engine touches
+        no device itself and uses the runner's cache manager (how the host-side tests drive it)."""
+        if config is not None and settings:
+            raise SnowLLMError("give Engine a config or keyword settings, not both")
+        self.config = c = config if config is not None else EngineConfig.from_kwargs(**settings)
         self.model, self.device = model, torch.device(device)
-        self.max_num_seqs, self.max_model_len = max_num_seqs, max_model_len
-        self.enforce_eager, self.exact_stats = enforce_eager, exact_stats
-        specs = model.cache_specs()
-        if num_kv_blocks is None:
-            # max_model_len is the shared capacity in tokens; one partial page per request on top
-            num_kv_blocks = pages_for(max_model_len, page_size) + max_num_seqs
-        per_page = sum(CacheManager.bytes_per_page(specs, page_size, model.dtype).values())
-        free, total = torch.cuda.mem_get_info(self.device)
-        budget = free - int(total * (1.0 - gpu_memory_utilization))
-        if per_page * num_kv_blocks > budget:
-            raise CapacityError(
-                f"{num_kv_blocks} cache pages of {per_page} bytes need {per_page * num_kv_blocks >> 20} MiB, "
-                f"the memory budget leaves {max(budget, 0) >> 20} MiB (gpu_memory_utilization="
-                f"{gpu_memory_utilization}); lower max_model_len or num_kv_blocks")
-        self.cache = CacheManager(specs, page_size, num_kv_blocks, max_num_seqs, model.dtype, self.device)
-        self.runner = ModelRunner(model, self.cache, self.device, use_graphs=not enforce_eager)
-        self.scheduler = Scheduler(self.cache, max_num_seqs, int(prefill_chunk), max_model_len, preempt)
-        self.sampler = Sampler(stop_token_ids, seed, self.device)
+        self.max_num_seqs, self.max_model_len = c.max_num_seqs, c.max_model_len
+        self.enforce_eager, self.exact_stats = c.enforce_eager, c.exact_stats
+        if runner is None:
+            specs = model.cache_specs()
+            num_kv_blocks = c.num_kv_blocks
+            if num_kv_blocks is None:
+                # max_model_len is the shared capacity in tokens; one partial page per request on top
+                num_kv_blocks = pages_for(c.max_model_len, c.page_size) + c.max_num_seqs
+            per_page = sum(CacheManager.bytes_per_page(specs, c.page_size, model.dtype).values())
+            free, total = torch.cuda.mem_get_info(self.device)
+            ceiling = int(total * c.gpu_memory_utilization)
+            budget = free - (total - ceiling)
+            if per_page * num_kv_blocks > budget:
+                raise CapacityError(
+                    f"{num_kv_blocks} cache pages of {per_page} bytes need {per_page * num_kv_blocks >> 20} MiB, "
+                    f"the memory budget leaves {max(budget, 0) >> 20} MiB (gpu_memory_utilization="
+                    f"{c.gpu_memory_utilization}); lower max_model_len or num_kv_blocks")
+            self.cache = CacheManager(specs, c.page_size, num_kv_blocks, c.max_num_seqs, model.dtype, self.device)
+            self.runner = ModelRunner(model, self.cache, self.device, use_graphs=not c.enforce_eager,
+                                      max_graphs=c.max_graphs, graph_ceiling_bytes=ceiling)
+            self.sampler = sampler or Sampler(c.stop_token_ids, c.seed, self.device)
+            self.status = status or kernels.StatusWatch()
+            self._landing = [torch.empty(MAX_NUM_SEQS, dtype=torch.int32).pin_memory() for _ in range(2)]
+        else:
+            self.runner, self.cache = runner, runner.cache
+            self.sampler = sampler or Sampler(c.stop_token_ids, c.seed, self.device)
+            self.status = status
+            self._landing = [torch.empty(MAX_NUM_SEQS, dtype=torch.int32) for _ in range(2)]
+        self.scheduler = Scheduler(self.cache, c.max_num_seqs, c.max_num_batched_tokens, c.max_model_len,
+                                   c.preempt)
         self.acct = StepAccounting()
         self.steps = 0
-        self.overlap_steps = overlap_steps
+        self.step_errors = 0               # steps that failed: their requests ended with finish_reason "error"
+        self.last_error: str | None = None
+        self.overlap_steps = c.overlap_steps
         self._arrivals = 0
         self._flight = None                # (requests, pinned host tokens, event) of the step not yet read back
-        self._landing = [torch.empty(MAX_NUM_SEQS, dtype=torch.int32).pin_memory() for _ in range(2)]
         self._landing_turn = 0
 
     # -- the reference's names ------------------------------------------------------------
@@ -138,44 +158,83 @@ class Engine:
 
     def step(self) -> str:
         """One scheduling round and one model step: "prefill", "decode", "mixed" or "idle" ("drain" when
-        the round only read back the tokens of the step before).
+        the round only read back the tokens of the step before; "error" when the step failed).
 
         Overlapped steps (``overlap_steps``): the sampled tokens stay on the device, where the next step's
         embedding finds them, and reach the host one step late.  So the host plans and launches step k + 1
         while step k still runs; a request that ended on a stop token is found out one step late too, and
         the row it was given in between is thrown away.  Steps whose sampling looks at the generated tokens
-        (penalties, n-gram bans), and steps in which pages could run out, first read everything back."""
+        (penalties, n-gram bans), and steps in which pages could run out, first read everything back.
+
+        A step that fails (an exception on the host, a kernel that reports a wait that ran out) ends the
+        requests it touched with ``finish_reason == "error"``, gives back what they hold, records the
+        reason in ``last_error`` and leaves the engine usable: waiting requests run in the next steps
+        (snowllm/engine/async_engine.py:225-236, 283-286)."""
         t0 = time.perf_counter()
-        if self._flight is not None and self.cache.min_free_pages() < len(self.scheduler.running) + 1:
-            self._land()                   # a decoding request might be preempted: its tokens must be known
-        self.scheduler.retire_finished()
-        plan = self.scheduler.schedule()
-        if not plan:
-            if self._flight is None:
-                return "idle"
-            self._land()
-            return "drain"
+        plan = None
+        try:
+            with span("engine.step"):
+                if self._flight is not None and self.cache.min_free_pages() < len(self.scheduler.running) + 1:
+                    self._land()               # a decoding request might be preempted: its tokens must be known
+                self.scheduler.retire_finished()
+                plan = self.scheduler.schedule()
+                if not plan:
+                    if self._flight is None:
+                        return "idle"
+                    self._land()
+                    return "drain"
+                kind, prefill, decode = self._run(plan)
+        except Exception as e:  # noqa: BLE001 - whatever went wrong, the engine goes on without these requests
+            self._fail_step(e, plan)
+            return "error"
+        if self.exact_stats:
+            torch.cuda.synchronize(self.device)
+        self.acct.add(prefill, decode, time.perf_counter() - t0)
+        self.steps += 1
+        return kind
+
+    def _run(self, plan):
         entries = [StepEntry(s.request.cache, s.tokens, [s.count - 1] if s.wants_logits else [])
                    for s in plan]
         decode = sum(1 for s in plan if s.count == 1 and s.start >= len(s.request.prompt))
         logits = self.runner.step(entries)
         for s in plan:
             s.request.num_computed += s.count
+        if self.status is not None:
+            self.status.peek()
         self._land()                       # the step before: its tokens are on the host by now, or soon
         sampled = [s.request for s in plan if s.wants_logits]
         if sampled:
             if self.overlap_steps and not self.sampler.needs_history(sampled):
                 self._take_off(logits, sampled)
             else:
-                for r, tok in zip(sampled, self.sampler.sample(logits, sampled)):
+                tokens = self.sampler.sample(logits, sampled)      # reads back: the host is in step with the device
+                if self.status is not None:
+                    self.status.check()
+                for r, tok in zip(sampled, tokens):
                     if not r.done:
                         self.sampler.append(r, tok)
-        if self.exact_stats:
-            torch.cuda.synchronize(self.device)
         prefill = sum(s.count for s in plan) - decode
-        self.acct.add(prefill, decode, time.perf_counter() - t0)
-        self.steps += 1
-        return "mixed" if prefill and decode else ("prefill" if prefill else "decode")
+        return ("mixed" if prefill and decode else ("prefill" if prefill else "decode")), prefill, decode
+
+    def _fail_step(self, e: Exception, plan) -> None:
+        """End the requests a failed step touched; everything they hold comes back."""
+        self.step_errors += 1
+        self.last_error = why = f"{type(e).__name__}: {e}"
+        flight, self._flight = self._flight, None
+        hit = list(self.scheduler.running) if plan is None or isinstance(e, KernelError) \
+            else [s.request for s in plan]
+        if flight is not None:
+            # tokens of the step before that the host has not read: read them if the device still answers
+            try:
+                self._flight = flight
+                self._land()
+            except Exception:  # noqa: BLE001
+                self._flight = None
+                hit += [r for i, r in enumerate(flight[0]) if r.in_flight == i]
+        for r in hit:
+            if not r.done or r.cache is not None:
+                self.scheduler.fail(r, why)
 
     def _take_off(self, logits, sampled) -> None:
         """Sample on the device into the runner's pending tokens and start their copy to the host."""
@@ -184,6 +243,8 @@ class Engine:
         host = self._landing[self._landing_turn]
         self._landing_turn ^= 1
         host[:n].copy_(self.runner.pending_tokens[:n], non_blocking=True)
+        if self.status is not None:
+            self.status.peek()
         event = torch.cuda.Event()
         event.record()
         for i, r in enumerate(sampled):
@@ -198,6 +259,8 @@ class Engine:
         sampled, host, event = self._flight
         self._flight = None
         event.synchronize()
+        if self.status is not None:
+            self.status.check()
         tokens = host[:len(sampled)].tolist()
         for i, (r, tok) in enumerate(zip(sampled, tokens)):
             if r.in_flight == i and not r.done:
@@ -218,8 +281,14 @@ class Engine:
         return [r.out for r in reqs]
 
     def stats(self) -> EngineStats:
+        """Counters of the engine.  ``accounting`` holds tokens, seconds and rates by kind of step; the
+        seconds are device times only with ``exact_stats`` (every step then ends with a synchronise).
+        Without it a step's time is the host's time to plan and launch it, which under overlapped steps
+        is shorter than the device's: the rates then say how fast the host feeds the device."""
         return EngineStats(running=len(self.running), waiting=len(self.waiting),
                            free_slots=self.cache.slots.free_count,
                            free_kv_blocks=self.cache.min_free_pages(),
                            preemptions=self.scheduler.preemptions, steps=self.steps,
-                           accounting=self.acct.snapshot())
+                           accounting=self.acct.snapshot(), step_errors=self.step_errors,
+                           failed_requests=self.scheduler.failed,
+                           graphs=self.runner.graphs.snapshot() if hasattr(self.runner, "graphs") else {})

@@ -10,6 +10,7 @@ from ..cache import CacheManager
 from ..config.engine import DEFAULT_PAGE_SIZE
 from ..errors import CapacityError
 from ..loader import load
+from ..ops import kernels
 from .runner import ModelRunner, StepEntry
 
 ROUND_TO = 64      # a request's token count is rounded up to this when the pool is sized
@@ -25,6 +26,7 @@ class Replay:
         self.cache = CacheManager(self.model.cache_specs(), page_size, num_pages, max_requests,
                                   self.model.dtype, device)
         self.runner = ModelRunner(self.model, self.cache, device)
+        self.status = kernels.StatusWatch()
         self.live: dict = {}
 
     def step(self, entries, end=()):
@@ -43,10 +45,12 @@ class Replay:
                                     f"({self.cache.free_pages()} free)")
             batch.append(StepEntry(rc, tokens, list(e.get("want", ()))))
         logits = self.runner.step(batch)
+        self.status.peek()
         wanted = sum(len(b.want) for b in batch)
         result = logits.float().cpu() if wanted else None
         if not wanted:
             torch.cuda.current_stream().synchronize()
+        self.status.check()                # a kernel that gave up waiting: raise rather than write wrong logits
         for name in end:
             rc = self.live.pop(name, None)
             if rc is not None:

@@ -36,6 +36,7 @@ class Request:
     num_computed: int = 0               # tokens of ``tokens`` that are in the cache
     done: bool = False
     finish_reason: str | None = None    # "stop", "length", "abort", "error"
+    error: str | None = None            # with finish_reason "error": what went wrong
     preemptions: int = 0
     arrival: int = 0                    # the engine's count of requests when this one was added
     in_flight: int = -1                 # >= 0: the last sampled token is still on the device, at this place

@@ -13,10 +13,11 @@ import numpy as np
 import torch
 
 from ..cache import CacheManager, RequestCache
-from ..config.engine import MAX_NUM_SEQS
+from ..config.engine import DEFAULT_MAX_GRAPHS, MAX_NUM_SEQS
 from ..errors import CapacityError, KernelError, SnowLLMError
 from ..ops import kernels
-from .context import ATTENTION_CHUNK, HostStaging, StepContext
+from .context import HostStaging, StepContext
+from .graphs import GraphCache
 
 
 @dataclass
@@ -27,10 +28,14 @@ class StepEntry:
 
 
 class ModelRunner:
-    def __init__(self, model, cache: CacheManager, device="cuda", use_graphs: bool = False):
+    def __init__(self, model, cache: CacheManager, device="cuda", use_graphs: bool = False,
+                 max_graphs: int = DEFAULT_MAX_GRAPHS, graph_ceiling_bytes: int | None = None):
         """``use_graphs``: steps that hold one token per request and want every row's logits (decode
-        steps) are captured once per batch size as a CUDA graph and replayed
-        (snowllm/engine/runner.py:498-526, 555-581); everything else runs launch by launch."""
+        steps) are captured as CUDA graphs, one per (batch size, longest sequence rounded up to a power
+        of two), and replayed (snowllm/engine/runner.py:498-526, 555-581); everything else runs launch
+        by launch.  At most ``max_graphs`` captures are kept (the least recently used one goes), and
+        none is made that would take the device memory in use past ``graph_ceiling_bytes``: such
+        steps run launch by launch, as do all steps after a capture ran out of memory."""
         if not torch.cuda.is_available():
             raise KernelError("no CUDA device: this engine runs on the GPU only")
         if not model.bound:
@@ -46,7 +51,8 @@ class ModelRunner:
         self.tokens = 0
         self.taps = None       # set to a list to collect what parts tap (tests and debugging)
         self.use_graphs = use_graphs
-        self.graphs: dict = {}
+        self.graphs = GraphCache(max_graphs, graph_ceiling_bytes, in_use=self._bytes_in_use,
+                                 release=torch.cuda.empty_cache, oom_errors=(torch.OutOfMemoryError,))
         self.graph_pool = None
         self.graph_replays = 0
         self.eager_steps = 0
@@ -59,9 +65,10 @@ class ModelRunner:
         if not entries:
             return torch.empty(0, self.model.vocab_size, dtype=torch.float32, device=self.device)
         decode_only = all(len(e.tokens) == 1 and list(e.want) == [0] for e in entries)
+        logits = None
         if self.use_graphs and decode_only and self.taps is None:
             logits = self._graph_step(entries)
-        else:
+        if logits is None:
             ctx = self.build_context(entries)
             with torch.no_grad():
                 logits = self.model.forward(ctx, self.cache)
@@ -78,19 +85,24 @@ class ModelRunner:
                              pending_tokens=self.pending_tokens, **kw)
 
     # -- decode steps as CUDA graphs ------------------------------------------------------------
-    def _graph_step(self, entries) -> torch.Tensor:
+    def _bytes_in_use(self) -> int:
+        free, total = torch.cuda.mem_get_info(self.device)
+        return total - free
+
+    def _graph_step(self, entries):
+        """Replay the capture that serves this step (made now, if there is room for it); None when the
+        step has to run launch by launch."""
         P = self.cache.page_size
         B = len(entries)
         longest = max(e.cache.num_tokens + 1 for e in entries)
-        # the table width and the number of key chunks are part of the captured launches: both are
-        # rounded up to a power of two so that a graph serves a range of lengths
-        width = _pow2_at_least(-(-longest // P))
-        chunks = _pow2_at_least(-(-longest // ATTENTION_CHUNK))
-        key = (B, width, chunks)
-        graph = self.graphs.get(key)
+        # the table width and the number of key chunks are part of the captured launches: the longest
+        # sequence is rounded up to a power of two so that one capture serves a range of lengths
+        max_len = _pow2_at_least(longest)
+        width = -(-max_len // P)
+        key = (B, max_len)
+        graph = self.graphs.get(key, lambda: self._capture(key, entries))
         if graph is None:
-            graph = self._capture(key, entries)
-            self.graphs[key] = graph
+            return None
         graph.refresh(self.build_context(entries, max_pages=width, host_only=True))
         graph.graph.replay()
         self.graph_replays += 1
@@ -98,17 +110,18 @@ class ModelRunner:
 
     def _capture(self, key, entries):
         import dataclasses
-        B, width, chunks = key
+        B, max_len = key
+        width = -(-max_len // self.cache.page_size)
         host = self.build_context(entries, max_pages=width, host_only=True)
         graph = CapturedDecode(torch.empty(host.size, dtype=torch.int32, device=self.device), self.staging)
         graph.refresh(host)
-        ctx = self.build_context(entries, max_pages=width, into=graph.buffer, fixed_chunks=chunks)
+        ctx = self.build_context(entries, max_pages=width, into=graph.buffer, capture_max_len=max_len)
         # Warm-up outside the graph, so that nothing is created for the first time while capturing.
         # It must leave no trace: its state slots are the spare slot nobody owns; the keys and values
         # it writes are the ones the replay writes again.
         spare = torch.full_like(ctx.seg_slot, self.cache.slots.dummy)
         with torch.no_grad():
-            self.model.forward(dataclasses.replace(ctx, seg_slot=spare, _plans={}), self.cache)
+            self.model.forward(dataclasses.replace(ctx, seg_slot=spare, memo={}), self.cache)
         torch.cuda.synchronize(self.device)
         g = torch.cuda.CUDAGraph()
         if self.graph_pool is None:
@@ -141,7 +154,7 @@ class CapturedDecode:
 
 def build_context(entries: Sequence[StepEntry], cache: CacheManager, dtype, device, staging: HostStaging,
                   vocab_size: int, max_position: int = 1 << 30, taps=None, max_pages: int | None = None,
-                  into: torch.Tensor | None = None, host_only: bool = False, fixed_chunks: int | None = None,
+                  into: torch.Tensor | None = None, host_only: bool = False, capture_max_len: int | None = None,
                   pending_tokens: torch.Tensor | None = None):
     """Turn a step's entries into the flat batch on the device (one host-to-device copy).
     ``max_pages`` fixes the block-table width; ``into`` is a device buffer that already holds the
@@ -214,4 +227,4 @@ def build_context(entries: Sequence[StepEntry], cache: CacheManager, dtype, devi
         row_seg=view(2), cu_seqlens=view(3), seg_start=view(4), seg_slot=view(5), logit_rows=view(6),
         num_logit_rows=len(logit_rows), block_tables={key: tab[g] for g, key in enumerate(groups)},
         page_size=P, host_positions=positions.astype(np.int64), host_seg_start=list(starts),
-        host_seg_len=list(lens), taps=taps, pending_tokens=pending_tokens, fixed_chunks=fixed_chunks)
+        host_seg_len=list(lens), taps=taps, pending_tokens=pending_tokens, capture_max_len=capture_max_len)

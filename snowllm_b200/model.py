@@ -11,6 +11,7 @@ import torch
 from .errors import ConfigError
 from .parts.registry import lookup
 from .parts.spec import ModelSpec, PagedKVSpec, PartSpec
+from .trace import span
 
 
 def _make(family: str, spec: PartSpec, dtype):
@@ -44,6 +45,7 @@ class Model:
                     raise ConfigError(f"run entry {i} cannot read entry {entry.cache_of}'s cache: "
                                       f"{mine} against {theirs}")
         self.bound = False
+        self.bound_bytes: dict = {}        # id(part) -> {local tensor name -> bytes on the device}, set by the loader
 
     # -- structure ------------------------------------------------------------------------
     def parts(self):
@@ -87,6 +89,18 @@ class Model:
                     out[i] = spec
         return out
 
+    def weight_bytes_per_step(self, picked: dict | None = None) -> int:
+        """Bytes of weights one step reads: what each part of each run entry says it reads of the tensors
+        it declared (a layer that the run list names twice is read twice), the final norm and the head.
+        ``picked``: {run entry index -> experts picked in the step} for parts that read only those."""
+        def of(part, n=None):
+            return part.bytes_read(self.bound_bytes.get(id(part), {}), n)
+        total = of(self.embedding) + of(self.final_norm) + of(self.head)
+        for i, entry in enumerate(self.run):
+            for part in self.blocks[entry.layer].parts():
+                total += of(part, (picked or {}).get(i))
+        return total
+
     @property
     def vocab_size(self) -> int:
         return self.spec.vocab_size
@@ -94,13 +108,16 @@ class Model:
     # -- forward --------------------------------------------------------------------------
     def forward(self, ctx, cache) -> torch.Tensor:
         """Float logits [len(ctx.logit_rows), vocab] of one step."""
-        residual = self.embedding.forward(ctx)
+        with span("embedding"):
+            residual = self.embedding.forward(ctx)
         delta = None
         for i, entry in enumerate(self.run):
             owner = i if entry.cache_of is None else entry.cache_of
-            delta = self.blocks[entry.layer].forward(ctx, residual, delta, cache.view(owner, ctx.block_tables),
-                                                     owns_cache=entry.cache_of is None)
+            with span(f"run[{i}]:layer{entry.layer}"):
+                delta = self.blocks[entry.layer].forward(ctx, residual, delta, cache.view(owner, ctx.block_tables),
+                                                         owns_cache=entry.cache_of is None)
         if ctx.num_logit_rows == 0:
             return torch.empty(0, self.spec.vocab_size, dtype=torch.float32, device=residual.device)
-        x = self.final_norm.forward(ctx, residual, delta, rows=ctx.logit_rows)
-        return self.head.forward(ctx, x)
+        with span("head"):
+            x = self.final_norm.forward(ctx, residual, delta, rows=ctx.logit_rows)
+            return self.head.forward(ctx, x)

@@ -44,10 +44,12 @@ _SIGNATURES = {
         "snk_attention_prefill_tma": [P, P, LL, P, I, I, P, I, P, I, I, I, I, F, P],
         "snk_attention_decode_tma": [P, P, LL, P, I, I, P, P, P, P, P, I, I, I, I, I, I, F, P],
         "snk_attention_decode_status": [],
+        "snk_attention_decode_status_peek": [P, P],
     },
     "attention_tc": {
         "snk_attention_prefill_tc": [P, LL, P, LL, P, I, I, P, I, P, I, I, I, I, F, P],
         "snk_attention_tc_status": [],
+        "snk_attention_tc_status_peek": [P, P],
     },
     "gemm": {
         "snk_gemm_simt": [P, P, P, I, I, I, P, I, P, I, I, I, I, P],
@@ -59,12 +61,14 @@ _SIGNATURES = {
         "snk_gemm_tc": [P, P, P, I, I, I, P, I, I, I, I, P, P],
         "snk_gemm_tc_scratch_bytes": [I, I, I, I],
         "snk_gemm_tc_status": [],
+        "snk_gemm_tc_status_peek": [P, P],
         "snk_gemm_tc_parts": [P, P, P, I, I, I, P, P],
         "snk_gather_rows_bf16": [P, P, P, I, I, I, P],
     },
     "gemm_tc2": {
         "snk_gemm_tc2": [P, P, P, I, I, I, P, I, I, I, P],
         "snk_gemm_tc2_status": [P],
+        "snk_gemm_tc2_status_peek": [P, P],
     },
     "moe": {
         "snk_moe_route": [P, P, I, P, P, P, I, I, I, I, I, F, I, P],
@@ -111,7 +115,24 @@ def libraries_for(names) -> None:
     build.build(tuple(dict.fromkeys(names)))
 
 
+def set_pdl(on: bool) -> None:
+    """Switch programmatic dependent launch on or off for every library loaded so far (launches made from
+    now on; a captured graph keeps what it was captured with)."""
+    for name in list(_SIGNATURES):
+        if build.is_loaded(name):
+            f = build.load(name).snk_pdl_set
+            f.argtypes, f.restype = [c_int], None
+            f(int(bool(on)))
+
+
 _launches = 0
+
+# When a list: every wrapper appends (its name, kernels it launched, bytes it has to move, flops it has to do)
+# for each call, in launch order: the ledger that a measurement lays beside a profiler's kernel times.  The
+# bytes are the algorithmic ones (each operand and result once); None where a wrapper does not say.  Some
+# figures need a look at device data (which experts own rows, how long each row's sequence is): with the
+# ledger on, a wrapper may synchronise.  Off (None), it costs nothing.
+ledger: list | None = None
 
 
 def launch_count() -> int:
@@ -119,10 +140,18 @@ def launch_count() -> int:
     return _launches
 
 
-def check(status: int, what: str, launches: int = 1) -> None:
+def _nbytes(*tensors) -> int:
+    return sum(t.numel() * t.element_size() for t in tensors if t is not None)
+
+
+def check(status: int, what: str, launches: int = 1, work=None) -> None:
+    """``work``: a function giving (bytes, flops) of the call; evaluated only when the ledger is on."""
     global _launches
     if status == 0:
         _launches += launches
+        if ledger is not None and launches:
+            nbytes, flops = work() if work is not None else (None, None)
+            ledger.append((what, launches, nbytes, flops))
         return
     if status in _ERRORS:
         raise KernelError(f"{what}: {_ERRORS[status]}")
@@ -186,7 +215,8 @@ def embedding(ids: torch.Tensor, table: torch.Tensor, out: torch.Tensor | None =
         out = torch.empty(M, H, dtype=torch.float32, device=table.device)
     _chk(out, "embedding output", torch.float32, (M, H))
     check(fn("snk_embedding")(_ptr(ids), _ptr(pending), pending.numel() if pending is not None else 0,
-                              _ptr(table), _ptr(out), M, H, V, code_of(table.dtype), _stream()), "embedding")
+                              _ptr(table), _ptr(out), M, H, V, code_of(table.dtype), _stream()), "embedding",
+          work=lambda: (M * H * table.element_size() + _nbytes(out, ids), 0))
     return out
 
 
@@ -234,7 +264,9 @@ def add_rmsnorm(residual: torch.Tensor, delta, gamma: torch.Tensor, eps: float,
     check(fn("snk_add_rmsnorm")(_ptr(residual), _ptr(delta), _ptr(gamma), g32, _ptr(out), _ptr(rows),
                                 R, H, float(eps), code_of(dtype), _ptr(moe.y if moe else None),
                                 _ptr(moe.pair_pos if moe else None), _ptr(moe.weights if moe else None),
-                                moe.weights.shape[1] if moe else 0, _stream()), "add_rmsnorm")
+                                moe.weights.shape[1] if moe else 0, _stream()), "add_rmsnorm",
+          work=lambda: (R * H * 4 + _nbytes(out, gamma) + (_nbytes(delta) + M * H * 4 if delta is not None else 0)
+                        + ((moe.weights.shape[1] + 1) * M * H * 4 if moe else 0), 0))
     return out
 
 
@@ -256,7 +288,7 @@ def swiglu(gate_up: torch.Tensor, out: torch.Tensor | None = None, interleaved: 
         out = torch.empty(M, inter, dtype=gate_up.dtype, device=gate_up.device)
     _chk(out, "swiglu output", gate_up.dtype, (M, inter))
     check(fn("snk_swiglu")(_ptr(gate_up), _ptr(out), M, inter, int(interleaved), code_of(gate_up.dtype), _stream()),
-          "swiglu")
+          "swiglu", work=lambda: (_nbytes(gate_up, out), 0))
     return out
 
 
@@ -294,11 +326,41 @@ def qk_norm_rope_cache(qkv, q_gamma, k_gamma, eps, inv_freq, rot_dim, positions,
         _ptr(qkv), _ptr(q_gamma), _ptr(k_gamma), g32, int(has_norm), float(eps), _ptr(inv_freq),
         int(rot_dim if inv_freq is not None else 0), _ptr(positions), _ptr(row_seg), _ptr(block_table),
         block_table.shape[1], page_size, _ptr(pool), _ptr(q_out), M, num_heads, num_kv_heads, head_dim,
-        int(write_kv), code_of(dtype), _stream()), "qk_norm_rope_cache")
+        int(write_kv), code_of(dtype), _stream()), "qk_norm_rope_cache",
+        work=lambda: (2 * _nbytes(qkv), 0))
     return q_out
 
 
 ATTENTION_TILE = 32
+
+
+def _rows_attention_work(q, pool, positions, rows, window):
+    """(bytes, flops) of attention for single rows: each row reads its keys and values of every kv head
+    once (a look at the positions: only called with the ledger on)."""
+    pos = positions.cpu().long()
+    if rows is not None:
+        pos = pos[rows.cpu().long()]
+    keys = pos + 1
+    if window:
+        keys = keys.clamp(max=int(window))
+    total = int(keys.sum())
+    nh, hd = q.shape[1], q.shape[2]
+    return (total * 2 * pool.shape[2] * hd * pool.element_size() + 2 * len(pos) * nh * hd * q.element_size(),
+            4 * nh * hd * total)
+
+
+def _tiles_attention_work(q, pool, tiles, window):
+    """(bytes, flops) of attention for prompt tiles: the rows of a tile share their keys and values."""
+    t = tiles.cpu().long()
+    nh, hd = q.shape[1], q.shape[2]
+    nbytes = flops = 0
+    for _, _, n, p0 in t.tolist():
+        last = p0 + n                                   # keys the tile's last row sees
+        first = max(0, p0 - int(window) + 1) if window else 0
+        pairs = sum(min(p + 1, int(window)) if window else p + 1 for p in range(p0, p0 + n))
+        nbytes += (last - first) * 2 * pool.shape[2] * hd * pool.element_size() + 2 * n * nh * hd * q.element_size()
+        flops += 4 * nh * hd * pairs
+    return nbytes, flops
 
 
 def attention_scratch_bytes(M: int, num_heads: int, head_dim: int, num_chunks: int) -> int:
@@ -340,7 +402,7 @@ def paged_attention(q, pool, block_table, page_size, positions, row_seg, scale, 
         _ptr(q), _ptr(pool), _ptr(block_table), block_table.shape[1], page_size, _ptr(positions),
         _ptr(row_seg), _ptr(out), _ptr(scratch), served, nh, nkv, hd, int(window or 0), int(chunk),
         int(num_chunks), float(scale), code_of(dtype), _ptr(rows), _stream()), "paged_attention",
-        launches=2 if num_chunks > 1 else 1)
+        launches=2 if num_chunks > 1 else 1, work=lambda: _rows_attention_work(q, pool, positions, rows, window))
     return out
 
 
@@ -380,11 +442,12 @@ def attention_prefill(q, pool, block_table, page_size, tiles, scale, out, window
         check(fn("snk_attention_prefill_tma")(
             _ptr(q), _ptr(pool), pool.shape[0], _ptr(block_table), block_table.shape[1], page_size, _ptr(tiles),
             tiles.shape[0], _ptr(out), nh, pool.shape[2], hd, int(window or 0), float(scale), _stream()),
-            "attention_prefill_tma")
+            "attention_prefill_tma", work=lambda: _tiles_attention_work(q, pool, tiles, window))
     else:
         check(fn("snk_attention_prefill")(
             _ptr(q), _ptr(pool), _ptr(block_table), block_table.shape[1], page_size, _ptr(tiles), tiles.shape[0],
-            _ptr(out), nh, pool.shape[2], hd, int(window or 0), float(scale), _stream()), "attention_prefill")
+            _ptr(out), nh, pool.shape[2], hd, int(window or 0), float(scale), _stream()), "attention_prefill",
+            work=lambda: _tiles_attention_work(q, pool, tiles, window))
     return out
 
 
@@ -412,7 +475,7 @@ def attention_prefill_tc(q, pool, block_table, page_size, tiles, scale, out, win
     check(fn("snk_attention_prefill_tc")(
         _ptr(q), M, _ptr(pool), pool.shape[0], _ptr(block_table), block_table.shape[1], page_size, _ptr(tiles),
         tiles.shape[0], _ptr(out), nh, pool.shape[2], hd, int(window or 0), float(scale), _stream()),
-        "attention_prefill_tc")
+        "attention_prefill_tc", work=lambda: _tiles_attention_work(q, pool, tiles, window))
     return out
 
 
@@ -475,17 +538,60 @@ def attention_decode_mma(q, pool, block_table, page_size, positions, row_seg, sc
         check(fn("snk_attention_decode_tma")(
             _ptr(q), _ptr(pool), pool.shape[0], _ptr(block_table), block_table.shape[1], page_size, _ptr(positions),
             _ptr(row_seg), _ptr(rows), _ptr(out), _ptr(scratch), served, nh, pool.shape[2], hd, int(window or 0),
-            int(num_chunks), float(scale), _stream()), "attention_decode_tma")
+            int(num_chunks), float(scale), _stream()), "attention_decode_tma",
+            work=lambda: _rows_attention_work(q, pool, positions, rows, window))
     else:
         check(fn("snk_attention_decode_mma")(
             _ptr(q), _ptr(pool), _ptr(block_table), block_table.shape[1], page_size, _ptr(positions), _ptr(row_seg),
             _ptr(rows), _ptr(out), _ptr(scratch), served, nh, pool.shape[2], hd, int(window or 0), int(num_chunks),
-            float(scale), _stream()), "attention_decode_mma")
+            float(scale), _stream()), "attention_decode_mma",
+            work=lambda: _rows_attention_work(q, pool, positions, rows, window))
     if num_chunks > 1:
         check(fn("snk_attention_merge")(_ptr(scratch), _ptr(positions), _ptr(out), served, nh, hd, int(window or 0),
                                         DECODE_MMA_CHUNK, int(num_chunks), BF16, _ptr(rows), _stream()),
-              "attention_merge")
+              "attention_merge", work=lambda: (served * nh * (hd + 2) * 4 * int(num_chunks) + served * nh * hd * 2, 0))
     return out
+
+
+class StatusWatch:
+    """The error words of the kernels whose waits are bounded (TMA and tcgen05 kernels: a wait that runs out
+    makes the block give up, and its rows of the output are then not to be trusted), read where the host
+    synchronises with the stream anyway.
+
+    ``peek()`` queues, on the current stream, a copy of every loaded library's status word into pinned host
+    memory; it neither waits nor clears.  After the host has synchronised with the stream (an event, a
+    read-back), ``check()`` raises KernelError if a word is set, and clears it on the device.  The words are
+    sticky, so an error is never lost between a peek and a later check."""
+    WORDS = (("gemm_tc", "snk_gemm_tc_status_peek", 1, lambda: gemm_tc_status()),
+             ("gemm_tc2", "snk_gemm_tc2_status_peek", 1, lambda: gemm_tc2_status()[0]),
+             ("attention_tc", "snk_attention_tc_status_peek", 1, lambda: attention_tc_status()),
+             ("attention_mma", "snk_attention_decode_status_peek", 2, lambda: attention_decode_status()))
+
+    def __init__(self):
+        self.host = torch.zeros(sum(w[2] for w in self.WORDS), dtype=torch.int32).pin_memory()
+        self._base = self.host.data_ptr()
+
+    def peek(self) -> None:
+        at = 0
+        for library, peek, words, _ in self.WORDS:
+            if build.is_loaded(library):
+                check(fn(peek)(c_void_p(self._base + 4 * at), _stream()), peek, launches=0)
+            at += words
+
+    def check(self) -> None:
+        """Call after the host has synchronised with a stream position behind a ``peek``."""
+        if not bool(self.host.any()):
+            return
+        at, found = 0, []
+        for library, _, words, clear in self.WORDS:
+            codes = self.host[at:at + words].tolist()
+            if any(codes):
+                found.append(f"{library} (code {codes if words > 1 else codes[0]})")
+                clear()
+            at += words
+        self.host.zero_()
+        raise KernelError("a bounded wait ran out inside a kernel of " + ", ".join(found) +
+                          ": the step's results are not to be trusted")
 
 
 # --- short convolution -----------------------------------------------------------------
@@ -513,11 +619,24 @@ def short_conv(bcx, weight, state, cu_seqlens, seg_start, seg_slot, row_seg, out
     _chk(out, "conv output", dtype, (M, H))
     check(fn("snk_short_conv")(_ptr(bcx), _ptr(weight), w32, _ptr(state), _ptr(cu_seqlens), _ptr(seg_start),
                                _ptr(seg_slot), _ptr(row_seg), _ptr(out), M, B, H, L, code_of(dtype),
-                               _stream()), "short_conv", launches=2 if L > 1 and M != B else 1)
+                               _stream()), "short_conv", launches=2 if L > 1 and M != B else 1,
+          work=lambda: (_nbytes(bcx, out, weight) + 2 * B * max(L - 1, 0) * H * state.element_size(), 2 * M * H * (L + 2)))
     return out
 
 
 # --- matrix products -------------------------------------------------------------------
+
+def _gemm_work(rows, a, w, out, offsets):
+    """(bytes, flops) of a product: a's rows and the result once, of a grouped W only the groups that own
+    rows (a look at the offsets: only called with the ledger on)."""
+    K = a.shape[1]
+    N = w.shape[-2]
+    wbytes = _nbytes(w)
+    if offsets is not None:
+        o = offsets.cpu()
+        wbytes = wbytes // w.shape[0] * int((o[1:] > o[:-1]).sum())
+    return rows * K * a.element_size() + wbytes + _nbytes(out), 2 * rows * N * K
+
 
 def gemm_simt(a, w, out_dtype=None, out=None, a_rows=None, a_div=1, offsets=None, rows_out=None,
               max_rows_per_group=None):
@@ -547,7 +666,8 @@ def gemm_simt(a, w, out_dtype=None, out=None, a_rows=None, a_div=1, offsets=None
         raise KernelError("gemm output is the compute dtype or float32")
     check(fn("snk_gemm_simt")(_ptr(a), _ptr(w), _ptr(out), M, N, K, _ptr(a_rows), int(a_div), _ptr(offsets),
                               G, int(max_rows_per_group if grouped else M),
-                              int(out_dtype == torch.float32), code_of(dtype), _stream()), "gemm_simt")
+                              int(out_dtype == torch.float32), code_of(dtype), _stream()), "gemm_simt",
+          work=lambda: _gemm_work(M, a, w, out, offsets))
     return out
 
 
@@ -585,7 +705,8 @@ def gemm_skinny(a, w, out_dtype=None, out=None, a_rows=None, a_div=1, offsets=No
         raise KernelError("gemm output is bfloat16 or float32 (bfloat16 with swiglu)")
     check(fn("snk_gemm_skinny")(_ptr(a), _ptr(w), _ptr(out), M, N, K, _ptr(a_rows), int(a_div), _ptr(offsets),
                                 G, int(rows_hint if rows_hint is not None else M),
-                                int(out_dtype == torch.float32), int(swiglu), _stream()), "gemm_skinny")
+                                int(out_dtype == torch.float32), int(swiglu), _stream()), "gemm_skinny",
+          work=lambda: _gemm_work(M, a, w, out, offsets))
     return out
 
 
@@ -626,7 +747,7 @@ def gemm_tc(a, w, out_dtype=None, out=None, offsets=None, swiglu=False):
     scratch = torch.empty(need, dtype=torch.uint8, device=a.device) if need else None
     check(fn("snk_gemm_tc")(_ptr(a), _ptr(w), _ptr(out), M, N, K, _ptr(offsets), G, row_tiles,
                             int(out_dtype == torch.float32), int(swiglu), _ptr(scratch), _stream()), "gemm_tc",
-          launches=2 if need else 1)
+          launches=2 if need else 1, work=lambda: _gemm_work(M, a, w, out, offsets))
     return out
 
 
@@ -655,7 +776,8 @@ def gemm_tc2(a, w, out_dtype=None, out=None, offsets=None, swiglu=False):
     if out_dtype not in (torch.bfloat16, torch.float32) or (swiglu and out_dtype != torch.bfloat16):
         raise KernelError("gemm output is bfloat16 or float32 (bfloat16 with swiglu)")
     check(fn("snk_gemm_tc2")(_ptr(a), _ptr(w), _ptr(out), M, N, K, _ptr(offsets), G,
-                             int(out_dtype == torch.float32), int(swiglu), _stream()), "gemm_tc2")
+                             int(out_dtype == torch.float32), int(swiglu), _stream()), "gemm_tc2",
+          work=lambda: _gemm_work(M, a, w, out, offsets))
     return out
 
 
@@ -687,7 +809,8 @@ def gather_rows(x, rows, div=1, out=None):
     if out is None:
         out = torch.empty(R, K, dtype=x.dtype, device=x.device)
     _chk(out, "gather output", x.dtype, (R, K))
-    check(fn("snk_gather_rows_bf16")(_ptr(x), _ptr(out), _ptr(rows), int(div), R, K, _stream()), "gather_rows")
+    check(fn("snk_gather_rows_bf16")(_ptr(x), _ptr(out), _ptr(rows), int(div), R, K, _stream()), "gather_rows",
+          work=lambda: (2 * _nbytes(out), 0))
     return out
 
 
@@ -716,7 +839,8 @@ def moe_route(x, router_w, bias, top_k, norm_topk_prob, scaling):
         parts = torch.empty(nbytes, dtype=torch.uint8, device=x.device)
         planes = ctypes.c_int(0)
         check(fn("snk_gemm_tc_parts")(_ptr(x), _ptr(router_w), _ptr(parts), M, E, H, ctypes.byref(planes),
-                                      _stream()), "gemm_tc_parts")
+                                      _stream()), "gemm_tc_parts",
+              work=lambda: (_nbytes(x, router_w) + M * E * 4 * max(planes.value, 1), 2 * M * E * H))
         check(fn("snk_moe_topk")(_ptr(parts), _ptr(bias), _ptr(ids), _ptr(wts), M, E, top_k,
                                  int(bool(norm_topk_prob)), float(scaling), 0, planes.value, _stream()), "moe_topk")
         return ids, wts
@@ -730,7 +854,7 @@ def moe_route(x, router_w, bias, top_k, norm_topk_prob, scaling):
         return ids, wts
     check(fn("snk_moe_route")(_ptr(x), _ptr(router_w), w32, _ptr(bias), _ptr(ids), _ptr(wts), M, H, E,
                               top_k, int(bool(norm_topk_prob)), float(scaling), code_of(dtype), _stream()),
-          "moe_route")
+          "moe_route", work=lambda: (_nbytes(x, router_w, ids, wts), 2 * M * E * H))
     return ids, wts
 
 
@@ -762,7 +886,7 @@ def moe_route_sort(x, router_w, bias, top_k, norm_topk_prob, scaling):
     check(fn("snk_moe_route_sort")(_ptr(x), _ptr(router_w), w32, _ptr(bias), _ptr(logits), _ptr(ids), _ptr(wts),
                                    _ptr(offsets), _ptr(pair_pos), _ptr(sorted_pair), M, H, E, top_k,
                                    int(bool(norm_topk_prob)), float(scaling), code_of(dtype), _stream()),
-          "moe_route_sort", launches=2)
+          "moe_route_sort", launches=2, work=lambda: (_nbytes(x, router_w, ints, floats), 2 * M * E * H))
     return ids, wts, offsets, pair_pos, sorted_pair
 
 
@@ -803,7 +927,7 @@ def argmax(logits, out=None):
     if out is None:
         out = torch.empty(B, dtype=torch.int32, device=logits.device)
     _chk(out, "argmax output", torch.int32, (B,))
-    check(fn("snk_argmax")(_ptr(logits), _ptr(out), B, V, _stream()), "argmax")
+    check(fn("snk_argmax")(_ptr(logits), _ptr(out), B, V, _stream()), "argmax", work=lambda: (_nbytes(logits), 0))
     return out
 
 
@@ -830,5 +954,5 @@ def sample(logits, temperature, top_k, top_p, uniform, out=None):
         out = torch.empty(B, dtype=torch.int32, device=logits.device)
     _chk(out, "sample output", torch.int32, (B,))
     check(fn("snk_sample")(_ptr(logits), _ptr(temperature), _ptr(top_k), _ptr(top_p), _ptr(uniform),
-                           _ptr(out), B, V, _stream()), "sample")
+                           _ptr(out), B, V, _stream()), "sample", work=lambda: (_nbytes(logits), 0))
     return out

@@ -124,7 +124,7 @@ def attention_decode(a):
 
 
 def attention_prefill(a):
-    from ..engine.context import prefill_tiles
+    from ..parts.attention_plan import prefill_tiles
     pool, bt, gen = _cache(a, a.tokens, 1)
     q = bf16(a.tokens, a.heads, a.head_dim, gen=gen)
     tc = not a.rowwise and kernels.attention_prefill_tc_ok(q, a.page_size)       # --rowwise: the mma.sync kernel

@@ -11,9 +11,9 @@ from __future__ import annotations
 
 import torch
 
-from ..engine.context import PREFILL_MIN_ROWS
 from ..errors import ConfigError
 from ..ops import kernels, linear
+from . import attention_plan as plan
 from .base import Part
 from .registry import lookup, register_mixer
 from .spec import INIT_ONES, KEEP_SMALL, PagedKVSpec, TensorSpec
@@ -70,14 +70,14 @@ class Attention(Part):
             self.num_kv_heads, self.head_dim, write_kv=owns_cache)
         o = torch.empty(ctx.M, self.num_heads * self.head_dim, dtype=q.dtype, device=q.device)
         rows = rows_host = None
-        if kernels.attention_prefill_ok(q) and max(ctx.host_seg_len) >= PREFILL_MIN_ROWS:
+        if kernels.attention_prefill_ok(q) and max(ctx.host_seg_len) >= plan.PREFILL_MIN_ROWS:
             # prompt portions on the tensor cores; rows of short segments (decoded tokens) row by row
             if kernels.attention_prefill_tc_ok(q, cache.page_size):
-                tiles, rows, rows_host = ctx.attention_split(kernels.PREFILL_TC_TILE_ROWS)
+                tiles, rows, rows_host = plan.split(ctx, kernels.PREFILL_TC_TILE_ROWS)
                 kernels.attention_prefill_tc(q, cache.pool, cache.block_table, cache.page_size, tiles, self.scale,
                                              o, window=self.window)
             else:
-                tiles, rows, rows_host = ctx.attention_split(kernels.PREFILL_TILE_ROWS)
+                tiles, rows, rows_host = plan.split(ctx, kernels.PREFILL_TILE_ROWS)
                 kernels.attention_prefill(q, cache.pool, cache.block_table, cache.page_size, tiles, self.scale, o,
                                           window=self.window)
             if not rows_host:
@@ -85,14 +85,14 @@ class Attention(Part):
         served = ctx.M if rows_host is None else len(rows_host)
         if kernels.attention_decode_mma_ok(q, self.num_kv_heads):
             # rows of decoded tokens on the tensor cores: keys in chunks of 256, merged in order
-            num_chunks = ctx.attention_chunks(self.window, rows_host, kernels.DECODE_MMA_CHUNK)
+            num_chunks = plan.chunks(ctx, self.window, rows_host, kernels.DECODE_MMA_CHUNK)
             scratch = ctx.scratch(kernels.attention_scratch_bytes(
                 served, self.num_heads, self.head_dim, num_chunks)) if num_chunks > 1 else None
             kernels.attention_decode_mma(q, cache.pool, cache.block_table, cache.page_size, ctx.positions,
                                          ctx.row_seg, self.scale, num_chunks, o, window=self.window,
                                          scratch=scratch, rows=rows)
             return linear(o, self.wo, out_dtype=torch.float32)
-        chunk, num_chunks = ctx.attention_plan(self.window, rows_host)
+        chunk, num_chunks = plan.plan(ctx, self.window, rows_host)
         scratch = ctx.scratch(kernels.attention_scratch_bytes(
             served, self.num_heads, self.head_dim, num_chunks)) if num_chunks > 1 else None
         kernels.paged_attention(q, cache.pool, cache.block_table, cache.page_size, ctx.positions,

@@ -44,3 +44,10 @@ class Part:
     def parts(self):
         """Parts nested in this one (their tensors are declared and bound through it)."""
         return ()
+
+    def bytes_read(self, bound: Mapping[str, int], picked: int | None = None) -> int:
+        """Bytes of its weights that one step reads, for roofline arithmetic.  ``bound``: {local tensor name ->
+        bytes as kept on the device} of what this part declared.  The default is every tensor once; a part
+        that reads only some of its weights (routed experts: ``picked`` of them were chosen in the step)
+        says so here."""
+        return sum(bound.values())

@@ -5,21 +5,28 @@ The float residual sum is fused into the norm that follows it, so a block takes 
 previous block left and returns its own last delta; the model adds the final one."""
 from __future__ import annotations
 
+from ..trace import span
 from .registry import register_block
 
 
 class PreNormBlock:
     def __init__(self, mixer, ffn, mixer_norm, ffn_norm):
         self.mixer, self.ffn, self.mixer_norm, self.ffn_norm = mixer, ffn, mixer_norm, ffn_norm
+        self._names = tuple(f"{what}:{type(part).__name__}" for what, part in
+                            (("norm", mixer_norm), ("mixer", mixer), ("norm", ffn_norm), ("ffn", ffn)))
 
     def parts(self):
         return (self.mixer_norm, self.mixer, self.ffn_norm, self.ffn)
 
     def forward(self, ctx, residual, delta, cache, owns_cache=True):
-        x = self.mixer_norm.forward(ctx, residual, delta)
-        delta = self.mixer.forward(ctx, x, cache, owns_cache)
-        x = self.ffn_norm.forward(ctx, residual, delta)
-        return self.ffn.forward(ctx, x)
+        with span(self._names[0]):
+            x = self.mixer_norm.forward(ctx, residual, delta)
+        with span(self._names[1]):
+            delta = self.mixer.forward(ctx, x, cache, owns_cache)
+        with span(self._names[2]):
+            x = self.ffn_norm.forward(ctx, residual, delta)
+        with span(self._names[3]):
+            return self.ffn.forward(ctx, x)
 
 
 register_block("prenorm", PreNormBlock)

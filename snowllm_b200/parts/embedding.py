@@ -24,6 +24,9 @@ class Embedding(Part):
     def bind(self, tensors):
         self.weight = tensors["weight"]
 
+    def bytes_read(self, bound, picked=None):
+        return 0        # a step gathers one row per token: nothing beside the matrices
+
     def forward(self, ctx):
         """The float residual stream [M, H] of the step's tokens."""
         return kernels.embedding(ctx.token_ids, self.weight, pending=ctx.pending_tokens)
@@ -45,6 +48,10 @@ class LinearHead(Part):
 
     def bind(self, tensors):
         self.weight = tensors["weight"]
+
+    def bytes_read(self, bound, picked=None):
+        # tied: nothing was declared here, yet the whole table is read as the head
+        return self.weight.numel() * self.weight.element_size() if self.weight is not None else 0
 
     def forward(self, ctx, x):
         return linear(x, self.weight, out_dtype=torch.float32)

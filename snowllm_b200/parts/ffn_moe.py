@@ -61,6 +61,13 @@ class SigmoidMoE(Part):
         self.interleaved = self.intermediate_size % 8 == 0
         self.w13 = interleave_gate_up(gate, up) if self.interleaved else torch.cat((gate, up), 1).contiguous()
 
+    def bytes_read(self, bound, picked=None):
+        """Router and bias whole; of the experts only those that were picked (``picked`` None: all)."""
+        experts = sum(n for name, n in bound.items() if name.split(".")[0] in ("gate", "up", "down", "gate_up"))
+        rest = sum(bound.values()) - experts
+        share = 1.0 if picked is None else min(picked, self.num_experts) / self.num_experts
+        return rest + int(experts * share)
+
     def route(self, x):
         return kernels.moe_route(x, self.router, self.bias, self.top_k, self.norm_topk_prob,
                                  self.routed_scaling_factor)

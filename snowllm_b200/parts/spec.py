@@ -82,12 +82,41 @@ class ModelSpec:
 
 @dataclass(frozen=True)
 class PagedKVSpec:
-    """Keys and values that grow with the sequence, kept in pages.  ``window`` None keeps
-    every key; an integer keeps the last ``window`` positions (the query's own included),
-    so pages that fall wholly behind the window are given back."""
+    """Rows that grow with the sequence, kept in pages.  ``window`` None keeps every row; an integer keeps
+    the last ``window`` positions (the query's own included), so pages that fall wholly behind the window
+    are given back.
+
+    The spec chooses the layout of its pools (``pool_shapes``); the cache manager only makes them.
+    Keys and values of one width lie in one tensor [pages, 2, kv heads, page_size, head_dim].  With
+    ``v_head_dim`` of another width they are two tensors [pages, kv heads, page_size, width]; with
+    ``v_head_dim`` 0 there is the key tensor alone (a latent row per position, a cache of keys only).
+    ``cache_dtype`` None keeps the rows in the compute dtype; "float32" or "bfloat16" fixes it."""
     num_kv_heads: int
     head_dim: int
     window: int | None = None
+    v_head_dim: int | None = None
+    cache_dtype: str | None = None
+
+    @property
+    def fused(self) -> bool:
+        return self.v_head_dim is None or self.v_head_dim == self.head_dim
+
+    def pool_shapes(self, num_pages: int, page_size: int) -> tuple:
+        if self.fused:
+            return ((num_pages, 2, self.num_kv_heads, page_size, self.head_dim),)
+        shapes = [(num_pages, self.num_kv_heads, page_size, self.head_dim)]
+        if self.v_head_dim:
+            shapes.append((num_pages, self.num_kv_heads, page_size, self.v_head_dim))
+        return tuple(shapes)
+
+    def elements_per_page(self, page_size: int) -> int:
+        total = 0
+        for shape in self.pool_shapes(1, page_size):
+            n = 1
+            for d in shape[1:]:
+                n *= d
+            total += n
+        return total
 
 
 @dataclass(frozen=True)

@@ -68,6 +68,8 @@ def load_into(model, read, names, meta, has, device) -> None:
         by_part.setdefault(id(part), (part, {}))[1][spec.local] = t
     for part, tensors in by_part.values():
         part.bind(tensors)
+    model.bound_bytes = {key: {local: t.numel() * t.element_size() for local, t in tensors.items()}
+                         for key, (_, tensors) in by_part.items()}
     model.finish_binding()
 
 

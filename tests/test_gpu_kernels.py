@@ -725,7 +725,7 @@ def test_gemm_tc_grouped_after_gather(K):
 def test_attention_prefill_tiles(K, nh, nkv, hd, P, window):
     """The tensor-core prompt kernel: a portion from position 0, one in the middle of a long request
     (not aligned to tiles or pages), a short one; pages scattered; unwritten cache entries are NaN."""
-    from snowllm_b200.engine.context import prefill_tiles
+    from snowllm_b200.parts.attention_plan import prefill_tiles
     torch.manual_seed(40)
     dtype = torch.bfloat16
     starts, lens = [0, 333, 700], [200, 150, 17]
@@ -778,7 +778,7 @@ def test_attention_prefill_tiles(K, nh, nkv, hd, P, window):
 def test_attention_prefill_tc_tiles(K, nh, nkv, P, window):
     """The tcgen05 prompt kernel (head size 64): a portion from position 0, one in the middle of a long request
     (not aligned to tiles or pages), a short one; pages scattered; unwritten cache entries are NaN."""
-    from snowllm_b200.engine.context import prefill_tiles
+    from snowllm_b200.parts.attention_plan import prefill_tiles
     torch.manual_seed(42)
     dtype, hd = torch.bfloat16, 64
     starts, lens = [0, 333, 700], [300, 150, 17]

@@ -44,11 +44,8 @@ def step_mixer(part, dtype, xs, cuts, page_size=16, pages=64):
     (requests with steps left go into each step together); returns outputs per request."""
     from snowllm_b200.cache import CacheManager
     cache = CacheManager({0: part.cache_spec()}, page_size, pages, len(xs), dtype, "cuda")
-    for pool in cache.pools.values():
-        pool.fill_(float("nan"))
-    for st in cache.states.values():
-        for t in st:
-            t.fill_(float("nan"))
+    for t in cache.paged_tensors() + cache.state_tensors():
+        t.fill_(float("nan"))
     rcs = [cache.admit() for _ in xs]
     done = [0] * len(xs)
     outs = [[] for _ in xs]

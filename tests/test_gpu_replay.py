@@ -34,12 +34,11 @@ def requests_for(cfg, seed=0):
 def poison_free(rp):
     """Fill every free page and every free state slot with NaN."""
     free = [p for pool in rp.cache.groups.values() for p in pool._free]
-    for pool in rp.cache.pools.values():
+    for pool in rp.cache.paged_tensors():
         pool[free] = float("nan")
     free_slots = list(rp.cache.slots._free) + [rp.cache.slots.dummy]
-    for st in rp.cache.states.values():
-        for t in st:
-            t[free_slots] = float("nan")
+    for t in rp.cache.state_tensors():
+        t[free_slots] = float("nan")
 
 
 def run_in_process(model_dir, dtype, steps, max_tokens, page_size=16, poison=False, stats=None):

@@ -105,27 +105,75 @@ def test_pages_run_out_the_last_admitted_is_preempted_and_replayed():
     assert cm.free_pages()[("paged", None)] == 4 and cm.slots.free_count == 2
 
 
-def test_one_request_and_no_page_left_is_a_capacity_error():
+def test_request_that_the_pool_cannot_hold_alone_is_refused_when_added():
+    """Prompt plus every token it may generate must fit the pool with nothing else in it; the refusal
+    touches nothing else."""
     cm, s = make(num_pages=2, max_seqs=2, budget=100, max_len=100)
-    r = req(31, new=20)
-    s.add(r)
-    with pytest.raises(CapacityError, match="cannot hold one request"):
-        run(s)
+    ok = req(20, new=12)                              # 32 tokens: the two pages exactly
+    s.add(ok)
+    with pytest.raises(CapacityError, match="even alone.*4 pages"):
+        s.add(req(31, new=20))
+    with pytest.raises(CapacityError, match="even alone"):
+        s.add(req(40, new=1))
+    assert list(s.waiting) == [ok]
+    run(s)
+    assert ok.done and ok.finish_reason == "length" and len(ok.out) == 12
+    assert cm.free_pages()[("paged", None)] == 2 and cm.slots.free_count == 2
 
 
-def test_prompt_that_can_never_fit_is_a_capacity_error():
-    cm, s = make(num_pages=2, budget=100)
-    s.add(req(40))
-    with pytest.raises(CapacityError, match="cannot admit"):
-        s.schedule()
+def test_lone_request_without_a_page_ends_in_error_and_the_queue_goes_on():
+    """What add() cannot foresee (here: the pool shrank under a running request) ends that request with
+    finish_reason "error"; it gives everything back and the next request runs."""
+    cm, s = make(num_pages=3, max_seqs=1, budget=100, max_len=100)
+    a, b = req(31, new=10), req(10, new=2)
+    s.add(a)
+    s.add(b)
+    fake_step(s, s.schedule())                        # a's prompt: two pages, one token out
+    held = cm.groups[("paged", None)].alloc(1)        # someone else takes the last page
+    plan = s.schedule()                               # position 31 fits a's second page
+    fake_step(s, plan)
+    plan = s.schedule()                               # position 32 needs a third page: none, and a runs alone
+    assert a.done and a.finish_reason == "error" and "cannot hold one request" in a.error
+    assert a.cache is None and s.failed == 1
+    assert [x.request for x in plan] == [b]           # admitted in the same round, into a's slot
+    cm.groups[("paged", None)].release(held)
+    fake_step(s, plan)
+    run(s)
+    assert b.done and b.finish_reason == "length"
+    assert cm.free_pages()[("paged", None)] == 3 and cm.slots.free_count == 1
 
 
-def test_preemption_off_raises_instead():
+def test_preemption_off_ends_the_request_that_found_no_page():
     cm, s = make(num_pages=4, max_seqs=2, budget=100, preempt=False)
-    s.add(req(30, new=8))
-    s.add(req(30, new=8))
-    with pytest.raises(CapacityError, match="preemption is off"):
-        run(s)
+    a, b = req(30, new=8), req(30, new=8)
+    s.add(a)
+    s.add(b)
+    run(s)
+    failed = [r for r in (a, b) if r.finish_reason == "error"]
+    assert len(failed) == 1 and "preemption is off" in failed[0].error
+    other = b if failed[0] is a else a
+    assert other.finish_reason == "length" and len(other.out) == 8
+    assert cm.free_pages()[("paged", None)] == 4 and cm.slots.free_count == 2
+
+
+def test_decode_pass_takes_turns_when_the_budget_is_below_the_number_of_decoders():
+    cm, s = make(num_pages=32, max_seqs=4, budget=16, max_len=64)
+    reqs = [req(4, new=6) for _ in range(4)]
+    for r in reqs:
+        s.add(r)
+    fake_step(s, s.schedule())                        # all four prompts in one step
+    assert all(len(r.out) == 1 for r in reqs)
+    s.max_num_batched_tokens = 3                      # fewer tokens per step than decoding requests
+    served = []
+    for _ in range(4):
+        plan = s.schedule()
+        assert len(plan) == 3 and all(x.count == 1 for x in plan)
+        served.append([reqs.index(x.request) for x in plan])
+        fake_step(s, plan)
+    assert served == [[0, 1, 2], [3, 0, 1], [2, 3, 0], [1, 2, 3]]
+    assert all(len(r.out) == 4 for r in reqs)         # everyone advanced alike
+    run(s)
+    assert all(r.finish_reason == "length" for r in reqs)
 
 
 def test_abort_gives_everything_back():
