@@ -17,15 +17,16 @@ ROUND_TO = 64      # a request's token count is rounded up to this when the pool
 
 
 class Replay:
-    def __init__(self, model_dir, dtype: str, max_tokens: int, max_requests: int = 8,
-                 page_size: int = DEFAULT_PAGE_SIZE, device="cuda"):
+    def __init__(self, model, dtype: str, max_tokens: int, max_requests: int = 8,
+                 page_size: int = DEFAULT_PAGE_SIZE, device="cuda", use_graphs: bool = False):
+        """``model``: a model folder, or a model whose weights are bound already."""
         if ROUND_TO % page_size:
             raise ValueError(f"page_size {page_size} must divide {ROUND_TO}")
-        self.model = load(model_dir, dtype, device)
+        self.model = model if hasattr(model, "forward") else load(model, dtype, device)
         num_pages = -(-max_tokens // ROUND_TO) * (ROUND_TO // page_size)
         self.cache = CacheManager(self.model.cache_specs(), page_size, num_pages, max_requests,
                                   self.model.dtype, device)
-        self.runner = ModelRunner(self.model, self.cache, device)
+        self.runner = ModelRunner(self.model, self.cache, device, use_graphs=use_graphs)
         self.status = kernels.StatusWatch()
         self.live: dict = {}
 

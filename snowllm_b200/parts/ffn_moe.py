@@ -78,6 +78,7 @@ class SigmoidMoE(Part):
             x, self.router, self.bias, self.top_k, self.norm_topk_prob, self.routed_scaling_factor)
         if ctx is not None:
             ctx.tap("moe_route", ids)
+            ctx.tap("moe_route_input", x)
         cap = min(M, M * k)          # an expert gets a token at most once
         act = grouped_linear_swiglu(x, self.w13, offsets, M * k, cap, sorted_pair, k, self.interleaved)
         y = grouped_linear(act, self.w2, offsets, M * k, cap, out_dtype=torch.float32)

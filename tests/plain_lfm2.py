@@ -9,6 +9,15 @@ Anchoring.  SnowLLM's own model code cannot be imported or compiled on a CPU (it
 modules load a closed HIP kernel library at import time), so this file rests on
 the formulas alone.  Each function cites the place in SnowLLM/SnowLLM (path within
 that project) from which its formula is read.
+
+Rounding variant.  Inside ``with stores_rounded_to(torch.bfloat16):`` every intermediate
+that a bfloat16 engine keeps in bfloat16 between two kernels is rounded to it (``_store``):
+norm outputs, the products that do not feed the residual stream (in_proj, q/k/v, the
+SwiGLU activation), the conv's g = B*x and y = C*conv, q and k after head norm and
+rotation, the attention output.  The arithmetic between two stores stays float32, as do
+the residual stream, the products that feed it, the router and the logits.  A bfloat16
+run is compared with this variant, so that what is left is accumulation order, not the
+roundings themselves.  Outside the ``with`` nothing is rounded.
 """
 from __future__ import annotations
 
@@ -19,6 +28,31 @@ import struct
 
 import torch
 import torch.nn.functional as F
+
+_STORE_DTYPE = None
+
+
+class stores_rounded_to:
+    """Context manager: round what a reduced-precision engine stores between kernels to ``dtype``
+    (None or float32: round nothing)."""
+
+    def __init__(self, dtype):
+        self.dtype = None if dtype in (None, torch.float32, "float32") else \
+            (torch.bfloat16 if dtype == "bfloat16" else dtype)
+
+    def __enter__(self):
+        global _STORE_DTYPE
+        self.before, _STORE_DTYPE = _STORE_DTYPE, self.dtype
+
+    def __exit__(self, *exc):
+        global _STORE_DTYPE
+        _STORE_DTYPE = self.before
+
+
+def _store(x):
+    """A value as it comes back after being kept in the engine's storage dtype."""
+    return x if _STORE_DTYPE is None else x.to(_STORE_DTYPE).float()
+
 
 _ST_DTYPES = {
     "F32": torch.float32, "BF16": torch.bfloat16, "F16": torch.float16,
@@ -75,6 +109,11 @@ def rmsnorm(x, weight, eps):
     return x * torch.rsqrt(x.square().mean(-1, keepdim=True) + eps) * weight.float()
 
 
+def rmsnorm_stored(x, weight, eps):
+    """The norm of the residual stream as the layer after it reads it (one store)."""
+    return _store(rmsnorm(x, weight, eps))
+
+
 def rope_angles(positions, hd, theta):
     """ang[m, i] = pos[m] * theta^(-2i/hd), float32
     (snowllm/models/lfm2/layers.py:116-117; snowllm/ops/rope.py:11-24)."""
@@ -99,11 +138,11 @@ def short_conv_mixer(u, w_in, w_conv, w_out):
     current token); y = C*conv; out_proj(y).  u: [T, H]; w_conv: [H, L]."""
     T, H = u.shape
     L = w_conv.shape[-1]
-    bcx = u @ w_in.T
+    bcx = _store(u @ w_in.T)
     B, C, x = bcx.chunk(3, dim=-1)
-    g = B * x
+    g = _store(B * x)
     conv = F.conv1d(g.T[None], w_conv.reshape(H, 1, L), padding=L - 1, groups=H)[0, :, :T].T
-    return (C * conv) @ w_out.T
+    return _store(C * conv) @ w_out.T
 
 
 def attention_mixer(u, wq, wk, wv, wo, q_norm, k_norm, eps, n_heads, n_kv, hd, theta,
@@ -115,13 +154,13 @@ def attention_mixer(u, wq, wk, wv, wo, q_norm, k_norm, eps, n_heads, n_kv, hd, t
     last ``window`` keys, the query's own included."""
     T = u.shape[0]
     pos = torch.arange(T, device=u.device) if positions is None else positions
-    q = (u @ wq.T).view(T, n_heads, hd)
-    k = (u @ wk.T).view(T, n_kv, hd)
-    v = (u @ wv.T).view(T, n_kv, hd)
+    q = _store(u @ wq.T).view(T, n_heads, hd)
+    k = _store(u @ wk.T).view(T, n_kv, hd)
+    v = _store(u @ wv.T).view(T, n_kv, hd)
     q = rmsnorm(q, q_norm, eps)
     k = rmsnorm(k, k_norm, eps)
     ang = rope_angles(pos, hd, theta)
-    q, k = apply_rope(q, ang), apply_rope(k, ang)
+    q, k = _store(apply_rope(q, ang)), _store(apply_rope(k, ang))
     group = n_heads // n_kv
     q = q.view(T, n_kv, group, hd)
     scores = torch.einsum("tghd,sgd->tghs", q, k) * hd ** -0.5
@@ -131,12 +170,17 @@ def attention_mixer(u, wq, wk, wv, wo, q_norm, k_norm, eps, n_heads, n_kv, hd, t
         mask = mask | (i[None, :] <= i[:, None] - window)
     scores = scores.masked_fill(mask[:, None, None, :], float("-inf"))
     out = torch.einsum("tghs,sgd->tghd", scores.softmax(-1), v).reshape(T, n_heads * hd)
-    return out @ wo.T
+    return _store(out) @ wo.T
 
 
 def dense_ffn(u, w1, w3, w2):
-    """SwiGLU: w2(silu(w1 u) * w3 u) (snowllm/models/lfm2/layers.py:81-88)."""
-    return (F.silu(u @ w1.T) * (u @ w3.T)) @ w2.T
+    """SwiGLU: w2(silu(w1 u) * w3 u) (snowllm/models/lfm2/layers.py:81-88).  Rounding variant: the
+    activation is stored once; a width that is no multiple of 8 makes the engine store gate and up
+    first (its fused store needs gate and up rows interleaved by 8)."""
+    g, p = u @ w1.T, u @ w3.T
+    if w1.shape[0] % 8:
+        g, p = _store(g), _store(p)
+    return _store(F.silu(g) * p) @ w2.T
 
 
 def route(u, gate_w, expert_bias, top_k, norm_topk_prob, scaling, forced_ids=None, margins=None):
@@ -232,13 +276,13 @@ def hidden_states(cfg, tensors, ids, forced_routes=None, margins=None):
     x = table[torch.as_tensor(ids, dtype=torch.long, device=table.device)].float()
     for i in range(cfg["num_hidden_layers"]):
         p = f"model.layers.{i}."
-        x = x + layer_mixer(cfg, tensors, i, rmsnorm(x, tensors[p + "operator_norm.weight"], eps))
+        x = x + layer_mixer(cfg, tensors, i, rmsnorm_stored(x, tensors[p + "operator_norm.weight"], eps))
         got = []
-        x = x + layer_ffn(cfg, tensors, i, rmsnorm(x, tensors[p + "ffn_norm.weight"], eps),
+        x = x + layer_ffn(cfg, tensors, i, rmsnorm_stored(x, tensors[p + "ffn_norm.weight"], eps),
                           None if forced_routes is None else forced_routes.get(i), got)
         if margins is not None and got:
             margins[i] = got[0]
-    return rmsnorm(x, tensors["model.embedding_norm.weight"], eps)
+    return rmsnorm_stored(x, tensors["model.embedding_norm.weight"], eps)
 
 
 def logits(cfg, tensors, ids, forced_routes=None, margins=None):

@@ -954,3 +954,111 @@ def test_attention_decode_mma(K, nh, nkv, hd, P, window):
         got = out[5].float().cpu().view(nh, hd)
         for h in range(nh):
             assert (got[h] - vs[5][far, h // (nh // nkv)]).abs().max() < 0.02
+
+
+# ---------------------------------------------------------------------------------------------
+def paged_sequence(dtype, N, nkv, hd, P, seed, scale=1.0):
+    """A sequence of N random keys and values in scattered pages: (pool with NaN where nothing was written,
+    block table as a list, keys, values as float on the GPU)."""
+    g = torch.Generator(device="cuda").manual_seed(seed)
+    pages = -(-N // P)
+    k = (torch.randn(pages * P, nkv, hd, device="cuda", generator=g) * scale).to(dtype)
+    v = torch.randn(pages * P, nkv, hd, device="cuda", generator=g).to(dtype)
+    table = torch.randperm(pages + 3, generator=torch.Generator().manual_seed(seed))[:pages]
+    pool = torch.full((pages + 3, 2, nkv, P, hd), float("nan"), dtype=dtype, device="cuda")
+    pool[table.cuda(), 0] = k.view(pages, P, nkv, hd).transpose(1, 2)
+    pool[table.cuda(), 1] = v.view(pages, P, nkv, hd).transpose(1, 2)
+    if N % P:                                                  # the last page's tail was never written
+        pool[int(table[-1]), :, :, N % P:] = float("nan")
+    return pool, table.tolist(), k[:N].float(), v[:N].float()
+
+
+def attention_from_pages(q, pool, table, P, positions, scale):
+    """float64 attention of rows q [M, nh, hd] at ``positions``, recomputed from the cache pages themselves
+    (the check of tests/test_lfm2_long_attention.py:28-47 in SnowLLM)."""
+    M, nh, hd = q.shape
+    nkv = pool.shape[2]
+    kv = pool[torch.tensor(table, device="cuda")].double()         # [pages, 2, nkv, P, hd]
+    k = kv[:, 0].transpose(1, 2).reshape(-1, nkv, hd)
+    v = kv[:, 1].transpose(1, 2).reshape(-1, nkv, hd)
+    out = torch.zeros(M, nh, hd, dtype=torch.float64, device="cuda")
+    for m, p in enumerate(positions):
+        for g in range(nkv):
+            heads = slice(g * (nh // nkv), (g + 1) * (nh // nkv))
+            s = (q[m, heads].double().cuda() @ k[:p + 1, g].T) * scale
+            out[m, heads] = torch.softmax(s, -1) @ v[:p + 1, g]
+    return out.reshape(M, nh * hd)
+
+
+def rel_l2(got, want):
+    got, want = got.double().cuda(), want.double().cuda()
+    return float(((got - want).norm(dim=-1) / want.norm(dim=-1).clamp_min(1e-30)).max())
+
+
+@pytest.mark.parametrize("N", [8192, 33000])
+def test_attention_over_long_contexts(K, N):
+    """8,192 and 33,000 cached keys (the lengths the measurements run and beyond the longest prompts of the
+    dense configurations): decoded rows over 32 and 129 chunks of keys, exactly as many chunks as needed and
+    rounded up as a captured step has them; the last rows of a 2,048-row and of an 8,192-row portion through
+    the tcgen05 prompt kernel (16 to 258 key tiles per block); head size 128 through the mma.sync prompt
+    kernel.  Each against float64 attention recomputed from the cache pages, rel-L2 < 0.005 per row."""
+    dtype, nh, nkv, hd, P = torch.bfloat16, 8, 2, 64, 16
+    scale = hd ** -0.5
+    pool, table, k, v = paged_sequence(dtype, N, nkv, hd, P, seed=N)
+    other_pool_rows = N - 300
+    # decoded rows: two requests in one launch, the long one and a shorter one in the same pool's pages
+    bt = i32([table, table])
+    positions = [N - 1, other_pool_rows - 1]
+    q = rnd(dtype, 2, nh, hd)
+    want = attention_from_pages(q, pool, table, P, positions, scale)
+    need = (N - 1) // 256 + 1
+    for chunks in (need, 1 << (need - 1).bit_length()):
+        out = torch.full((2, nh * hd), float("nan"), dtype=dtype, device="cuda")
+        K.attention_decode_mma(dev(q, dtype), pool, bt, P, i32(positions), i32([0, 1]), scale, chunks, out)
+        assert out.isfinite().all()
+        assert rel_l2(out, want) < 0.005, f"{chunks} chunks"
+    assert K.attention_decode_status() == 0
+    # the row-wise kernel (what float32 and other head sizes use) over the same keys, in chunks and whole
+    for chunk, chunks in ((256, need), (None, 1)):
+        out = K.paged_attention(dev(q, dtype), pool, bt, P, i32(positions), i32([0, 1]), scale, chunk=chunk,
+                                num_chunks=chunks)
+        assert rel_l2(out, want) < 0.005
+    # a far key among thousands: the last row's query points at key 3, in the first of all chunks
+    direction = F.normalize(torch.randn(hd), dim=0)
+    page, slot = table[0], 3
+    saved = pool[page, 0, :, slot].clone()
+    pool[page, 0, :, slot] = (direction * 24).to(dtype).cuda()
+    q_far = q.clone()
+    q_far[0] = (direction * 24).to(dtype).float()
+    out = torch.zeros(2, nh * hd, dtype=dtype, device="cuda")
+    K.attention_decode_mma(dev(q_far, dtype), pool, bt, P, i32(positions), i32([0, 1]), scale, need, out)
+    got = out[0].float().cpu().view(nh, hd)
+    for h in range(nh):
+        assert (got[h] - v[3, h // (nh // nkv)].cpu()).abs().max() < 0.02
+    pool[page, 0, :, slot] = saved
+    # prompt portions that end at the sequence's end: their last rows, the first row, rows at tile edges
+    for rows in (2048, 8192):
+        first = N - rows
+        tiles = [[0, r, min(128, rows - r), first + r] for r in range(0, rows, 128)]
+        qp = rnd(dtype, rows, nh, hd)
+        out = torch.full((rows, nh * hd), float("nan"), dtype=dtype, device="cuda")
+        K.attention_prefill_tc(dev(qp, dtype), pool, i32([table]), P, i32(tiles), scale, out)
+        assert K.attention_tc_status() == 0 and out.isfinite().all()
+        check = [0, 127, 128, rows // 2 + 5, rows - 3, rows - 2, rows - 1]
+        want_p = attention_from_pages(qp[check], pool, table, P, [first + r for r in check], scale)
+        assert rel_l2(out[check], want_p) < 0.005, f"portion of {rows} rows"
+    # head size 128: the mma.sync prompt kernel and the decode kernel
+    hd2 = 128
+    pool2, table2, _, _ = paged_sequence(dtype, N, 1, hd2, P, seed=N + 1)
+    rows, first = 2048, N - 2048
+    tiles = [[0, r, min(64, rows - r), first + r] for r in range(0, rows, 64)]
+    qp = rnd(dtype, rows, 3, hd2)
+    out = torch.full((rows, 3 * hd2), float("nan"), dtype=dtype, device="cuda")
+    K.attention_prefill(dev(qp, dtype), pool2, i32([table2]), P, i32(tiles), hd2 ** -0.5, out)
+    check = [0, 63, 64, rows - 3, rows - 2, rows - 1]
+    want_p = attention_from_pages(qp[check], pool2, table2, P, [first + r for r in check], hd2 ** -0.5)
+    assert rel_l2(out[check], want_p) < 0.005
+    out = torch.full((1, 3 * hd2), float("nan"), dtype=dtype, device="cuda")
+    K.attention_decode_mma(dev(qp[-1:], dtype), pool2, i32([table2]), P, i32([N - 1]), i32([0]), hd2 ** -0.5, need, out)
+    assert rel_l2(out, want_p[-1:]) < 0.005
+    assert K.attention_decode_status() == 0

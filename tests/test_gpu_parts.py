@@ -9,7 +9,9 @@ from helpers import rel_rows
 
 pytestmark = pytest.mark.gpu
 DTYPES = [torch.float32, torch.bfloat16]
-TOL = {torch.float32: 1e-5, torch.bfloat16: 2e-2}
+# bfloat16 parts are compared with the plain functions' rounding variant (plain.stores_rounded_to): what is
+# left is summation order and single elements that fall to the other side of a rounding boundary
+TOL = {torch.float32: 1e-5, torch.bfloat16: 5e-3}
 
 
 def make_part(family, kind, dtype, names, params, seed=0, scale=None):
@@ -82,11 +84,12 @@ def test_attention_mixer(dtype, nh, nkv, hd, window, norm):
     torch.manual_seed(1)
     xs = [torch.randn(n, H).to(dtype).float() for n in (41, 17, 64)]
     ones = torch.ones(hd)
-    want = [plain.attention_mixer(x, t["q_proj"], t["k_proj"], t["v_proj"], t["out_proj"],
-                                  t.get("q_norm", ones), t.get("k_norm", ones), eps if norm else 0.0, nh, nkv, hd,
-                                  theta, window=window) for x in xs]
-    if not norm:      # without a q/k norm the plain function's norm must be the identity: compare unnormalised
-        want = [attention_no_norm(x, t, nh, nkv, hd, theta, window) for x in xs]
+    with plain.stores_rounded_to(dtype):
+        want = [plain.attention_mixer(x, t["q_proj"], t["k_proj"], t["v_proj"], t["out_proj"],
+                                      t.get("q_norm", ones), t.get("k_norm", ones), eps if norm else 0.0, nh, nkv,
+                                      hd, theta, window=window) for x in xs]
+        if not norm:      # without a q/k norm the plain function's norm must be the identity: compare unnormalised
+            want = [attention_no_norm(x, t, nh, nkv, hd, theta, window) for x in xs]
     first = None
     for cuts in CUTS:
         got = step_mixer(part, dtype, xs, cuts)
@@ -101,11 +104,12 @@ def test_attention_mixer(dtype, nh, nkv, hd, window, norm):
 
 def attention_no_norm(x, t, nh, nkv, hd, theta, window):
     T = x.shape[0]
-    q = (x @ t["q_proj"].T).view(T, nh, hd)
-    k = (x @ t["k_proj"].T).view(T, nkv, hd)
-    v = (x @ t["v_proj"].T).view(T, nkv, hd)
+    st = plain._store
+    q = st(x @ t["q_proj"].T).view(T, nh, hd)
+    k = st(x @ t["k_proj"].T).view(T, nkv, hd)
+    v = st(x @ t["v_proj"].T).view(T, nkv, hd)
     ang = plain.rope_angles(torch.arange(T), hd, theta)
-    q, k = plain.apply_rope(q, ang), plain.apply_rope(k, ang)
+    q, k = st(plain.apply_rope(q, ang)), st(plain.apply_rope(k, ang))
     out = torch.zeros(T, nh, hd)
     for i in range(T):
         lo = 0 if window is None else max(0, i - window + 1)
@@ -113,7 +117,7 @@ def attention_no_norm(x, t, nh, nkv, hd, theta, window):
             g = h // (nh // nkv)
             p = torch.softmax((k[lo:i + 1, g] @ q[i, h]) * hd ** -0.5, 0)
             out[i, h] = p @ v[lo:i + 1, g]
-    return out.reshape(T, -1) @ t["out_proj"].T
+    return st(out.reshape(T, -1)) @ t["out_proj"].T
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
@@ -123,7 +127,8 @@ def test_short_conv_mixer(dtype, H, L):
     part, t = make_part("mixer", "short_conv", dtype, names, dict(hidden_size=H, kernel_size=L))
     torch.manual_seed(2)
     xs = [torch.randn(n, H).to(dtype).float() for n in (41, 17, 64)]
-    want = [plain.short_conv_mixer(x, t["in"], t["conv"].reshape(H, L), t["out"]) for x in xs]
+    with plain.stores_rounded_to(dtype):
+        want = [plain.short_conv_mixer(x, t["in"], t["conv"].reshape(H, L), t["out"]) for x in xs]
     first = None
     for cuts in CUTS:
         got = step_mixer(part, dtype, xs, cuts)
@@ -143,7 +148,8 @@ def test_feed_forwards(dtype):
     part, t = make_part("ffn", "swiglu", dtype, dict(gate="g", up="u", down="d"),
                         dict(hidden_size=H, intermediate_size=112))
     got = part.forward(None, x.to("cuda", dtype)).cpu()
-    assert float(rel_rows(got, plain.dense_ffn(x, t["g"], t["u"], t["d"])).max()) < TOL[dtype]
+    with plain.stores_rounded_to(dtype):
+        assert float(rel_rows(got, plain.dense_ffn(x, t["g"], t["u"], t["d"])).max()) < TOL[dtype]
     for E, k, norm, bias, scaling in ((6, 2, True, True, 1.0), (9, 4, False, False, 2.5)):
         names = dict(router="r", expert_bias="b", experts="e.", expert_gate="w1", expert_up="w3",
                      expert_down="w2", fused_gate_up="gu", fused_down="dn")
@@ -154,8 +160,9 @@ def test_feed_forwards(dtype):
         w1 = torch.stack([t[f"e.{e}.w1"] for e in range(E)])
         w3 = torch.stack([t[f"e.{e}.w3"] for e in range(E)])
         w2 = torch.stack([t[f"e.{e}.w2"] for e in range(E)])
-        want = plain.moe_ffn(x, t["r"], t.get("b") if bias else None, w1, w3, w2, k, norm, scaling,
-                             forced_ids=ids.cpu())
+        with plain.stores_rounded_to(dtype):
+            want = plain.moe_ffn(x, t["r"], t.get("b") if bias else None, w1, w3, w2, k, norm, scaling,
+                                 forced_ids=ids.cpu())
         delta = part.forward(None, x.to("cuda", dtype))          # an ExpertSum: the weighted sum is still to be formed
         got = delta.dense().cpu()
         assert float(rel_rows(got, want).max()) < TOL[dtype]
@@ -182,7 +189,8 @@ def test_norm_embedding_head_and_position(dtype):
     r = res.cuda()
     out = norm.forward(None, r, delta.cuda()).cpu()
     assert torch.allclose(r.cpu(), res + delta, atol=1e-6)
-    assert float(rel_rows(out, plain.rmsnorm(res + delta, t["w"], 1e-4)).max()) < TOL[dtype]
+    with plain.stores_rounded_to(dtype):
+        assert float(rel_rows(out, plain.rmsnorm_stored(res + delta, t["w"], 1e-4)).max()) < TOL[dtype]
     emb, te = make_part("embedding", "embedding", dtype, dict(weight="e"), dict(vocab_size=V, hidden_size=H))
     head, th = make_part("head", "linear_head", dtype, dict(weight="h"), dict(vocab_size=V, hidden_size=H, tied=False))
     x = torch.randn(4, H).to(dtype)
@@ -215,7 +223,9 @@ def test_prenorm_block_arrangement(dtype):
     residual = x0.cuda()
     delta = block.forward(ctx, residual, d0.cuda(), cache.view(0, ctx.block_tables), True).cpu()
     x = x0 + d0
-    x = x + plain.short_conv_mixer(plain.rmsnorm(x, t1["w"], 1e-5), tm["in"], tm["conv"].reshape(H, L), tm["out"])
-    want_delta = plain.dense_ffn(plain.rmsnorm(x, t2["w"], 1e-5), tf["g"], tf["u"], tf["d"])
+    with plain.stores_rounded_to(dtype):
+        x = x + plain.short_conv_mixer(plain.rmsnorm_stored(x, t1["w"], 1e-5), tm["in"], tm["conv"].reshape(H, L),
+                                       tm["out"])
+        want_delta = plain.dense_ffn(plain.rmsnorm_stored(x, t2["w"], 1e-5), tf["g"], tf["u"], tf["d"])
     assert float(rel_rows(residual.cpu(), x).max()) < TOL[dtype]
     assert float(rel_rows(delta, want_delta).max()) < TOL[dtype] * 3

@@ -13,109 +13,19 @@ import pytest
 import torch
 
 import plain_lfm2 as plain
-from helpers import (TOL, decode_tail_trace, gather_logits, max_live_tokens, mixed_trace, portions_trace,
-                     random_prompt, rel_all, rel_rows, tol_request, whole_trace)
+from helpers import (check_against_plain, decode_tail_trace, gather_logits, max_live_tokens, mixed_trace,
+                     portions_trace, random_prompt, rel_rows, run_in_process, whole_trace)
 from tiny_configs import ALL
 
 pytestmark = pytest.mark.gpu
 ROOT = pathlib.Path(__file__).resolve().parent.parent
 
-# Router picks may differ from the plain implementation's only where its selection margin (gap
-# between the k-th and the (k+1)-th score) is below what the dtype's rounding can move a score by.
-ROUTE_MARGIN = {"float32": 1e-4, "bfloat16": 5e-2}
 LENGTHS = {"a": 70, "b": 133, "c": 45, "d": 97, "e": 150, "f": 64}
 CUTS = {"whole": whole_trace, "decode_tail": decode_tail_trace, "portions": portions_trace, "mixed": mixed_trace}
 
 
 def requests_for(cfg, seed=0):
     return {k: random_prompt(cfg["vocab_size"], n, seed + i) for i, (k, n) in enumerate(LENGTHS.items())}
-
-
-def poison_free(rp):
-    """Fill every free page and every free state slot with NaN."""
-    free = [p for pool in rp.cache.groups.values() for p in pool._free]
-    for pool in rp.cache.paged_tensors():
-        pool[free] = float("nan")
-    free_slots = list(rp.cache.slots._free) + [rp.cache.slots.dummy]
-    for t in rp.cache.state_tensors():
-        t[free_slots] = float("nan")
-
-
-def run_in_process(model_dir, dtype, steps, max_tokens, page_size=16, poison=False, stats=None):
-    """Replay ``steps``; returns (outputs per step, {request -> {layer -> ids [T, k]}}).  ``poison``:
-    whatever is free is NaN before every step."""
-    from snowllm_b200.engine.replay import Replay
-    rp = Replay(model_dir, dtype, max_tokens, max_requests=4, page_size=page_size)
-    moe_layers = [i for i, b in enumerate(rp.model.blocks) if hasattr(b.ffn, "route")]
-    outputs, routes = [], {}
-    used: set = set()
-    for s in steps:
-        if poison:
-            poison_free(rp)
-        rp.runner.taps = []
-        outputs.append(rp.step(s["entries"], s["end"]))
-        if stats is not None:
-            held = {p for rc in rp.live.values() for t in rc.tables.values() for p in t if p >= 0}
-            stats["reused"] = stats.get("reused", False) or bool(held & used)
-            used |= held
-        picks = [t.cpu() for name, t in rp.runner.taps if name == "moe_route"]
-        assert len(picks) == len(moe_layers)
-        row = 0
-        for e in s["entries"]:
-            n = len(e["tokens"])
-            for layer, ids in zip(moe_layers, picks):
-                routes.setdefault(e["id"], {}).setdefault(layer, []).append(ids[row:row + n])
-            row += n
-    assert all(p.free_count == p.total for p in rp.cache.groups.values()), "pages were lost"
-    assert rp.cache.slots.free_count == rp.cache.max_seqs
-    routes = {k: {layer: torch.cat(v) for layer, v in d.items()} for k, d in routes.items()}
-    return outputs, routes
-
-
-def check_against_plain(model_dir, dtype, reqs, steps, outputs, routes):
-    cfg, tensors = plain.read_model_dir(model_dir)
-    got = gather_logits(steps, outputs)
-    worst = 0.0
-    for k, toks in reqs.items():
-        forced = routes.get(k) or None
-        if not forced:
-            want = plain.logits(cfg, tensors, toks)
-        else:
-            # the picks must be the plain implementation's wherever its margin is clear
-            mg = {}
-            want = plain.logits(cfg, tensors, toks, forced_routes=forced, margins=mg)
-            plain_ids = plain_routes(cfg, tensors, toks, forced)
-            for layer, ids in forced.items():
-                differs = (ids.long().sort(-1).values != plain_ids[layer].sort(-1).values).any(-1)
-                unclear = mg[layer] < ROUTE_MARGIN[dtype]
-                assert not (differs & ~unclear).any(), \
-                    f"request {k} layer {layer}: picks differ at positions {torch.nonzero(differs & ~unclear).flatten().tolist()} with a clear margin"
-        err = rel_rows(got[k], want)
-        worst = max(worst, float(err.max()))
-        bad = torch.nonzero(err > TOL[dtype]).flatten().tolist()
-        assert not bad, f"request {k}: first wrong position {bad[0]} of {len(toks)} (rel {float(err[bad[0]]):.3g}); all: {bad[:20]}"
-        whole = rel_all(got[k], want)
-        assert whole < tol_request(dtype, cfg["num_hidden_layers"]), \
-            f"request {k}: rel-L2 over all positions {whole:.3g}"
-    return worst
-
-
-def plain_routes(cfg, tensors, toks, forced):
-    """The plain router's own picks at each routed layer, given the residual stream that the forced
-    picks produce up to that layer (so one early difference does not cascade into the comparison)."""
-    out = {}
-    eps = cfg["norm_eps"]
-    x = tensors["model.embed_tokens.weight"][torch.as_tensor(toks)].float()
-    for i in range(cfg["num_hidden_layers"]):
-        p = f"model.layers.{i}."
-        x = x + plain.layer_mixer(cfg, tensors, i, plain.rmsnorm(x, tensors[p + "operator_norm.weight"], eps))
-        u = plain.rmsnorm(x, tensors[p + "ffn_norm.weight"], eps)
-        if i in forced:
-            bias = tensors[p + "feed_forward.expert_bias"] if cfg.get("use_expert_bias") else None
-            out[i], _ = plain.route(u, tensors[p + "feed_forward.gate.weight"], bias, cfg["num_experts_per_tok"],
-                                    cfg.get("norm_topk_prob", False), cfg.get("routed_scaling_factor", 1.0))
-        x = x + plain.layer_ffn(cfg, tensors, i, u, forced.get(i))
-    return out
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
