@@ -156,12 +156,25 @@ __global__ void paged_attention_kernel(
       }
     }
     s = valid ? s : -INFINITY;
-    const float tmax = warp_max(s);
-    const float m_new = fmaxf(mx, tmax);                   // finite: each tile run has a valid key
-    const float corr = expf(mx - m_new);                   // exp(-inf) = 0 on the first tile
-    const float p = valid ? expf(s - m_new) : 0.f;
-    l = l * corr + warp_sum(p);
-    mx = m_new;
+    float p, corr;
+    if constexpr (sizeof(T) == 2) {
+      // bfloat16: base-2 exponents against a whole-number reference, P rounded to bfloat16 for P V as the
+      // tensor-core kernels do (csrc/attention_mma.cu, "Rounding of P"); the row sum keeps the unrounded values
+      s *= 1.4426950408889634f;
+      const float m_new = fmaxf(mx, ceilf(warp_max(s)));   // finite: each tile run has a valid key
+      corr = exp2f(mx - m_new);                            // a power of two; 0 on the first tile
+      p = valid ? exp2f(s - m_new) : 0.f;
+      l = l * corr + warp_sum(p);
+      p = __bfloat162float(__float2bfloat16_rn(p));
+      mx = m_new;
+    } else {
+      const float tmax = warp_max(s);
+      const float m_new = fmaxf(mx, tmax);                 // finite: each tile run has a valid key
+      corr = expf(mx - m_new);                             // exp(-inf) = 0 on the first tile
+      p = valid ? expf(s - m_new) : 0.f;
+      l = l * corr + warp_sum(p);
+      mx = m_new;
+    }
 #pragma unroll
     for (int i = 0; i < DPL; ++i) o[i] *= corr;
     const T* vrow = reinterpret_cast<const T*>(vs);
@@ -194,7 +207,7 @@ __global__ void paged_attention_kernel(
       if (d < hd) po[d] = o[i];
     }
     if (lane == 0) {
-      part_ml[slot * 2] = mx;
+      part_ml[slot * 2] = sizeof(T) == 2 ? mx * 0.6931471805599453f : mx;   // the merge works with natural exponents
       part_ml[slot * 2 + 1] = l;
     }
   }

@@ -17,6 +17,14 @@
 //
 // The tile order is fixed by positions alone, so a row's result does not depend on what else the
 // launch holds.  Head sizes 64 and 128; other sizes and float32 go through csrc/attention.cu.
+//
+// Rounding of P.  P = 2^(s log2 e - m) is rounded to bfloat16 for the P V product (the row sum is taken from
+// the unrounded values).  The reference m is the running maximum rounded UP to a whole number: whatever tile
+// walk, chunking or kernel a row goes through, its references differ by whole numbers, the P values by exact
+// powers of two, and the rounded mantissas are the same.  So which key gets which rounding error does not
+// depend on how the keys were cut, every rescaling of O and of the row sum is exact, and a plain
+// implementation can round P the same way (tests/plain_lfm2.py does).  All bfloat16 attention kernels of
+// this engine follow the rule.
 // Pool layout: [page, 2 (k, v), kv head, page_size, head_dim].
 #include "tma.cuh"
 
@@ -180,6 +188,7 @@ attention_prefill_kernel(const bf16* __restrict__ q, const bf16* __restrict__ po
       for (int h = 0; h < 2; ++h) {
         mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 1));
         mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 2));
+        mx[h] = ceilf(mx[h]);                              // a whole power of two as the reference (see the file's head)
       }
       float alpha[2], base[2];
 #pragma unroll
@@ -449,6 +458,7 @@ attention_prefill_tma_kernel(const __grid_constant__ CUtensorMap map_kv, const b
       for (int h = 0; h < 2; ++h) {
         mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 1));
         mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 2));
+        mx[h] = ceilf(mx[h]);                              // a whole power of two as the reference (see the file's head)
       }
       float alpha[2], base[2];
 #pragma unroll
@@ -657,6 +667,7 @@ attention_decode_mma_kernel(const bf16* __restrict__ q, const bf16* __restrict__
     for (int h = 0; h < 2; ++h) {
       mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 1));
       mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 2));
+      mx[h] = ceilf(mx[h]);                               // a whole power of two as the reference (see the file's head)
       row_max[h] = mx[h];                                 // finite: the warp has a valid key
     }
     uint32_t pf[FA_BK / 16][4];
@@ -915,6 +926,7 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_kv, const bf
     for (int h = 0; h < 2; ++h) {
       mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 1));
       mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 2));
+      mx[h] = ceilf(mx[h]);                               // a whole power of two as the reference (see the file's head)
       row_max[h] = mx[h];
     }
     uint32_t pf[FA_BK / 16][4];

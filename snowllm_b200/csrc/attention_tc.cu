@@ -343,7 +343,8 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
       mx *= scale_log2;                                  // the scale is positive
       float alpha = 1.f;
       if (mx > m_ref + AT_RESCALE_STEP || m_ref == -INFINITY) {
-        const float m_new = mx == -INFINITY ? -INFINITY : mx;
+        const float m_new = mx == -INFINITY ? -INFINITY : ceilf(mx);       // a whole number: P's rounding does not
+                                                                           // depend on the tile walk (csrc/attention_mma.cu)
         alpha = m_new == -INFINITY ? 1.f : at_exp2(m_ref - m_new);       // m_ref = -inf: nothing summed yet, 0
         m_ref = m_new;
       }

@@ -68,7 +68,9 @@ class Attention(Part):
             qkv, self.q_norm, self.k_norm, self.qk_norm_eps or 0.0, inv_freq, rot_dim, ctx.positions,
             ctx.row_seg, cache.block_table, cache.page_size, cache.pool, self.num_heads,
             self.num_kv_heads, self.head_dim, write_kv=owns_cache)
+        ctx.tap("attention_q", q)
         o = torch.empty(ctx.M, self.num_heads * self.head_dim, dtype=q.dtype, device=q.device)
+        ctx.tap("attention_o", o)            # filled by the launches below
         rows = rows_host = None
         if kernels.attention_prefill_ok(q) and max(ctx.host_seg_len) >= plan.PREFILL_MIN_ROWS:
             # prompt portions on the tensor cores; rows of short segments (decoded tokens) row by row

@@ -21,12 +21,17 @@ class PreNormBlock:
     def forward(self, ctx, residual, delta, cache, owns_cache=True):
         with span(self._names[0]):
             x = self.mixer_norm.forward(ctx, residual, delta)
+        ctx.tap("mixer_in", x)
         with span(self._names[1]):
             delta = self.mixer.forward(ctx, x, cache, owns_cache)
+        ctx.tap("mixer_out", delta)
         with span(self._names[2]):
             x = self.ffn_norm.forward(ctx, residual, delta)
+        ctx.tap("ffn_in", x)
         with span(self._names[3]):
-            return self.ffn.forward(ctx, x)
+            delta = self.ffn.forward(ctx, x)
+        ctx.tap("ffn_out", delta)
+        return delta
 
 
 register_block("prenorm", PreNormBlock)

@@ -8,32 +8,32 @@ import torch
 import plain_lfm2 as plain
 from tiny_configs import ALL
 
-# Relative L2 error allowed between the engine and the plain implementation.
+# Relative L2 error allowed between the engine's logits and the plain implementation's.
 # float32: both sides sum in float32 in different orders: a few 1e-6 per product, about 1e-5 after a
 # handful of layers; the bound holds for every single position.
 # bfloat16: the engine is compared with the plain implementation's rounding variant
-# (``plain.stores_rounded_to``), which rounds to bfloat16 exactly where the engine stores bfloat16.  What
-# is left is the order of float sums, values that sit on a rounding boundary and fall to the other side
-# (one bfloat16 step, 2^-8 of ONE element among hundreds), and P rounded before P.V in the tensor-core
-# attention kernels: some 1e-3 per position.  A real fault (a wrong page, slot, key or expert) gives
-# errors of order 1; a missing or doubled rounding gives several 1e-3 on every position, which the bound
-# over a whole request catches.
-TOL = {"float32": 2e-5, "bfloat16": 1e-2}
+# (``plain.stores_rounded_to``), which rounds to bfloat16 exactly where the engine stores bfloat16.  Part by
+# part the two agree almost bit for bit (``check_parts``).  Over a whole model they drift apart all the same:
+# float sums in another order move a value by 1e-7, a value that sits on a rounding boundary then falls to
+# the other side (one bfloat16 step), and attention hands a key's or value's flipped element on to every
+# later position of the request.  That drift is a fraction of the rounding noise itself, and the noise is
+# known: it is what the rounding variant differs from the float variant on the same request.  So the bounds
+# are stated in units of it: the engine must lie closer to the rounding variant than the rounding variant
+# lies to the float result (over a request; twice that for a single position), and inside the caps that the
+# comparison with the float result alone used to have (SnowLLM's own acceptance bound for its bf16 kernels,
+# rel-L2 < 0.025 for 3 layers, tests/test_lfm2_reference.py:66-161, scaled in quadrature with the layers;
+# 0.1 for a single position).  A wrong page, slot, key, row or expert gives errors of order 1.
+TOL = {"float32": 2e-5, "bfloat16": 0.1}
+NOISE_SHARE_REQUEST, NOISE_SHARE_POSITION = 1.0, 2.0
 
 
 def tol_request(dtype: str, num_layers: int) -> float:
-    return 2e-5 if dtype == "float32" else 4e-3
-
-
-# Bounds against an oracle WITHOUT a rounding variant (the toy architectures' written-out computations):
-# SnowLLM's own acceptance bound for its bf16 kernels against a float reference, rel-L2 < 0.025 for a 3-layer
-# model (tests/test_lfm2_reference.py:66-161), scaled in quadrature with the layers; single positions, the
-# largest of some hundred samples of that error, get 0.1.
-TOL_UNROUNDED = {"float32": 2e-5, "bfloat16": 0.1}
-
-
-def tol_request_unrounded(dtype: str, num_layers: int) -> float:
     return 2e-5 if dtype == "float32" else 0.025 * (max(num_layers, 3) / 3) ** 0.5
+
+
+# Bounds against an oracle WITHOUT a rounding variant (the toy architectures' written-out computations): the caps.
+TOL_UNROUNDED = TOL
+tol_request_unrounded = tol_request
 
 
 def rel_all(got, want) -> float:
@@ -93,7 +93,7 @@ def run_in_process(model, dtype, steps, max_tokens, page_size=16, poison=False, 
     from snowllm_b200.engine.replay import Replay
     rp = Replay(model, dtype, max_tokens, max_requests=max_requests, page_size=page_size, use_graphs=use_graphs)
     moe_layers = [i for i, b in enumerate(rp.model.blocks) if hasattr(b.ffn, "route")]
-    outputs, routes, route_inputs = [], {}, {}
+    outputs, routes, route_inputs, parts = [], {}, {}, {}
     used: set = set()
     for s in steps:
         if poison:
@@ -109,20 +109,68 @@ def run_in_process(model, dtype, steps, max_tokens, page_size=16, poison=False, 
         picks = [t.cpu() for name, t in rp.runner.taps if name == "moe_route"]
         inputs = [t.float().cpu() for name, t in rp.runner.taps if name == "moe_route_input"]
         assert len(picks) == len(moe_layers) == len(inputs)
+        by_name = {name: [(t.dense() if hasattr(t, "dense") else t).float().cpu()
+                          for n, t in rp.runner.taps if n == name] for name in PART_TAPS} if stats is not None else {}
         row = 0
         for e in s["entries"]:
             n = len(e["tokens"])
             for layer, ids, x in zip(moe_layers, picks, inputs):
                 routes.setdefault(e["id"], {}).setdefault(layer, []).append(ids[row:row + n])
                 route_inputs.setdefault(e["id"], {}).setdefault(layer, []).append(x[row:row + n])
+            for name, per_layer in by_name.items():
+                for layer, t in enumerate(per_layer):
+                    parts.setdefault(e["id"], {}).setdefault(layer, {}).setdefault(name, []).append(t[row:row + n])
             row += n
     assert all(p.free_count == p.total for p in rp.cache.groups.values()), "pages were lost"
     assert rp.cache.slots.free_count == rp.cache.max_seqs
     if stats is not None:
         stats["graph_replays"] = rp.runner.graph_replays
+        stats["parts"] = {k: {layer: {name: torch.cat(v) for name, v in d.items()} for layer, d in layers.items()}
+                          for k, layers in parts.items()}
     routes = {k: {layer: (torch.cat(v), torch.cat(route_inputs[k][layer])) for layer, v in d.items()}
               for k, d in routes.items()}
     return outputs, routes
+
+
+PART_TAPS = ("mixer_in", "mixer_out", "ffn_in", "ffn_out")
+# A part's output against the plain part run on the engine's OWN input to that part (both tapped, in position
+# order over all the steps of a request).  float32: the float bound.  bfloat16: the distance is measured in
+# units of the part's own rounding noise (what the plain part's rounding variant differs from its float
+# result on that input); a rounding too many or too few inside a part moves its output by about
+# noise / sqrt(stores in the part), 0.5 to 0.7 of the noise for the two to four stores a part has.
+# Measured on the tiny and the full-size models: 0.00 in the median (the same bits), up to 0.13 for feed-forwards
+# and short convolutions, up to 0.30 for attention (a flipped element of a key or value reaches every later row).
+PART_NOISE_SHARE = {"attention": 0.45, "other": 0.25}
+
+
+def check_parts(model, dtype, parts, routes) -> None:
+    """Every mixer and every feed-forward of every layer alone, on what the engine itself fed it.  The plain
+    part sees the whole sequence at once, the engine saw it in the steps' cuts, through its cache."""
+    cfg, tensors = model if isinstance(model, tuple) else plain.read_model_dir(model)
+    dev = tensors["model.embed_tokens.weight"].device
+    log = __import__("os").environ.get("SNK_TEST_NOISE_LOG")
+    for k, layers in parts.items():
+        for layer, t in sorted(layers.items()):
+            forced = routes.get(k, {}).get(layer)
+            forced = forced[0].to(dev) if forced is not None else None
+            for what, run in (("mixer", lambda u: plain.layer_mixer(cfg, tensors, layer, u)),
+                              ("ffn", lambda u: plain.layer_ffn(cfg, tensors, layer, u, forced))):
+                u, got = t[what + "_in"].to(dev), t[what + "_out"].to(dev)
+                with torch.no_grad():
+                    exact = run(u)
+                    with plain.stores_rounded_to(dtype):
+                        want = run(u)
+                err = rel_all(got, want)
+                noise = rel_all(want, exact)
+                paged = what == "mixer" and cfg["layer_types"][layer] != "conv"
+                bound = 2e-5 if dtype == "float32" else PART_NOISE_SHARE["attention" if paged else "other"] * noise
+                if log:
+                    with open(log, "a") as f:
+                        f.write(f"part {cfg['hidden_size']} L{layer} {cfg['layer_types'][layer][:4]} {what} T{len(u)} "
+                                f"err {err:.3e} noise {noise:.3e} ratio {err / max(noise, 1e-30):.3f} "
+                                f"rowmax {float(rel_rows(got, want).max()):.3e}\n")
+                assert err <= bound, (f"request {k} layer {layer} {what}: rel-L2 {err:.3g} against the plain part on "
+                                      f"the same input (bound {bound:.3g}, rounding noise of the part {noise:.3g})")
 
 
 def check_picks(cfg, tensors, dtype, routes) -> None:
@@ -164,12 +212,21 @@ def check_against_plain(model, dtype, reqs, steps, outputs, routes):
         with plain.stores_rounded_to(dtype):
             want = plain.logits(cfg, tensors, toks, forced_routes=forced)
         err = rel_rows(got[k].to(dev), want).cpu()
-        worst = max(worst, float(err.max()))
-        bad = torch.nonzero(err > TOL[dtype]).flatten().tolist()
-        assert not bad, f"request {k}: first wrong position {bad[0]} of {len(toks)} (rel {float(err[bad[0]]):.3g}); all: {bad[:20]}"
         whole = rel_all(got[k].to(dev), want)
-        assert whole < tol_request(dtype, cfg["num_hidden_layers"]), \
-            f"request {k}: rel-L2 over all positions {whole:.3g}"
+        per_position, per_request = TOL[dtype], tol_request(dtype, cfg["num_hidden_layers"])
+        if dtype != "float32":
+            noise = rel_all(want, plain.logits(cfg, tensors, toks, forced_routes=forced))
+            per_position = min(per_position, NOISE_SHARE_POSITION * noise)
+            per_request = min(per_request, NOISE_SHARE_REQUEST * noise)
+            if __import__("os").environ.get("SNK_TEST_NOISE_LOG"):
+                with open(__import__("os").environ["SNK_TEST_NOISE_LOG"], "a") as f:
+                    f.write(f"logits {cfg['hidden_size']} L{cfg['num_hidden_layers']} T{len(toks)} all {whole:.5f} "
+                            f"noise {noise:.5f} pos_max {float(err.max()):.5f}\n")
+        worst = max(worst, float(err.max()))
+        bad = torch.nonzero(err > per_position).flatten().tolist()
+        assert not bad, (f"request {k}: first wrong position {bad[0]} of {len(toks)} (rel {float(err[bad[0]]):.3g}, "
+                         f"bound {per_position:.3g}); all: {bad[:20]}")
+        assert whole < per_request, f"request {k}: rel-L2 over all positions {whole:.3g} (bound {per_request:.3g})"
     return worst
 
 

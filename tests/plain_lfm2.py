@@ -14,7 +14,10 @@ Rounding variant.  Inside ``with stores_rounded_to(torch.bfloat16):`` every inte
 that a bfloat16 engine keeps in bfloat16 between two kernels is rounded to it (``_store``):
 norm outputs, the products that do not feed the residual stream (in_proj, q/k/v, the
 SwiGLU activation), the conv's g = B*x and y = C*conv, q and k after head norm and
-rotation, the attention output.  The arithmetic between two stores stays float32, as do
+rotation, the attention output, and the softmax weights P on their way into P.V (written
+as 2^(s log2 e - m) with m the row's maximum rounded up to a whole number, so that the
+rounded mantissas do not depend on m; the row sum keeps the unrounded values).  The
+arithmetic between two stores stays float32, as do
 the residual stream, the products that feed it, the router and the logits.  A bfloat16
 run is compared with this variant, so that what is left is accumulation order, not the
 roundings themselves.  Outside the ``with`` nothing is rounded.
@@ -169,7 +172,14 @@ def attention_mixer(u, wq, wk, wv, wo, q_norm, k_norm, eps, n_heads, n_kv, hd, t
     if window is not None:
         mask = mask | (i[None, :] <= i[:, None] - window)
     scores = scores.masked_fill(mask[:, None, None, :], float("-inf"))
-    out = torch.einsum("tghs,sgd->tghd", scores.softmax(-1), v).reshape(T, n_heads * hd)
+    if _STORE_DTYPE is None:
+        probs = scores.softmax(-1)
+    else:
+        # the rounding variant: P = 2^(s log2 e - m), m a whole number; P is stored, the row sum is not
+        s2 = scores * 1.4426950408889634
+        p = torch.exp2(s2 - torch.ceil(s2.amax(-1, keepdim=True)))
+        probs = _store(p) / p.sum(-1, keepdim=True)
+    out = torch.einsum("tghs,sgd->tghd", probs, v).reshape(T, n_heads * hd)
     return _store(out) @ wo.T
 
 
@@ -266,32 +276,38 @@ def layer_ffn(cfg, tensors, i, u, forced_ids=None, margins=None):
                    cfg.get("routed_scaling_factor", 1.0), forced_ids, margins)
 
 
-def hidden_states(cfg, tensors, ids, forced_routes=None, margins=None):
+def hidden_states(cfg, tensors, ids, forced_routes=None, margins=None, trace=None):
     """Embedding, then per layer x += mixer(norm(x)); x += ffn(norm(x)), then the final
     norm (snowllm/models/lfm2/layers.py:97-104, 119-131).  ``forced_routes``: {layer -> ids [T, k]}
     that replace the router's selection in that layer; ``margins``: a dict that receives
-    {layer -> selection margin per position}."""
+    {layer -> selection margin per position}; ``trace``: a list that receives (name, tensor) of each
+    layer's mixer input, mixer output, feed-forward input and feed-forward output, in order."""
     eps = cfg["norm_eps"]
     table = tensors["model.embed_tokens.weight"]
     x = table[torch.as_tensor(ids, dtype=torch.long, device=table.device)].float()
     for i in range(cfg["num_hidden_layers"]):
         p = f"model.layers.{i}."
-        x = x + layer_mixer(cfg, tensors, i, rmsnorm_stored(x, tensors[p + "operator_norm.weight"], eps))
+        u = rmsnorm_stored(x, tensors[p + "operator_norm.weight"], eps)
+        d = layer_mixer(cfg, tensors, i, u)
+        x = x + d
         got = []
-        x = x + layer_ffn(cfg, tensors, i, rmsnorm_stored(x, tensors[p + "ffn_norm.weight"], eps),
-                          None if forced_routes is None else forced_routes.get(i), got)
+        u2 = rmsnorm_stored(x, tensors[p + "ffn_norm.weight"], eps)
+        d2 = layer_ffn(cfg, tensors, i, u2, None if forced_routes is None else forced_routes.get(i), got)
+        x = x + d2
+        if trace is not None:
+            trace += [("mixer_in", u), ("mixer_out", d), ("ffn_in", u2), ("ffn_out", d2)]
         if margins is not None and got:
             margins[i] = got[0]
     return rmsnorm_stored(x, tensors["model.embedding_norm.weight"], eps)
 
 
-def logits(cfg, tensors, ids, forced_routes=None, margins=None):
+def logits(cfg, tensors, ids, forced_routes=None, margins=None, trace=None):
     """[T, V] float32 logits of one whole sequence; the head is the embedding when
     tie_word_embeddings (snowllm/models/lfm2/weights.py:63-66), else lm_head.weight."""
     tied = cfg.get("tie_word_embeddings", True)
     head = tensors["model.embed_tokens.weight"] if tied else tensors["lm_head.weight"]
     with torch.no_grad():
-        return hidden_states(cfg, tensors, ids, forced_routes, margins) @ head.float().T
+        return hidden_states(cfg, tensors, ids, forced_routes, margins, trace) @ head.float().T
 
 
 def greedy(cfg, tensors, prompt, n_new):

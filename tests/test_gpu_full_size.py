@@ -12,7 +12,7 @@ step of 64 rows."""
 import pytest
 import torch
 
-from helpers import (check_against_plain, gather_logits, max_live_tokens, mixed_trace, random_prompt, rel_rows,
+from helpers import (check_against_plain, check_parts, gather_logits, max_live_tokens, mixed_trace, random_prompt, rel_rows,
                      run_in_process)
 
 pytestmark = pytest.mark.gpu
@@ -97,6 +97,7 @@ def test_four_requests_mixed_with_reused_poisoned_pages(setup, dtype):
     assert stats["reused"], "the trace was meant to use pages again"
     got = gather_logits(steps, outputs)
     assert all(v.isfinite().all() for v in got.values()), "a stale (NaN) page or slot was read"
+    check_parts((CONFIG, plain_tensors), dtype, stats["parts"], routes)
     check_against_plain((CONFIG, plain_tensors), dtype, reqs, steps, outputs, routes)
     statuses_are_clear()
 
@@ -109,7 +110,9 @@ def test_one_step_of_2048_rows(setup, dtype):
     model = engine_model(tensors, dtype)
     toks = random_prompt(V, 2048, 5)
     steps = [{"step": 0, "entries": [{"id": "p", "tokens": toks, "want": list(range(2048))}], "end": ["p"]}]
-    outputs, routes = run_in_process(model, dtype, steps, 2048, max_requests=1)
+    stats = {}
+    outputs, routes = run_in_process(model, dtype, steps, 2048, max_requests=1, stats=stats)
+    check_parts((CONFIG, plain_tensors), dtype, stats["parts"], routes)
     check_against_plain((CONFIG, plain_tensors), dtype, {"p": toks}, steps, outputs, routes)
     statuses_are_clear()
 
@@ -136,7 +139,7 @@ def check_tails(model, dtype, reqs, outputs, routes):
     """The last three positions of every request (the rows the three steps asked for) against the plain
     implementation, which runs each request whole with the engine's picks."""
     import plain_lfm2 as plain
-    from helpers import TOL, check_picks
+    from helpers import NOISE_SHARE_POSITION, TOL, check_picks, rel_all
     cfg, tensors = model
     check_picks(cfg, tensors, dtype, routes)
     dev = tensors["model.embed_tokens.weight"].device
@@ -144,6 +147,9 @@ def check_tails(model, dtype, reqs, outputs, routes):
         forced = {layer: ids.to(dev) for layer, (ids, _) in routes[k].items()}
         with plain.stores_rounded_to(dtype):
             want = plain.logits(cfg, tensors, toks, forced_routes=forced)[-3:]
+        bound = TOL[dtype]
+        if dtype != "float32":            # in units of the rounding noise, as helpers.check_against_plain has it
+            bound = min(bound, NOISE_SHARE_POSITION * rel_all(want, plain.logits(cfg, tensors, toks, forced_routes=forced)[-3:]))
         got = torch.stack([outputs[s][row] for s in range(3)]).to(dev)
         err = rel_rows(got, want)
-        assert float(err.max()) < TOL[dtype], f"request {k}: rel {err.tolist()} at its last three positions"
+        assert float(err.max()) < bound, f"request {k}: rel {err.tolist()} at its last three positions (bound {bound:.3g})"

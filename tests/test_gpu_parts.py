@@ -115,7 +115,13 @@ def attention_no_norm(x, t, nh, nkv, hd, theta, window):
         lo = 0 if window is None else max(0, i - window + 1)
         for h in range(nh):
             g = h // (nh // nkv)
-            p = torch.softmax((k[lo:i + 1, g] @ q[i, h]) * hd ** -0.5, 0)
+            sc = (k[lo:i + 1, g] @ q[i, h]) * hd ** -0.5
+            if plain._STORE_DTYPE is None:
+                p = torch.softmax(sc, 0)
+            else:                                          # P stored on its way into P.V (see plain_lfm2)
+                s2 = sc * 1.4426950408889634
+                e = torch.exp2(s2 - torch.ceil(s2.max()))
+                p = st(e) / e.sum()
             out[i, h] = p @ v[lo:i + 1, g]
     return st(out.reshape(T, -1)) @ t["out_proj"].T
 

@@ -13,7 +13,7 @@ import pytest
 import torch
 
 import plain_lfm2 as plain
-from helpers import (check_against_plain, decode_tail_trace, gather_logits, max_live_tokens, mixed_trace,
+from helpers import (check_against_plain, check_parts, decode_tail_trace, gather_logits, max_live_tokens, mixed_trace,
                      portions_trace, random_prompt, rel_rows, run_in_process, whole_trace)
 from tiny_configs import ALL
 
@@ -35,7 +35,9 @@ def test_cuts_match_the_plain_implementation(model_dirs, name, dtype, cut):
     d = model_dirs(name, dtype)
     reqs = requests_for(ALL[name])
     steps = CUTS[cut](reqs)
-    outputs, routes = run_in_process(d, dtype, steps, max_live_tokens(steps))
+    stats = {}
+    outputs, routes = run_in_process(d, dtype, steps, max_live_tokens(steps), stats=stats)
+    check_parts(d, dtype, stats["parts"], routes)
     check_against_plain(d, dtype, reqs, steps, outputs, routes)
 
 

@@ -8,6 +8,7 @@ calls in a row (the second call finds the first call's leftovers in the shared s
 refuses a call that would not fit, and that no device memory is allocated while it runs.  The file name
 makes pytest collect it last."""
 import ctypes
+import gc
 
 import pytest
 import torch
@@ -76,15 +77,17 @@ def test_static_entry_matches_the_regular_one_twice_in_a_row(dtype):
         if first:                                     # set-up call: looks up the array's address on this device
             assert call_static(lib, c, out, dtype) == 0
             first = False
+        # Nothing may be taken from the device during the call.  Tensors that earlier tests left behind can be
+        # collected at any moment (and give memory back), so they are collected now, and the check is one-sided.
+        gc.collect()
         torch.cuda.synchronize()
-        before = torch.cuda.memory_allocated(), torch.cuda.mem_get_info()[0]
+        allocated, free = torch.cuda.memory_allocated(), torch.cuda.mem_get_info()[0]
         assert call_static(lib, c, out, dtype) == 0
         torch.cuda.synchronize()
-        assert (torch.cuda.memory_allocated(), torch.cuda.mem_get_info()[0]) == before, "device memory moved"
+        assert torch.cuda.memory_allocated() <= allocated and torch.cuda.mem_get_info()[0] >= free, \
+            "the call took device memory"
         assert out.isfinite().all()
-        tol = 2e-5 if dtype == torch.float32 else 2e-2     # the kernel tests' bounds; the same code runs, so 0 is expected
-        assert (out.float() - want.float()).abs().max().item() <= tol
-        assert torch.equal(out, want)
+        assert torch.equal(out, want)                     # the same kernels run on the same inputs: the same bits
 
 
 def test_static_entry_refuses_what_does_not_fit():
