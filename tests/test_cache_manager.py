@@ -121,3 +121,38 @@ def test_bytes_per_page():
     import torch
     b = CacheManager.bytes_per_page(SPECS, 16, torch.bfloat16)
     assert b[("paged", None)] == 2 * (2 * 2 * 16 * 16 * 2) and b[("paged", 20)] == 2 * 1 * 16 * 32 * 2
+
+
+def test_spec_chooses_the_pool_layout_and_a_mixer_may_hold_pages_and_state():
+    """Keys and values of one width share a tensor; of two widths they are two tensors; a cache of keys only
+    (a latent row per position) is one; the cache dtype may differ from the compute dtype; a tuple of specs
+    gives a tuple of views in the same order."""
+    import torch
+    specs = {0: PagedKVSpec(2, 16),
+             1: PagedKVSpec(2, 16, v_head_dim=8),
+             2: PagedKVSpec(1, 40, v_head_dim=0, cache_dtype="float32"),
+             3: (PagedKVSpec(3, 8, window=32), SlotStateSpec(((5,), (2, 3)), ("f32", "compute"))),
+             4: SlotStateSpec(((4,),))}
+    cm = CacheManager(specs, page_size=4, num_pages={("paged", None): 6, ("paged", 32): 9}, max_seqs=2,
+                      dtype=torch.bfloat16, device="cpu")
+    tables = {key: torch.zeros(1, 3, dtype=torch.int32) for key in cm.groups}
+    v0 = cm.view(0, tables)
+    assert v0.pool.shape == (6, 2, 2, 4, 16) and v0.pool.dtype == torch.bfloat16 and len(v0.pools) == 1
+    v1 = cm.view(1, tables)
+    assert [tuple(t.shape) for t in v1.pools] == [(6, 2, 4, 16), (6, 2, 4, 8)] and v1.pool is v1.pools[0]
+    v2 = cm.view(2, tables)
+    assert [tuple(t.shape) for t in v2.pools] == [(6, 1, 4, 40)] and v2.pool.dtype == torch.float32
+    paged, state = cm.view(3, tables)
+    assert paged.pool.shape == (9, 2, 3, 4, 8) and paged.block_table is tables[("paged", 32)]
+    assert [tuple(t.shape) for t in state.tensors] == [(3, 5), (3, 2, 3)]
+    assert state.tensors[0].dtype == torch.float32 and state.tensors[1].dtype == torch.bfloat16
+    assert cm.view(4, tables).tensors[0].shape == (3, 4) and cm.view(7, tables) is None
+    assert len(cm.paged_tensors()) == 5 and len(cm.state_tensors()) == 3
+    per_page = CacheManager.bytes_per_page(specs, 4, torch.bfloat16)
+    assert per_page[("paged", None)] == (2 * 2 * 4 * 16) * 2 + (2 * 4 * 16 + 2 * 4 * 8) * 2 + (1 * 4 * 40) * 4
+    assert per_page[("paged", 32)] == 2 * 3 * 4 * 8 * 2
+    assert cm.bytes_per_token() == (per_page[("paged", None)] + per_page[("paged", 32)]) // 4
+    with pytest.raises(TypeError, match="cache dtype"):
+        CacheManager({0: PagedKVSpec(1, 8, cache_dtype="int8")}, 4, 2, 1)
+    with pytest.raises(TypeError, match="unknown cache spec"):
+        CacheManager({0: (PagedKVSpec(1, 8), "state")}, 4, 2, 1)

@@ -180,9 +180,22 @@ def test_sampling_is_seeded_and_penalties_bite(model_dirs):
     grams = [tuple(seq[i:i + 2]) for i in range(len(seq) - 1)]
     new = grams[len(p) - 1:]
     assert len(set(new)) == len(new) and not set(new) & set(grams[:len(p) - 1])
-    pen = eng.generate([p], SamplingParams(temperature=0, max_new_tokens=40, repetition_penalty=1.5,
-                                            frequency_penalty=0.5, presence_penalty=0.5))[0]
-    assert len(set(pen)) >= len(set(plain_out))
+    # penalties through the engine: every token it picks is the best one of the plain logits with the penalties
+    # applied by hand (snowllm/engine/sampler.py:187-219: seen tokens' logits divided by the repetition penalty
+    # when positive, multiplied when negative; minus frequency x count and presence for generated tokens)
+    rep, freq, pres = 1.5, 0.02, 0.01
+    pen = eng.generate([p], SamplingParams(temperature=0, max_new_tokens=24, repetition_penalty=rep,
+                                            frequency_penalty=freq, presence_penalty=pres))[0]
+    assert pen != plain_out[:24], "the penalties changed nothing"
+    cfg, tensors = plain.read_model_dir(d)
+    from collections import Counter
+    for i, tok in enumerate(pen):
+        row = plain.logits(cfg, tensors, p + pen[:i])[-1].clone()
+        counts = Counter(pen[:i])
+        for t in set(p) | set(pen[:i]):
+            row[t] = row[t] / rep if row[t] > 0 else row[t] * rep
+            row[t] -= freq * counts.get(t, 0) + (pres if counts.get(t, 0) else 0.0)
+        assert float(row.max() - row[tok]) <= 1e-4, f"token {i}: {tok} is not the best penalised token"
 
 
 def test_command_line_generates(model_dirs):

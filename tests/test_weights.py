@@ -104,3 +104,32 @@ def test_missing_file_and_bad_header(tmp_path):
     (tmp_path / "model.safetensors").write_bytes(b"\x05\x00\x00\x00\x00\x00\x00\x00{bad}")
     with pytest.raises(WeightError, match="header"):
         Checkpoint(tmp_path)
+
+
+def test_weight_bytes_a_step_reads_come_from_what_parts_declared():
+    """Every declared tensor once, in the dtype it is kept in; of routed experts the picked share; a tied
+    head reads the embedding table; a layer that the run list names twice is read twice."""
+    import torch
+
+    from snowllm_b200.loader import build_model
+    from snowllm_b200.weights import load_tensors, random_tensors
+    from tiny_configs import TINY_A, TINY_B
+    for cfg in (TINY_A, TINY_B):
+        model = build_model(cfg, "bfloat16")
+        tensors = random_tensors(model, 0, torch.bfloat16)
+        load_tensors(model, tensors, "cpu")
+        kept = {n: (4 if n.endswith("expert_bias") else 2) * t.numel() for n, t in tensors.items()}
+        if not cfg["tie_word_embeddings"]:             # the table is then only gathered from: a row per token
+            del kept["model.embed_tokens.weight"]
+        assert model.weight_bytes_per_step() == sum(kept.values())
+        moe_entries = [i for i, e in enumerate(model.run) if hasattr(model.blocks[e.layer].ffn, "route")]
+        E = cfg["num_experts"]
+        experts = {i: sum(v for n, v in kept.items() if f"layers.{model.run[i].layer}.feed_forward.experts." in n)
+                   for i in moe_entries}
+        picked = {i: 1 + i % 3 for i in moe_entries}
+        want = sum(kept.values()) - sum(experts[i] - experts[i] * picked[i] // E for i in moe_entries)
+        assert abs(model.weight_bytes_per_step(picked) - want) <= len(moe_entries)
+    from snowllm_b200.parts.spec import RunEntry
+    model.run = list(model.run) + [RunEntry(1)]
+    twice = sum(v for n, v in kept.items() if ".layers.1." in n)
+    assert model.weight_bytes_per_step() == sum(kept.values()) + twice
