@@ -75,6 +75,7 @@ _SIGNATURES = {
         "snk_moe_topk": [P, P, P, P, I, I, I, I, F, I, I, P],
         "snk_moe_route_sort": [P, P, I, P, P, P, P, P, P, P, I, I, I, I, I, F, I, P],
         "snk_moe_sort": [P, P, P, P, I, I, P],
+        "snk_norm_route_sort": [P, P, P, I, P, I, F, P, P, P, I, P, I, P, P, P, P, P, P, I, I, I, I, F, I, P, P],
         "snk_moe_combine": [P, P, P, P, I, I, I, P],
     },
     "sampling": {
@@ -888,6 +889,66 @@ def moe_route_sort(x, router_w, bias, top_k, norm_topk_prob, scaling):
                                    int(bool(norm_topk_prob)), float(scaling), code_of(dtype), _stream()),
           "moe_route_sort", launches=2, work=lambda: (_nbytes(x, router_w, ints, floats), 2 * M * E * H))
     return ids, wts, offsets, pair_pos, sorted_pair
+
+
+NORM_ROUTE_MAX_ROWS = 32
+# Off by default: measured in the decode step of the 8B-A1B sizes it gains nothing (batch 1: 1.488 ms against
+# 1.471 ms with the three launches it replaces; batch 8: 3.012 against 2.966 ms).  Inside a captured step the
+# three launches hide one another's start, and one block per row walks norm, 32 dot products, selection and
+# sort one after the other (12.4 us against 3.3 + 4.2 + 5.4 us).
+FUSE_ROUTER = os.environ.get("SNOWLLM_B200_FUSE_ROUTER", "0") != "0"
+
+
+def norm_route_sort_ok(residual, delta, gamma, router_w, top_k) -> bool:
+    """Whether the one-launch front of a routed feed-forward (csrc/moe.cu: norm_route_sort_kernel) takes these
+    operands (the switch ``FUSE_ROUTER`` is the caller's business)."""
+    M, H = residual.shape
+    E = router_w.shape[0]
+    plain = delta is None or isinstance(delta, ExpertSum) or (torch.is_tensor(delta) and delta.data_ptr() % 16 == 0)
+    return (M <= NORM_ROUTE_MAX_ROWS and H % 4 == 0 and H <= 32768 and top_k <= 32 and plain
+            and residual.data_ptr() % 16 == 0 and (max(H, 2 * E + 4) + 40 + 2 * E) * 4 <= 200 * 1024)
+
+
+def norm_route_sort(residual, delta, gamma, eps, dtype, router_w, bias, top_k, norm_topk_prob, scaling, ticket):
+    """``residual += delta`` (a float tensor, an ``ExpertSum`` or None), RMSNorm into ``dtype``, the sigmoid
+    router on the normalised rows, and the sort of the (token, pick) pairs by expert, in one launch for the
+    few rows of a decode step: (x, ids, weights, offsets, pair_pos, sorted_pair), the same values as
+    ``add_rmsnorm`` followed by ``moe_route_sort`` give.  ``ticket``: one int32 on the device, zero before
+    the first call; the kernel leaves it zero."""
+    M, H = residual.shape
+    E = router_w.shape[0]
+    _chk(residual, "residual", torch.float32)
+    moe = None
+    if isinstance(delta, ExpertSum):
+        moe, delta = delta, None
+        _chk(moe.y, "expert outputs", torch.float32)
+        _chk(moe.pair_pos, "pair positions", torch.int32, (M * moe.weights.shape[1],))
+        _chk(moe.weights, "top-k weights", torch.float32)
+    if delta is not None:
+        _chk(delta, "residual delta", torch.float32, (M, H))
+    g32 = _small(gamma, "norm weight", dtype)
+    _chk(gamma, "norm weight", shape=(H,))
+    w32 = _small(router_w, "router weight", dtype)
+    _chk(router_w, "router weight", shape=(E, H))
+    if bias is not None:
+        _chk(bias, "expert bias", torch.float32, (E,))
+    _chk(ticket, "ticket", torch.int32, (1,))
+    dev = residual.device
+    x = torch.empty(M, H, dtype=dtype, device=dev)
+    pairs = M * top_k
+    ints = torch.empty(pairs * 3 + E + 1, dtype=torch.int32, device=dev)
+    wts = torch.empty(M, top_k, dtype=torch.float32, device=dev)
+    ids, pair_pos, sorted_pair = ints[:pairs].view(M, top_k), ints[pairs:2 * pairs], ints[2 * pairs:3 * pairs]
+    offsets = ints[3 * pairs:]
+    check(fn("snk_norm_route_sort")(
+        _ptr(residual), _ptr(delta), _ptr(gamma), g32, _ptr(x), H, float(eps), _ptr(moe.y if moe else None),
+        _ptr(moe.pair_pos if moe else None), _ptr(moe.weights if moe else None), moe.weights.shape[1] if moe else 0,
+        _ptr(router_w), w32, _ptr(bias), _ptr(ids), _ptr(wts), _ptr(offsets), _ptr(pair_pos), _ptr(sorted_pair),
+        M, E, top_k, int(bool(norm_topk_prob)), float(scaling), code_of(dtype), _ptr(ticket), _stream()),
+        "norm_route_sort",
+        work=lambda: (2 * M * H * 4 + _nbytes(x, router_w, ints, wts) + (_nbytes(delta) if delta is not None else 0)
+                      + (moe.weights.shape[1] * M * H * 4 if moe else 0), 2 * M * E * H))
+    return x, ids, wts, offsets, pair_pos, sorted_pair
 
 
 def moe_sort(topk_ids, num_experts):

@@ -9,8 +9,12 @@ Interfaces (duck-typed; these base classes only hold what is common):
                ``forward(ctx, x[M,H], cache, owns_cache) -> float delta [M,H]``
 * feed-forward ``forward(ctx, x[M,H]) -> float delta [M,H]`` (or a ``kernels.ExpertSum``, a delta still in
                pieces that norms add up themselves; ``.dense()`` gives the tensor)
+               Optional: ``forward_from_residual(ctx, residual, delta, norm) -> delta | None``: the norm
+               before the feed-forward taken into its first kernel (None: not for this step or this norm;
+               the block then calls the norm and ``forward``).  It must give what the two calls give.
 * norm:        ``forward(ctx, residual, delta, rows=None) -> x[M,H]`` (adds delta into the float
-               residual, then normalises into the compute dtype)
+               residual, then normalises into the compute dtype).  A norm that is x * rsqrt(mean(x^2) + eps)
+               * weight over the whole width says so with ``fusable_rms = True`` (and ``weight``, ``eps``).
 * position:    ``rotary(device) -> (inv_freq float [rot_dim/2] | None, rot_dim)``
 * block:       ``forward(ctx, residual, delta, cache, owns_cache) -> delta`` (how mixer, feed-
                forward and norms are arranged around the residual stream)

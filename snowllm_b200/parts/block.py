@@ -25,6 +25,13 @@ class PreNormBlock:
         with span(self._names[1]):
             delta = self.mixer.forward(ctx, x, cache, owns_cache)
         ctx.tap("mixer_out", delta)
+        fused = getattr(self.ffn, "forward_from_residual", None)
+        if fused is not None:          # a feed-forward that can take the norm before it into its first kernel
+            with span(self._names[3]):
+                out = fused(ctx, residual, delta, self.ffn_norm)
+            if out is not None:
+                ctx.tap("ffn_out", out)
+                return out
         with span(self._names[2]):
             x = self.ffn_norm.forward(ctx, residual, delta)
         ctx.tap("ffn_in", x)

@@ -27,6 +27,7 @@ class SigmoidMoE(Part):
         self.routed_scaling_factor = routed_scaling_factor
         self.router = self.bias = self.w13 = self.w2 = None
         self._fused = False
+        self._ticket = None            # the counter of the one-launch front end (zero between launches)
 
     def declare(self, has):
         H, I, E = self.hidden_size, self.intermediate_size, self.num_experts
@@ -72,10 +73,30 @@ class SigmoidMoE(Part):
         return kernels.moe_route(x, self.router, self.bias, self.top_k, self.norm_topk_prob,
                                  self.routed_scaling_factor)
 
+    def forward_from_residual(self, ctx, residual, delta, norm):
+        """The norm that precedes this feed-forward, the router and the sort in one launch, for the few rows
+        of a decode step (csrc/moe.cu: norm_route_sort_kernel); None when this step or this norm is not
+        one it takes, and the block then runs the norm and ``forward`` one after the other."""
+        weight, eps = getattr(norm, "weight", None), getattr(norm, "eps", None)
+        if getattr(norm, "fusable_rms", False) is not True or weight is None or eps is None:
+            return None
+        if not kernels.FUSE_ROUTER or not kernels.norm_route_sort_ok(residual, delta, weight, self.router, self.top_k):
+            return None
+        if self._ticket is None or self._ticket.device != residual.device:
+            self._ticket = torch.zeros(1, dtype=torch.int32, device=residual.device)
+        x, *routed = kernels.norm_route_sort(residual, delta, weight, eps, self.dtype, self.router, self.bias,
+                                             self.top_k, self.norm_topk_prob, self.routed_scaling_factor,
+                                             self._ticket)
+        if ctx is not None:
+            ctx.tap("ffn_in", x)
+        return self._experts(ctx, x, *routed)
+
     def forward(self, ctx, x):
+        return self._experts(ctx, x, *kernels.moe_route_sort(
+            x, self.router, self.bias, self.top_k, self.norm_topk_prob, self.routed_scaling_factor))
+
+    def _experts(self, ctx, x, ids, weights, offsets, pair_pos, sorted_pair):
         M, k = x.shape[0], self.top_k
-        ids, weights, offsets, pair_pos, sorted_pair = kernels.moe_route_sort(
-            x, self.router, self.bias, self.top_k, self.norm_topk_prob, self.routed_scaling_factor)
         if ctx is not None:
             ctx.tap("moe_route", ids)
             ctx.tap("moe_route_input", x)

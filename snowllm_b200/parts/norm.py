@@ -10,6 +10,8 @@ from .spec import INIT_ONES, KEEP_SMALL, TensorSpec
 
 class RMSNorm(Part):
     libraries = ("elementwise",)
+    fusable_rms = True     # x * rsqrt(mean(x^2) + eps) * weight over the whole width: what a part that fuses
+                           # the norm before it into its own first kernel may take over (weight, eps)
 
     def __init__(self, dtype, names, *, size: int, eps: float):
         super().__init__(dtype, names)

@@ -1062,3 +1062,48 @@ def test_attention_over_long_contexts(K, N):
     K.attention_decode_mma(dev(qp[-1:], dtype), pool2, i32([table2]), P, i32([N - 1]), i32([0]), hd2 ** -0.5, need, out)
     assert rel_l2(out, want_p[-1:]) < 0.005
     assert K.attention_decode_status() == 0
+
+
+# ---------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("M,H,E,k,bias,norm_topk,scaling", [(1, 2048, 32, 4, True, True, 1.0), (8, 2048, 32, 4, True, True, 1.0),
+                                                             (32, 96, 16, 4, False, False, 2.0), (5, 80, 5, 3, True, True, 0.5),
+                                                             (3, 1000, 64, 8, True, False, 1.0), (17, 128, 4, 1, True, False, 1.0)])
+def test_norm_route_sort_in_one_launch(K, dtype, M, H, E, k, bias, norm_topk, scaling):
+    """The one-launch front of a routed feed-forward against the three launches it replaces: the same bits for
+    the residual, the normalised rows, the picks and their weights; a valid sort; and again on a second
+    call (the ticket counter went back to zero)."""
+    from helpers import Guards
+    torch.manual_seed(70)
+    eps = 1e-5
+    gamma = dev(rnd(dtype, H) + 1.0, dtype)
+    wr = dev(rnd(dtype, E, H, scale=H ** -0.5), dtype)
+    b = dev(torch.randn(E) * 0.01) if bias else None
+    ticket = torch.zeros(1, dtype=torch.int32, device="cuda")
+    prev_k = 3
+    for round_ in range(2):
+        start = torch.randn(M, H, device="cuda")
+        pieces = K.ExpertSum(torch.randn(M * prev_k, H, device="cuda"), torch.randperm(M * prev_k).int().cuda(),
+                             torch.rand(M, prev_k, device="cuda"))
+        for delta in (torch.randn(M, H, device="cuda"), pieces, None):
+            assert K.norm_route_sort_ok(start, delta, gamma, wr, k)
+            res_a, res_b = start.clone(), start.clone()
+            x_a = K.add_rmsnorm(res_a, delta, gamma, eps, dtype)
+            ids_a, w_a, off_a, pos_a, sorted_a = K.moe_route_sort(x_a, wr, b, k, norm_topk, scaling)
+            x_b, ids_b, w_b, off_b, pos_b, sorted_b = K.norm_route_sort(res_b, delta, gamma, eps, dtype, wr, b, k,
+                                                                         norm_topk, scaling, ticket)
+            assert torch.equal(res_a, res_b) and torch.equal(x_a, x_b)
+            assert torch.equal(ids_a, ids_b) and torch.equal(w_a, w_b) and torch.equal(off_a, off_b)
+            assert int(ticket) == 0
+            # the sort: every pair once, inside its expert's rows, and pair_pos its inverse
+            flat = ids_b.flatten().long().cpu()
+            sp, pp, off = sorted_b.long().cpu(), pos_b.long().cpu(), off_b.long().cpu()
+            assert sorted(sp.tolist()) == list(range(M * k)) and torch.equal(pp[sp], torch.arange(M * k))
+            for e in range(E):
+                assert bool((flat[sp[off[e]:off[e + 1]]] == e).all())
+    # nothing outside the buffers the caller sized (the outputs are made inside the wrapper; the residual is not)
+    g = Guards()
+    res = g((M, H), torch.float32, like=torch.randn(M, H, device="cuda"))
+    tk = g((1,), torch.int32, fill=0)
+    K.norm_route_sort(res, torch.randn(M, H, device="cuda"), gamma, eps, dtype, wr, b, k, norm_topk, scaling, tk)
+    g.check("norm_route_sort")

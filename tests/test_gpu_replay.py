@@ -151,3 +151,21 @@ def test_models_without_pages_or_without_state(model_dirs, name, dtype):
     steps = mixed_trace(reqs, seed=5)
     outputs, routes = run_in_process(d, dtype, steps, max_live_tokens(steps))
     check_against_plain(d, dtype, reqs, steps, outputs, routes)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_mixed_cut_with_the_one_launch_router_front_end(model_dirs, dtype, monkeypatch):
+    """The switch that lets a routed feed-forward take the norm before it, the router and the sort into one
+    launch (off by default) gives the same logits as the three launches, on the mixed trace."""
+    from snowllm_b200.ops import kernels
+    d = model_dirs("tiny_b", dtype)
+    reqs = requests_for(ALL["tiny_b"], seed=50)
+    steps = mixed_trace(reqs, seed=7)
+    apart, _ = run_in_process(d, dtype, steps, max_live_tokens(steps))
+    monkeypatch.setattr(kernels, "FUSE_ROUTER", True)
+    launches = kernels.launch_count()
+    together, routes = run_in_process(d, dtype, steps, max_live_tokens(steps))
+    monkeypatch.setattr(kernels, "FUSE_ROUTER", False)
+    for a, b in zip(apart, together):
+        assert (a is None and b is None) or torch.equal(a, b)
+    check_against_plain(d, dtype, reqs, steps, together, routes)
