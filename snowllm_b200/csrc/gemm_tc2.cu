@@ -275,10 +275,15 @@ __device__ __forceinline__ T2GItem t2g_item(int item, const int* first, const in
   const int row_tiles = (cnt + 2 * T2_BM - 1) / (2 * T2_BM);
   const int in_group = item - first[lo];
   const int ft = in_group / row_tiles, tt = in_group % row_tiles;
-  t.row0 = begin + tt * 2 * T2_BM;
-  t.row_end = begin + cnt;
+  // A group's rows are dealt evenly to its row tiles (in steps of 16): every tile streams the same rows of W,
+  // so a group of 270 rows as 144 + 128 costs two half-length products, where 256 + 16 costs a full one and
+  // a second pass over W for 16 rows (with 2,048 tokens, top 4 of 32 experts, half the groups are just
+  // above 256 rows).
+  const int per = ((cnt + row_tiles - 1) / row_tiles + 15) & ~15;
+  t.row0 = begin + tt * per;
+  t.row_end = min(begin + cnt, t.row0 + per);
   const int left = t.row_end - t.row0;
-  t.nt = left >= 2 * T2_BM ? 2 * T2_BM : (left + 15) & ~15;
+  t.nt = left <= 0 ? 16 : (left + 15) & ~15;
   t.w_row0 = lo * N;
   t.f0 = ft * T2_BN;
   t.valid = true;
