@@ -229,3 +229,51 @@ def test_smoke_entry():
     sys.path.insert(0, str(ROOT))
     import __graft_entry__
     __graft_entry__.smoke()
+
+
+@pytest.mark.parametrize("overlap", [True, False])
+def test_many_requests_under_pressure_match_calm_runs(model_dirs, overlap):
+    """Thirty requests of random lengths and reply limits, some with stop tokens, one aborted on the way, four
+    at a time in a pool so small that requests are preempted and replayed, portions of 24 tokens, captured
+    decode steps: every request ends with the tokens it gets when it runs alone in a roomy engine, and every
+    page and slot comes back."""
+    import random
+
+    from snowllm_b200.engine import SamplingParams
+    d = model_dirs("tiny_a", "float32")
+    rng = random.Random(7)
+    jobs = []
+    for i in range(30):
+        prompt = random_prompt(256, rng.randint(3, 90), 200 + i)
+        jobs.append((prompt, rng.randint(4, 40)))
+    roomy = engine_for(d, max_num_seqs=1, max_model_len=256)
+    alone = []
+    for prompt, n in jobs:
+        alone.append(roomy.generate([prompt], SamplingParams(temperature=0, max_new_tokens=n))[0])
+    # stop tokens for every fourth request: a token its calm run produced in the middle
+    params = []
+    for i, ((prompt, n), out) in enumerate(zip(jobs, alone)):
+        stop = (out[len(out) // 2],) if i % 4 == 0 else ()
+        params.append(SamplingParams(temperature=0, max_new_tokens=n, stop_token_ids=stop))
+    tight = engine_for(d, max_num_seqs=4, max_model_len=160, num_kv_blocks=11, prefill_chunk=24, overlap_steps=overlap)
+    reqs = [tight.add(prompt, p) for (prompt, _), p in zip(jobs, params)]
+    steps = 0
+    while tight.scheduler.has_work():
+        tight.step()
+        steps += 1
+        if steps == 25:
+            tight.abort(reqs[11])
+        assert steps < 5000
+    tight.run()
+    assert tight.stats().preemptions > 0, "the pool was meant to be too small for four requests at a time"
+    for i, (r, out, p) in enumerate(zip(reqs, alone, params)):
+        if i == 11:
+            assert r.finish_reason in ("abort", "length", "stop")
+            assert r.out == out[:len(r.out)]
+            continue
+        want = out[:out.index(p.stop_token_ids[0]) + 1] if p.stop_token_ids else out
+        assert r.out == want, f"request {i}: {r.out} against {want} (preempted {r.preemptions} times)"
+        assert r.finish_reason == ("stop" if p.stop_token_ids else "length")
+    st = tight.stats()
+    assert st.free_kv_blocks == 11 and st.free_slots == 4 and st.running == 0 and st.waiting == 0
+    assert st.step_errors == 0 and st.failed_requests == 0
