@@ -89,3 +89,19 @@ def test_unknown_part_kind_is_a_config_error():
     from snowllm_b200.parts.registry import lookup
     with pytest.raises(ConfigError, match="short_conv"):
         lookup("mixer", "mamba9")
+
+
+def test_trace_spans_cost_nothing_when_off(monkeypatch):
+    from snowllm_b200 import trace
+    monkeypatch.setattr(trace, "_forced", False)
+    a, b = trace.span("one"), trace.span("two")
+    assert a is b                                          # the shared do-nothing context
+    with a:
+        pass
+    trace.enable(True)
+    try:
+        with trace.span("named"):                          # an NVTX range and a record_function region; fine without a GPU
+            pass
+        assert trace.enabled()
+    finally:
+        trace.enable(False)

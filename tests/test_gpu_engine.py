@@ -277,3 +277,27 @@ def test_many_requests_under_pressure_match_calm_runs(model_dirs, overlap):
     st = tight.stats()
     assert st.free_kv_blocks == 11 and st.free_slots == 4 and st.running == 0 and st.waiting == 0
     assert st.step_errors == 0 and st.failed_requests == 0
+
+
+def test_named_spans_show_up_on_a_profilers_timeline(model_dirs, tmp_path):
+    """With tracing on, the engine's step and every part's work carry a name in a torch.profiler session; the
+    command line's --enable-profiler writes a Chrome trace."""
+    from torch.profiler import ProfilerActivity, profile
+
+    from snowllm_b200 import trace
+    from snowllm_b200.engine import SamplingParams
+    d = model_dirs("tiny_a", "float32")
+    eng = engine_for(d, max_num_seqs=2, enforce_eager=True)
+    assert trace.span("x") is trace.span("y")              # off: one shared do-nothing context
+    with profile(activities=[ProfilerActivity.CPU]) as prof:   # a running session switches the spans on
+        eng.generate([random_prompt(256, 9, 1)], SamplingParams(temperature=0, max_new_tokens=3))
+    names = {e.name for e in prof.events()}
+    for want in ("engine.step", "embedding", "mixer:ShortConv", "mixer:Attention", "ffn:SigmoidMoE", "ffn:SwiGLU",
+                 "norm:RMSNorm", "head", "run[2]:layer2"):
+        assert want in names, f"no span named {want!r} (have {sorted(n for n in names if ':' in n)[:8]} ...)"
+    out = tmp_path / "prof"
+    proc = subprocess.run([sys.executable, "-m", "snowllm_b200", str(d), "--dtype", "float32", "--prompt-ids", "1,2,3",
+                           "--default-max-tokens", "2", "--max-model-len", "64", "--enable-profiler", "--profile-dir",
+                           str(out)], capture_output=True, text=True, cwd=ROOT, timeout=600)
+    assert proc.returncode == 0, proc.stderr[-2000:]
+    assert (out / "trace.json").stat().st_size > 1000
