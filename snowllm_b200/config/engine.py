@@ -10,7 +10,12 @@ from dataclasses import dataclass, fields
 
 from ..errors import SnowLLMError
 
-DEFAULT_PAGE_SIZE = 16                 # tokens per cache page
+# Tokens per cache page.  64: a page of one kv head is then one 8 KB TMA box, and a 256-key chunk of the decode
+# attention 8 boxes instead of 32 (measured against pages of 16: the 64-request decode step of the 8B-A1B sizes
+# 5.62 -> 5.52 ms, of the dense 1.2B sizes at context 32,768 6.37 -> 6.03 ms; pages of 128 and 256 gain a little
+# more there, but 256 is past what the tcgen05 prompt kernel takes, and 64 is what the replay tool's pool is
+# counted in).
+DEFAULT_PAGE_SIZE = 64
 DEFAULT_GPU_UTIL = 0.9                 # fraction of device memory the engine may fill
 DEFAULT_PREFILL_CHUNK = 8192           # token budget of one step (--max-num-batched-tokens)
 MAX_NUM_SEQS = 256

@@ -21,6 +21,8 @@ def engine_for(model_dir, dtype="float32", **kw):
     from snowllm_b200.engine import Engine
     model = snowllm_b200.load(model_dir, dtype)
     kw.setdefault("max_model_len", 512)
+    if "num_kv_blocks" in kw:
+        kw.setdefault("page_size", 16)          # the tests that count pages count pages of 16 tokens
     return Engine(model, **kw)
 
 
