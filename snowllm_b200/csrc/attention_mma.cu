@@ -306,6 +306,7 @@ attention_prefill_tma_kernel(const __grid_constant__ CUtensorMap map_kv, const b
   const uint32_t sm_kv = (uint32_t)__cvta_generic_to_shared(fp_smem);       // [FP_STAGES][k | v][PANELS][64][64]
   const uint32_t sm_q = sm_kv + FP_STAGES * STAGE;                          // [64][HD], swz<CH>
   __shared__ uint64_t full[FP_STAGES];
+  __shared__ int gave_up;                                 // a wait ran out: no more loads, no more waits
 
   const int* tile = tiles + (size_t)(n_tiles - 1 - blockIdx.x) * 4;
   const int seg = tile[0], row0 = tile[1], rows = tile[2], pos0 = tile[3];
@@ -323,6 +324,7 @@ attention_prefill_tma_kernel(const __grid_constant__ CUtensorMap map_kv, const b
   if (threadIdx.x == 0) {
 #pragma unroll
     for (int i = 0; i < FP_STAGES; ++i) mbar_init(&full[i], 1);
+    gave_up = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   }
@@ -336,6 +338,7 @@ attention_prefill_tma_kernel(const __grid_constant__ CUtensorMap map_kv, const b
   // warp 0 issues tile kt's pages: those that hold a key of [key_lo, last_pos]
   auto issue = [&](int kt) {
     if (warp != 0 || kt >= n_kt) return;
+    if (__any_sync(0xffffffffu, *const_cast<volatile int*>(&gave_up))) return;     // the warp as one
     const int k0 = k_first + kt * FA_BK;
     const int first_page = max(k0, key_lo) / page_size;
     const int n_pages = min(k0 + FA_BK - 1, last_pos) / page_size - first_page + 1;
@@ -386,10 +389,12 @@ attention_prefill_tma_kernel(const __grid_constant__ CUtensorMap map_kv, const b
     issue(kt + FP_STAGES - 1);                            // into the stage that tile kt - 1 left
     const int st = kt % FP_STAGES;
     const uint32_t parity = (uint32_t)(kt / FP_STAGES) & 1u;
-    if (!mbar_try_wait(&full[st], parity)) {
+    if (!*const_cast<volatile int*>(&gave_up) && !mbar_try_wait(&full[st], parity)) {
       const uint64_t start = global_ns();
       while (!mbar_try_wait(&full[st], parity)) {
+        if (*const_cast<volatile int*>(&gave_up)) break;
         if (global_ns() - start > FP_WAIT_NS) {
+          gave_up = 1;                                    // the tiles that follow are not waited for (the output is void)
           atomicCAS(&g_fa_status, 0, 1);
           break;
         }
@@ -497,6 +502,7 @@ attention_prefill_tma_kernel(const __grid_constant__ CUtensorMap map_kv, const b
     }
     __syncthreads();                                      // the stage is free for tile kt + FP_STAGES
   }
+  if (*const_cast<volatile int*>(&gave_up)) drain_after_abort();            // copies in flight land before the block returns
 #pragma unroll
   for (int h = 0; h < 2; ++h) {
     row_sum[h] += __shfl_xor_sync(0xffffffffu, row_sum[h], 1);
@@ -859,6 +865,7 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_kv, const bf
     while (!mbar_try_wait(&bar, 0)) {
       if (global_ns() - start > FD_WAIT_NS) {
         atomicCAS(&g_fd_status, 0, 1);
+        drain_after_abort();                              // the copies in flight land before the block goes on and returns
         break;
       }
     }

@@ -227,6 +227,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         const int k0 = k_first + t * AT_BK;
         tile_pages(t, fp_k, np_k);
         at_wait(&sh->k_empty[ks], ((t / AT_KSTAGES) & 1) ^ 1, aborted, AT_ERR_KV_FREE);
+        if (__any_sync(0xffffffffu, *aborted)) break;      // a wait ran out: nothing more is issued
         if (lane == 0) mbar_expect_tx(&sh->k_full[ks], (uint32_t)np_k * page_size * 128u);
         __syncwarp();
         if (lane < np_k)
@@ -237,6 +238,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         const int j = t - 1, vs = j % AT_VSTAGES;
         const int k0 = k_first + j * AT_BK;
         at_wait(&sh->v_empty[vs], ((j / AT_VSTAGES) & 1) ^ 1, aborted, AT_ERR_KV_FREE);
+        if (__any_sync(0xffffffffu, *aborted)) break;
         if (lane == 0) mbar_expect_tx(&sh->v_full[vs], (uint32_t)np_v * page_size * 128u);
         __syncwarp();
         if (lane < np_v)
@@ -256,6 +258,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         const int st = j % AT_KSTAGES;
         at_wait(&sh->k_full[st], (j / AT_KSTAGES) & 1, aborted, AT_ERR_KV);
         at_wait(&sh->s_empty, (j & 1) ^ 1, aborted, AT_ERR_S_FREE);
+        if (*aborted) return;
         tc_fence_after();
         const uint32_t k_addr = smem_u32(sm_k + (size_t)st * AT_KV_BYTES);
 #pragma unroll
@@ -270,6 +273,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         const int st = j % AT_VSTAGES;
         at_wait(&sh->p_full, j & 1, aborted, AT_ERR_P);
         at_wait(&sh->v_full[st], (j / AT_VSTAGES) & 1, aborted, AT_ERR_KV);
+        if (*aborted) break;
         tc_fence_after();
         const uint32_t p_addr = smem_u32(sm_p);
         const uint32_t v_addr = smem_u32(sm_v + (size_t)st * AT_KV_BYTES);
@@ -307,6 +311,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
       const int st = j % AT_VSTAGES;
       const int k0 = k_first + j * AT_BK;
       at_wait(&sh->s_full, j & 1, aborted, AT_ERR_S);
+      if (__any_sync(0xffffffffu, *aborted)) break;        // the whole warp leaves together
       tc_fence_after();
       uint32_t r[4][32];
 #pragma unroll
@@ -423,6 +428,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
       }
     }
   }
+  if (*aborted) drain_after_abort();
   tc_fence_before();
   __syncthreads();
   if (warp == 1) {

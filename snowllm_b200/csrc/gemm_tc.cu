@@ -23,8 +23,9 @@
 // a tile never mixes groups in its stored rows.
 //
 // Every wait on an mbarrier is bounded by wall time: when it runs out the block records an error
-// code (see snk_gemm_tc_status), lets its remaining steps run through without waiting, frees its
-// tensor memory and returns.
+// code (see snk_gemm_tc_status), issues no more loads and products, gives the copies in flight a moment
+// to land, frees its tensor memory and returns.  snk_gemm_tc_test_lose_loads makes that happen for a test:
+// the producers then issue no loads, so the waits for operands run out.
 // (the role of snowllm/ops/gemm.py:33-41 and the expert products of snowllm/ops/inference.py:60-76
 // at prefill shapes)
 #include "tma.cuh"
@@ -42,6 +43,7 @@
 enum { TC_ERR_WAIT_FULL = 1, TC_ERR_WAIT_EMPTY = 2, TC_ERR_WAIT_ACC = 3, TC_ERR_WAIT_ACC_FREE = 4 };
 
 __device__ int g_tc_status;            // 0, or the first error code a block recorded
+__device__ int g_tc_lose_loads;        // test hook: producers issue no loads (the operands then never arrive)
 
 // Wait for a phase, for TC_WAIT_NS at most.  `aborted` (shared) short-cuts every later wait of the block.
 __device__ __forceinline__ void mbar_wait(uint64_t* bar, uint32_t parity, volatile int* aborted, int code) {
@@ -177,13 +179,16 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   if (warp == 0) {
     if (lane == 0) {
       int it = 0;                                        // k-blocks issued so far, over all tiles
-      for (int item = blockIdx.x; item < items; item += gridDim.x) {
+      const bool lose_loads = *const_cast<volatile int*>(&g_tc_lose_loads) != 0;
+      for (int item = blockIdx.x; item < items && !*aborted; item += gridDim.x) {
         const TcTile t = tc_tile(item % total, row_tiles, M, N, BN, offsets, groups);
         if (!t.valid) continue;
         const int kt_begin = (item / total) * k_per, kt_end = min(k_tiles, kt_begin + k_per);
         for (int kt = kt_begin; kt < kt_end; ++kt, ++it) {
           const int s = it % STAGES;
           mbar_wait(&sh->empty[s], ((it / STAGES) & 1) ^ 1, aborted, TC_ERR_WAIT_EMPTY);
+          if (*aborted) break;                             // a wait ran out: nothing more is issued
+          if (lose_loads) continue;
           mbar_expect_tx(&sh->full[s], STAGE_BYTES);
           unsigned char* stage = tiles + (size_t)s * STAGE_BYTES;
           tma_load_2d(stage, &map_a, &sh->full[s], kt * TC_BK, t.row0);
@@ -195,7 +200,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     if (lane == 0) {
       const uint32_t idesc = instr_desc_bf16(TC_BM, BN);
       int it = 0, local = 0;
-      for (int item = blockIdx.x; item < items; item += gridDim.x) {
+      for (int item = blockIdx.x; item < items && !*aborted; item += gridDim.x) {
         const TcTile t = tc_tile(item % total, row_tiles, M, N, BN, offsets, groups);
         if (!t.valid) continue;
         const int kt_begin = (item / total) * k_per, kt_end = min(k_tiles, kt_begin + k_per);
@@ -206,6 +211,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         for (int kt = kt_begin; kt < kt_end; ++kt, ++it) {
           const int s = it % STAGES;
           mbar_wait(&sh->full[s], (it / STAGES) & 1, aborted, TC_ERR_WAIT_FULL);
+          if (*aborted) break;
           tc_fence_after();
           const uint32_t a_addr = smem_u32(tiles + (size_t)s * STAGE_BYTES);
           const uint32_t w_addr = a_addr + TC_BM * TC_BK * 2;
@@ -217,6 +223,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
           }
           umma_commit(&sh->empty[s]);                    // the stage is free once these MMAs have read it
         }
+        if (*aborted) break;
         umma_commit(&sh->acc_full[buf]);
         ++local;
       }
@@ -231,6 +238,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       OutT* Cp = C + (size_t)(item / total) * M * N;        // the part's plane (C itself without a split)
       const int buf = local & 1;
       mbar_wait(&sh->acc_full[buf], (local >> 1) & 1, aborted, TC_ERR_WAIT_ACC);
+      if (__any_sync(0xffffffffu, *aborted)) break;        // the whole warp leaves together
       tc_fence_after();
 #pragma unroll 1
       for (int c0 = 0; c0 < BN; c0 += 32) {
@@ -247,6 +255,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       ++local;
     }
   }
+  if (*aborted) drain_after_abort();
   tc_fence_before();
   __syncthreads();
   if (warp == 1) {
@@ -405,6 +414,12 @@ SNK_API int snk_gemm_tc_parts(const void* A, const void* W, void* parts, int M, 
   if (rc) return rc;
   *splits_out = splits;
   return launch_tc<128, float, false>(map_a, map_w, parts, M, N, K, nullptr, 1, (M + TC_BM - 1) / TC_BM, splits, stream);
+}
+
+// Test hook: with on != 0 the producers of later launches issue no loads, so that the bounded waits run out
+// (about 1.5 s) and the launches return with an error status instead of a product.  Synchronises.
+SNK_API int snk_gemm_tc_test_lose_loads(int on) {
+  return (int)cudaMemcpyToSymbol(g_tc_lose_loads, &on, sizeof(int));
 }
 
 // Queue a copy of the status word into ``host`` (pinned host memory, one int) on ``stream`` without waiting

@@ -14,8 +14,9 @@
 //                      arrival on the leader's accumulator-free barrier (remote from the peer)
 //
 // Row tiles are 256 rows.  Grouped products run the kernel further down, with the operands changed round.
-// Every mbarrier wait is bounded by wall time (see snk_gemm_tc2_status).  No TMA load is multicast: each
-// block loads what it owns.
+// Every mbarrier wait is bounded by wall time (see snk_gemm_tc2_status); when one runs out both blocks of the pair
+// stop issuing loads and products, give the copies in flight a moment to land, free their tensor memory and
+// return.  No TMA load is multicast: each block loads what it owns.
 #include "tcgen05.cuh"
 
 #define T2_BM 128                     // rows of A per block (256 per pair)
@@ -37,6 +38,7 @@
 enum { T2_ERR_FULL = 1, T2_ERR_EMPTY = 2, T2_ERR_ACC = 3, T2_ERR_ACC_FREE = 4, T2_ERR_PEER = 5 };
 
 __device__ int g_t2_status;
+__device__ int g_t2_lose_loads;      // test hook: producers issue no loads (the operands then never arrive)
 __device__ unsigned int g_t2_tmem[2];  // the tensor-memory base addresses the two blocks of cluster 0 were given (a probe)
 
 __device__ __forceinline__ void t2_wait(uint64_t* bar, uint32_t parity, volatile int* aborted, int code) {
@@ -47,6 +49,7 @@ __device__ __forceinline__ void t2_wait(uint64_t* bar, uint32_t parity, volatile
     if (*aborted) return;
     if (global_ns() - start > T2_WAIT_NS) {
       *aborted = 1;
+      st_cluster_u32(const_cast<int*>(aborted), cluster_ctarank() ^ 1u, 1u);   // the other block of the pair stops too
       atomicCAS(&g_t2_status, 0, code);
       return;
     }
@@ -132,12 +135,15 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
   if (warp == 0) {
     if (lane == 0) {
       int it = 0;
-      for (int tile = pair; tile < total; tile += pairs) {
+      const bool lose_loads = *const_cast<volatile int*>(&g_t2_lose_loads) != 0;
+      for (int tile = pair; tile < total && !*aborted; tile += pairs) {
         const T2Tile t = t2_tile(tile, row_tiles, M, N);
         if (!t.valid) continue;
         for (int kt = 0; kt < k_tiles; ++kt, ++it) {
           const int s = it % T2_STAGES;
           t2_wait(&sh->empty[s], ((it / T2_STAGES) & 1) ^ 1, aborted, T2_ERR_EMPTY);
+          if (*aborted) break;                           // a wait ran out: nothing more is issued
+          if (lose_loads) continue;
           // both blocks' bytes count towards the leader's barrier: it is the leader that issues the MMAs
           if (rank == 0) mbar_expect_tx(&sh->full[s], 2 * T2_STAGE_BYTES);
           const uint32_t bar = cluster_addr(&sh->full[s], 0);
@@ -151,7 +157,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     if (lane == 0 && rank == 0) {                        // the leader issues for the pair; the peer's warp rests
       const uint32_t idesc = instr_desc_bf16(2 * T2_BM, T2_BN);
       int it = 0, local = 0;
-      for (int tile = pair; tile < total; tile += pairs) {
+      for (int tile = pair; tile < total && !*aborted; tile += pairs) {
         const T2Tile t = t2_tile(tile, row_tiles, M, N);
         if (!t.valid) continue;
         const int buf = local % T2_ACC_BUFFERS;
@@ -162,6 +168,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
         for (int kt = 0; kt < k_tiles; ++kt, ++it) {
           const int s = it % T2_STAGES;
           t2_wait(&sh->full[s], (it / T2_STAGES) & 1, aborted, T2_ERR_FULL);   // both blocks' stage s
+          if (*aborted) break;
           tc_fence_after();
           const uint32_t a_addr = smem_u32(tiles + (size_t)s * T2_STAGE_BYTES);
           const uint32_t w_addr = a_addr + T2_BM * T2_BK * 2;
@@ -171,6 +178,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                        (kt > 0 || k > 0) ? 1u : 0u);
           umma2_commit(&sh->empty[s], 3);                // the stage is free in both blocks once these MMAs have read it
         }
+        if (*aborted) break;
         umma2_commit(&sh->acc_full[buf], 3);
         ++local;
       }
@@ -185,6 +193,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
       const int buf = local % T2_ACC_BUFFERS;
       const int use = local / T2_ACC_BUFFERS;
       t2_wait(&sh->acc_full[buf], use & 1, aborted, T2_ERR_ACC);
+      if (__any_sync(0xffffffffu, *aborted)) break;      // the whole warp leaves together
       tc_fence_after();
 #pragma unroll 1
       for (int c0 = 0; c0 < T2_BN; c0 += 32) {
@@ -205,6 +214,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
       ++local;
     }
   }
+  if (*aborted) drain_after_abort();
   tc_fence_before();
   cluster_sync();                                        // nobody of the pair touches tensor memory or barriers any more
   if (warp == 1) {
@@ -347,6 +357,7 @@ gemm_tc2_grouped_kernel(const __grid_constant__ T2GMaps maps, const __grid_const
   const int total = first[groups];
 
   int it = 0;                                            // k-blocks so far (producer and MMA thread)
+  const bool lose_loads = *const_cast<volatile int*>(&g_t2_lose_loads) != 0;
   auto issue_loads = [&](int item) {
     const T2GItem t = t2g_item(item, first, offsets, groups, N);
     const int half = t.nt >> 1, box = t2g_box(half);
@@ -354,6 +365,8 @@ gemm_tc2_grouped_kernel(const __grid_constant__ T2GMaps maps, const __grid_const
     for (int kt = 0; kt < k_tiles; ++kt, ++it) {
       const int s = it % T2_STAGES;
       t2_wait(&sh->empty[s], ((it / T2_STAGES) & 1) ^ 1, aborted, T2_ERR_EMPTY);
+      if (*aborted) return;                              // a wait ran out: nothing more is issued
+      if (lose_loads) continue;
       if (rank == 0) mbar_expect_tx(&sh->full[s], 2 * bytes);
       const uint32_t bar = cluster_addr(&sh->full[s], 0);
       unsigned char* stage = tiles + (size_t)s * T2G_STAGE_BYTES;
@@ -364,11 +377,11 @@ gemm_tc2_grouped_kernel(const __grid_constant__ T2GMaps maps, const __grid_const
 
   if (warp == 0) {
     if (lane == 0)
-      for (int item = pair; item < total; item += pairs) issue_loads(item);
+      for (int item = pair; item < total && !*aborted; item += pairs) issue_loads(item);
   } else if (warp == 1) {
     if (lane == 0 && rank == 0) {
       int local = 0;
-      for (int item = pair; item < total; item += pairs, ++local) {
+      for (int item = pair; item < total && !*aborted; item += pairs, ++local) {
         const T2GItem t = t2g_item(item, first, offsets, groups, N);
         const uint32_t idesc = instr_desc_bf16(2 * T2_BM, t.nt);
         const int buf = local % T2_ACC_BUFFERS;
@@ -379,6 +392,7 @@ gemm_tc2_grouped_kernel(const __grid_constant__ T2GMaps maps, const __grid_const
         for (int kt = 0; kt < k_tiles; ++kt, ++it) {
           const int s = it % T2_STAGES;
           t2_wait(&sh->full[s], (it / T2_STAGES) & 1, aborted, T2_ERR_FULL);
+          if (*aborted) break;
           tc_fence_after();
           const uint32_t w_addr = smem_u32(tiles + (size_t)s * T2G_STAGE_BYTES);
           const uint32_t a_addr = w_addr + T2_BM * T2_BK * 2;
@@ -388,6 +402,7 @@ gemm_tc2_grouped_kernel(const __grid_constant__ T2GMaps maps, const __grid_const
                        (kt > 0 || k > 0) ? 1u : 0u);
           umma2_commit(&sh->empty[s], 3);
         }
+        if (*aborted) break;
         umma2_commit(&sh->acc_full[buf], 3);
       }
     }
@@ -400,6 +415,7 @@ gemm_tc2_grouped_kernel(const __grid_constant__ T2GMaps maps, const __grid_const
       const int buf = local % T2_ACC_BUFFERS;
       const int use = local / T2_ACC_BUFFERS;
       t2_wait(&sh->acc_full[buf], use & 1, aborted, T2_ERR_ACC);
+      if (__any_sync(0xffffffffu, *aborted)) break;      // the whole warp leaves together
       tc_fence_after();
       const int col0 = t.f0 + (int)rank * T2_BM + lane_group * 32;     // this warp's 32 columns of C: one per lane
 #pragma unroll 1
@@ -441,6 +457,7 @@ gemm_tc2_grouped_kernel(const __grid_constant__ T2GMaps maps, const __grid_const
       }
     }
   }
+  if (*aborted) drain_after_abort();
   tc_fence_before();
   cluster_sync();
   if (warp == 1) {
@@ -501,6 +518,12 @@ SNK_API int snk_gemm_tc2(const void* A, const void* W, void* C, int M, int N, in
   if (swiglu) return launch_tc2<bf16, true>(map_a, map_w, C, M, N, K, row_tiles, stream);
   if (out_f32) return launch_tc2<float, false>(map_a, map_w, C, M, N, K, row_tiles, stream);
   return launch_tc2<bf16, false>(map_a, map_w, C, M, N, K, row_tiles, stream);
+}
+
+// Test hook: with on != 0 the producers of later launches issue no loads, so that the bounded waits run out
+// (about 1.5 s) and the launches return with an error status instead of a product.  Synchronises.
+SNK_API int snk_gemm_tc2_test_lose_loads(int on) {
+  return (int)cudaMemcpyToSymbol(g_t2_lose_loads, &on, sizeof(int));
 }
 
 // Queue a copy of the status word into ``host`` (pinned host memory, one int) on ``stream`` without waiting

@@ -47,6 +47,14 @@ __device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* m
       : "memory");
 }
 
+// After a wait has run out the block stops issuing work; before it returns it gives the copies it still has in
+// flight this long to land in its shared memory (they take microseconds when they land at all).
+#define SNK_DRAIN_NS 200000ull
+__device__ __forceinline__ void drain_after_abort() {
+  const uint64_t start = global_ns();
+  while (global_ns() - start < SNK_DRAIN_NS) {}
+}
+
 // ---------------------------------------------------------------------------------------------
 // Tensor maps: 2-D, bfloat16, rows of `k` elements (row pitch k * 2 bytes), box box_cols x box_rows,
 // 128-byte swizzle, zero fill outside.  Cached by (pointer, rows, k, box).

@@ -62,6 +62,7 @@ _SIGNATURES = {
         "snk_gemm_tc_scratch_bytes": [I, I, I, I],
         "snk_gemm_tc_status": [],
         "snk_gemm_tc_status_peek": [P, P],
+        "snk_gemm_tc_test_lose_loads": [I],
         "snk_gemm_tc_parts": [P, P, P, I, I, I, P, P],
         "snk_gather_rows_bf16": [P, P, P, I, I, I, P],
     },
@@ -69,6 +70,7 @@ _SIGNATURES = {
         "snk_gemm_tc2": [P, P, P, I, I, I, P, I, I, I, P],
         "snk_gemm_tc2_status": [P],
         "snk_gemm_tc2_status_peek": [P, P],
+        "snk_gemm_tc2_test_lose_loads": [I],
     },
     "moe": {
         "snk_moe_route": [P, P, I, P, P, P, I, I, I, I, I, F, I, P],
@@ -800,6 +802,14 @@ def gemm_tc_status() -> int:
     (synchronises the device; 1: operands never arrived, 2: a stage never came back, 3: the
     accumulator never became ready)."""
     return int(fn("snk_gemm_tc_status")())
+
+
+def lose_loads(on: bool) -> None:
+    """Test hook of the two tcgen05 product libraries: while on, their producers issue no loads, so the
+    bounded waits inside the kernels run out and a launch returns with an error status (see
+    ``gemm_tc_status``, ``gemm_tc2_status``, ``StatusWatch``) instead of a product."""
+    check(fn("snk_gemm_tc_test_lose_loads")(int(on)), "gemm_tc test hook", 0)
+    check(fn("snk_gemm_tc2_test_lose_loads")(int(on)), "gemm_tc2 test hook", 0)
 
 
 def gather_rows(x, rows, div=1, out=None):
