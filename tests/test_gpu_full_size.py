@@ -111,7 +111,7 @@ def test_one_step_of_2048_rows(setup, dtype):
     toks = random_prompt(V, 2048, 5)
     steps = [{"step": 0, "entries": [{"id": "p", "tokens": toks, "want": list(range(2048))}], "end": ["p"]}]
     stats = {}
-    outputs, routes = run_in_process(model, dtype, steps, 2048, max_requests=1, stats=stats)
+    outputs, routes = run_in_process(model, dtype, steps, 2048, max_requests=1, stats=stats, page_size=64)
     check_parts((CONFIG, plain_tensors), dtype, stats["parts"], routes)
     check_against_plain((CONFIG, plain_tensors), dtype, {"p": toks}, steps, outputs, routes)
     statuses_are_clear()
@@ -129,7 +129,7 @@ def test_64_prompts_in_one_step_then_decode_steps_of_64_rows(setup, dtype):
              {"step": 1, "entries": [{"id": k, "tokens": [v[-2]], "want": [0]} for k, v in reqs.items()], "end": []},
              {"step": 2, "entries": [{"id": k, "tokens": [v[-1]], "want": [0]} for k, v in reqs.items()],
               "end": list(reqs)}]
-    outputs, routes = run_in_process(model, dtype, steps, max_live_tokens(steps), max_requests=64)
+    outputs, routes = run_in_process(model, dtype, steps, max_live_tokens(steps), max_requests=64, page_size=64)
     assert outputs[1].shape == (64, V)
     check_tails((CONFIG, plain_tensors), dtype, reqs, outputs, routes)
     statuses_are_clear()

@@ -45,8 +45,8 @@ def test_captured_decode_steps_give_the_logits_of_launch_by_launch_steps(model_d
     assert kernels.attention_decode_status() == 0
 
 
-@pytest.mark.parametrize("name", ["tiny_e", "tiny_f"])
-def test_decode_tail_through_captured_steps_matches_the_plain_implementation(model_dirs, name):
+@pytest.mark.parametrize("name,page_size", [("tiny_e", 16), ("tiny_f", 16), ("tiny_e", 64)])
+def test_decode_tail_through_captured_steps_matches_the_plain_implementation(model_dirs, name, page_size):
     """The decode-tail cut (most of a request in one step, its last tokens one by one) with the one-token
     steps replayed from captures, against the plain implementation; the routers' picks come from the same
     trace run launch by launch (a tapped step is never a captured one)."""
@@ -55,9 +55,10 @@ def test_decode_tail_through_captured_steps_matches_the_plain_implementation(mod
     reqs = {k: random_prompt(V, n, 90 + i) for i, (k, n) in enumerate({"a": 310, "b": 530, "c": 77}.items())}
     steps = decode_tail_trace(reqs, tail=70)
     stats = {}
-    captured, _ = run_in_process(d, "bfloat16", steps, max_live_tokens(steps), use_graphs=True, taps=False, stats=stats)
+    captured, _ = run_in_process(d, "bfloat16", steps, max_live_tokens(steps), use_graphs=True, taps=False, stats=stats,
+                                 page_size=page_size)
     assert stats["graph_replays"] == 3 * 70
-    plainly, routes = run_in_process(d, "bfloat16", steps, max_live_tokens(steps))
+    plainly, routes = run_in_process(d, "bfloat16", steps, max_live_tokens(steps), page_size=page_size)
     for a, b in zip(captured, plainly):
         assert float(((a - b).norm(dim=-1) / b.norm(dim=-1)).max()) < 1e-5
     check_against_plain(d, "bfloat16", reqs, steps, captured, routes)

@@ -893,7 +893,8 @@ def test_products_with_swiglu_store(K, M, I, K_):
 # ---------------------------------------------------------------------------------------------
 @pytest.mark.parametrize("nh,nkv,hd,P,window", [(4, 1, 64, 16, None), (32, 8, 64, 16, None), (16, 1, 128, 64, None),
                                                 (6, 2, 128, 8, None), (8, 2, 64, 16, 300), (3, 3, 64, 16, 37),
-                                                (4, 2, 64, 4, None), (2, 1, 128, 32, 520)])
+                                                (4, 2, 64, 4, None), (2, 1, 128, 32, 520), (8, 2, 64, 64, None),
+                                                (4, 2, 64, 64, 300), (32, 8, 64, 128, None)])
 def test_attention_decode_mma(K, nh, nkv, hd, P, window):
     """The tensor-core kernel for decoded rows: requests of very different lengths (one chunk, a chunk
     edge, many chunks), scattered pages, unwritten cache entries NaN, a row list, windows."""
@@ -995,14 +996,15 @@ def rel_l2(got, want):
     return float(((got - want).norm(dim=-1) / want.norm(dim=-1).clamp_min(1e-30)).max())
 
 
-@pytest.mark.parametrize("N", [8192, 33000])
-def test_attention_over_long_contexts(K, N):
-    """8,192 and 33,000 cached keys (the lengths the measurements run and beyond the longest prompts of the
-    dense configurations): decoded rows over 32 and 129 chunks of keys, exactly as many chunks as needed and
+@pytest.mark.parametrize("N,P", [(8192, 16), (33000, 16), (33000, 64), (131072, 64)])
+def test_attention_over_long_contexts(K, N, P):
+    """8,192, 33,000 and 131,072 cached keys (the lengths the measurements run, beyond the longest prompts of
+    the dense configurations, and the longest context the reference publishes a run for), in pages of 16 and
+    of 64 tokens: decoded rows over 32, 129 and 512 chunks of keys, exactly as many chunks as needed and
     rounded up as a captured step has them; the last rows of a 2,048-row and of an 8,192-row portion through
-    the tcgen05 prompt kernel (16 to 258 key tiles per block); head size 128 through the mma.sync prompt
+    the tcgen05 prompt kernel (16 to 1,024 key tiles per block); head size 128 through the mma.sync prompt
     kernel.  Each against float64 attention recomputed from the cache pages, rel-L2 < 0.005 per row."""
-    dtype, nh, nkv, hd, P = torch.bfloat16, 8, 2, 64, 16
+    dtype, nh, nkv, hd = torch.bfloat16, 8, 2, 64
     scale = hd ** -0.5
     pool, table, k, v = paged_sequence(dtype, N, nkv, hd, P, seed=N)
     other_pool_rows = N - 300
