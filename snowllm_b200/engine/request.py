@@ -49,6 +49,19 @@ class Request:
             return self.prompt + self.out + [-(self.in_flight + 1)]
         return self.prompt + self.out
 
+    def tokens_at(self, start: int, count: int) -> list:
+        """``tokens[start:start + count]`` without joining the lists (a decode step asks for one token of a
+        request that may hold a hundred thousand)."""
+        n, end = len(self.prompt), start + count
+        if end <= n:
+            return self.prompt[start:end]
+        piece = self.prompt[start:n] if start < n else []
+        lo = max(start - n, 0)
+        piece = piece + self.out[lo:end - n]
+        if self.in_flight >= 0 and end > n + len(self.out) and start <= n + len(self.out):
+            piece = piece + [-(self.in_flight + 1)]
+        return piece
+
     @property
     def generated(self) -> int:
         """Tokens sampled so far, the one in flight included."""

@@ -36,7 +36,7 @@ class Segment:
 
     @property
     def tokens(self) -> list:
-        return self.request.tokens[self.start:self.start + self.count]
+        return self.request.tokens_at(self.start, self.count)
 
 
 class Scheduler:

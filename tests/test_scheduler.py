@@ -231,3 +231,18 @@ def test_tokens_in_flight_count_as_generated_and_appear_as_references():
     assert b.cache is None and s.running == [a]
     plan = s.schedule()
     assert plan[0].tokens == [-1] and plan[0].start == 6 and a.tokens[-2:] == [11, -1]
+
+
+def test_a_segments_tokens_are_cut_without_joining_the_lists():
+    """Request.tokens_at(start, count) is tokens[start:start + count] for every cut, with and without a
+    token still on the device (a decode step of a long request must not copy its whole history)."""
+    import random
+    rng = random.Random(0)
+    for _ in range(2000):
+        r = Request(prompt=list(range(100, 100 + rng.randint(1, 9))), params=SamplingParams())
+        r.out = list(range(500, 500 + rng.randint(0, 6)))
+        r.in_flight = rng.choice([-1, 0, 3])
+        full = r.tokens
+        start = rng.randint(0, len(full))
+        count = rng.randint(0, len(full) - start + 2)
+        assert r.tokens_at(start, count) == full[start:start + count]
