@@ -233,12 +233,13 @@ def test_smoke_entry():
     __graft_entry__.smoke()
 
 
-@pytest.mark.parametrize("overlap", [True, False])
-def test_many_requests_under_pressure_match_calm_runs(model_dirs, overlap):
-    """Thirty requests of random lengths and reply limits, some with stop tokens, one aborted on the way, four
-    at a time in a pool so small that requests are preempted and replayed, portions of 24 tokens, captured
-    decode steps: every request ends with the tokens it gets when it runs alone in a roomy engine, and every
-    page and slot comes back."""
+@pytest.mark.parametrize("overlap,max_graphs", [(True, 3), (False, 64)])
+def test_many_requests_under_pressure_match_calm_runs(model_dirs, overlap, max_graphs):
+    """Thirty requests of random lengths and reply limits, some with stop tokens, one aborted on the way, arriving
+    a few at a time while others run, four at a time in a pool so small that requests are preempted and
+    replayed, portions of 24 tokens, captured decode steps (with room for three captures only, so that
+    captures are dropped and made again): every request ends with the tokens it gets when it runs alone in a
+    roomy engine, and every page and slot comes back."""
     import random
 
     from snowllm_b200.engine import SamplingParams
@@ -257,10 +258,15 @@ def test_many_requests_under_pressure_match_calm_runs(model_dirs, overlap):
     for i, ((prompt, n), out) in enumerate(zip(jobs, alone)):
         stop = (out[len(out) // 2],) if i % 4 == 0 else ()
         params.append(SamplingParams(temperature=0, max_new_tokens=n, stop_token_ids=stop))
-    tight = engine_for(d, max_num_seqs=4, max_model_len=160, num_kv_blocks=11, prefill_chunk=24, overlap_steps=overlap)
-    reqs = [tight.add(prompt, p) for (prompt, _), p in zip(jobs, params)]
+    tight = engine_for(d, max_num_seqs=4, max_model_len=160, num_kv_blocks=11, prefill_chunk=24, overlap_steps=overlap,
+                       max_graphs=max_graphs)
+    arrivals = list(zip(jobs, params))
+    reqs = [tight.add(prompt, p) for (prompt, _), p in arrivals[:12]]
     steps = 0
-    while tight.scheduler.has_work():
+    while tight.scheduler.has_work() or len(reqs) < len(arrivals):
+        if steps % 9 == 0:                               # the others arrive while the first ones run
+            for (prompt, _), p in arrivals[len(reqs):len(reqs) + 2]:
+                reqs.append(tight.add(prompt, p))
         tight.step()
         steps += 1
         if steps == 25:
@@ -268,6 +274,8 @@ def test_many_requests_under_pressure_match_calm_runs(model_dirs, overlap):
         assert steps < 5000
     tight.run()
     assert tight.stats().preemptions > 0, "the pool was meant to be too small for four requests at a time"
+    if max_graphs == 3:
+        assert tight.stats().graphs["evictions"] > 0, "three captures were meant to be too few"
     for i, (r, out, p) in enumerate(zip(reqs, alone, params)):
         if i == 11:
             assert r.finish_reason in ("abort", "length", "stop")
