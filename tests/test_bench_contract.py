@@ -71,3 +71,32 @@ def test_roofline_denominators_come_from_the_measured_file_when_it_is_there():
         assert source == "measured" and pk["hbm_gbs"] == float(d["hbm_gbs"]) and pk["bf16_tflops"] == float(d["bf16_tflops"])
     else:
         assert source == "fallback" and pk == bench.FALLBACK_PEAKS
+
+
+import pytest
+
+
+@pytest.mark.gpu
+def test_bench_line_has_the_contracts_keys():
+    """A short run on four of the layers: one JSON line with every key of the contract, a flat `config` of at most
+    20 keys that names both layer counts, launches counted, host bytes counted."""
+    p = run("--layers", "4", "--steps", "3", "--warmup", "3")
+    assert p.returncode == 0, p.stderr[-2000:]
+    lines = [ln for ln in p.stdout.strip().splitlines() if ln.startswith("{")]
+    assert len(lines) == 1
+    d = json.loads(lines[0])
+    for key in ("metric", "value", "unit", "n_gpus", "steps", "warmup", "ms_per_step", "higher_is_better", "scaling",
+                "vs_baseline", "dtype", "data", "config", "clocks", "e2e", "gpu_launches", "prefill", "roofline", "points"):
+        assert key in d, key
+    assert d["n_gpus"] == 1 and d["steps"] == 3 and d["warmup"] == 3 and d["higher_is_better"] is True
+    assert d["dtype"] == "bf16" and d["vs_baseline"] is None and d["value"] > 0 and d["ms_per_step"] > 0
+    cfg = d["config"]
+    assert len(cfg) <= 20 and all(not isinstance(v, (dict, list)) for v in cfg.values())
+    assert cfg["layers"] == 24 and cfg["layers_run"] == 4 and cfg["global_batch"] == 8 and cfg["seq_len"] == 8192
+    assert d["gpu_launches"] > 0
+    assert {"value", "unit", "h2d_bytes_per_step", "d2h_bytes_per_step"} <= set(d["e2e"]) and d["e2e"]["h2d_bytes_per_step"] > 0
+    assert {"value", "tokens", "ms", "frac"} <= set(d["prefill"]) and d["prefill"]["tokens"] == 2048
+    assert {"bound", "achieved", "peak", "unit", "frac"} <= set(d["roofline"]) and d["roofline"]["bound"] == "hbm"
+    assert abs(d["roofline"]["frac"] - d["roofline"]["achieved"] / d["roofline"]["peak"]) < 1e-3
+    assert {"decode_b1", "decode_b64"} <= set(d["points"])
+    assert {"sm_mhz", "sm_max_mhz", "reasons"} <= set(d["clocks"])
