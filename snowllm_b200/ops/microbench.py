@@ -25,7 +25,7 @@ L2_FLUSH_BYTES = 256 << 20
 
 
 def timed(fn, iters: int, flush: bool = True) -> float:
-    """Mean microseconds of ``fn()`` over ``iters`` launches, L2 flushed (a 256 MB buffer read and written) before each."""
+    """Mean microseconds of ``fn()`` over ``iters`` launches, L2 flushed (a 256 MB buffer read) before each."""
     scrub = torch.empty(L2_FLUSH_BYTES, dtype=torch.uint8, device="cuda") if flush else None
     for _ in range(3):
         fn()
@@ -33,8 +33,9 @@ def timed(fn, iters: int, flush: bool = True) -> float:
     total = 0.0
     for _ in range(iters):
         if scrub is not None:
-            scrub.add_(1)        # read and written: a plain fill's lines leave L2 first and what was there before
-                                 # stays (a kernel that reads the same 470 MB every turn then finds a quarter of it)
+            scrub.max()          # a READ of 256 MB: L2 then holds clean lines of the scrub buffer.  (A fill's lines
+                                 # leave L2 first and the last turn's operands stay; a buffer written leaves L2 full
+                                 # of lines that must go back to memory while the timed kernel runs.)
         start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         start.record()
         fn()
